@@ -1,0 +1,74 @@
+// Shared helpers for the sm_100a kernels of gogguf_b200.
+//
+// Conventions of every launcher (functions marked GG_API):
+//   * plain C linkage, int status: 0 ok, a positive value is a cudaError_t,
+//     negative values are refusals (-1 size/argument, -2 dtype combination).
+//   * dtype codes: 0 = float32, 1 = bfloat16.
+//   * all pointers are device pointers; the last argument is the stream.
+//   * nothing is allocated; scratch is passed in by the caller.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define GG_API extern "C" __attribute__((visibility("default"))) int
+
+#define GG_F32 0
+#define GG_BF16 1
+
+#define GG_ERR_ARG (-1)
+#define GG_ERR_DTYPE (-2)
+#define GG_ERR_DEVICE (-3)
+#define GG_ERR_TIMEOUT (-4)
+#define GG_ERR_TMAP (-5)
+
+typedef __nv_bfloat16 bf16;
+
+static inline int gg_last_error() { return (int)cudaGetLastError(); }
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The
+// order of the additions depends only on the block size, never on the data or
+// on what else runs, so results are reproducible.
+__device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats of shared memory */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+// Dispatch helpers: call `expr` with `T` bound to the type of a dtype code.
+#define GG_DISPATCH_DTYPE(code, T, ...)                       \
+    do {                                                      \
+        if ((code) == GG_F32) { typedef float T; __VA_ARGS__; } \
+        else if ((code) == GG_BF16) { typedef bf16 T; __VA_ARGS__; } \
+        else return GG_ERR_DTYPE;                             \
+    } while (0)

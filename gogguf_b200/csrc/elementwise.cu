@@ -1,0 +1,216 @@
+// Row-wise and element-wise kernels: embedding gather, RMSNorm, rotary tables,
+// fused per-head QK-norm + rotary + cache write, SwiGLU, residual add.
+//
+// They replace the reference's rmsnorm / rope_heads / swiglu / add_inplace PTX
+// kernels (pkg/gpu/cuda/ptx.go:428-496, 498-564, 634-677, 891-924), which run
+// one vector per launch; these run every token of a step in one launch.
+// Reductions, the inverse root, the rotation and the SiLU are done in float32
+// (angles in float64); the residual stream is float32 in both precisions.
+#include "common.cuh"
+
+// ----------------------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
+                                    float* __restrict__ out, int H, int V) {
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    float* o = out + (size_t)t * H;
+    if (tok < 0 || tok >= V) {  // padding row
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const TW* r = table + (size_t)tok * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f<TW>(r[i]);
+}
+
+GG_API gg_embed_gather(const void* table, int table_dtype, const int* tokens, float* out,
+                       int T, int H, int V, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || V <= 0) return GG_ERR_ARG;
+    GG_DISPATCH_DTYPE(table_dtype, TW,
+        embed_gather_kernel<TW><<<T, 256, 0, stream>>>((const TW*)table, tokens, out, H, V));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- RMSNorm
+// out[r,:] = x[src(r),:] * (1/sqrt(mean(x^2)+eps)) * w ; src(r) = rows ? rows[r] : r.
+// x is the float32 residual stream.  A negative source row gives a zero row.
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                               const float* __restrict__ w, TO* __restrict__ out, int H, float eps) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    TO* o = out + (size_t)r * H;
+    if (src < 0) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f<TO>(0.f);
+        return;
+    }
+    const float* xr = x + (size_t)src * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = xr[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f<TO>(xr[i] * scale * w[i]);
+}
+
+GG_API gg_rmsnorm(const float* x, const int* rows, const float* w, void* out, int out_dtype,
+                  int R, int H, float eps, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (H <= 0) return GG_ERR_ARG;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    GG_DISPATCH_DTYPE(out_dtype, TO,
+        rmsnorm_kernel<TO><<<R, threads, 0, stream>>>(x, rows, w, (TO*)out, H, eps));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- rotary tables
+// cos/sin[t, i] of angle = pos[t] * inv_freq[i], computed in float64 (the reference computes
+// its tables in float64 too, pkg/ops/rope_tables.go:6-20) and stored as float32.
+__global__ void rope_tables_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
+                                   float* __restrict__ cosv, float* __restrict__ sinv, int T, int half) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= T * half) return;
+    const int t = idx / half, i = idx - t * half;
+    int p = positions[t];
+    if (p < 0) p = 0;
+    double s, c;
+    sincos((double)p * inv_freq[i], &s, &c);
+    cosv[idx] = (float)c;
+    sinv[idx] = (float)s;
+}
+
+GG_API gg_rope_tables(const int* positions, const double* inv_freq, float* cosv, float* sinv,
+                      int T, int half, cudaStream_t stream) {
+    if (T <= 0 || half <= 0) return 0;
+    const int n = T * half;
+    rope_tables_kernel<<<(n + 255) / 256, 256, 0, stream>>>(positions, inv_freq, cosv, sinv, T, half);
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- QK-norm + rotary + cache write
+// One warp per (token, head) of the fused projection output qkv[T, (nq + 2 nkv) * d]:
+//   q heads: optional RMSNorm over d with weight qw, rotary, written to q_out[T, nq, d];
+//   k heads: optional RMSNorm with kw, rotary, written into the paged key pool;
+//   v heads: copied into the paged value pool.
+// Order as in the reference: norm first, rotation after (pkg/model/qwen3/model.go:227-236).
+// Pool layout: [page][kv_head][page_size][d]; the page of position p of sequence b is
+// page_table[b * max_pages + p / page_size].  Pools may be null (a layer that reads another
+// layer's cache writes none); then k and v heads are skipped.
+template <typename T>
+__global__ void qk_norm_rope_cache_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out,
+    const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+    const float* __restrict__ cosv, const float* __restrict__ sinv,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+    const int* __restrict__ page_table, int max_pages, int page_size,
+    T* __restrict__ k_pool, T* __restrict__ v_pool,
+    int ntok, int nq, int nkv, int d, int rot) {
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nheads = nq + 2 * nkv;
+    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (wid >= (long long)ntok * nheads) return;
+    const int t = (int)(wid / nheads), h = (int)(wid - (long long)t * nheads);
+    const int b = seq_of_token[t];
+    const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+    if (!is_q && (k_pool == nullptr || b < 0)) return;
+    float* buf = sm + warp * d;
+    const T* src = qkv + ((size_t)t * nheads + h) * d;
+    T* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * nq + h) * d;
+    } else {
+        const int pos = positions[t];
+        const int page = page_table[(size_t)b * max_pages + pos / page_size];
+        const int kvh = is_k ? h - nq : h - nq - nkv;
+        T* pool = is_k ? k_pool : v_pool;
+        dst = pool + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * d;
+    }
+    if (!is_q && !is_k) {  // value head: plain copy
+        for (int i = lane; i < d; i += 32) dst[i] = src[i];
+        return;
+    }
+    const float* w = is_q ? qw : kw;
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) { float v = to_f<T>(src[i]); buf[i] = v; ss = fmaf(v, v, ss); }
+    float scale = 1.f;
+    if (w != nullptr) {
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)d + eps);
+    }
+    __syncwarp();
+    const int half = rot >> 1;
+    const float* c = cosv + (size_t)t * half;
+    const float* s = sinv + (size_t)t * half;
+    for (int i = lane; i < d; i += 32) {
+        float v = buf[i] * scale * (w ? w[i] : 1.f);
+        float o;
+        if (i < half) {
+            const float p = buf[i + half] * scale * (w ? w[i + half] : 1.f);
+            o = v * c[i] - p * s[i];
+        } else if (i < rot) {
+            const int j = i - half;
+            const float p = buf[j] * scale * (w ? w[j] : 1.f);
+            o = p * s[j] + v * c[j];
+        } else {
+            o = v;
+        }
+        dst[i] = from_f<T>(o);
+    }
+}
+
+GG_API gg_qk_norm_rope_cache(const void* qkv, int dtype, void* q_out, const float* qw, const float* kw, float eps,
+                             const float* cosv, const float* sinv, const int* positions, const int* seq_of_token,
+                             const int* page_table, int max_pages, int page_size, void* k_pool, void* v_pool,
+                             int ntok, int nq, int nkv, int d, int rot, cudaStream_t stream) {
+    if (ntok <= 0) return 0;
+    if (d <= 0 || d > 1024 || rot < 0 || rot > d || (rot & 1) || nq <= 0 || nkv <= 0 || page_size <= 0) return GG_ERR_ARG;
+    const int warps = 4;
+    const long long total = (long long)ntok * (nq + 2 * nkv);
+    const unsigned grid = (unsigned)((total + warps - 1) / warps);
+    const size_t smem = (size_t)warps * d * sizeof(float);
+    GG_DISPATCH_DTYPE(dtype, T,
+        qk_norm_rope_cache_kernel<T><<<grid, warps * 32, smem, stream>>>(
+            (const T*)qkv, (T*)q_out, qw, kw, eps, cosv, sinv, positions, seq_of_token, page_table, max_pages,
+            page_size, (T*)k_pool, (T*)v_pool, ntok, nq, nkv, d, rot));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- SwiGLU
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(z) = z / (1 + exp(-z)) (pkg/ops/ops.go:316-318).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long n, int I) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const long long t = idx / I;
+    const int i = (int)(idx - t * I);
+    const float g = to_f<T>(gu[t * 2 * I + i]);
+    const float u = to_f<T>(gu[t * 2 * I + I + i]);
+    out[idx] = from_f<T>(g / (1.0f + expf(-g)) * u);
+}
+
+GG_API gg_swiglu(const void* gu, int dtype, void* out, int ntok, int I, cudaStream_t stream) {
+    if (ntok <= 0) return 0;
+    if (I <= 0) return GG_ERR_ARG;
+    const long long n = (long long)ntok * I;
+    GG_DISPATCH_DTYPE(dtype, T,
+        swiglu_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const T*)gu, (T*)out, n, I));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- residual add
+// x (float32) += delta.  The fast path folds this into the producing product's epilogue;
+// this is the stand-alone form (pkg/gpu/cuda/ptx.go:891-924 add_inplace).
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__ delta, long long n) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < n) x[idx] += to_f<T>(delta[idx]);
+}
+
+GG_API gg_residual_add(float* x, const void* delta, int dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    GG_DISPATCH_DTYPE(dtype, T,
+        residual_add_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, (const T*)delta, n));
+    return gg_last_error();
+}

@@ -1,0 +1,148 @@
+"""Python face of the CUDA kernels: one thin function per launcher.
+
+Arguments are torch tensors on the GPU; every function launches on torch's current stream and
+allocates nothing (outputs and scratch are passed in).  There is no CPU or library fallback: a
+tensor that is not on a CUDA device, or a missing compiler, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import KernelError, kernel
+
+F32, BF16 = 0, 1
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {dt}")
+
+
+def _p(t: Optional[torch.Tensor]) -> int:
+    if t is None:
+        return 0
+    if not t.is_cuda:
+        raise KernelError("kernel argument is not on a CUDA device (there is no CPU path)")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, dt: torch.dtype, what: str) -> None:
+    if t.dtype != dt:
+        raise KernelError(f"{what} must be {dt}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+
+
+# ------------------------------------------------------------------------------- elementwise
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] (float32) = table[tokens[t], :]; negative ids give zero rows."""
+    _need(tokens, torch.int32, "tokens")
+    _need(out, torch.float32, "out")
+    V, H = table.shape
+    kernel("elementwise", "gg_embed_gather")(_p(table), dtype_code(table.dtype), _p(tokens), _p(out),
+                                              tokens.numel(), H, V, _stream())
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * weight; x float32, weight float32, out float32/bfloat16."""
+    _need(x, torch.float32, "x")
+    _need(weight, torch.float32, "norm weight")
+    H = x.shape[-1]
+    R = rows.numel() if rows is not None else x.numel() // H
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    if weight.numel() != H or out.shape[-1] != H or out.numel() < R * H:
+        raise KernelError("rmsnorm: shapes disagree")
+    kernel("elementwise", "gg_rmsnorm")(_p(x), _p(rows), _p(weight), _p(out), dtype_code(out.dtype),
+                                         R, H, float(eps), _stream())
+
+
+def rope_tables(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+    _need(positions, torch.int32, "positions")
+    _need(inv_freq, torch.float64, "inv_freq")
+    _need(cos, torch.float32, "cos")
+    _need(sin, torch.float32, "sin")
+    T, half = positions.numel(), inv_freq.numel()
+    kernel("elementwise", "gg_rope_tables")(_p(positions), _p(inv_freq), _p(cos), _p(sin), T, half, _stream())
+
+
+def qk_norm_rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Tensor],
+                       k_weight: Optional[torch.Tensor], eps: float, cos: torch.Tensor, sin: torch.Tensor,
+                       positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor,
+                       page_size: int, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                       n_tokens: int, nq: int, nkv: int, d: int, rot: int) -> None:
+    if q_out.dtype != qkv.dtype or (k_pool is not None and k_pool.dtype != qkv.dtype):
+        raise KernelError("qk_norm_rope_cache: qkv, q_out and the cache must share one dtype")
+    kernel("elementwise", "gg_qk_norm_rope_cache")(
+        _p(qkv), dtype_code(qkv.dtype), _p(q_out), _p(q_weight), _p(k_weight), float(eps), _p(cos), _p(sin),
+        _p(positions), _p(seq_of_token), _p(page_table), page_table.shape[-1], page_size, _p(k_pool), _p(v_pool),
+        n_tokens, nq, nkv, d, rot, _stream())
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, n_tokens: int, inter: int) -> None:
+    if gate_up.dtype != out.dtype:
+        raise KernelError("swiglu: input and output must share one dtype")
+    kernel("elementwise", "gg_swiglu")(_p(gate_up), dtype_code(gate_up.dtype), _p(out), n_tokens, inter, _stream())
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
+    _need(x, torch.float32, "x")
+    if delta.numel() != x.numel() or not delta.is_contiguous():
+        raise KernelError("residual_add: shapes disagree")
+    kernel("elementwise", "gg_residual_add")(_p(x), _p(delta), dtype_code(delta.dtype), x.numel(), _stream())
+
+
+# ------------------------------------------------------------------------------- matrix product
+def gemm_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+               m: Optional[int] = None) -> None:
+    """out[M, N] (+)= x[M, K] @ w[N, K]^T on the CUDA cores with float32 accumulation."""
+    N, K = w.shape
+    M = x.shape[0] if m is None else m
+    if x.shape[-1] != K or out.shape[-1] != N:
+        raise KernelError(f"gemm: x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
+    if x.stride(-1) != 1 or out.stride(-1) != 1 or not w.is_contiguous():
+        raise KernelError("gemm: operands must be row-major")
+    kernel("gemm_plain", "gg_gemm_plain")(_p(x), dtype_code(x.dtype), _p(w), dtype_code(w.dtype), _p(out),
+                                           dtype_code(out.dtype), int(accumulate), M, N, K,
+                                           x.stride(0), out.stride(0), _stream())
+
+
+# ------------------------------------------------------------------------------- attention
+def attention_plain(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                    positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor,
+                    page_size: int, n_tokens: int, nq: int, nkv: int, d: int, scale: float, window: int) -> None:
+    if not (q.dtype == k_pool.dtype == v_pool.dtype == out.dtype):
+        raise KernelError("attention: q, cache and out must share one dtype")
+    kernel("attention_plain", "gg_attention_plain")(
+        _p(q), _p(k_pool), _p(v_pool), _p(out), dtype_code(q.dtype), _p(positions), _p(seq_of_token),
+        _p(page_table), page_table.shape[-1], page_size, n_tokens, nq, nkv, d, float(scale), int(window), _stream())
+
+
+# ------------------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None) -> None:
+    _need(logits, torch.float32, "logits")
+    _need(out, torch.int32, "out")
+    R = logits.shape[0] if rows is None else rows
+    kernel("sampling", "gg_argmax")(_p(logits), logits.stride(0), _p(out), R, logits.shape[1], _stream())
+
+
+def sample(logits: torch.Tensor, temps: torch.Tensor, uniforms: torch.Tensor, out: torch.Tensor,
+           rows: Optional[int] = None) -> None:
+    _need(logits, torch.float32, "logits")
+    _need(temps, torch.float32, "temps")
+    _need(uniforms, torch.float64, "uniforms")
+    _need(out, torch.int32, "out")
+    R = logits.shape[0] if rows is None else rows
+    kernel("sampling", "gg_sample")(_p(logits), logits.stride(0), _p(temps), _p(uniforms), _p(out), R,
+                                     logits.shape[1], _stream())

@@ -1,0 +1,44 @@
+"""Dense SwiGLU feed-forward: down( silu(gate h) * (up h) ), no bias
+(pkg/model/qwen3/model.go:273-286, pkg/ops/inplace.go:14-19)."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..config.spec import PartSpec
+from ..csrc import kernels as K
+from ..weights.loader import TensorDecl
+from .base import Linear, Runtime, StepContext
+from .registry import register_feed_forward
+
+
+@register_feed_forward("swiglu")
+class SwiGLU:
+    @classmethod
+    def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
+        h, i = spec["hidden_size"], spec["intermediate_size"]
+        return {
+            "gate_proj.weight": TensorDecl(shape=(i, h)),
+            "up_proj.weight": TensorDecl(shape=(i, h)),
+            "down_proj.weight": TensorDecl(shape=(h, i)),
+        }
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        g, u = rt.matrix(weights["gate_proj.weight"]), rt.matrix(weights["up_proj.weight"])
+        if g.dtype != u.dtype:
+            g, u = g.float(), u.float()
+        # gate rows first, then up rows: one product for both
+        self.gate_up = Linear(torch.cat([g, u], dim=0), rt)
+        self.down = Linear(weights["down_proj.weight"], rt)
+        self.rt = rt
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
+        T = ctx.n_tokens
+        gu = ctx.ws.get("ffn_gate_up", (T, 2 * self.inter), self.rt.dtype)
+        act = ctx.ws.get("ffn_act", (T, self.inter), self.rt.dtype)
+        self.gate_up(h, gu, ws=ctx.ws)
+        K.swiglu(gu, act, T, self.inter)
+        self.down(act, residual, accumulate=True, ws=ctx.ws)
