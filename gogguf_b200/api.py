@@ -1,0 +1,97 @@
+"""The library's entry point, in the manner of the reference's facade (gogguf.go:14-82):
+
+    engine = gogguf_b200.load(folder, LoadOptions(dtype="bfloat16"))
+    ctx = engine.new_context()
+    results = ctx.generate([[1, 2, 3], [4, 5]], GenerateParams(max_tokens=16,
+                           sampler=SamplerConfig(temp=0.8, seed=7)))
+
+`load` reads a model folder (config.json + model.safetensors), `Engine.new_context` makes a cache
+and a stepper (runtime.Engine.NewContext, pkg/runtime/context.go:29-38), `Context.generate` runs the
+generation loop (Context.Generate, context.go:100-130) and `Context.forward_token_ids` is the raw
+hook (Engine.ForwardTokenIDs, pkg/runtime/engine.go:79-81).  Prompts are token ids: the tokenizer
+and chat templates of the reference are outside this library.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Union
+
+import torch
+
+from .engine.generate import GenerateParams, GenerationResult, Generator
+from .engine.model import Model
+from .engine.step import StepEntry, Stepper
+from .sampling.sampler import Sampler, SamplerConfig, greedy as Greedy  # noqa: N812
+
+
+@dataclass
+class LoadOptions:
+    """Where the reference has NGL and GPUMaxSeq (pkg/runtime/options.go:6-9) this library has the
+    compute dtype and the cache size: the whole model always runs on the GPU."""
+    dtype: str = "bfloat16"
+    device: str = "cuda:0"
+    max_tokens: int = 0           # cache capacity in tokens; 0: the model's context length
+    max_batch: int = 64
+    fast: bool = True             # False: plain kernels only (for comparisons)
+    graphs: bool = True           # replay captured decode steps where possible
+
+
+class Engine:
+    def __init__(self, model: Model, options: LoadOptions):
+        self.model = model
+        self.options = options
+
+    def context_length(self) -> int:
+        """pkg/runtime/engine.go: ContextLength from the model's metadata."""
+        return self.model.spec.max_positions
+
+    def new_context(self, max_tokens: Optional[int] = None, max_batch: Optional[int] = None) -> "Context":
+        mt = max_tokens or self.options.max_tokens or self.context_length()
+        return Context(self, mt, max_batch or self.options.max_batch)
+
+    def close(self) -> None:
+        self.model = None
+
+
+class Context:
+    def __init__(self, engine: Engine, max_tokens: int, max_batch: int):
+        self.engine = engine
+        model = engine.model
+        self.cache = model.new_cache(max_tokens)
+        if engine.options.graphs and model.rt.device.type == "cuda":
+            from .engine.graphs import GraphStepper
+            self.stepper = GraphStepper(model, self.cache)
+        else:
+            self.stepper = Stepper(model, self.cache)
+        self.generator = Generator(self.stepper, model.spec.vocab_size, model.spec.max_positions,
+                                   default_stop=model.spec.stop_token_ids, max_batch=max_batch)
+
+    def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
+                 params: Optional[GenerateParams] = None) -> Union[GenerationResult, List[GenerationResult]]:
+        """One prompt (a list of ids) gives one result; a list of prompts gives a list."""
+        single = len(prompts) > 0 and isinstance(prompts[0], int)
+        res = self.generator.generate([list(prompts)] if single else [list(p) for p in prompts], params)
+        return res[0] if single else res
+
+    def forward_token_ids(self, tokens: Sequence[int]) -> torch.Tensor:
+        """Logits [len(tokens), vocab] of one fresh sequence (float32, on the device)."""
+        slot = self.cache.open()
+        try:
+            out = self.stepper.step([StepEntry(slot, list(tokens), want=list(range(len(tokens))))])
+            return out.clone()
+        finally:
+            self.cache.close(slot)
+
+
+def load(path: str, options: Optional[LoadOptions] = None) -> Engine:
+    """gogguf.Load (gogguf.go:52-55): model folder -> engine."""
+    options = options or LoadOptions()
+    if not torch.cuda.is_available():
+        raise RuntimeError("gogguf_b200 needs a CUDA device (B200); there is no CPU path")
+    model = Model.load(path, dtype=options.dtype, device=options.device, fast=options.fast)
+    return Engine(model, options)
+
+
+def new_sampler(cfg: SamplerConfig) -> Sampler:
+    """gogguf.NewSampler (gogguf.go:63-66)."""
+    return Sampler(cfg)

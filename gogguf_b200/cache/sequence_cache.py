@@ -157,7 +157,7 @@ class SequenceCache:
                 self._views[i] = None
         for i, src in enumerate(cache_of):
             if src is not None:
-                if src not in self._views:
+                if self._views.get(src) is None:
                     raise CacheError(f"schedule entry {i} reads the cache of entry {src}, which has none")
                 self._views[i] = self._views[src]
 

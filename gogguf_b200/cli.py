@@ -1,0 +1,157 @@
+"""Command line, in the manner of the reference's `gogguf` (cmd/gogguf/main.go:21-51):
+
+    gogguf_b200 run -m DIR -p "1 2 3" [-p "4 5"] [-n 128] [--temp 0] [--top-k 0] [--top-p 1] [--min-p 0]
+                    [--repeat-penalty 1] [--repeat-last-n 64] [--seed 0] [--dtype bfloat16]
+    gogguf_b200 info -m DIR
+    gogguf_b200 inspect DIR
+    gogguf_b200 random -c CONFIG.json -o DIR [--seed 0] [--dtype bfloat16] [--std S] [--norm-std S]
+
+`run` keeps the reference's option names and defaults (cmd/gogguf/run.go:17-34).  A prompt is a list
+of token ids (the tokenizer is outside this library); several -p make a batch.  Dropped: -hf
+(network), --chat/--thinking/-i (text templates), -ngl (the whole model is always on the GPU).
+`info` prints what the reference's info prints (cmd/gogguf/info.go:27-44), `inspect` every
+configuration key and tensor (cmd/gogguf/inspect.go:13-41).  `random` is the random-weights mode.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import re
+import sys
+from typing import List, Optional
+
+
+def _ids(text: str) -> List[int]:
+    parts = [p for p in re.split(r"[\s,]+", text.strip()) if p]
+    try:
+        return [int(p) for p in parts]
+    except ValueError:
+        raise SystemExit(f"prompt must be token ids separated by spaces or commas, got {text!r}")
+
+
+def cmd_run(a) -> int:
+    import gogguf_b200 as gg
+    if not a.m:
+        raise SystemExit("usage: gogguf_b200 run -m DIR -p \"token ids\" [-n 128]")
+    prompts: List[List[int]] = [_ids(p) for p in (a.p or [])]
+    if a.prompt_file:
+        with open(a.prompt_file) as f:
+            prompts += [_ids(line) for line in f if line.strip()]
+    if not prompts:
+        raise SystemExit("give a prompt with -p (token ids) or --prompt-file")
+    engine = gg.load(a.m, gg.LoadOptions(dtype=a.dtype, max_tokens=a.cache_tokens, max_batch=a.max_batch))
+    ctx = engine.new_context()
+    params = gg.GenerateParams(
+        max_tokens=a.n,
+        sampler=gg.SamplerConfig(temp=a.temp, top_k=a.top_k, top_p=a.top_p, min_p=a.min_p, seed=a.seed),
+        repeat_penalty=a.repeat_penalty, repeat_last_n=a.repeat_last_n,
+        stop_token_ids=None if a.stop_ids is None else _ids(a.stop_ids))
+    for r in ctx.generate(prompts, params):
+        print(" ".join(str(t) for t in r.tokens))
+        print(f"# prompt {r.prompt_tokens} tokens, generated {len(r.tokens)}, finish: {r.finish_reason}",
+              file=sys.stderr)
+    return 0
+
+
+def _folder_summary(folder: str):
+    from .config.registry import load_config
+    from .weights.safetensors_io import open_model_files
+    cfg = load_config(folder)
+    files = open_model_files(folder)
+    tensors = []
+    for f in files:
+        for n in f.names():
+            dt, shape = f.info(n)
+            numel = 1
+            for s in shape:
+                numel *= s
+            tensors.append((n, dt, shape, numel * (8 if "64" in str(dt) else 4 if "32" in str(dt) else
+                                                   2 if "16" in str(dt) else 1)))
+        f.close()
+    return cfg, tensors
+
+
+def cmd_info(a) -> int:
+    if not a.m:
+        raise SystemExit("usage: gogguf_b200 info -m DIR")
+    cfg, tensors = _folder_summary(a.m)
+    d = cfg.to_dict()
+    print(f"Folder: {a.m}")
+    print(f"Architecture: {d.get('architectures', ['?'])[0]}")
+    print(f"Tensors: {len(tensors)}")
+    print(f"Weights size: {sum(t[3] for t in tensors) / 1e6:.1f} MB")
+    if hasattr(cfg, "parameter_count"):
+        print(f"Parameters: {cfg.parameter_count():,}")
+    if hasattr(cfg, "kv_bytes_per_token"):
+        print(f"Cache per token (bfloat16): {cfg.kv_bytes_per_token(2)} bytes")
+    print(f"Context: {cfg.to_spec().max_positions} tokens")
+    return 0
+
+
+def cmd_inspect(a) -> int:
+    cfg, tensors = _folder_summary(a.folder)
+    for k, v in cfg.to_dict().items():
+        print(f"{k} = {json.dumps(v)}")
+    for n, dt, shape, nbytes in sorted(tensors):
+        print(f"{n}\t{str(dt).replace('torch.', '')}\t{list(shape)}\t{nbytes}")
+    return 0
+
+
+def cmd_random(a) -> int:
+    from .config.registry import load_config
+    from .engine.model import write_random_model
+    cfg = load_config(a.c)
+    write_random_model(cfg, a.seed, a.o, dtype=a.dtype, std=a.std, norm_std=a.norm_std)
+    print(f"wrote {os.path.join(a.o, 'config.json')} and model.safetensors (seed {a.seed}, {a.dtype})")
+    return 0
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="gogguf_b200", description="Qwen3 inference on B200")
+    sub = ap.add_subparsers(dest="cmd")
+    r = sub.add_parser("run", help="generate tokens")
+    r.add_argument("-m", help="model folder (config.json + model.safetensors)")
+    r.add_argument("-p", action="append", help="prompt as token ids; repeat for a batch")
+    r.add_argument("--prompt-file", help="one prompt of token ids per line")
+    r.add_argument("-n", type=int, default=128, help="most new tokens")
+    r.add_argument("--temp", type=float, default=0.0, help="temperature (0 = greedy)")
+    r.add_argument("--top-k", type=int, default=0, help="top-k sampling (0 = off)")
+    r.add_argument("--top-p", type=float, default=1.0, help="nucleus sampling (1 = off)")
+    r.add_argument("--min-p", type=float, default=0.0, help="min-p sampling (0 = off)")
+    r.add_argument("--repeat-penalty", type=float, default=1.0, help="penalty for repeated tokens (1 = off)")
+    r.add_argument("--repeat-last-n", type=int, default=64, help="history window of the repeat penalty")
+    r.add_argument("--seed", type=int, default=0, help="seed of the sampling draws")
+    r.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    r.add_argument("--stop-ids", default=None, help="stop token ids (default: the model's eos_token_id)")
+    r.add_argument("--cache-tokens", type=int, default=0, help="cache capacity in tokens (0 = context length)")
+    r.add_argument("--max-batch", type=int, default=64)
+    r.set_defaults(fn=cmd_run)
+    i = sub.add_parser("info", help="short summary of a model folder")
+    i.add_argument("-m")
+    i.set_defaults(fn=cmd_info)
+    s = sub.add_parser("inspect", help="every configuration key and tensor")
+    s.add_argument("folder")
+    s.set_defaults(fn=cmd_inspect)
+    g = sub.add_parser("random", help="write a model folder with random weights")
+    g.add_argument("-c", required=True, help="config.json (or a folder holding one)")
+    g.add_argument("-o", required=True, help="output folder")
+    g.add_argument("--seed", type=int, default=0)
+    g.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    g.add_argument("--std", type=float, default=None, help="std of matrices (default: initializer_range)")
+    g.add_argument("--norm-std", type=float, default=0.02, help="std of norm weights around 1")
+    g.set_defaults(fn=cmd_random)
+    return ap
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    ap = build_parser()
+    a = ap.parse_args(argv)
+    if not getattr(a, "fn", None):
+        ap.print_help()
+        return 1
+    try:
+        return a.fn(a)
+    except (ValueError, RuntimeError, OSError) as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 1

@@ -1,0 +1,135 @@
+"""The generation loop above the step function.
+
+One *batch* is a set of requests that start together: their prompts, of unequal lengths, run in one
+prefill step; then every live sequence goes on by one token per step.  A sequence that ends (stop
+token, token limit, context limit) leaves the batch at once and its slot and pages are given back;
+the others go on in a smaller batch.  Requests beyond what one batch may hold run in further
+batches, one after another, which reuse the slots.
+
+Rules taken from the reference's session (pkg/runtime/session.go:50-81, :133-159): the default
+limit is 128 new tokens; a sampled stop token ends the sequence and is neither appended to the
+output nor fed to the model; a sampler result below 0 ends it too; the `on_token` callback may end
+it by returning False; a sequence whose next position would reach the context length ends (the
+reference returns an error for its single sequence, session.go:69-72; in a batch the sequence ends
+with reason "length" and the others go on).  Stop *strings* need a tokenizer and are out of scope.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence, Tuple
+
+from ..sampling.sampler import Sampler, SamplerConfig
+from .step import StepEntry
+
+
+@dataclass
+class GenerateParams:
+    """pkg/runtime GenerateParams as used by session.go:133-159."""
+    max_tokens: int = 128
+    sampler: SamplerConfig = field(default_factory=SamplerConfig)
+    repeat_penalty: float = 1.0
+    repeat_last_n: int = 64
+    stop_token_ids: Optional[Sequence[int]] = None     # None: the model's own (eos_token_id)
+    on_token: Optional[Callable[[int, int], bool]] = None   # (request index, token) -> go on?
+
+
+@dataclass
+class GenerationResult:
+    tokens: List[int]
+    finish_reason: str        # "stop" | "length" | "callback"
+    prompt_tokens: int
+
+
+def plan_batches(prompt_lens: Sequence[int], max_new: int, max_batch: int, capacity_tokens: int,
+                 page_size: int, context: int) -> List[List[int]]:
+    """Split requests, in order, into batches that fit: at most `max_batch` sequences, and pages for
+    every sequence's prompt plus its new tokens (bounded by the context) within the cache."""
+    if max_batch <= 0:
+        raise ValueError("max_batch must be positive")
+    batches: List[List[int]] = []
+    cur: List[int] = []
+    used = 0
+    for i, n in enumerate(prompt_lens):
+        if n <= 0:
+            raise ValueError(f"request {i}: empty prompt")
+        if n > context:
+            raise ValueError(f"request {i}: prompt of {n} tokens exceeds the context of {context}")
+        need_tokens = min(n + max(max_new, 0), context)
+        need = -(-need_tokens // page_size) * page_size
+        if need > capacity_tokens:
+            raise ValueError(f"request {i}: needs room for {need} tokens but the cache holds {capacity_tokens}")
+        if cur and (len(cur) >= max_batch or used + need > capacity_tokens):
+            batches.append(cur)
+            cur, used = [], 0
+        cur.append(i)
+        used += need
+    if cur:
+        batches.append(cur)
+    return batches
+
+
+class Generator:
+    """Runs batches of requests on a stepper (anything with `.step(entries)` and `.cache`)."""
+
+    def __init__(self, stepper, vocab_size: int, context: int, default_stop: Sequence[int] = (),
+                 max_batch: int = 64):
+        self.stepper = stepper
+        self.cache = stepper.cache
+        self.vocab_size = vocab_size
+        self.context = context
+        self.default_stop = tuple(default_stop)
+        self.max_batch = max_batch
+
+    def generate(self, prompts: Sequence[Sequence[int]], params: Optional[GenerateParams] = None
+                 ) -> List[GenerationResult]:
+        params = params or GenerateParams()
+        max_new = params.max_tokens if params.max_tokens > 0 else 128      # session.go:134-137
+        results: List[Optional[GenerationResult]] = [None] * len(prompts)
+        batches = plan_batches([len(p) for p in prompts], max_new, self.max_batch,
+                               self.cache.max_tokens, self.cache.page_size, self.context)
+        for batch in batches:
+            self._run_batch(batch, prompts, params, max_new, results)
+        return [r for r in results if r is not None]
+
+    def _run_batch(self, batch: List[int], prompts, params: GenerateParams, max_new: int, results) -> None:
+        stop = set(self.default_stop if params.stop_token_ids is None else params.stop_token_ids)
+        sampler = Sampler(params.sampler, params.repeat_penalty, params.repeat_last_n)
+        cache = self.cache
+        slots = {i: cache.open() for i in batch}
+        generated = {i: [] for i in batch}
+        live: List[int] = list(batch)
+        try:
+            entries = [StepEntry(slots[i], list(prompts[i]), want=[len(prompts[i]) - 1]) for i in live]
+            logits = self.stepper.step(entries)
+            while live:
+                hist = [list(prompts[i]) + generated[i] for i in live] if sampler.penalised else None
+                nxt = sampler.sample(logits, streams=live, steps=[len(generated[i]) for i in live],
+                                     histories=hist)
+                go_on: List[int] = []
+                for i, t in zip(live, nxt):
+                    reason = None
+                    if t < 0 or t in stop:                              # session.go:58-65
+                        reason = "stop"
+                    else:
+                        generated[i].append(int(t))
+                        if params.on_token is not None and not params.on_token(i, int(t)):
+                            reason = "callback"
+                        elif len(generated[i]) >= max_new:
+                            reason = "length"
+                        elif len(prompts[i]) + len(generated[i]) > self.context:
+                            # the token's own position would lie outside the context (session.go:68-72)
+                            reason = "length"
+                    if reason is None:
+                        go_on.append(i)
+                    else:
+                        results[i] = GenerationResult(generated[i], reason, len(prompts[i]))
+                        cache.close(slots.pop(i))
+                live = go_on
+                if not live:
+                    break
+                entries = [StepEntry(slots[i], [generated[i][-1]], want=[0]) for i in live]
+                logits = self.stepper.step(entries)
+        finally:
+            for i, s in list(slots.items()):
+                cache.close(s)
+                slots.pop(i)

@@ -1,0 +1,162 @@
+"""Choosing the next token: greedy, temperature, top-k, top-p, min-p, repeat penalty.
+
+Options and their meaning follow the reference's sampler (pkg/sampler/chain.go:9-70):
+`temp` 0 = greedy; `top_k` 0 = off; `top_p` 1 = off; `min_p` 0 = off; `seed` seeds the draws.
+Greedy and plain temperature sampling run on the GPU (csrc/sampling.cu) over the whole batch; the
+other options run this module's host chain on the logits of the rows that need them, in the
+reference's order: temperature, top-k, min-p, mask to -1e10, softmax, top-p, draw.
+
+Random draws are counter based: u = uniform01(seed, stream, step) with `stream` the request's index
+and `step` the number of tokens it has generated, so a sequence's draws do not depend on what else
+is in its batch.  (The reference draws from one PCG stream per sampler object, chain.go:23; its bit
+stream is not reproduced.)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+_M64 = (1 << 64) - 1
+
+
+def _mix64(z: int) -> int:
+    z = (z + 0x9E3779B97F4A7C15) & _M64
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M64
+    return z ^ (z >> 31)
+
+
+def uniform01(seed: int, stream: int, step: int) -> float:
+    """A uniform number in [0, 1) that depends only on (seed, stream, step)."""
+    z = _mix64(seed & _M64)
+    z = _mix64(z ^ (stream & _M64))
+    z = _mix64(z ^ (step & _M64))
+    return (z >> 11) / float(1 << 53)
+
+
+@dataclass(frozen=True)
+class SamplerConfig:
+    """pkg/sampler/chain.go:9-15."""
+    temp: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    min_p: float = 0.0
+    seed: int = 0
+
+    @property
+    def greedy(self) -> bool:
+        """chain.go:19-21: no temperature, no top-k, no top-p."""
+        return self.temp <= 0 and self.top_k <= 0 and (self.top_p <= 0 or self.top_p >= 1)
+
+    @property
+    def on_device(self) -> bool:
+        """Greedy and plain temperature sampling have kernels; the masks run on the host."""
+        return self.greedy or (self.top_k <= 0 and (self.top_p <= 0 or self.top_p >= 1) and self.min_p <= 0)
+
+
+def greedy(logits: Sequence[float]) -> int:
+    """First index of the maximum (pkg/sampler/greedy.go:4-17); -1 for no logits."""
+    a = np.asarray(logits)
+    if a.size == 0:
+        return -1
+    return int(np.argmax(a))
+
+
+def apply_repeat_penalty(logits: np.ndarray, history: Sequence[int], penalty: float, last_n: int) -> None:
+    """In place; each distinct id among the last `last_n` of the history once
+    (pkg/sampler/penalties.go:5-32)."""
+    if penalty == 1 or logits.size == 0 or len(history) == 0:
+        return
+    h = history[-last_n:] if last_n > 0 and len(history) > last_n else history
+    for t in set(int(x) for x in h):
+        if 0 <= t < logits.size:
+            logits[t] = logits[t] / penalty if logits[t] > 0 else logits[t] * penalty
+
+
+def _softmax64(x: np.ndarray) -> np.ndarray:
+    e = np.exp((x - x.max()).astype(np.float64))
+    return e / e.sum()
+
+
+def sample_host(logits: np.ndarray, cfg: SamplerConfig, u: float) -> int:
+    """The whole chain on one row of float32 logits with the uniform draw `u` given."""
+    n = logits.size
+    if n == 0:
+        return -1
+    if cfg.greedy:
+        return greedy(logits)
+    x = logits.astype(np.float32, copy=True)
+    if cfg.temp > 0 and cfg.temp != 1:
+        x = (x.astype(np.float64) * (1.0 / float(cfg.temp))).astype(np.float32)
+    mask = np.ones(n, dtype=bool)
+    if 0 < cfg.top_k < n:
+        order = np.argsort(-x.astype(np.float64), kind="stable")
+        keep = np.zeros(n, dtype=bool)
+        keep[order[:cfg.top_k]] = True
+        mask &= keep
+    if cfg.min_p > 0:
+        p = _softmax64(x)
+        x[p < float(cfg.min_p) * p.max()] = np.float32(-1e10)
+        mask &= ~(x <= -1e9)
+    x[~mask] = np.float32(-1e10)
+    probs = _softmax64(x)
+    if 0 < cfg.top_p < 1:
+        idx = np.flatnonzero(mask)
+        idx = idx[np.argsort(-probs[idx], kind="stable")]
+        cum = np.cumsum(probs[idx])
+        cut = int(np.searchsorted(cum, float(np.float32(cfg.top_p)) - 1e-6, side="left"))
+        keep = np.zeros(n, dtype=bool)
+        keep[idx[:cut + 1]] = True
+        mask &= keep
+    allowed = np.flatnonzero(mask)
+    total = float(probs[allowed].sum())
+    if total <= 0:
+        return greedy(probs.astype(np.float32))
+    r = u * total
+    run = np.cumsum(probs[allowed])
+    hit = np.flatnonzero(r - run <= 0)
+    return int(allowed[hit[0]]) if hit.size else int(allowed[-1])
+
+
+class Sampler:
+    """Samples one token per row of a [rows, vocab] float32 logits tensor."""
+
+    def __init__(self, cfg: SamplerConfig, repeat_penalty: float = 1.0, repeat_last_n: int = 64):
+        self.cfg = cfg
+        self.repeat_penalty = float(repeat_penalty)
+        self.repeat_last_n = int(repeat_last_n) if repeat_last_n else 64   # 0 means 64 (session.go:87-91)
+        self._out: Optional[torch.Tensor] = None
+
+    @property
+    def penalised(self) -> bool:
+        return self.repeat_penalty > 0 and self.repeat_penalty != 1
+
+    def sample(self, logits: torch.Tensor, streams: Sequence[int], steps: Sequence[int],
+               histories: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
+        """`streams[r]`: request index of row r; `steps[r]`: tokens it has generated so far;
+        `histories[r]`: prompt + generated ids (only read when a repeat penalty is set)."""
+        rows = len(streams)
+        us = [uniform01(self.cfg.seed, s, k) for s, k in zip(streams, steps)]
+        if logits.is_cuda and self.cfg.on_device and not self.penalised:
+            from ..csrc import kernels as K
+            if self._out is None or self._out.numel() < rows:
+                self._out = torch.empty(max(rows, 64), dtype=torch.int32, device=logits.device)
+            out = self._out[:rows]
+            if self.cfg.greedy:
+                K.argmax(logits, out, rows)
+            else:
+                temps = torch.full((rows,), float(self.cfg.temp), dtype=torch.float32).to(logits.device, non_blocking=True)
+                uni = torch.tensor(us, dtype=torch.float64).to(logits.device, non_blocking=True)
+                K.sample(logits, temps, uni, out, rows)
+            return out.cpu().tolist()
+        host = logits[:rows].detach().to("cpu", torch.float32).numpy()
+        res = []
+        for r in range(rows):
+            row = host[r].copy()
+            if self.penalised and histories is not None:
+                apply_repeat_penalty(row, histories[r], self.repeat_penalty, self.repeat_last_n)
+            res.append(sample_host(row, self.cfg, us[r]))
+        return res

@@ -325,8 +325,7 @@ def generate_greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int]
     out: List[int] = []
     for _ in range(n):
         logits = forward(cfg, w, seq, wide)[-1]
-        t = int(torch.argmax(logits).item()) if True else greedy(logits.tolist())
-        # torch.argmax returns the first maximum as well
+        t = greedy(logits.tolist())
         if t in stop:
             break
         out.append(t)

@@ -1,0 +1,145 @@
+"""The cache's bookkeeping on the CPU: no slot or page lost, held twice or freed twice."""
+import random
+
+import pytest
+import torch
+
+from gogguf_b200.cache import CacheError, CacheFull, FreeList, KVRequest, SequenceCache, StateRequest
+
+
+def test_free_list():
+    f = FreeList(3)
+    a, b, c = f.take(), f.take(), f.take()
+    assert sorted([a, b, c]) == [0, 1, 2] and f.free_count == 0
+    with pytest.raises(CacheFull):
+        f.take()
+    f.give(b)
+    with pytest.raises(CacheError):
+        f.give(b)                      # freed twice
+    with pytest.raises(CacheError):
+        f.give(7)                      # never existed
+    assert f.take() == b               # last freed is first reused
+    f.check()
+
+
+def make_cache(max_tokens=640, window=None, state=False, max_slots=None):
+    reqs = [KVRequest(2, 8), KVRequest(2, 8, window=window) if window else KVRequest(2, 8), None]
+    cache_of = [None, None, None]
+    if state:
+        reqs.append(StateRequest((3,), torch.float32))
+        cache_of.append(None)
+    return SequenceCache(reqs, cache_of, max_tokens, dtype=torch.float32, device="cpu", max_slots=max_slots)
+
+
+def test_groups_by_need():
+    c = make_cache(window=16)
+    assert len(c.groups) == 2 and c.groups[0].k.shape == (1, 10, 2, 64, 8)
+    same = make_cache()
+    assert len(same.groups) == 1 and same.groups[0].k.shape[0] == 2
+    assert same.view(0).k.data_ptr() != same.view(1).k.data_ptr()
+    assert same.view(2) is None
+
+
+def test_plan_commit_lengths_and_capacity():
+    c = make_cache(max_tokens=256)          # 4 pages
+    a, b = c.open(), c.open()
+    c.plan([a, b], [65, 3])                 # 2 + 1 pages
+    assert c.length(a) == 0                 # lengths move only at commit (cache.go:37-45)
+    c.commit([a, b], [65, 3])
+    assert (c.length(a), c.length(b)) == (65, 3)
+    c.plan([b], [61])                       # still in b's first page
+    c.commit([b], [61])
+    with pytest.raises(CacheFull):
+        c.plan([a, b], [64, 64])            # needs 2 more pages, 1 free; nothing may be reserved
+    assert c.groups[0].pages.free_count == 1
+    c.plan([b], [1])
+    c.commit([b], [1])
+    assert c.groups[0].pages.free_count == 0
+    c.check()
+    c.close(a)
+    assert c.groups[0].pages.free_count == 2
+    with pytest.raises(CacheError):
+        c.close(a)                          # closed twice
+    with pytest.raises(CacheError):
+        c.plan([a], [1])                    # not open
+    with pytest.raises(CacheError):
+        c.plan([b, b], [1, 1])
+    c.check()
+
+
+def test_slots_and_pages_are_reused():
+    c = make_cache(max_tokens=128, max_slots=2)
+    s1 = c.open()
+    c.plan([s1], [100]); c.commit([s1], [100])
+    pages1 = list(c.groups[0].seq_pages[s1])
+    c.close(s1)
+    s2 = c.open()
+    assert s2 == s1 and c.length(s2) == 0
+    c.plan([s2], [70]); c.commit([s2], [70])
+    assert set(c.groups[0].seq_pages[s2]) == set(pages1)
+    c.check()
+
+
+def test_window_group_gives_pages_back():
+    c = make_cache(max_tokens=64 * 8, window=70)
+    s = c.open()
+    c.plan([s], [64 * 4]); c.commit([s], [64 * 4])
+    full, win = c.groups
+    assert full.pages.held_count == 4
+    # length 256, window 70: positions below 187 are out of every later window; pages 0 and 1 (0..127) go
+    assert win.pages.held_count == 2
+    assert win.table_row(s, 6)[2:4] == win.seq_pages[s][2:4]
+    c.plan([s], [1]); c.commit([s], [1])
+    assert win.pages.held_count == 3 and full.pages.held_count == 5
+    c.check()
+    c.close(s)
+    assert win.pages.held_count == 0 and full.pages.held_count == 0
+    c.check()
+
+
+def test_state_is_zeroed_when_a_slot_is_opened():
+    c = make_cache(state=True, max_slots=2)
+    s = c.open()
+    c.view(3).state[s] += 5.0
+    c.close(s)
+    s2 = c.open()
+    assert s2 == s and float(c.view(3).state[s2].abs().sum()) == 0.0
+
+
+def test_reading_another_entrys_cache():
+    reqs = [KVRequest(1, 4), KVRequest(1, 4)]
+    c = SequenceCache(reqs, [None, 0], 64, dtype=torch.float32, device="cpu")
+    assert c.view(1) is c.view(0) and c.groups[0].k.shape[0] == 1
+    with pytest.raises(CacheError):
+        SequenceCache([None, KVRequest(1, 4)], [None, 0], 64, dtype=torch.float32, device="cpu")
+
+
+def test_random_traffic_keeps_the_books():
+    rng = random.Random(0)
+    c = make_cache(max_tokens=64 * 12, window=40, max_slots=5)
+    live = {}
+    for _ in range(400):
+        op = rng.random()
+        if op < 0.3 and c.slots.free_count:
+            live[c.open()] = 0
+        elif op < 0.5 and live:
+            s = rng.choice(list(live))
+            c.close(s); del live[s]
+        elif live:
+            ss = rng.sample(list(live), rng.randint(1, len(live)))
+            ns = [rng.randint(1, 90) for _ in ss]
+            try:
+                c.plan(ss, ns)
+            except CacheFull:
+                pass
+            else:
+                c.commit(ss, ns)
+                for s, n in zip(ss, ns):
+                    live[s] += n
+        c.check()
+        for s, n in live.items():
+            assert c.length(s) == n
+    for s in list(live):
+        c.close(s)
+    c.check()
+    assert all(g.pages.held_count == 0 for g in c.groups) and c.slots.held_count == 0

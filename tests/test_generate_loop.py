@@ -1,0 +1,133 @@
+"""The generation loop's decisions, with a scripted model on the CPU (no GPU)."""
+import pytest
+import torch
+
+from gogguf_b200.cache import KVRequest, SequenceCache
+from gogguf_b200.engine.generate import GenerateParams, Generator, plan_batches
+from gogguf_b200.sampling import SamplerConfig
+
+V = 16
+
+
+class ScriptedStepper:
+    """Stands in for the stepper: the next token of a sequence is (last token + 1) % V."""
+
+    def __init__(self, max_tokens=64 * 8, max_slots=None):
+        self.cache = SequenceCache([KVRequest(1, 4)], [None], max_tokens, dtype=torch.float32, device="cpu",
+                                   max_slots=max_slots)
+        self.steps = []
+
+    def step(self, entries):
+        slots = [e.slot for e in entries]
+        counts = [len(e.tokens) for e in entries]
+        self.cache.plan(slots, counts)
+        self.steps.append([(e.slot, len(e.tokens)) for e in entries])
+        rows = []
+        for e in entries:
+            for w in e.want:
+                row = torch.zeros(V)
+                row[(e.tokens[w] + 1) % V] = 5.0
+                rows.append(row)
+        self.cache.commit(slots, counts)
+        self.cache.check()
+        return torch.stack(rows)
+
+
+def gen(stepper, context=1000, **kw):
+    return Generator(stepper, V, context, **kw)
+
+
+def test_plan_batches():
+    assert plan_batches([5, 3, 9], 4, max_batch=2, capacity_tokens=640, page_size=64, context=100) == [[0, 1], [2]]
+    # capacity: each needs 2 pages (70+20=90 -> 128), 3 pages in all -> one per batch
+    assert plan_batches([70, 70], 20, 8, 192, 64, 1000) == [[0], [1]]
+    # the context bounds what a sequence can hold
+    assert plan_batches([60, 60], 500, 8, 128, 64, context=64) == [[0, 1]]
+    with pytest.raises(ValueError):
+        plan_batches([0], 4, 2, 640, 64, 100)
+    with pytest.raises(ValueError):
+        plan_batches([200], 4, 2, 640, 64, 100)
+    with pytest.raises(ValueError):
+        plan_batches([100], 100, 2, 128, 64, 1000)
+
+
+def test_unequal_prompts_and_token_limit():
+    st = ScriptedStepper()
+    out = gen(st).generate([[1, 2, 3], [7]], GenerateParams(max_tokens=3))
+    assert [r.tokens for r in out] == [[4, 5, 6], [8, 9, 10]]
+    assert all(r.finish_reason == "length" for r in out)
+    assert st.steps[0] == [(st.steps[0][0][0], 3), (st.steps[0][1][0], 1)]      # prompts in one step
+    assert all(n == 1 for step in st.steps[1:] for _, n in step)                # then one token each
+    assert len(st.steps) == 3            # the third token is sampled but never fed
+    assert st.cache.live_slots == 0
+
+
+def test_stop_token_is_neither_kept_nor_fed_and_others_go_on():
+    st = ScriptedStepper()
+    out = gen(st).generate([[1], [9]], GenerateParams(max_tokens=6, stop_token_ids=[4]))
+    assert out[0].tokens == [2, 3] and out[0].finish_reason == "stop"           # 4 is not appended
+    assert out[1].tokens == [10, 11, 12, 13, 14, 15] and out[1].finish_reason == "length"
+    sizes = [len(s) for s in st.steps]
+    assert sizes == [2, 2, 2, 1, 1, 1]   # the batch shrinks when the first sequence ends
+    fed = sum(n for s in st.steps for _, n in s)
+    assert fed == 2 + 2 + 2 + 1 + 1 + 1  # the stop token itself was never fed
+    st.cache.check()
+
+
+def test_default_stop_tokens_come_from_the_model():
+    st = ScriptedStepper()
+    out = gen(st, default_stop=(3,)).generate([[1]], GenerateParams(max_tokens=9))
+    assert out[0].tokens == [2] and out[0].finish_reason == "stop"
+    out = gen(st, default_stop=(3,)).generate([[1]], GenerateParams(max_tokens=4, stop_token_ids=[]))
+    assert out[0].tokens == [2, 3, 4, 5]
+
+
+def test_batches_follow_one_another_and_reuse_slots():
+    st = ScriptedStepper(max_slots=2)
+    prompts = [[i] for i in range(5)]
+    out = gen(st, max_batch=2).generate(prompts, GenerateParams(max_tokens=2))
+    assert [r.tokens for r in out] == [[i + 1, i + 2] for i in range(5)]
+    prefills = [s for s in st.steps if any(n >= 1 for _, n in s)][::2]
+    used = {slot for s in st.steps for slot, _ in s}
+    assert used <= {0, 1} and st.cache.live_slots == 0
+
+
+def test_context_limit_ends_one_sequence_only():
+    st = ScriptedStepper()
+    out = gen(st, context=6).generate([[1, 2, 3, 4], [1]], GenerateParams(max_tokens=5))
+    # 4 prompt tokens: positions 4 and 5 can be fed, the token that would sit at 6 cannot
+    assert out[0].tokens == [5, 6, 7] and out[0].finish_reason == "length"
+    assert out[1].tokens == [2, 3, 4, 5, 6]
+    assert max(st.cache.lengths) == 0 and st.cache.live_slots == 0
+
+
+def test_callback_can_end_a_sequence():
+    st = ScriptedStepper()
+    seen = []
+
+    def cb(i, t):
+        seen.append((i, t))
+        return not (i == 0 and t == 3)
+
+    out = gen(st).generate([[1], [5]], GenerateParams(max_tokens=4, on_token=cb))
+    assert out[0].tokens == [2, 3] and out[0].finish_reason == "callback"
+    assert out[1].tokens == [6, 7, 8, 9]
+
+
+def test_max_tokens_zero_means_128():
+    st = ScriptedStepper(max_tokens=64 * 4)
+    out = gen(st).generate([[1]], GenerateParams(max_tokens=0))
+    assert len(out[0].tokens) == 128       # session.go:134-137
+
+
+def test_temperature_draws_do_not_depend_on_the_batch():
+    p = GenerateParams(max_tokens=4, sampler=SamplerConfig(temp=1.5, seed=11))
+
+    class Flat(ScriptedStepper):
+        def step(self, entries):
+            super().step(entries)
+            return torch.zeros(sum(len(e.want) for e in entries), V)     # uniform distribution
+
+    alone = gen(Flat()).generate([[3]], p)[0].tokens
+    both = gen(Flat()).generate([[3], [9, 9]], p)
+    assert both[0].tokens == alone and both[1].tokens != alone
