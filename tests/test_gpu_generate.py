@@ -1,0 +1,81 @@
+"""Generation through the entry point against the plain implementation; long decoding; first tokens."""
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import TOL_BF16, TOL_F32, make_folder, random_tokens, read_folder, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def test_greedy_generation_through_the_entry_point(tmp_path_factory):
+    import gogguf_b200 as gg
+    folder = make_folder(tmp_path_factory.getbasetemp(), "A", "float32")
+    cfg, w = read_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], 5, 1), random_tokens(cfg["vocab_size"], 3, 2)]
+    engine = gg.load(folder, gg.LoadOptions(dtype="float32", max_tokens=1024))
+    ctx = engine.new_context()
+    out = ctx.generate(prompts, gg.GenerateParams(max_tokens=4, stop_token_ids=[]))
+    for p, r in zip(prompts, out):
+        assert r.tokens == plain.generate_greedy(cfg, w, p, 4, wide=True)
+        assert r.finish_reason == "length" and r.prompt_tokens == len(p)
+    # a stop token ends one sequence early; the other goes on and its tokens do not change
+    ref0 = plain.generate_greedy(cfg, w, prompts[0], 12, wide=True)
+    ref1 = plain.generate_greedy(cfg, w, prompts[1], 12, wide=True)
+    stop = next(t for t in ref0[2:] if t not in ref1)
+    out = ctx.generate(prompts, gg.GenerateParams(max_tokens=12, stop_token_ids=[stop]))
+    assert out[0].tokens == ref0[:ref0.index(stop)] and out[0].finish_reason == "stop"
+    assert out[1].tokens == ref1
+    # a single prompt gives a single result
+    one = ctx.generate(prompts[0], gg.GenerateParams(max_tokens=3, stop_token_ids=[]))
+    assert one.tokens == ref0[:3]
+    ctx.cache.check()
+    assert ctx.cache.live_slots == 0
+
+
+def test_temperature_sampling_follows_the_plain_sampler(tmp_path_factory):
+    import gogguf_b200 as gg
+    folder = make_folder(tmp_path_factory.getbasetemp(), "B", "float32", scale=8.0)
+    cfg, w = read_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], n, 20 + n) for n in (7, 1, 4)]
+    engine = gg.load(folder, gg.LoadOptions(dtype="float32", max_tokens=1024))
+    params = gg.GenerateParams(max_tokens=5, sampler=gg.SamplerConfig(temp=0.8, seed=123), stop_token_ids=[])
+    out = engine.new_context().generate(prompts, params)
+    for i, (p, r) in enumerate(zip(prompts, out)):
+        seq = list(p)
+        for k, tok in enumerate(r.tokens):
+            logits = plain.forward(cfg, w, seq, wide=True)[-1].float().tolist()
+            assert tok == plain.sample(logits, 0.8, 0, 1.0, 0.0, plain.uniform01(123, i, k)), (i, k)
+            seq.append(tok)
+    # the masked options run the host chain on the same logits
+    params = gg.GenerateParams(max_tokens=4, sampler=gg.SamplerConfig(temp=0.9, top_k=7, top_p=0.9, seed=5),
+                               repeat_penalty=1.3, stop_token_ids=[])
+    out = engine.new_context().generate(prompts[:1], params)
+    seq = list(prompts[0])
+    for k, tok in enumerate(out[0].tokens):
+        logits = plain.forward(cfg, w, seq, wide=True)[-1].float().tolist()
+        plain.repeat_penalty(logits, seq, 1.3, 64)
+        assert tok == plain.sample(logits, 0.9, 7, 0.9, 0.0, plain.uniform01(5, 0, k))
+        seq.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(tmp_path_factory, dtype):
+    from gogguf_b200.engine import Model, StepEntry, Stepper
+    name = "W"
+    folder = make_folder(tmp_path_factory.getbasetemp(), name, dtype, scale=1.0 if dtype == "float32" else 4.0)
+    cfg, w = read_folder(folder)
+    toks = random_tokens(cfg["vocab_size"], 330, 4)
+    oracle = plain.forward(cfg, w, toks, wide=True)
+    tol = TOL_F32 if dtype == "float32" else TOL_BF16
+    model = Model.load(folder, dtype=dtype)
+    cache = model.new_cache(512)
+    st = Stepper(model, cache)
+    s = cache.open()
+    # the first tokens of a sequence, one by one from position 0, then hundreds of single steps
+    for i, t in enumerate(toks):
+        got = st.step([StepEntry(s, [t], want=[0])])
+        if i < 4 or i % 37 == 0 or i > 320:
+            assert rel_err(got, oracle[i:i + 1]) < tol, i
+    cache.close(s)
+    cache.check()
