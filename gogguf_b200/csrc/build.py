@@ -45,6 +45,7 @@ MODULES: Dict[str, str] = {
     "gemm_plain": "gemm_plain.cu",
     "attention_plain": "attention_plain.cu",
     "sampling": "sampling.cu",
+    "gemm_tcgen05": "gemm_tcgen05.cu",
 }
 
 _HEADERS = ["common.cuh"]

@@ -1,0 +1,416 @@
+// bfloat16 matrix product on the 5th-generation tensor cores of sm_100a:
+//   D[i, j] = sum_k A[i, k] * B[j, k],  A[RA, K] and B[RB, K] both K-major, float32 accumulate.
+//
+// One CTA computes one 128 x BN tile of D over a slab of K:
+//   * warp 0, one thread: TMA producer.  cp.async.bulk.tensor loads a [128 x 64] tile of A and a
+//     [BN x 64] tile of B per pipeline stage into 128-byte-swizzled shared memory and signals the
+//     stage's "full" mbarrier with the byte count.
+//   * warp 1, one thread: issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16) four times per
+//     stage with the accumulator in tensor memory, then tcgen05.commit to the stage's "empty"
+//     mbarrier (frees the stage when the tensor core has read it) and, after the last stage, to
+//     the "accumulator ready" mbarrier.  Warp 1 also allocates and frees the tensor memory.
+//   * warps 2..5: epilogue.  tcgen05.ld brings the accumulator to registers (each warp its own 32
+//     lanes of tensor memory), converts and stores.
+//
+// Two orientations share the kernel.  Prefill ("normal"): A = activations x[M, K], B = weights
+// W[N, K], out[m, n] = D[m, n].  Decode ("swap"): A = weights, so that the 128-row side of the
+// instruction is filled by output features and a small batch of tokens is the N side (16..128);
+// out[m, n] = D[n, m].  In decode the product is a stream of weights from HBM: the grid is
+// widened by splitting K over blockIdx.z, partial sums go to a float32 scratch buffer and a second
+// kernel adds them in a fixed order (no float atomics: results do not depend on timing).
+//
+// Every mbarrier wait is bounded; a wait that runs out records a code in the status word, raises
+// the CTA's abort flag, and all roles fall through to the common exit, which lets copies in flight
+// land and frees the tensor memory.
+//
+// The reference multiplies with a one-thread-per-row scalar PTX kernel (pkg/gpu/cuda/ptx.go:67-129).
+#include <cuda.h>
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;           // rows of A per tile = MMA M
+constexpr int BK = 64;            // bf16 elements per stage row = 128 bytes = one swizzle atom
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int NUM_THREADS = 192;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // about one second
+
+enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up (own limit, or another role raised the abort flag).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    int spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 63) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes, 128-byte swizzle:
+// 8-row groups are 1024 bytes apart (stride byte offset), the leading byte offset is not used.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);        // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                         // leading byte offset (ignored for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset
+    d |= (uint64_t)1 << 46;                         // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor, kind::f16: bf16 x bf16 -> f32, both operands K-major.
+__device__ __forceinline__ uint32_t make_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <int BN> constexpr int tmem_cols() { return BN < 32 ? 32 : BN; }
+
+template <int BN, int STAGES, bool SWAP>
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(
+    const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+    void* __restrict__ out, int out_mode, long long ldo, int M, int N, int K, int kb_per_split,
+    float* __restrict__ partial, int* __restrict__ status) {
+    constexpr int B_BYTES = BN * BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* accum = empty + STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(accum + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+    const int num_kb = (K + BK - 1) / BK;
+    const int kb0 = split * kb_per_split;
+    const int nkb = min(num_kb, kb0 + kb_per_split) - kb0;   // >= 1 by construction of the grid
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(accum, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols<BN>()) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+                if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, 1)) break;
+                mbar_expect_tx(&full[s], STAGE_BYTES);
+                uint8_t* sa = smem + s * STAGE_BYTES;
+                tma_load_2d(sa, &tmA, &full[s], (kb0 + i) * BK, tile_a * BM);
+                tma_load_2d(sa + A_BYTES, &tmB, &full[s], (kb0 + i) * BK, tile_b * BN);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(BM, BN);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+                ok = mbar_wait(&full[s], ph, abort_flag, status, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                const uint64_t adesc = make_smem_desc(sa);
+                const uint64_t bdesc = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // advance 32 bytes (16 bf16) along K inside the swizzle atom: +2 in 16-byte units
+                    umma(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty[s]);
+            }
+            if (ok) umma_commit(accum);
+        }
+    } else {
+        // epilogue: warp w reads tensor-memory lanes 32*(w%4) .. +31 (row i of D is lane i)
+        const int q = warp & 3;
+        const int row = q * 32 + lane;           // row of the D tile held by this thread
+        if (mbar_wait(accum, 0, abort_flag, status, 3)) {
+            tc_fence_after();
+            const int gi = tile_a * BM + row;    // global row of D (A side)
+            const int RA = SWAP ? N : M, RB = SWAP ? M : N;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (tile_b * BN + c0 >= RB) break;          // whole warp agrees: columns beyond the extent
+                uint32_t r[16];
+                tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                tmem_ld_wait();
+                if (gi >= RA) continue;
+                const int gj0 = tile_b * BN + c0;
+                if (partial != nullptr) {
+                    float* p = partial + (size_t)split * M * N;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int gj = gj0 + j;
+                        if (gj < RB) {
+                            if (SWAP) p[(size_t)gj * N + gi] = __uint_as_float(r[j]);
+                            else p[(size_t)gi * N + gj] = __uint_as_float(r[j]);
+                        }
+                    }
+                } else if (SWAP) {
+                    // out[m = gj][n = gi]: for a fixed j the 32 lanes write 32 consecutive n
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int gj = gj0 + j;
+                        if (gj < RB) {
+                            const float v = __uint_as_float(r[j]);
+                            const size_t o = (size_t)gj * ldo + gi;
+                            if (out_mode == OUT_BF16) ((bf16*)out)[o] = __float2bfloat16_rn(v);
+                            else if (out_mode == OUT_F32) ((float*)out)[o] = v;
+                            else ((float*)out)[o] += v;
+                        }
+                    }
+                } else {
+                    // out[m = gi][n = gj0 .. gj0+15]: 16 consecutive n per thread
+                    const size_t o = (size_t)gi * ldo + gj0;
+                    const bool whole = gj0 + 16 <= RB;
+                    if (out_mode == OUT_BF16) {
+                        bf16* op = (bf16*)out + o;
+                        if (whole && ((((uintptr_t)op) & 15) == 0)) {
+                            uint32_t pk[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                                pk[j] = *reinterpret_cast<uint32_t*>(&h2);
+                            }
+                            reinterpret_cast<uint4*>(op)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            reinterpret_cast<uint4*>(op)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (gj0 + j < RB) op[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        }
+                    } else {
+                        float* op = (float*)out + o;
+                        if (whole && ((((uintptr_t)op) & 15) == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                                float4* dst = reinterpret_cast<float4*>(op) + j;
+                                if (out_mode == OUT_F32_ACC) {
+                                    const float4 old = *dst;
+                                    v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                                }
+                                *dst = v;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (gj0 + j < RB) {
+                                    if (out_mode == OUT_F32_ACC) op[j] += __uint_as_float(r[j]);
+                                    else op[j] = __uint_as_float(r[j]);
+                                }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // a wait ran out: give copies and instructions in flight time to land before the memory goes away
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols<BN>()) : "memory");
+    }
+}
+
+// out[m, n] = epilogue( sum over splits of partial[s, m, n] ), splits added in index order.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, int out_mode,
+                                     long long ldo, int M, int N, int splits) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = (long long)M * N;
+    if (idx >= total) return;
+    const int m = (int)(idx / N), n = (int)(idx - (long long)m * N);
+    float s = 0.f;
+    for (int k = 0; k < splits; ++k) s += partial[(size_t)k * total + idx];
+    const size_t o = (size_t)m * ldo + n;
+    if (out_mode == OUT_BF16) ((bf16*)out)[o] = __float2bfloat16_rn(s);
+    else if (out_mode == OUT_F32) ((float*)out)[o] = s;
+    else ((float*)out)[o] += s;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A [rows, K] bf16 matrix with row stride ld (elements), boxes of [box_rows x 64], 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return GG_ERR_TMAP;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : GG_ERR_TMAP;
+}
+
+template <int BN, int STAGES, bool SWAP>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N, int K,
+           int splits, int kb_per_split, float* partial, int* status, cudaStream_t stream) {
+    constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int RA = SWAP ? N : M, RB = SWAP ? M : N;
+    dim3 grid((RA + BM - 1) / BM, (RB + BN - 1) / BN, splits);
+    gemm_tc_kernel<BN, STAGES, SWAP><<<grid, NUM_THREADS, smem, stream>>>(
+        ta, tb, out, out_mode, ldo, M, N, K, kb_per_split, splits > 1 ? partial : nullptr, status);
+    return gg_last_error();
+}
+
+}  // namespace
+
+// Number of K splits the launcher would use for a product of this shape (0: the shape is not taken).
+// The caller sizes the scratch buffer with it: splits * M * N floats when splits > 1.
+GG_API gg_gemm_tc_splits(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0 || (K % 8) != 0) return 0;
+    if (M > 128) return 1;
+    const int num_kb = (K + BK - 1) / BK;
+    const int tiles = (N + BM - 1) / BM;
+    int splits = (296 + tiles - 1) / tiles;      // aim at two CTAs' worth of work per SM on 148 SMs
+    if (splits > num_kb / 4) splits = num_kb / 4;  // at least four 64-wide slabs per CTA
+    if (splits > 16) splits = 16;
+    if (splits < 1) splits = 1;
+    // no empty split: the last one must own at least one slab
+    int per = (num_kb + splits - 1) / splits;
+    splits = (num_kb + per - 1) / per;
+    return splits;
+}
+
+// out[M, N] (mode) = x[M, K] (bf16, row stride ldx) * w[N, K]^T (bf16, contiguous).
+// out_mode: 0 bf16 store, 1 float32 store, 2 float32 add (residual).  scratch: float32 buffer of at
+// least splits * M * N elements when gg_gemm_tc_splits(M, N, K) > 1 (may be null otherwise).
+// status: one int on the device, zero-initialised by the caller; a non-zero value after the kernel
+// means a bounded wait ran out (1 producer, 2 issuer, 3 epilogue).
+GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, int N, int K, long long ldx,
+                  long long ldo, float* scratch, long long scratch_elems, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K % 8) != 0 || (ldx % 8) != 0 || ldx < K || ldo < N) return GG_ERR_ARG;
+    if ((((uintptr_t)x) & 15) || (((uintptr_t)w) & 15) || out_mode < 0 || out_mode > 2 || status == nullptr) return GG_ERR_ARG;
+    const int num_kb = (K + BK - 1) / BK;
+    const bool swap = M <= 128;
+    int splits = gg_gemm_tc_splits(M, N, K);
+    if (splits > 1 && (scratch == nullptr || scratch_elems < (long long)splits * M * N)) return GG_ERR_ARG;
+    const int per = (num_kb + splits - 1) / splits;
+    CUtensorMap ta, tb;
+    int rc;
+    if (swap) {
+        const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+        if ((rc = make_map(&ta, w, N, K, K, BM)) != 0) return rc;
+        if ((rc = make_map(&tb, x, M, K, ldx, bn)) != 0) return rc;
+        if (bn == 16) rc = launch<16, 8, true>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, status, stream);
+        else if (bn == 32) rc = launch<32, 8, true>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, status, stream);
+        else if (bn == 64) rc = launch<64, 8, true>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, status, stream);
+        else rc = launch<128, 6, true>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, status, stream);
+    } else {
+        const int bn = N > 128 ? 256 : 128;
+        if ((rc = make_map(&ta, x, M, K, ldx, BM)) != 0) return rc;
+        if ((rc = make_map(&tb, w, N, K, K, bn)) != 0) return rc;
+        if (bn == 256) rc = launch<256, 4, false>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, status, stream);
+        else rc = launch<128, 6, false>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, status, stream);
+    }
+    if (rc != 0) return rc;
+    if (splits > 1) {
+        const long long total = (long long)M * N;
+        splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(scratch, out, out_mode, ldo, M, N, splits);
+        return gg_last_error();
+    }
+    return 0;
+}

@@ -1,11 +1,88 @@
-"""Host side of the tcgen05 tensor-core product: tensor maps, tile choice, launch."""
+"""Host side of the tcgen05 tensor-core product (csrc/gemm_tcgen05.cu)."""
 from __future__ import annotations
 
-from typing import Callable, Optional
+from typing import Callable, Dict, Optional
 
 import torch
 
+from .build import KernelError, kernel, module
+
+OUT_BF16, OUT_F32, OUT_F32_ACC = 0, 1, 2
+
+_status: Dict[torch.device, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """One int32 on the device that kernels with bounded waits write to when a wait runs out."""
+    device = torch.device(device)
+    t = _status.get(device)
+    if t is None:
+        t = _status[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return t
+
+
+def check_status(device: torch.device) -> None:
+    """Raise if a bounded wait ran out in any kernel since the last check (reads one int: a sync)."""
+    t = _status.get(torch.device(device))
+    if t is None:
+        return
+    v = int(t.item())
+    if v != 0:
+        t.zero_()
+        raise KernelError(f"a bounded wait inside a tensor-core kernel ran out (code {v}: "
+                          "1 TMA producer, 2 MMA issuer, 3 epilogue); results of that step are invalid")
+
+
+def splits_for(M: int, N: int, K: int) -> int:
+    module("gemm_tcgen05")
+    raw = module("gemm_tcgen05").lib.gg_gemm_tc_splits
+    return int(raw(int(M), int(N), int(K)))
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+            m: Optional[int] = None, scratch: Optional[torch.Tensor] = None) -> None:
+    """out[M, N] (+)= x[M, K] @ w[N, K]^T, bfloat16 operands, float32 accumulation on the tensor cores."""
+    N, K = w.shape
+    M = x.shape[0] if m is None else m
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc takes bfloat16 operands")
+    if out.dtype == torch.bfloat16:
+        if accumulate:
+            raise KernelError("gemm_tc: sums are kept in float32")
+        mode = OUT_BF16
+    elif out.dtype == torch.float32:
+        mode = OUT_F32_ACC if accumulate else OUT_F32
+    else:
+        raise KernelError(f"gemm_tc: output dtype {out.dtype}")
+    if x.stride(-1) != 1 or out.stride(-1) != 1 or not w.is_contiguous():
+        raise KernelError("gemm_tc: operands must be row-major")
+    st = status_word(x.device)
+    kernel("gemm_tcgen05", "gg_gemm_tc")(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), mode, M, N, K, x.stride(0), out.stride(0),
+        scratch.data_ptr() if scratch is not None else 0, scratch.numel() if scratch is not None else 0,
+        st.data_ptr(), torch.cuda.current_stream().cuda_stream)
+
 
 def make_linear(weight: torch.Tensor) -> Optional[Callable]:
-    """A callable f(x, out, accumulate, m, ws) for this weight, or None if its sizes are not taken."""
-    return None
+    """A callable f(x, out, accumulate, m, ws) for this weight, or None if its sizes are not taken
+    (K must be a multiple of 8 so that rows start on 16-byte boundaries for TMA)."""
+    N, K = weight.shape
+    if K % 8 != 0 or weight.data_ptr() % 16 != 0:
+        return None
+
+    def run(x, out, accumulate, m, ws):
+        M = x.shape[0] if m is None else m
+        if x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
+            from . import kernels as Kn
+            Kn.gemm_plain(x, weight, out, accumulate, m)
+            return
+        splits = splits_for(M, N, K)
+        scratch = None
+        if splits > 1:
+            if ws is None:
+                scratch = torch.empty(splits * M * N, dtype=torch.float32, device=x.device)
+            else:
+                scratch = ws.get("gemm_splitk", (splits * M * N,), torch.float32)
+        gemm_tc(x, weight, out, accumulate, m, scratch)
+
+    return run

@@ -1,0 +1,205 @@
+"""Each kernel alone against a plain float32/float64 PyTorch reference of the same op, at sizes other
+than the engine's (odd widths, head sizes in steps of 16, vocabularies that are no power of two)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def K():
+    from gogguf_b200.csrc import kernels
+    return kernels
+
+
+def rel(a, b):
+    a, b = a.double(), b.double()
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+
+# ------------------------------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_embed_gather(dt):
+    g = torch.Generator(device=DEV).manual_seed(0)
+    table = torch.randn(331, 72, device=DEV, generator=g).to(dt)
+    toks = torch.tensor([5, 330, -1, 0, 17], dtype=torch.int32, device=DEV)
+    out = torch.full((5, 72), 9.0, device=DEV)
+    K().embed_gather(table, toks, out)
+    want = table[toks.clamp_min(0).long()].float()
+    want[2] = 0
+    assert torch.equal(out, want)
+
+
+@pytest.mark.parametrize("H,eps", [(72, 1e-6), (1000, 1e-5), (4096, 3e-6), (5120 + 8, 1e-6)])
+@pytest.mark.parametrize("odt", [torch.float32, torch.bfloat16])
+def test_rmsnorm(H, eps, odt):
+    g = torch.Generator(device=DEV).manual_seed(1)
+    x = torch.randn(7, H, device=DEV, generator=g) * 3
+    w = 1 + 0.1 * torch.randn(H, device=DEV, generator=g)
+    out = torch.empty(7, H, device=DEV, dtype=odt)
+    K().rmsnorm(x, w, eps, out)
+    xd = x.double()
+    want = xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + eps) * w.double()
+    assert rel(out, want) < (2e-6 if odt == torch.float32 else 5e-3)
+    rows = torch.tensor([6, -1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(3, H, device=DEV, dtype=odt)
+    K().rmsnorm(x, w, eps, out2, rows)
+    assert torch.equal(out2[0], out[6]) and torch.equal(out2[2], out[0]) and float(out2[1].abs().sum()) == 0
+
+
+def test_rope_tables_in_float64():
+    pos = torch.tensor([0, 1, 777, 40000, -1], dtype=torch.int32, device=DEV)
+    d, theta = 48, 50000.0
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(d // 2, dtype=torch.float64) / d).to(DEV)
+    cos = torch.empty(5, d // 2, device=DEV)
+    sin = torch.empty(5, d // 2, device=DEV)
+    K().rope_tables(pos, inv, cos, sin)
+    ang = pos.clamp_min(0).double()[:, None] * inv[None, :]
+    assert float((cos.double() - torch.cos(ang)).abs().max()) < 1e-7
+    assert float((sin.double() - torch.sin(ang)).abs().max()) < 1e-7
+
+
+def plain_norm_rope(x, w, eps, cos, sin, rot):
+    xd = x.double()
+    if w is not None:
+        xd = xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + eps) * w.double()
+    half = rot // 2
+    x0, x1, rest = xd[..., :half], xd[..., half:rot], xd[..., rot:]
+    c, s = cos.double()[:, None, :], sin.double()[:, None, :]
+    return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c, rest], -1)
+
+
+@pytest.mark.parametrize("nq,nkv,d,rot,norm", [(4, 2, 16, 16, True), (6, 1, 32, 32, True), (3, 3, 48, 48, True),
+                                               (5, 5, 80, 64, False), (8, 2, 128, 128, True), (2, 1, 256, 256, True)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_qk_norm_rope_cache(nq, nkv, d, rot, norm, dt):
+    g = torch.Generator(device=DEV).manual_seed(2)
+    ps, n_pages, B = 64, 6, 2
+    # two sequences: 70 new tokens from position 60 (crosses a page edge), and 3 tokens from 0; one padding row
+    starts, counts = [60, 0], [70, 3]
+    T = sum(counts) + 1
+    qkv = (torch.randn(T, (nq + 2 * nkv) * d, device=DEV, generator=g)).to(dt)
+    qw = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)) if norm else None
+    kw = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)) if norm else None
+    positions = torch.tensor(list(range(60, 130)) + [0, 1, 2] + [0], dtype=torch.int32, device=DEV)
+    sot = torch.tensor([0] * 70 + [1] * 3 + [-1], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[4, 1, 5], [2, 0, 0]], dtype=torch.int32, device=DEV)
+    inv = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot).to(DEV)
+    cos = torch.empty(T, rot // 2, device=DEV); sin = torch.empty(T, rot // 2, device=DEV)
+    K().rope_tables(positions, inv, cos, sin)
+    kp = torch.full((n_pages, nkv, ps, d), 7.0, device=DEV, dtype=dt)
+    vp = torch.full((n_pages, nkv, ps, d), 7.0, device=DEV, dtype=dt)
+    q = torch.empty(T, nq * d, device=DEV, dtype=dt)
+    K().qk_norm_rope_cache(qkv, q, qw, kw, 1e-5, cos, sin, positions, sot, table, ps, kp, vp, T, nq, nkv, d, rot)
+    x = qkv.float().reshape(T, nq + 2 * nkv, d)
+    wq = plain_norm_rope(x[:, :nq], qw, 1e-5, cos, sin, rot)
+    wk = plain_norm_rope(x[:, nq:nq + nkv], kw, 1e-5, cos, sin, rot)
+    wv = x[:, nq + nkv:].double()
+    tol = 3e-6 if dt == torch.float32 else 6e-3
+    assert rel(q.reshape(T, nq, d), wq) < tol
+    written = torch.zeros(n_pages, ps, dtype=torch.bool)
+    for t in range(T - 1):
+        b, p = int(sot[t]), int(positions[t])
+        page = int(table[b, p // ps])
+        written[page, p % ps] = True
+        assert rel(kp[page, :, p % ps], wk[t]) < tol
+        assert rel(vp[page, :, p % ps].double(), wv[t]) < (1e-7 if dt == torch.float32 else 1e-9) or torch.equal(vp[page, :, p % ps].float(), x[t, nq + nkv:])
+    # nothing else was touched (the padding row writes nothing)
+    untouched = ~written.to(DEV)
+    assert bool((kp.float()[untouched.nonzero(as_tuple=True)[0], :, untouched.nonzero(as_tuple=True)[1]] == 7.0).all())
+    # a layer that reads another layer's cache writes none
+    kp2 = kp.clone()
+    K().qk_norm_rope_cache(qkv * 2, q, qw, kw, 1e-5, cos, sin, positions, sot, table, ps, None, None, T, nq, nkv, d, rot)
+    assert torch.equal(kp, kp2)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_swiglu_and_residual_add(dt):
+    g = torch.Generator(device=DEV).manual_seed(3)
+    T, I = 5, 104
+    gu = (torch.randn(T, 2 * I, device=DEV, generator=g) * 4).to(dt)
+    out = torch.empty(T, I, device=DEV, dtype=dt)
+    K().swiglu(gu, out, T, I)
+    gd, ud = gu[:, :I].double(), gu[:, I:].double()
+    assert rel(out, gd / (1 + torch.exp(-gd)) * ud) < (2e-6 if dt == torch.float32 else 5e-3)
+    x = torch.randn(T, I, device=DEV, generator=g)
+    x0 = x.clone()
+    K().residual_add(x, out)
+    assert torch.equal(x, x0 + out.float())
+
+
+# ------------------------------------------------------------------------------------------ products
+@pytest.mark.parametrize("M,N,K_", [(1, 7, 5), (3, 64, 64), (70, 130, 257), (129, 96, 72), (5, 331, 104)])
+@pytest.mark.parametrize("xdt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32)])
+def test_gemm_plain(M, N, K_, xdt, wdt):
+    g = torch.Generator(device=DEV).manual_seed(4)
+    x = torch.randn(M, K_, device=DEV, generator=g).to(xdt)
+    w = torch.randn(N, K_, device=DEV, generator=g).to(wdt)
+    want = x.double() @ w.double().T
+    out = torch.empty(M, N, device=DEV)
+    K().gemm_plain(x, w, out)
+    assert rel(out, want) < 2e-6
+    res = torch.randn(M, N, device=DEV, generator=g)
+    acc = res.clone()
+    K().gemm_plain(x, w, acc, accumulate=True)
+    assert rel(acc, res.double() + want) < 2e-6
+    if xdt == torch.bfloat16:
+        ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        K().gemm_plain(x, w, ob)
+        assert rel(ob, want) < 5e-3
+    # batch invariance: a row's result does not depend on the other rows (bitwise)
+    one = torch.empty(1, N, device=DEV)
+    K().gemm_plain(x[M // 2:M // 2 + 1].contiguous(), w, one)
+    assert torch.equal(one[0], out[M // 2])
+
+
+TC_SHAPES = [(1, 128, 64), (8, 256, 512), (16, 4096, 4096), (17, 384, 1024), (64, 1000, 520), (128, 768, 2048),
+             (129, 256, 64), (300, 520, 264), (2048, 1024, 4096), (70, 96, 72), (5, 331, 104), (1000, 72, 48)]
+
+
+@pytest.mark.parametrize("M,N,K_", TC_SHAPES)
+def test_gemm_tcgen05(M, N, K_):
+    from gogguf_b200.csrc import tcgen05_gemm as tc
+    g = torch.Generator(device=DEV).manual_seed(5)
+    x = torch.randn(M, K_, device=DEV, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K_, device=DEV, generator=g).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    # float32 accumulation over K terms: the rounding error grows like sqrt(K) * 2^-24
+    tol = 2e-6 + 2e-7 * math.sqrt(K_)
+    splits = tc.splits_for(M, N, K_)
+    scratch = torch.empty(max(1, splits * M * N), device=DEV) if splits > 1 else None
+    out = torch.full((M, N), float("nan"), device=DEV)
+    tc.gemm_tc(x, w, out, scratch=scratch)
+    tc.check_status(DEV)
+    assert rel(out, want) < tol, (splits,)
+    res = torch.randn(M, N, device=DEV, generator=g)
+    acc = res.clone()
+    tc.gemm_tc(x, w, acc, accumulate=True, scratch=scratch)
+    assert rel(acc, res.double() + want) < tol
+    ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    tc.gemm_tc(x, w, ob, scratch=scratch)
+    tc.check_status(DEV)
+    assert rel(ob, want) < 5e-3
+    # the plain twin agrees
+    twin = torch.empty(M, N, device=DEV)
+    K().gemm_plain(x, w, twin)
+    assert rel(out, twin) < tol
+
+
+def test_gemm_tcgen05_strided_rows_and_padding_rows():
+    from gogguf_b200.csrc import tcgen05_gemm as tc
+    g = torch.Generator(device=DEV).manual_seed(6)
+    big = torch.randn(40, 512, device=DEV, generator=g).to(torch.bfloat16)
+    x = big[:, :256]                       # row stride 512, K = 256
+    w = torch.randn(200, 256, device=DEV, generator=g).to(torch.bfloat16)
+    outbig = torch.zeros(40, 300, device=DEV)
+    out = outbig[:, :200]
+    splits = tc.splits_for(24, 200, 256)
+    scratch = torch.empty(max(1, splits * 24 * 200), device=DEV)
+    tc.gemm_tc(x, w, out, m=24, scratch=scratch)      # only the first 24 rows are computed
+    tc.check_status(DEV)
+    assert rel(out[:24], x[:24].double() @ w.double().T) < 3e-6
+    assert float(outbig[24:].abs().sum()) == 0 and float(outbig[:, 200:].abs().sum()) == 0
