@@ -222,12 +222,22 @@ class _Module:
             raw.restype = ctypes.c_int
 
             def call(*args, _raw=raw, _n=fname):
+                global _launches
+                _launches += 1
                 rc = _raw(*args)
                 if rc != 0:
                     raise KernelError(f"{_n} failed: {describe_status(rc)}")
 
             f = self.funcs[fname] = call
         return f
+
+
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many launcher calls this process has made (each starts one kernel, a few start two)."""
+    return _launches
 
 
 _loaded: Dict[str, _Module] = {}

@@ -1,8 +1,123 @@
-"""Decode steps as CUDA graphs (placeholder until capture is wired: runs eagerly)."""
+"""Decode steps as CUDA graphs.
+
+A decode step (every sequence brings one token and wants its logits) launches a few hundred small
+kernels; their launch cost would bound the step.  `GraphStepper` captures the device side of such
+a step once per (batch bucket, page-table width bucket) and replays it: the integer inputs (tokens,
+positions, slots, lengths, page tables) live in a fixed device buffer that is refilled by one copy
+before each replay, so lengths and pages may change from step to step without a new capture.  A
+batch smaller than its bucket is padded with rows that the kernels skip.  Every other step (prompts,
+several tokens per sequence, wanted places other than the one token) runs eagerly through
+`Stepper.step`.
+
+The reference captures one graph per cached matrix product (host-to-device copy + kernel +
+device-to-host copy, pkg/gpu/cuda/driver.c:1396-1557); here the whole step is one graph.
+"""
 from __future__ import annotations
 
-from .step import Stepper
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..parts.base import Workspace
+from .step import StepEntry, StepLayout, Stepper
+
+BATCH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+def _bucket(n: int, buckets: Sequence[int]) -> Optional[int]:
+    for b in buckets:
+        if n <= b:
+            return b
+    return None
+
+
+@dataclass
+class _Captured:
+    graph: torch.cuda.CUDAGraph
+    host: torch.Tensor
+    dev: torch.Tensor
+    ws: Workspace
+    logits: torch.Tensor
+    layout: StepLayout
+    kernels: int
 
 
 class GraphStepper(Stepper):
-    pass
+    def __init__(self, model, cache, min_width: int = 16):
+        super().__init__(model, cache)
+        self.min_width = min_width
+        self._graphs: Dict[Tuple[int, int], _Captured] = {}
+        self.replays = 0
+
+    def _width_bucket(self, slots: Sequence[int]) -> int:
+        w = max(self.cache.table_width(slots), self.min_width)
+        return 1 << (w - 1).bit_length()
+
+    def _capture(self, entries: Sequence[StepEntry], bucket: int, width: int) -> _Captured:
+        dev_t = self.model.rt.device
+        lay = StepLayout(bucket, bucket, bucket, [width] * len(self.cache.groups))
+        host = torch.empty(lay.total, dtype=torch.int32, pin_memory=True)
+        dev = torch.empty(lay.total, dtype=torch.int32, device=dev_t)
+        ws = Workspace(dev_t)
+        cap = _Captured(graph=torch.cuda.CUDAGraph(), host=host, dev=dev, ws=ws, logits=None, layout=lay, kernels=0)
+
+        def run():
+            ctx, lay2, rows = self.build_context(entries, host=host, dev=dev, pad_seqs=bucket,
+                                                 table_width=width, ws=ws)
+            ctx.max_ctx = width * self.cache.page_size      # an upper bound: lengths change between replays
+            x = self.run_layers(ctx)
+            return self.run_head(ctx, x, rows, bucket)
+
+        # warm-up on a side stream: allocates the workspace, sets kernel attributes, compiles what is missing
+        side = torch.cuda.Stream(device=dev_t)
+        side.wait_stream(torch.cuda.current_stream(dev_t))
+        with torch.cuda.stream(side):
+            run()
+        torch.cuda.current_stream(dev_t).wait_stream(side)
+        torch.cuda.synchronize(dev_t)
+        from ..csrc import build
+        n0 = build.launch_count()
+        with torch.cuda.graph(cap.graph):
+            # the copy of the integer inputs stays outside the graph: it is re-issued before every replay
+            ctx, lay2, rows = self._context_for_capture(entries, cap, bucket, width)
+            x = self.run_layers(ctx)
+            cap.logits = self.run_head(ctx, x, rows, bucket)
+        cap.kernels = build.launch_count() - n0
+        return cap
+
+    def _context_for_capture(self, entries, cap: _Captured, bucket: int, width: int):
+        # same views as build_context makes, without touching host memory or copying
+        from ..parts.base import StepContext
+        lay, dev = cap.layout, cap.dev
+        B = bucket
+        ctx = StepContext(
+            runtime=self.model.rt, ws=cap.ws, n_tokens=B, n_seqs=B,
+            tokens=lay.view(dev, "tokens"), positions=lay.view(dev, "positions"),
+            seq_of_token=lay.view(dev, "seq_of_token"), cu_seqlens=lay.view(dev, "cu_seqlens"),
+            slots=lay.view(dev, "slots"), ctx_lens=lay.view(dev, "ctx_lens"),
+            page_tables={g: lay.view(dev, f"pages{g}").view(B, width) for g in range(len(self.cache.groups))},
+            max_new=1, max_ctx=width * self.cache.page_size, decode=True)
+        return ctx, lay, lay.view(dev, "logit_rows")
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        decode = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries) and len(entries) > 0
+        bucket = _bucket(len(entries), BATCH_BUCKETS) if decode else None
+        if bucket is None:
+            return super().step(entries)
+        self._check(entries)
+        slots = [e.slot for e in entries]
+        counts = [1] * len(entries)
+        self.cache.plan(slots, counts)
+        width = self._width_bucket(slots)
+        key = (bucket, width)
+        cap = self._graphs.get(key)
+        if cap is None:
+            cap = self._graphs[key] = self._capture(entries, bucket, width)
+        # refill the integer inputs (this also issues the copy to the device) and replay
+        self.build_context(entries, host=cap.host, dev=cap.dev, pad_seqs=bucket, table_width=width, ws=cap.ws)
+        cap.graph.replay()
+        self.replays += 1
+        self.last_graph_kernels = cap.kernels
+        self.cache.commit(slots, counts)
+        return cap.logits[:len(entries)]

@@ -121,7 +121,7 @@ class Stepper:
         T = sum(counts) + n_pad
         n_want = sum(len(e.want) for e in entries)
         width = table_width if table_width is not None else cache.table_width(slots)
-        lay = StepLayout(T, B, n_want, [width] * len(cache.groups))
+        lay = StepLayout(T, B, max(n_want, pad_seqs), [width] * len(cache.groups))
         if host is None:
             host, dev = self._buffers(lay.total)
         if self._copied is not None:
