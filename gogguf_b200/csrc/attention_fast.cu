@@ -1,0 +1,491 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, float32
+// accumulate, online softmax in float32): one kernel for decode, one for prefill, one to merge splits.
+//
+// Decode (`attn_decode_kernel`): one CTA per (token, kv head, split of the key range), four warps.
+// The query heads that share the kv head are the rows of the 16-row MMA tile, so keys and values are
+// read once per group.  A decode step is a stream of the cache from HBM, so K and V go straight from
+// global memory into MMA fragments with 16-byte loads and no shared-memory staging: the contraction
+// index of Q.K^T (the head dimension) and the output columns of P.V may be permuted freely, and the
+// permutations are chosen so that each thread's fragment elements are contiguous in memory.  Each
+// warp keeps its own running maximum, sum and output; the warps are merged in shared memory, the
+// splits by `attn_combine_kernel` in a fixed order.
+//
+// Prefill (`attn_prefill_kernel`): one CTA per (64-query tile of one sequence, query head), four
+// warps of 16 query rows.  Key/value tiles of 64 positions (one cache page) are staged in swizzled
+// shared memory with cp.async, double buffered, and read with ldmatrix.  Causal and window masks are
+// applied in the tiles they cut; tiles outside the visible range are skipped.  Because keys and
+// values come from the cache, a prompt that continues a cached prefix runs through the same kernel.
+//
+// Replaces the reference's per-head attn_qk / softmax / attn_v launches (pkg/gpu/cuda/ptx.go:679-889,
+// host loop pkg/gpu/cuda/driver.c:411-465).
+#include "common.cuh"
+
+namespace {
+
+constexpr int PAGE = 64;
+
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint4 ldg16(const bf16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+// ------------------------------------------------------------------------------------------- decode
+// Rows of the MMA tile: query head r of the group (r < G <= 16).  Fragment conventions (g = lane / 4,
+// t = lane % 4): A regs {row g, row g+8} x {k low, k high}; B regs (k = 2t..2t+1 | 8+2t.., n = g);
+// C regs c0,c1 = row g, cols 2t, 2t+1; c2,c3 = row g+8.
+template <int D>
+__global__ void __launch_bounds__(128) attn_decode_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+    bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+    const int* __restrict__ page_table, int max_pages, int nq, int nkv, float scale_log2, int window, int nsplit) {
+    constexpr int NCH = D / 32;      // 32-wide chunks of the head dimension for Q.K^T
+    constexpr int NDB = D / 64;      // 64-wide blocks of output columns for P.V
+    constexpr int NT = D / 8;        // output n-tiles
+    __shared__ float sm_o[4][16][D];
+    __shared__ float sm_ml[4][16][2];
+    const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int G = nq / nkv;
+    const int b = seq_of_token[tok];
+    const int pos = b >= 0 ? positions[tok] : -1;
+
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    if (b >= 0) {
+        int lo = 0;
+        if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
+        const int first = lo >> 4, last = pos >> 4;
+        const int ntiles = last - first + 1;
+        const int tps = (ntiles + nsplit - 1) / nsplit;
+        const int t_begin = first + split * tps;
+        const int t_end = min(last + 1, t_begin + tps);
+
+        // Q fragments: row g (and g+8) of the group, permuted head dimension (see file header)
+        uint32_t qa[NCH][2][4];
+        {
+            const bf16* q0 = q + ((size_t)tok * nq + (size_t)kvh * G) * D;
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+                uint4 w0 = make_uint4(0, 0, 0, 0), w1 = make_uint4(0, 0, 0, 0);
+                if (g < G) w0 = ldg16(q0 + (size_t)g * D + c * 32 + t * 8);
+                if (g + 8 < G) w1 = ldg16(q0 + (size_t)(g + 8) * D + c * 32 + t * 8);
+                qa[c][0][0] = w0.x; qa[c][0][1] = w1.x; qa[c][0][2] = w0.y; qa[c][0][3] = w1.y;
+                qa[c][1][0] = w0.z; qa[c][1][1] = w1.z; qa[c][1][2] = w0.w; qa[c][1][3] = w1.w;
+            }
+        }
+        const int* pt = page_table + (size_t)b * max_pages;
+        for (int kt = t_begin + warp; kt < t_end; kt += 4) {
+            const int key0 = kt << 4;
+            const int page = pt[key0 / PAGE];
+            const size_t base = (((size_t)page * nkv + kvh) * PAGE + (key0 % PAGE)) * D;
+            // ---- S = Q K^T for 16 keys (two n-tiles of 8)
+            float s[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+                const bf16* kr = k_pool + base + (size_t)(j * 8 + g) * D + t * 8;
+                uint4 kw[NCH];
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) kw[c] = ldg16(kr + c * 32);
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) {
+                    mma16816(s[j], qa[c][0], kw[c].x, kw[c].y);
+                    mma16816(s[j], qa[c][1], kw[c].z, kw[c].w);
+                }
+            }
+            // ---- V rows of this thread: keys 2t, 2t+1, 8+2t, 9+2t; columns db*64 + g*8 .. +8
+            uint4 vw[NDB][4];
+            {
+                const bf16* vr = v_pool + base + g * 8;
+#pragma unroll
+                for (int db = 0; db < NDB; ++db) {
+                    vw[db][0] = ldg16(vr + (size_t)(2 * t) * D + db * 64);
+                    vw[db][1] = ldg16(vr + (size_t)(2 * t + 1) * D + db * 64);
+                    vw[db][2] = ldg16(vr + (size_t)(8 + 2 * t) * D + db * 64);
+                    vw[db][3] = ldg16(vr + (size_t)(9 + 2 * t) * D + db * 64);
+                }
+            }
+            // ---- mask, online softmax (log2 domain)
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int kidx = key0 + j * 8 + 2 * t + (e & 1);
+                    const float v = (kidx >= lo && kidx <= pos) ? s[j][e] * scale_log2 : -INFINITY;
+                    s[j][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            uint32_t pa[4];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float mn = fmaxf(m[r], mx[r]);
+                const float mu = mn == -INFINITY ? 0.f : mn;
+                const float corr = fast_exp2(m[r] - mu);
+                m[r] = mn;
+                const float p00 = fast_exp2(s[0][2 * r] - mu), p01 = fast_exp2(s[0][2 * r + 1] - mu);
+                const float p10 = fast_exp2(s[1][2 * r] - mu), p11 = fast_exp2(s[1][2 * r + 1] - mu);
+                l[r] = l[r] * corr + (p00 + p01 + p10 + p11);
+                pa[r] = pack_bf16(p00, p01);          // A reg r: row g + 8r, keys 2t, 2t+1
+                pa[2 + r] = pack_bf16(p10, p11);      // A reg 2+r: row g + 8r, keys 8+2t, 9+2t
+#pragma unroll
+                for (int i = 0; i < NT; ++i) { o[i][2 * r] *= corr; o[i][2 * r + 1] *= corr; }
+            }
+            // ---- O += P V
+#pragma unroll
+            for (int db = 0; db < NDB; ++db) {
+                const uint32_t* a0 = reinterpret_cast<const uint32_t*>(&vw[db][0]);
+                const uint32_t* a1 = reinterpret_cast<const uint32_t*>(&vw[db][1]);
+                const uint32_t* a2 = reinterpret_cast<const uint32_t*>(&vw[db][2]);
+                const uint32_t* a3 = reinterpret_cast<const uint32_t*>(&vw[db][3]);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    mma16816(o[db * 8 + 2 * w], pa, __byte_perm(a0[w], a1[w], 0x5410), __byte_perm(a2[w], a3[w], 0x5410));
+                    mma16816(o[db * 8 + 2 * w + 1], pa, __byte_perm(a0[w], a1[w], 0x7632), __byte_perm(a2[w], a3[w], 0x7632));
+                }
+            }
+        }
+    }
+    // ---- merge the four warps
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+        const int db = i >> 3, jn = i & 7;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int row = g + 8 * (e >> 1);
+            const int col = db * 64 + (2 * t + (e & 1)) * 8 + jn;    // undo the column permutation
+            sm_o[warp][row][col] = o[i][e];
+        }
+    }
+    if (t == 0) {
+        sm_ml[warp][g][0] = m[0]; sm_ml[warp][g][1] = l[0];
+        sm_ml[warp][g + 8][0] = m[1]; sm_ml[warp][g + 8][1] = l[1];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+        const int r = idx / D, c = idx - r * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_ml[w][r][0]);
+        float L = 0.f, acc = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = fast_exp2(sm_ml[w][r][0] - M);
+                L += sm_ml[w][r][1] * f;
+                acc += sm_o[w][r][c] * f;
+            }
+        }
+        const int head = kvh * G + r;
+        if (nsplit == 1) {
+            out[((size_t)tok * nq + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            const size_t pi = ((size_t)tok * nq + head) * nsplit + split;
+            part_o[pi * D + c] = acc;
+            if (c == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+        }
+    }
+}
+
+template <int D>
+__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    bf16* __restrict__ out, int nsplit) {
+    const size_t row = blockIdx.x;         // token * nq + head
+    const int c = threadIdx.x;
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(row * nsplit + s) * 2]);
+    float L = 0.f, acc = 0.f;
+    if (M != -INFINITY) {
+        for (int s = 0; s < nsplit; ++s) {
+            const float f = fast_exp2(part_ml[(row * nsplit + s) * 2] - M);
+            L += part_ml[(row * nsplit + s) * 2 + 1] * f;
+            acc += part_o[(row * nsplit + s) * D + c] * f;
+        }
+    }
+    out[row * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+}
+
+// ------------------------------------------------------------------------------------------- prefill
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, const void* p) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t* r, const void* p) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+
+// element (row, 16-byte chunk) of a [rows][D] bf16 tile with the chunk index XOR-swizzled by the row
+template <int D> __device__ __forceinline__ bf16* sw(bf16* tile, int row, int chunk) {
+    return tile + row * D + ((chunk ^ (row & 7)) << 3);
+}
+
+template <int D>
+__global__ void __launch_bounds__(128) attn_prefill_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool, bf16* __restrict__ out,
+    const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens, const int* __restrict__ seq_of_token,
+    const int* __restrict__ page_table, int max_pages, int n_seqs, int nq, int nkv, float scale_log2, int window) {
+    constexpr int CH = D / 8;        // 16-byte chunks per row
+    constexpr int KS = D / 16;       // k-steps of Q.K^T
+    constexpr int NT = D / 8;        // output n-tiles
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
+    bf16* Ks = Qs + 64 * D;          // two stages
+    bf16* Vs = Ks + 2 * 64 * D;      // two stages
+
+    // which (sequence, query tile) is this CTA?  tiles are numbered sequence by sequence
+    int b = -1, tile = blockIdx.x, n_new = 0, tok0 = 0;
+    for (int i = 0; i < n_seqs; ++i) {
+        const int a = cu_seqlens[i], e = cu_seqlens[i + 1];
+        if (seq_of_token[a] < 0) continue;                 // padding row of a padded batch
+        const int nt = (e - a + 63) >> 6;
+        if (tile < nt) { b = i; n_new = e - a; tok0 = a; break; }
+        tile -= nt;
+    }
+    if (b < 0) return;
+    const int h = blockIdx.y, kvh = h / (nq / nkv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int row0 = tile * 64;                              // first query row of this tile within the new tokens
+    const int rows = min(64, n_new - row0);
+    const int pos0 = ctx_lens[b] - n_new + row0;             // absolute position of query row 0
+    const int* pt = page_table + (size_t)b * max_pages;
+
+    int lo = 0;
+    if (window > 0 && pos0 - window + 1 > 0) lo = pos0 - window + 1;
+    const int kt_first = lo / PAGE, kt_last = (pos0 + rows - 1) / PAGE;
+
+    // ---- stage Q (rows beyond the tile are zero) and the first K/V tile
+    for (int idx = threadIdx.x; idx < 64 * CH; idx += 128) {
+        const int r = idx / CH, c = idx - r * CH;
+        bf16* dst = sw<D>(Qs, r, c);
+        if (r < rows) cp_async16(dst, q + ((size_t)(tok0 + row0 + r) * nq + h) * D + c * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    auto load_kv = [&](int kt, int stage) {
+        const size_t base = (((size_t)pt[kt] * nkv + kvh) * PAGE) * D;
+        bf16* kd = Ks + stage * 64 * D;
+        bf16* vd = Vs + stage * 64 * D;
+        for (int idx = threadIdx.x; idx < 64 * CH; idx += 128) {
+            const int r = idx / CH, c = idx - r * CH;
+            cp_async16(sw<D>(kd, r, c), k_pool + base + (size_t)r * D + c * 8);
+            cp_async16(sw<D>(vd, r, c), v_pool + base + (size_t)r * D + c * 8);
+        }
+    };
+    load_kv(kt_first, 0);
+    cp_async_commit();
+
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    uint32_t qa[KS][4];
+    const int qrow = warp * 16;      // this warp's 16 query rows
+
+    for (int kt = kt_first; kt <= kt_last; ++kt) {
+        const int stage = (kt - kt_first) & 1;
+        if (kt + 1 <= kt_last) load_kv(kt + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (kt == kt_first) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) ldsm_x4(qa[ks], sw<D>(Qs, qrow + (lane & 15), ks * 2 + (lane >> 4)));
+        }
+        const bf16* kd = Ks + stage * 64 * D;
+        const bf16* vd = Vs + stage * 64 * D;
+        // rows of this warp that can see any key of this tile?  (whole-warp decision, keeps barriers aligned)
+        const int key0 = kt * PAGE;
+        float s[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {       // pairs of n-tiles (16 keys)
+                uint32_t kb[4];
+                ldsm_x4(kb, sw<D>(const_cast<bf16*>(kd), np * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+                mma16816(s[2 * np], qa[ks], kb[0], kb[1]);
+                mma16816(s[2 * np + 1], qa[ks], kb[2], kb[3]);
+            }
+        }
+        // ---- mask + online softmax
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = qrow + g + 8 * (e >> 1);
+                const int p = pos0 + r;
+                const int kidx = key0 + nt * 8 + 2 * t + (e & 1);
+                bool ok = kidx <= p;
+                if (window > 0) ok = ok && (kidx > p - window);
+                const float v = ok ? s[nt][e] * scale_log2 : -INFINITY;
+                s[nt][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        float mu[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float mn = fmaxf(m[r], mx[r]);
+            mu[r] = mn == -INFINITY ? 0.f : mn;
+            const float corr = fast_exp2(m[r] - mu[r]);
+            m[r] = mn;
+            l[r] *= corr;
+#pragma unroll
+            for (int i = 0; i < NT; ++i) { o[i][2 * r] *= corr; o[i][2 * r + 1] *= corr; }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float p = fast_exp2(s[nt][e] - mu[e >> 1]);
+                s[nt][e] = p;
+                l[e >> 1] += p;
+            }
+        // ---- O += P V  (k = 16 keys per step, four steps per tile)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int np = 0; np < NT / 2; ++np) {
+                uint32_t vb[4];
+                ldsm_x4_trans(vb, sw<D>(const_cast<bf16*>(vd), kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), np * 2 + (lane >> 4)));
+                mma16816(o[2 * np], pa, vb[0], vb[1]);
+                mma16816(o[2 * np + 1], pa, vb[2], vb[3]);
+            }
+        }
+        __syncthreads();     // everyone is done with this stage before it is refilled
+    }
+    cp_async_wait<0>();
+    // ---- normalise and store
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = qrow + g + 8 * r;
+        if (row >= rows) continue;
+        const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+        bf16* dst = out + ((size_t)(tok0 + row0 + row) * nq + h) * D;
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+            *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t) = pack_bf16(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+    }
+}
+
+}  // namespace
+
+// Number of key-range splits the decode launcher uses for this shape; the caller sizes the scratch:
+// part_o needs ntok * nq * splits * d floats, part_ml ntok * nq * splits * 2 floats (when splits > 1).
+GG_API gg_attn_decode_splits(int ntok, int nkv, int max_ctx) {
+    if (ntok <= 0 || nkv <= 0) return 1;
+    long long ctas = (long long)ntok * nkv;
+    int splits = (int)((592 + ctas - 1) / ctas);          // about four CTAs per SM on 148 SMs
+    const int most = max_ctx / 128 > 0 ? max_ctx / 128 : 1;  // at least 128 keys per split
+    if (splits > most) splits = most;
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+    return splits;
+}
+
+// Decode-style attention: every token row is one query position (its own sequence row b, position
+// positions[tok]).  q, out: [ntok, nq, d] bf16; pools [page][nkv][64][d] bf16.  d must be 64 or 128,
+// nq / nkv at most 16, page size 64.  splits must be what gg_attn_decode_splits returned.
+GG_API gg_attn_decode(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_o, float* part_ml,
+                      const int* positions, const int* seq_of_token, const int* page_table, int max_pages,
+                      int page_size, int ntok, int nq, int nkv, int d, float scale, int window, int splits,
+                      cudaStream_t stream) {
+    if (ntok <= 0) return 0;
+    if (page_size != PAGE || nq <= 0 || nkv <= 0 || nq % nkv || nq / nkv > 16 || (d != 64 && d != 128) || splits < 1 ||
+        nkv > 65535 || splits > 65535)
+        return GG_ERR_ARG;
+    if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return GG_ERR_ARG;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    dim3 grid(ntok, nkv, splits);
+    if (d == 128)
+        attn_decode_kernel<128><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
+                                                          part_o, part_ml, positions, seq_of_token, page_table, max_pages,
+                                                          nq, nkv, scale_log2, window, splits);
+    else
+        attn_decode_kernel<64><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
+                                                         part_o, part_ml, positions, seq_of_token, page_table, max_pages,
+                                                         nq, nkv, scale_log2, window, splits);
+    int rc = gg_last_error();
+    if (rc != 0 || splits == 1) return rc;
+    if (d == 128) attn_combine_kernel<128><<<ntok * nq, 128, 0, stream>>>(part_o, part_ml, (bf16*)out, splits);
+    else attn_combine_kernel<64><<<ntok * nq, 64, 0, stream>>>(part_o, part_ml, (bf16*)out, splits);
+    return gg_last_error();
+}
+
+// Prefill attention for a ragged batch: sequence i brings tokens cu_seqlens[i]..cu_seqlens[i+1]-1, whose
+// absolute positions end at ctx_lens[i]-1.  max_tiles >= sum over sequences of ceil(new tokens / 64).
+GG_API gg_attn_prefill(const void* q, const void* k_pool, const void* v_pool, void* out, const int* cu_seqlens,
+                       const int* ctx_lens, const int* seq_of_token, const int* page_table, int max_pages,
+                       int page_size, int n_seqs, int max_tiles, int nq, int nkv, int d, float scale, int window,
+                       cudaStream_t stream) {
+    if (n_seqs <= 0 || max_tiles <= 0) return 0;
+    if (page_size != PAGE || nq <= 0 || nkv <= 0 || nq % nkv || (d != 64 && d != 128) || nq > 65535) return GG_ERR_ARG;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    dim3 grid(max_tiles, nq);
+    const int smem = 5 * 64 * d * 2;
+    cudaError_t e;
+    if (d == 128) {
+        static bool cfg128 = false;
+        if (!cfg128) {
+            e = cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess) return (int)e;
+            cfg128 = true;
+        }
+        attn_prefill_kernel<128><<<grid, 128, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
+                                                              cu_seqlens, ctx_lens, seq_of_token, page_table, max_pages, n_seqs,
+                                                              nq, nkv, scale_log2, window);
+    } else {
+        attn_prefill_kernel<64><<<grid, 128, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
+                                                             cu_seqlens, ctx_lens, seq_of_token, page_table, max_pages, n_seqs,
+                                                             nq, nkv, scale_log2, window);
+    }
+    return gg_last_error();
+}

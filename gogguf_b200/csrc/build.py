@@ -46,6 +46,7 @@ MODULES: Dict[str, str] = {
     "attention_plain": "attention_plain.cu",
     "sampling": "sampling.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
+    "attention_fast": "attention_fast.cu",
 }
 
 _HEADERS = ["common.cuh"]

@@ -30,7 +30,15 @@ TINY_W = dict(
     tie_word_embeddings=False, max_position_embeddings=512,
     sliding_window=37, layer_types=["sliding_attention", "full_attention", "full_attention", "sliding_attention"],
 )
-TINY = {"A": (TINY_A, 0, 0.02, 0.02), "B": (TINY_B, 1, 0.03, 0.05), "W": (TINY_W, 5, 0.05, 0.1)}
+# head size 64 and 4 query heads per kv head: the sizes the tensor-core attention kernels take
+TINY_M = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=136, num_attention_heads=8, num_key_value_heads=2, head_dim=64,
+    intermediate_size=200, vocab_size=523, rope_theta=200000.0, rms_norm_eps=2e-6,
+    tie_word_embeddings=True, max_position_embeddings=1024,
+    sliding_window=90, layer_types=["full_attention", "sliding_attention"],
+)
+TINY = {"M": (TINY_M, 9, 0.04, 0.05), "A": (TINY_A, 0, 0.02, 0.02), "B": (TINY_B, 1, 0.03, 0.05), "W": (TINY_W, 5, 0.05, 0.1)}
 
 
 def make_folder(tmp, name: str, store_dtype: str = "float32", scale: float = 1.0) -> str:

@@ -203,3 +203,163 @@ def test_gemm_tcgen05_strided_rows_and_padding_rows():
     tc.check_status(DEV)
     assert rel(out[:24], x[:24].double() @ w.double().T) < 3e-6
     assert float(outbig[24:].abs().sum()) == 0 and float(outbig[:, 200:].abs().sum()) == 0
+
+
+# ------------------------------------------------------------------------------------------ attention
+def make_paged(seqs, nkv, d, dt, seed, n_pages=None, ps=64):
+    """seqs: list of (context length after the step, new tokens).  Returns pools, table and per-sequence K, V."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    need = sum((c + ps - 1) // ps for c, _ in seqs)
+    n_pages = n_pages or need + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    width = max((c + ps - 1) // ps for c, _ in seqs) + 1
+    kp = torch.randn(n_pages, nkv, ps, d, device=DEV, generator=g).to(dt)
+    vp = torch.randn(n_pages, nkv, ps, d, device=DEV, generator=g).to(dt)
+    table = torch.zeros(len(seqs), width, dtype=torch.int32)
+    ks, vs = [], []
+    for b, (c, _) in enumerate(seqs):
+        pages = [perm.pop() for _ in range((c + ps - 1) // ps)]
+        table[b, :len(pages)] = torch.tensor(pages, dtype=torch.int32)
+        k = torch.cat([kp[p] for p in pages], dim=1)[:, :c]        # [nkv, c, d]
+        v = torch.cat([vp[p] for p in pages], dim=1)[:, :c]
+        ks.append(k)
+        vs.append(v)
+    return kp, vp, table.to(DEV), ks, vs
+
+
+def attention_reference(q, ks, vs, seqs, nq, nkv, scale, window):
+    outs = []
+    r = 0
+    G = nq // nkv
+    for b, (c, n) in enumerate(seqs):
+        for i in range(n):
+            pos = c - n + i
+            lo = max(0, pos - window + 1) if window else 0
+            for h in range(nq):
+                k = ks[b][h // G, lo:pos + 1].double()
+                v = vs[b][h // G, lo:pos + 1].double()
+                s = (k @ q[r, h].double()) * scale
+                outs.append(torch.softmax(s, 0) @ v)
+            r += 1
+    return torch.stack(outs).reshape(r, nq, -1)
+
+
+def step_meta(seqs):
+    pos, sot, cu, cl = [], [], [0], []
+    for b, (c, n) in enumerate(seqs):
+        pos += list(range(c - n, c))
+        sot += [b] * n
+        cu.append(cu[-1] + n)
+        cl.append(c)
+    mk = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return mk(pos), mk(sot), mk(cu), mk(cl)
+
+
+ATT_CASES = [
+    # nq, nkv, d, window, seqs [(context after the step, new tokens)]
+    (4, 2, 16, 0, [(5, 5), (70, 3)]),
+    (6, 1, 32, 0, [(130, 130), (1, 1), (64, 64)]),
+    (3, 3, 48, 37, [(100, 100), (200, 1)]),
+    (8, 2, 128, 0, [(300, 300), (65, 1), (129, 2)]),
+    (8, 2, 64, 70, [(257, 257), (500, 7)]),
+    (32, 8, 128, 0, [(1, 1), (200, 72)]),
+]
+
+
+@pytest.mark.parametrize("nq,nkv,d,window,seqs", ATT_CASES)
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_attention_plain(nq, nkv, d, window, seqs, dt):
+    kp, vp, table, ks, vs = make_paged(seqs, nkv, d, dt, seed=7)
+    pos, sot, cu, cl = step_meta(seqs)
+    T = pos.numel()
+    q = torch.randn(T, nq, d, device=DEV, generator=torch.Generator(device=DEV).manual_seed(8)).to(dt)
+    out = torch.empty(T, nq, d, device=DEV, dtype=dt)
+    scale = 1.0 / math.sqrt(d)
+    K().attention_plain(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window)
+    want = attention_reference(q, ks, vs, seqs, nq, nkv, scale, window)
+    assert rel(out, want) < (3e-6 if dt == torch.float32 else 6e-3)
+
+
+@pytest.mark.parametrize("nq,nkv,d,window,seqs", [c for c in ATT_CASES if c[2] in (64, 128)] + [
+    (4, 1, 128, 0, [(2048, 2048)]), (16, 1, 64, 100, [(700, 330), (90, 90)])])
+def test_attention_prefill_tensor_cores(nq, nkv, d, window, seqs):
+    from gogguf_b200.csrc import fast_attention as fa
+    dt = torch.bfloat16
+    kp, vp, table, ks, vs = make_paged(seqs, nkv, d, dt, seed=9)
+    pos, sot, cu, cl = step_meta(seqs)
+    T = pos.numel()
+    q = torch.randn(T, nq, d, device=DEV, generator=torch.Generator(device=DEV).manual_seed(10)).to(dt)
+    out = torch.full((T, nq, d), float("nan"), device=DEV, dtype=dt)
+    scale = 1.0 / math.sqrt(d)
+    fa.attn_prefill(q, kp, vp, out, cu, cl, sot, table, 64, len(seqs), T // 64 + len(seqs), nq, nkv, d, scale, window)
+    twin = torch.empty_like(out)
+    K().attention_plain(q, kp, vp, twin, pos, sot, table, 64, T, nq, nkv, d, scale, window)
+    want = attention_reference(q, ks, vs, seqs, nq, nkv, scale, window) if T <= 400 else twin
+    assert rel(out, want) < 8e-3
+    assert rel(out, twin) < 8e-3
+
+
+@pytest.mark.parametrize("nq,nkv,d,window,ctxs", [
+    (8, 2, 128, 0, [1, 64, 65, 300, 2049]), (32, 8, 128, 0, [2048] * 3 + [17]), (8, 8, 64, 0, [100, 1000]),
+    (16, 1, 64, 90, [500, 89, 90, 91]), (12, 2, 128, 33, [4000, 5])])
+def test_attention_decode_tensor_cores(nq, nkv, d, window, ctxs):
+    from gogguf_b200.csrc import fast_attention as fa
+    dt = torch.bfloat16
+    seqs = [(c, 1) for c in ctxs]
+    kp, vp, table, ks, vs = make_paged(seqs, nkv, d, dt, seed=11)
+    pos, sot, cu, cl = step_meta(seqs)
+    # a padding row in the middle must change nothing and give zeros
+    pos = torch.cat([pos[:1], torch.zeros(1, dtype=torch.int32, device=DEV), pos[1:]])
+    sot = torch.cat([sot[:1], torch.full((1,), -1, dtype=torch.int32, device=DEV), sot[1:]])
+    T = pos.numel()
+    q = torch.randn(T, nq, d, device=DEV, generator=torch.Generator(device=DEV).manual_seed(12)).to(dt)
+    scale = 1.0 / math.sqrt(d)
+    qr = torch.cat([q[:1], q[2:]])
+    want = attention_reference(qr, ks, vs, seqs, nq, nkv, scale, window)
+    for max_ctx in (max(ctxs), 8192):
+        splits = fa.decode_splits(T, nkv, max_ctx)
+        po = torch.empty(T * nq * splits * d, device=DEV)
+        pm = torch.empty(T * nq * splits * 2, device=DEV)
+        out = torch.full((T, nq, d), float("nan"), device=DEV, dtype=dt)
+        fa.attn_decode(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window, splits, po, pm)
+        got = torch.cat([out[:1], out[2:]])
+        assert rel(got, want) < 8e-3, (splits,)
+        assert float(out[1].float().abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("kind", ["plain_f32", "plain_bf16", "decode", "prefill"])
+def test_attention_finds_a_far_key_and_respects_the_window_edge(kind):
+    """Random numbers hide a key that is skipped among hundreds.  Here one far key (and, for the
+    window, the keys just inside and just outside its edge) is scaled so that it takes all the weight."""
+    from gogguf_b200.csrc import fast_attention as fa
+    dt = torch.float32 if kind == "plain_f32" else torch.bfloat16
+    nq, nkv, d, ctx = 8, 2, 128, 900
+    n_new = 1 if kind == "decode" else 130
+    seqs = [(ctx, n_new)]
+    scale = 1.0 / math.sqrt(d)
+    for window, hot in ((0, 3), (0, 447), (200, ctx - 200), (200, ctx - 201)):
+        kp, vp, table, ks, vs = make_paged(seqs, nkv, d, dt, seed=13)
+        pos, sot, cu, cl = step_meta(seqs)
+        T = pos.numel()
+        q = torch.randn(T, nq, d, device=DEV, generator=torch.Generator(device=DEV).manual_seed(14)).to(dt)
+        # the last query token and the key at `hot` point the same way, strongly
+        page, off = int(table[0, hot // 64]), hot % 64
+        kp[page, :, off] = 0
+        kp[page, :, off, 0] = 30.0
+        q[-1, :, 0] = 30.0
+        vp[page, :, off] = 5.0
+        out = torch.empty(T, nq, d, device=DEV, dtype=dt)
+        if kind.startswith("plain"):
+            K().attention_plain(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window)
+        elif kind == "decode":
+            splits = fa.decode_splits(T, nkv, 1024)
+            po = torch.empty(T * nq * splits * d, device=DEV); pm = torch.empty(T * nq * splits * 2, device=DEV)
+            fa.attn_decode(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window, splits, po, pm)
+        else:
+            fa.attn_prefill(q, kp, vp, out, cu, cl, sot, table, 64, 1, T // 64 + 1, nq, nkv, d, scale, window)
+        last = out[-1].float()
+        inside = window == 0 or hot >= (ctx - 1) - window + 1
+        if inside:
+            assert float((last - 5.0).abs().max()) < 0.05, (window, hot)     # all weight on the hot key
+        else:
+            assert float(last.abs().max()) < 4.0, (window, hot)              # the hot key is outside the window

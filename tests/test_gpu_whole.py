@@ -31,11 +31,14 @@ def test_whole_f32(tmp_path_factory, name, n):
     assert rel_err(got, want) < TOL_F32
 
 
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "M"])
 def test_whole_bf16(tmp_path_factory, name):
     folder = make_folder(tmp_path_factory.getbasetemp(), name, "bfloat16", scale=4.0)
     cfg, w = read_folder(folder)
-    tokens = random_tokens(cfg["vocab_size"], 90, seed=3)
+    tokens = random_tokens(cfg["vocab_size"], 200, seed=3)
     want = plain.forward(cfg, w, tokens, wide=True)
     got = engine_whole(folder, "bfloat16", tokens)
     assert rel_err(got, want) < TOL_BF16
+    # the plain kernels on the same bfloat16 weights (the twins of the tensor-core kernels) agree too
+    twin = engine_whole(folder, "bfloat16", tokens, fast=False)
+    assert rel_err(twin, want) < TOL_BF16
