@@ -47,9 +47,14 @@ MODULES: Dict[str, str] = {
     "sampling": "sampling.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_fast": "attention_fast.cu",
+    "gemm_tcgen05_static": "gemm_tcgen05_static.cu",
 }
 
 _HEADERS = ["common.cuh"]
+# further files a module's source includes (they take part in its hash)
+_INCLUDES: Dict[str, List[str]] = {
+    "gemm_tcgen05_static.cu": ["gemm_tcgen05.cu", "gemm_tcgen05_static.h"],
+}
 
 
 class KernelBuildError(RuntimeError):
@@ -104,7 +109,7 @@ def _build_dir() -> str:
 def _module_hash(src: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    for f in [src] + _HEADERS:
+    for f in [src] + _HEADERS + _INCLUDES.get(src, []):
         p = os.path.join(_HERE, f)
         if os.path.isfile(p):
             with open(p, "rb") as fh:
