@@ -145,6 +145,7 @@ def main():
                     help="fewer layers than the configuration has (same layer sizes); named in config")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (for short profiling runs)")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -267,8 +268,11 @@ def main():
 
     main_run = decode_run(a.batch, a.steps, a.warmup)
     print(f"[bench] decode batch {a.batch}: {main_run['tok_s']:.1f} tok/s, {main_run['ms_per_step']:.3f} ms/step", file=sys.stderr)
-    e2e = e2e_run(a.batch, a.steps, a.warmup)
-    print(f"[bench] e2e batch {a.batch}: {e2e['tok_s']:.1f} tok/s", file=sys.stderr)
+    if a.no_e2e:
+        e2e = {"tok_s": None, "h2d": None, "d2h": None}
+    else:
+        e2e = e2e_run(a.batch, a.steps, a.warmup)
+        print(f"[bench] e2e batch {a.batch}: {e2e['tok_s']:.1f} tok/s", file=sys.stderr)
     points, prefill = {}, None
     if not a.no_points:
         prefill = prefill_run()
