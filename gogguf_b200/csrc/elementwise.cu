@@ -54,10 +54,74 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f<TO>(xr[i] * scale * w[i]);
 }
 
+// Same result for rows of up to 8192 floats whose length is a multiple of 4: the row is read once with
+// 16-byte loads that are all in flight together and kept in registers for the second pass.  In a
+// decode step only a few rows exist, so the kernel's time is one memory latency, not two loops of them.
+template <typename TO, int VPT /* float4 per thread */>
+__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                                          const float* __restrict__ w, TO* __restrict__ out, int H, float eps) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    TO* o = out + (size_t)r * H;
+    const int nvec = H >> 2;
+    float4 v[VPT];
+    float ss = 0.f;
+    if (src >= 0) {
+        const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * H);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = threadIdx.x + j * 256;
+            v[j] = i < nvec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+            ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    ss = block_sum(ss, red);
+    const float scale = src >= 0 ? 1.0f / sqrtf(ss / (float)H + eps) : 0.f;
+    const float4* wr = reinterpret_cast<const float4*>(w);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i < nvec) {
+            const float4 ww = wr[i];
+            const float a = v[j].x * scale * ww.x, b = v[j].y * scale * ww.y;
+            const float c = v[j].z * scale * ww.z, d = v[j].w * scale * ww.w;
+            if (sizeof(TO) == 4) {
+                reinterpret_cast<float4*>(o)[i] = make_float4(a, b, c, d);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(o)[i] = pk;
+            }
+        }
+    }
+}
+
 GG_API gg_rmsnorm(const float* x, const int* rows, const float* w, void* out, int out_dtype,
                   int R, int H, float eps, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (H <= 0) return GG_ERR_ARG;
+    const bool aligned = (H % 4 == 0) && ((((uintptr_t)x) & 15) == 0) && ((((uintptr_t)w) & 15) == 0) &&
+                         ((((uintptr_t)out) & 15) == 0);
+    if (aligned && H <= 8192) {
+        const int vpt = (H / 4 + 255) / 256;     // 1..8
+        GG_DISPATCH_DTYPE(out_dtype, TO, {
+            if (vpt <= 1) rmsnorm_vec_kernel<TO, 1><<<R, 256, 0, stream>>>(x, rows, w, (TO*)out, H, eps);
+            else if (vpt <= 2) rmsnorm_vec_kernel<TO, 2><<<R, 256, 0, stream>>>(x, rows, w, (TO*)out, H, eps);
+            else if (vpt <= 4) rmsnorm_vec_kernel<TO, 4><<<R, 256, 0, stream>>>(x, rows, w, (TO*)out, H, eps);
+            else rmsnorm_vec_kernel<TO, 8><<<R, 256, 0, stream>>>(x, rows, w, (TO*)out, H, eps);
+        });
+        return gg_last_error();
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     GG_DISPATCH_DTYPE(out_dtype, TO,
         rmsnorm_kernel<TO><<<R, threads, 0, stream>>>(x, rows, w, (TO*)out, H, eps));

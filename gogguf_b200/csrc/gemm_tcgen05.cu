@@ -16,8 +16,13 @@
 // W[N, K], out[m, n] = D[m, n].  Decode ("swap"): A = weights, so that the 128-row side of the
 // instruction is filled by output features and a small batch of tokens is the N side (16..128);
 // out[m, n] = D[n, m].  In decode the product is a stream of weights from HBM: the grid is
-// widened by splitting K over blockIdx.z, partial sums go to a float32 scratch buffer and a second
-// kernel adds them in a fixed order (no float atomics: results do not depend on timing).
+// widened by splitting K over blockIdx.z and several CTAs share an SM.  The CTAs that hold the
+// partial sums of one output tile form a thread-block cluster: each dumps its accumulator into its
+// own shared memory, and after a cluster barrier every CTA adds one slice of the tile over all
+// ranks through distributed shared memory, always in rank order, and writes it out.  No scratch
+// memory, no second launch, no float atomics: results do not depend on timing.  (A second form
+// keeps the partial sums in a float32 scratch buffer in global memory and adds them in a second
+// kernel; it serves callers that ask for it and split counts beyond a cluster.)
 //
 // Every mbarrier wait is bounded; a wait that runs out records a code in the status word, raises
 // the CTA's abort flag, and all roles fall through to the common exit, which lets copies in flight
@@ -119,11 +124,26 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 template <int BN> constexpr int tmem_cols() { return BN < 32 ? 32 : BN; }
 
-template <int BN, int STAGES, bool SWAP>
-__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+constexpr int MAX_CLUSTER = 8;
+
+// cluster_reduce != 0: the grid was launched with clusters of gridDim.z CTAs along z (the K splits).
+template <int BN, int STAGES, bool SWAP, int MINB>
+__global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
     void* __restrict__ out, int out_mode, long long ldo, int M, int N, int K, int kb_per_split,
-    float* __restrict__ partial, int* __restrict__ status) {
+    float* __restrict__ partial, int cluster_reduce, int* __restrict__ status) {
     constexpr int B_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     extern __shared__ uint8_t smem_raw[];
@@ -196,7 +216,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(
         // epilogue: warp w reads tensor-memory lanes 32*(w%4) .. +31 (row i of D is lane i)
         const int q = warp & 3;
         const int row = q * 32 + lane;           // row of the D tile held by this thread
-        if (mbar_wait(accum, 0, abort_flag, status, 3)) {
+        mbar_wait(accum, 0, abort_flag, status, 3);
+        if (!*abort_flag) {
             tc_fence_after();
             const int gi = tile_a * BM + row;    // global row of D (A side)
             const int RA = SWAP ? N : M, RB = SWAP ? M : N;
@@ -206,6 +227,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(
                 uint32_t r[16];
                 tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
                 tmem_ld_wait();
+                if (cluster_reduce) {
+                    // own partial sums to own shared memory, [column][row]: the pipeline stages are free now
+                    float* stage = reinterpret_cast<float*>(smem);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) stage[(c0 + j) * BM + row] = __uint_as_float(r[j]);
+                    continue;
+                }
                 if (gi >= RA) continue;
                 const int gj0 = tile_b * BN + c0;
                 if (partial != nullptr) {
@@ -281,6 +309,34 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(
 
     tc_fence_before();
     __syncthreads();
+    if (cluster_reduce) {
+        // Every CTA of the cluster passes both barriers exactly once, whatever happened before.
+        cluster_sync_all();
+        if (!*abort_flag) {
+            const int S = gridDim.z;
+            const int RA = SWAP ? N : M, RB = SWAP ? M : N;
+            const int cols = min(BN, RB - tile_b * BN);
+            const int E = cols * BM;
+            const uint32_t stage = smem_u32(smem);
+            for (int e = split * NUM_THREADS + threadIdx.x; e < E; e += S * NUM_THREADS) {
+                float v[MAX_CLUSTER];
+#pragma unroll
+                for (int qq = 0; qq < MAX_CLUSTER; ++qq) v[qq] = qq < S ? ld_cluster_f32(stage + 4u * e, qq) : 0.f;
+                float acc = 0.f;
+#pragma unroll
+                for (int qq = 0; qq < MAX_CLUSTER; ++qq) acc += v[qq];      // rank order, fixed
+                const int j = e / BM, i = e - j * BM;
+                const int gi = tile_a * BM + i, gj = tile_b * BN + j;
+                if (gi < RA) {
+                    const size_t o = SWAP ? (size_t)gj * ldo + gi : (size_t)gi * ldo + gj;
+                    if (out_mode == OUT_BF16) ((bf16*)out)[o] = __float2bfloat16_rn(acc);
+                    else if (out_mode == OUT_F32) ((float*)out)[o] = acc;
+                    else ((float*)out)[o] += acc;
+                }
+            }
+        }
+        cluster_sync_all();     // nobody leaves while its shared memory may still be read
+    }
     if (*abort_flag) {
         // a wait ran out: give copies and instructions in flight time to land before the memory goes away
         const long long t0 = clock64();
@@ -338,35 +394,58 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long long ld, i
     return r == CUDA_SUCCESS ? 0 : GG_ERR_TMAP;
 }
 
-template <int BN, int STAGES, bool SWAP>
+template <int BN, int STAGES, bool SWAP, int MINB>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N, int K,
-           int splits, int kb_per_split, float* partial, int* status, cudaStream_t stream) {
+           int splits, int kb_per_split, float* partial, bool cluster, int* status, cudaStream_t stream) {
     constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256;
+    static_assert(STAGES * (A_BYTES + BN * BK * 2) >= BN * BM * 4, "the stages must hold a float32 tile");
     static bool configured = false;
+    auto kern = gemm_tc_kernel<BN, STAGES, SWAP, MINB>;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const int RA = SWAP ? N : M, RB = SWAP ? M : N;
     dim3 grid((RA + BM - 1) / BM, (RB + BN - 1) / BN, splits);
-    gemm_tc_kernel<BN, STAGES, SWAP><<<grid, NUM_THREADS, smem, stream>>>(
-        ta, tb, out, out_mode, ldo, M, N, K, kb_per_split, splits > 1 ? partial : nullptr, status);
+    float* part = (splits > 1 && !cluster) ? partial : nullptr;
+    const int cl = (splits > 1 && cluster) ? 1 : 0;
+    if (!cl) {
+        kern<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, out, out_mode, ldo, M, N, K, kb_per_split, part, 0, status);
+        return gg_last_error();
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, out, out_mode, ldo, M, N, K, kb_per_split, part, 1, status);
+    if (e != cudaSuccess) return (int)e;
     return gg_last_error();
 }
 
 }  // namespace
 
-// Number of K splits the launcher would use for a product of this shape (0: the shape is not taken).
-// The caller sizes the scratch buffer with it: splits * M * N floats when splits > 1.
-GG_API gg_gemm_tc_splits(int M, int N, int K) {
+// Number of K splits the launcher uses for a product of this shape (0: the shape is not taken).
+// use_cluster != 0: the splits of a tile form a thread-block cluster (at most 8) and no scratch is
+// needed.  use_cluster == 0: partial sums go through a scratch buffer of splits * M * N floats.
+GG_API gg_gemm_tc_splits(int M, int N, int K, int use_cluster) {
     if (M <= 0 || N <= 0 || K <= 0 || (K % 8) != 0) return 0;
     if (M > 128) return 1;
     const int num_kb = (K + BK - 1) / BK;
     const int tiles = (N + BM - 1) / BM;
-    int splits = (296 + tiles - 1) / tiles;      // aim at two CTAs' worth of work per SM on 148 SMs
-    if (splits > num_kb / 4) splits = num_kb / 4;  // at least four 64-wide slabs per CTA
-    if (splits > 16) splits = 16;
+    const int per_sm = M <= 16 ? 3 : 2;          // CTAs that share an SM in the decode forms
+    int splits = (148 * per_sm + tiles / 2) / tiles;
+    if (splits > num_kb / 2) splits = num_kb / 2;  // at least two 64-wide slabs per CTA
+    const int most = use_cluster ? MAX_CLUSTER : 16;
+    if (splits > most) splits = most;
     if (splits < 1) splits = 1;
     // no empty split: the last one must own at least one slab
     int per = (num_kb + splits - 1) / splits;
@@ -375,19 +454,22 @@ GG_API gg_gemm_tc_splits(int M, int N, int K) {
 }
 
 // out[M, N] (mode) = x[M, K] (bf16, row stride ldx) * w[N, K]^T (bf16, contiguous).
-// out_mode: 0 bf16 store, 1 float32 store, 2 float32 add (residual).  scratch: float32 buffer of at
-// least splits * M * N elements when gg_gemm_tc_splits(M, N, K) > 1 (may be null otherwise).
+// out_mode: 0 bf16 store, 1 float32 store, 2 float32 add (residual).
+// use_cluster != 0: K splits are reduced inside thread-block clusters; scratch is not touched.
+// use_cluster == 0: scratch must hold gg_gemm_tc_splits(M, N, K, 0) * M * N floats when that count is > 1.
 // status: one int on the device, zero-initialised by the caller; a non-zero value after the kernel
 // means a bounded wait ran out (1 producer, 2 issuer, 3 epilogue).
 GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, int N, int K, long long ldx,
-                  long long ldo, float* scratch, long long scratch_elems, int* status, cudaStream_t stream) {
+                  long long ldo, float* scratch, long long scratch_elems, int use_cluster, int* status,
+                  cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K % 8) != 0 || (ldx % 8) != 0 || ldx < K || ldo < N) return GG_ERR_ARG;
     if ((((uintptr_t)x) & 15) || (((uintptr_t)w) & 15) || out_mode < 0 || out_mode > 2 || status == nullptr) return GG_ERR_ARG;
     const int num_kb = (K + BK - 1) / BK;
     const bool swap = M <= 128;
-    int splits = gg_gemm_tc_splits(M, N, K);
-    if (splits > 1 && (scratch == nullptr || scratch_elems < (long long)splits * M * N)) return GG_ERR_ARG;
+    const bool cluster = use_cluster != 0;
+    int splits = gg_gemm_tc_splits(M, N, K, use_cluster);
+    if (splits > 1 && !cluster && (scratch == nullptr || scratch_elems < (long long)splits * M * N)) return GG_ERR_ARG;
     const int per = (num_kb + splits - 1) / splits;
     CUtensorMap ta, tb;
     int rc;
@@ -395,19 +477,19 @@ GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, 
         const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
         if ((rc = make_map(&ta, w, N, K, K, BM)) != 0) return rc;
         if ((rc = make_map(&tb, x, M, K, ldx, bn)) != 0) return rc;
-        if (bn == 16) rc = launch<16, 8, true>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, status, stream);
-        else if (bn == 32) rc = launch<32, 8, true>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, status, stream);
-        else if (bn == 64) rc = launch<64, 8, true>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, status, stream);
-        else rc = launch<128, 6, true>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, status, stream);
+        if (bn == 16) rc = launch<16, 4, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
+        else if (bn == 32) rc = launch<32, 4, true, 2>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
+        else if (bn == 64) rc = launch<64, 4, true, 2>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
+        else rc = launch<128, 3, true, 2>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
     } else {
         const int bn = N > 128 ? 256 : 128;
         if ((rc = make_map(&ta, x, M, K, ldx, BM)) != 0) return rc;
         if ((rc = make_map(&tb, w, N, K, K, bn)) != 0) return rc;
-        if (bn == 256) rc = launch<256, 4, false>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, status, stream);
-        else rc = launch<128, 6, false>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, status, stream);
+        if (bn == 256) rc = launch<256, 4, false, 1>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, false, status, stream);
+        else rc = launch<128, 6, false, 1>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, false, status, stream);
     }
     if (rc != 0) return rc;
-    if (splits > 1) {
+    if (splits > 1 && !cluster) {
         const long long total = (long long)M * N;
         splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(scratch, out, out_mode, ldo, M, N, splits);
         return gg_last_error();

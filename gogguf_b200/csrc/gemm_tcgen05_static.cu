@@ -40,7 +40,7 @@ int static_scratch(float** out) {
 GG_API gg_gemm_tc_static(const void* x, const void* w, void* out, int out_mode, int M, int N, int K,
                          long long ldx, long long ldo, int* status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    const int splits = gg_gemm_tc_splits(M, N, K);
+    const int splits = gg_gemm_tc_splits(M, N, K, 0);     // the scratch form, not the cluster form
     if (splits <= 0) return GG_ERR_ARG;
     float* scratch = nullptr;
     long long need = 0;
@@ -50,5 +50,5 @@ GG_API gg_gemm_tc_static(const void* x, const void* w, void* out, int out_mode, 
         const int rc = static_scratch(&scratch);
         if (rc != 0) return rc;
     }
-    return gg_gemm_tc(x, w, out, out_mode, M, N, K, ldx, ldo, scratch, need, status, stream);
+    return gg_gemm_tc(x, w, out, out_mode, M, N, K, ldx, ldo, scratch, need, 0, status, stream);
 }

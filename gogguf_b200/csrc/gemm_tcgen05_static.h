@@ -8,18 +8,20 @@
  * that may not take the allocator's locks or its implicit synchronisation, a process that has
  * handed its whole memory budget to a pool.  The regular entry point, gg_gemm_tc, needs a float32
  * scratch buffer from its caller whenever it splits the K dimension (small batches); such callers
- * have nowhere to get one.
+ * have nowhere to get one.  (gg_gemm_tc also has a form that adds its partial sums inside
+ * thread-block clusters and needs no scratch; this entry point is the scratch form, whose split of K
+ * may be finer and which does not depend on cluster launches.)
  *
  * What it does instead: the scratch lives in a file-scope `static __device__` array inside the
  * library, GG_STATIC_SCRATCH_FLOATS floats (16 MiB).  Every GPU on which the library is loaded
  * holds that array from load until the process exits.  The function computes
  *     out[M, N] (mode) = x[M, K] * w[N, K]^T      (bfloat16 operands, float32 accumulation)
- * exactly as gg_gemm_tc does, with the same kernels and the same split of K, so results are
- * bit-identical to gg_gemm_tc's.  The caller passes inputs, the output and the status word; the
+ * exactly as gg_gemm_tc's scratch form (use_cluster = 0) does, with the same kernels and the same
+ * split of K, so results are bit-identical to it.  The caller passes inputs, the output and the status word; the
  * function calls no cudaMalloc, cudaFree or any other allocating routine.
  *
  * Limits and rules:
- *   - splits * M * N (splits as gg_gemm_tc_splits(M, N, K) reports) must not exceed
+ *   - splits * M * N (splits as gg_gemm_tc_splits(M, N, K, 0) reports) must not exceed
  *     GG_STATIC_SCRATCH_FLOATS; larger products are refused with status -1 before anything is
  *     launched.  Products that need no split (M > 128, or few K slabs) never touch the array.
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with

@@ -130,11 +130,19 @@ def attention_plain(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
 
 
 # ------------------------------------------------------------------------------- sampling
+_argmax_scratch = {}
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None) -> None:
     _need(logits, torch.float32, "logits")
     _need(out, torch.int32, "out")
     R = logits.shape[0] if rows is None else rows
-    kernel("sampling", "gg_argmax")(_p(logits), logits.stride(0), _p(out), R, logits.shape[1], _stream())
+    scratch = _argmax_scratch.get(logits.device)
+    if scratch is None or scratch.numel() < R * 128:
+        scratch = _argmax_scratch[logits.device] = torch.empty(max(R, 64) * 128, dtype=torch.int32,
+                                                                device=logits.device)
+    kernel("sampling", "gg_argmax")(_p(logits), logits.stride(0), _p(out), R, logits.shape[1],
+                                     _p(scratch), scratch.numel(), _stream())
 
 
 def sample(logits: torch.Tensor, temps: torch.Tensor, uniforms: torch.Tensor, out: torch.Tensor,

@@ -76,10 +76,57 @@ __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __res
     if (threadIdx.x == 0) out[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
 }
 
-GG_API gg_argmax(const float* logits, long long ld, int* out, int R, int V, cudaStream_t stream) {
+// Two-stage form for a few long rows: `chunks` blocks per row each find the best of their slice, a second
+// launch picks among them (ties still go to the smallest index).
+__global__ void __launch_bounds__(SAMP_THREADS) argmax_partial_kernel(const float* __restrict__ logits, long long ld,
+                                                                       MaxIdx* __restrict__ part, int V, int chunks) {
+    __shared__ MaxIdx red[33];
+    const int r = blockIdx.x, c = blockIdx.y;
+    const float* x = logits + (size_t)r * ld;
+    const int per = ((V + chunks - 1) / chunks + 3) & ~3;
+    const int lo = c * per, hi = min(V, lo + per);
+    MaxIdx best{-INFINITY, 0x7fffffff};
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = x[i];
+        if (v > best.v || best.i == 0x7fffffff) best = MaxIdx{v, i};
+    }
+    best = block_argmax(best, red);
+    if (threadIdx.x == 0) part[(size_t)r * chunks + c] = best;
+}
+
+__global__ void argmax_final_kernel(const MaxIdx* __restrict__ part, int* __restrict__ out, int chunks) {
+    const int r = blockIdx.x;
+    MaxIdx best{-INFINITY, 0x7fffffff};
+    for (int c = threadIdx.x; c < chunks; c += 32) best = better(best, part[(size_t)r * chunks + c]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        MaxIdx y;
+        y.v = __shfl_xor_sync(0xffffffffu, best.v, o);
+        y.i = __shfl_xor_sync(0xffffffffu, best.i, o);
+        best = better(best, y);
+    }
+    if (threadIdx.x == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
+// scratch: at least R * 64 pairs of (float, int) = R * 128 four-byte words, or null for the one-block form.
+GG_API gg_argmax(const float* logits, long long ld, int* out, int R, int V, void* scratch, long long scratch_words,
+                 cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0 || ld < V) return GG_ERR_ARG;
-    argmax_kernel<<<R, SAMP_THREADS, 0, stream>>>(logits, ld, out, V);
+    int chunks = 1;
+    if (scratch != nullptr && V >= 16384) {
+        chunks = 592 / R;                       // about four blocks per SM in all
+        if (chunks > 64) chunks = 64;
+        if (chunks > V / 4096) chunks = V / 4096;
+        if ((long long)R * chunks * 2 > scratch_words) chunks = 1;
+    }
+    if (chunks <= 1) {
+        argmax_kernel<<<R, SAMP_THREADS, 0, stream>>>(logits, ld, out, V);
+        return gg_last_error();
+    }
+    dim3 grid(R, chunks);
+    argmax_partial_kernel<<<grid, SAMP_THREADS, 0, stream>>>(logits, ld, (MaxIdx*)scratch, V, chunks);
+    argmax_final_kernel<<<R, 32, 0, stream>>>((const MaxIdx*)scratch, out, chunks);
     return gg_last_error();
 }
 

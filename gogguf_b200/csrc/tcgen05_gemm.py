@@ -33,15 +33,17 @@ def check_status(device: torch.device) -> None:
                           "1 TMA producer, 2 MMA issuer, 3 epilogue); results of that step are invalid")
 
 
-def splits_for(M: int, N: int, K: int) -> int:
-    module("gemm_tcgen05")
+def splits_for(M: int, N: int, K: int, cluster: bool = False) -> int:
     raw = module("gemm_tcgen05").lib.gg_gemm_tc_splits
-    return int(raw(int(M), int(N), int(K)))
+    return int(raw(int(M), int(N), int(K), int(bool(cluster))))
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
-            m: Optional[int] = None, scratch: Optional[torch.Tensor] = None) -> None:
-    """out[M, N] (+)= x[M, K] @ w[N, K]^T, bfloat16 operands, float32 accumulation on the tensor cores."""
+            m: Optional[int] = None, scratch: Optional[torch.Tensor] = None, cluster: bool = False) -> None:
+    """out[M, N] (+)= x[M, K] @ w[N, K]^T, bfloat16 operands, float32 accumulation on the tensor cores.
+
+    Small M splits K.  cluster=True: the partial sums are added inside thread-block clusters (no scratch).
+    cluster=False: they go through `scratch` (splits_for(M, N, K) * M * N floats) and a second kernel."""
     N, K = w.shape
     M = x.shape[0] if m is None else m
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -60,7 +62,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     kernel("gemm_tcgen05", "gg_gemm_tc")(
         x.data_ptr(), w.data_ptr(), out.data_ptr(), mode, M, N, K, x.stride(0), out.stride(0),
         scratch.data_ptr() if scratch is not None else 0, scratch.numel() if scratch is not None else 0,
-        st.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        int(bool(cluster)), st.data_ptr(), torch.cuda.current_stream().cuda_stream)
 
 
 def make_linear(weight: torch.Tensor) -> Optional[Callable]:
@@ -76,13 +78,6 @@ def make_linear(weight: torch.Tensor) -> Optional[Callable]:
             from . import kernels as Kn
             Kn.gemm_plain(x, weight, out, accumulate, m)
             return
-        splits = splits_for(M, N, K)
-        scratch = None
-        if splits > 1:
-            if ws is None:
-                scratch = torch.empty(splits * M * N, dtype=torch.float32, device=x.device)
-            else:
-                scratch = ws.get("gemm_splitk", (splits * M * N,), torch.float32)
-        gemm_tc(x, weight, out, accumulate, m, scratch)
+        gemm_tc(x, weight, out, accumulate, m, None, cluster=True)
 
     return run

@@ -183,6 +183,20 @@ def test_gemm_tcgen05(M, N, K_):
     tc.gemm_tc(x, w, ob, scratch=scratch)
     tc.check_status(DEV)
     assert rel(ob, want) < 5e-3
+    # the cluster form (partial sums added through distributed shared memory, no scratch)
+    oc = torch.full((M, N), float("nan"), device=DEV)
+    tc.gemm_tc(x, w, oc, cluster=True)
+    tc.check_status(DEV)
+    assert rel(oc, want) < tol, (tc.splits_for(M, N, K_, True),)
+    accc = res.clone()
+    tc.gemm_tc(x, w, accc, accumulate=True, cluster=True)
+    assert rel(accc, res.double() + want) < tol
+    obc = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    tc.gemm_tc(x, w, obc, cluster=True)
+    assert rel(obc, want) < 5e-3
+    again = torch.empty(M, N, device=DEV)
+    tc.gemm_tc(x, w, again, cluster=True)
+    assert torch.equal(again, oc)            # the order of the additions is fixed: same bits every time
     # the plain twin agrees
     twin = torch.empty(M, N, device=DEV)
     K().gemm_plain(x, w, twin)
