@@ -18,7 +18,7 @@
 //
 // Replaces the reference's per-head attn_qk / softmax / attn_v launches (pkg/gpu/cuda/ptx.go:679-889,
 // host loop pkg/gpu/cuda/driver.c:411-465).
-#include "common.cuh"
+#include "tma_util.cuh"
 
 namespace {
 
@@ -416,6 +416,221 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
     }
 }
 
+
+// ------------------------------------------------------------------------------------------- decode, TMA ring
+// The same work as attn_decode_kernel with the cache streamed by TMA: one producer thread keeps a
+// ring of whole pages (64 keys: K and V, [64 x 64]-column boxes, 128-byte swizzle) in flight, four
+// consumer warps take 16 keys of each page, read fragments with ldmatrix and keep their own running
+// maximum, sum and output; they are merged at the end as in the other kernel.  The copy engine
+// decouples the loads from the arithmetic, which a warp that loads and computes in turn cannot.
+template <int D, int STAGES>
+__global__ void __launch_bounds__(160) attn_decode_tma_kernel(
+    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+    const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+    const int* __restrict__ page_table, int max_pages, int nq, int nkv, float scale_log2, int window, int nsplit,
+    int* __restrict__ status) {
+    constexpr int HALVES = D / 64;
+    constexpr int BOX_BYTES = 64 * 64 * 2;                 // 8 KB
+    constexpr int STAGE_BYTES = 2 * HALVES * BOX_BYTES;    // K halves then V halves
+    constexpr int KS = D / 16, NT = D / 8;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    volatile int* abort_flag = (volatile int*)(empty + STAGES);
+
+    const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int G = nq / nkv;
+    const int b = seq_of_token[tok];
+    const int pos = b >= 0 ? positions[tok] : -1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { tma::mbar_init(&full[s], 1); tma::mbar_init(&empty[s], 4); }
+        *abort_flag = 0;
+        tma::mbar_fence_init();
+        tma::prefetch_map(&tmK);
+        tma::prefetch_map(&tmV);
+    }
+    __syncthreads();
+
+    int lo = 0, p_begin = 0, p_end = 0;
+    if (b >= 0) {
+        if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
+        const int first = lo / PAGE, last = pos / PAGE;
+        const int pps = (last - first + 1 + nsplit - 1) / nsplit;
+        p_begin = first + split * pps;
+        p_end = min(last + 1, p_begin + pps);
+    }
+    const int npg = max(0, p_end - p_begin);
+
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    if (warp == 4) {
+        if (lane == 0) {
+            const int* pt = page_table + (size_t)b * max_pages;
+            for (int i = 0; i < npg; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+                if (!tma::mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, 11)) break;
+                tma::mbar_expect_tx(&full[s], STAGE_BYTES);
+                const int row = (pt[p_begin + i] * nkv + kvh) * PAGE;
+                uint8_t* dst = smem + s * STAGE_BYTES;
+#pragma unroll
+                for (int hf = 0; hf < HALVES; ++hf) {
+                    tma::load_2d(dst + hf * BOX_BYTES, &tmK, &full[s], hf * 64, row);
+                    tma::load_2d(dst + (HALVES + hf) * BOX_BYTES, &tmV, &full[s], hf * 64, row);
+                }
+            }
+        }
+    } else if (npg > 0) {
+        // Q fragments in the standard A layout: row = head of the group, k = head dimension
+        uint32_t qa[KS][4];
+        {
+            const bf16* q0 = q + ((size_t)tok * nq + (size_t)kvh * G) * D;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                const int c = ks * 16 + 2 * t;
+                qa[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)g * D + c) : 0u;
+                qa[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(g + 8) * D + c) : 0u;
+                qa[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)g * D + c + 8) : 0u;
+                qa[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(g + 8) * D + c + 8) : 0u;
+            }
+        }
+        const int krow = warp * 16;     // this warp's 16 keys of every page
+        for (int i = 0; i < npg; ++i) {
+            const int s = i % STAGES;
+            const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+            if (!tma::mbar_wait(&full[s], ph, abort_flag, status, 12)) break;
+            const uint8_t* st = smem + s * STAGE_BYTES;
+            const int key0 = (p_begin + i) * PAGE + krow;
+            float sc[2][4];
+            sc[0][0] = sc[0][1] = sc[0][2] = sc[0][3] = 0.f;
+            sc[1][0] = sc[1][1] = sc[1][2] = sc[1][3] = 0.f;
+            if (key0 <= pos && key0 + 15 >= lo) {      // whole-warp decision: any visible key among these 16?
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    const bf16* box = reinterpret_cast<const bf16*>(st + (ks >> 2) * BOX_BYTES);
+                    uint32_t kb[4];
+                    ldsm_x4(kb, sw<64>(const_cast<bf16*>(box), krow + (lane & 7) + ((lane >> 4) << 3), (ks & 3) * 2 + ((lane >> 3) & 1)));
+                    mma16816(sc[0], qa[ks], kb[0], kb[1]);
+                    mma16816(sc[1], qa[ks], kb[2], kb[3]);
+                }
+                float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int kidx = key0 + j * 8 + 2 * t + (e & 1);
+                        const float v = (kidx >= lo && kidx <= pos) ? sc[j][e] * scale_log2 : -INFINITY;
+                        sc[j][e] = v;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                    }
+                uint32_t pa[4];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                    const float mn = fmaxf(m[r], mx[r]);
+                    const float mu = mn == -INFINITY ? 0.f : mn;
+                    const float corr = fast_exp2(m[r] - mu);
+                    m[r] = mn;
+                    const float p00 = fast_exp2(sc[0][2 * r] - mu), p01 = fast_exp2(sc[0][2 * r + 1] - mu);
+                    const float p10 = fast_exp2(sc[1][2 * r] - mu), p11 = fast_exp2(sc[1][2 * r + 1] - mu);
+                    l[r] = l[r] * corr + (p00 + p01 + p10 + p11);
+                    pa[r] = pack_bf16(p00, p01);
+                    pa[2 + r] = pack_bf16(p10, p11);
+#pragma unroll
+                    for (int n = 0; n < NT; ++n) { o[n][2 * r] *= corr; o[n][2 * r + 1] *= corr; }
+                }
+#pragma unroll
+                for (int np = 0; np < NT / 2; ++np) {
+                    const bf16* box = reinterpret_cast<const bf16*>(st + (HALVES + (np >> 2)) * BOX_BYTES);
+                    uint32_t vb[4];
+                    ldsm_x4_trans(vb, sw<64>(const_cast<bf16*>(box), krow + (lane & 7) + (((lane >> 3) & 1) << 3), (np & 3) * 2 + (lane >> 4)));
+                    mma16816(o[2 * np], pa, vb[0], vb[1]);
+                    mma16816(o[2 * np + 1], pa, vb[2], vb[3]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) tma::mbar_arrive(&empty[s]);
+        }
+    }
+    __syncthreads();          // all pages consumed (or the CTA gave up): the ring can be reused for the merge
+    if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }       // let copies in flight land before the CTA goes away
+        __syncthreads();
+    }
+    float* sm_o = reinterpret_cast<float*>(smem);                 // [4][16][D]
+    float* sm_ml = sm_o + 4 * 16 * D;                             // [4][16][2]
+    if (warp < 4) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                sm_o[(warp * 16 + g + 8 * (e >> 1)) * D + n * 8 + 2 * t + (e & 1)] = o[n][e];
+        if (t == 0) {
+            sm_ml[(warp * 16 + g) * 2] = m[0]; sm_ml[(warp * 16 + g) * 2 + 1] = l[0];
+            sm_ml[(warp * 16 + g + 8) * 2] = m[1]; sm_ml[(warp * 16 + g + 8) * 2 + 1] = l[1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+        const int r = idx / D, c = idx - r * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_ml[(w * 16 + r) * 2]);
+        float L = 0.f, acc = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = fast_exp2(sm_ml[(w * 16 + r) * 2] - M);
+                L += sm_ml[(w * 16 + r) * 2 + 1] * f;
+                acc += sm_o[(w * 16 + r) * D + c] * f;
+            }
+        }
+        const int head = kvh * G + r;
+        if (nsplit == 1) {
+            out[((size_t)tok * nq + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            const size_t pi = ((size_t)tok * nq + head) * nsplit + split;
+            part_o[pi * D + c] = acc;
+            if (c == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+        }
+    }
+}
+
+template <int D, int STAGES>
+int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* q, void* out, float* part_o, float* part_ml,
+                      const int* positions, const int* seq_of_token, const int* page_table, int max_pages, int ntok,
+                      int nq, int nkv, float scale_log2, int window, int splits, int* status, cudaStream_t stream) {
+    constexpr int ring = STAGES * 4 * (D / 64) * 64 * 64;     // bytes: STAGES * 2 * HALVES * 8 KB
+    constexpr int merge = (4 * 16 * D + 4 * 16 * 2) * 4;
+    constexpr int smem = (ring > merge ? ring : merge) + 1024 + 256;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(ntok, nkv, splits);
+    attn_decode_tma_kernel<D, STAGES><<<grid, 160, smem, stream>>>(tk, tv, (const bf16*)q, (bf16*)out, part_o, part_ml, positions,
+                                                                   seq_of_token, page_table, max_pages, nq, nkv, scale_log2,
+                                                                   window, splits, status);
+    return gg_last_error();
+}
+
 }  // namespace
 
 // Number of key-range splits the decode launcher uses for this shape; the caller sizes the scratch:
@@ -487,5 +702,48 @@ GG_API gg_attn_prefill(const void* q, const void* k_pool, const void* v_pool, vo
                                                              cu_seqlens, ctx_lens, seq_of_token, page_table, max_pages, n_seqs,
                                                              nq, nkv, scale_log2, window);
     }
+    return gg_last_error();
+}
+
+// Splits for the TMA form: whole pages per CTA, about four waves of two CTAs per SM.
+GG_API gg_attn_decode_tma_splits(int ntok, int nkv, int max_ctx) {
+    if (ntok <= 0 || nkv <= 0) return 1;
+    const long long pairs = (long long)ntok * nkv;
+    int splits = (int)((4 * 296 + pairs - 1) / pairs);
+    const int pages = (max_ctx + PAGE - 1) / PAGE;
+    if (splits > pages / 2) splits = pages / 2;       // at least two pages per CTA
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+    return splits;
+}
+
+// As gg_attn_decode, with the cache streamed by TMA.  n_pages is the number of pages in the pools
+// (their first dimension); splits must be what gg_attn_decode_tma_splits returned; status as in the
+// tensor-core product (codes 11 producer, 12 consumer).
+GG_API gg_attn_decode_tma(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_o, float* part_ml,
+                          const int* positions, const int* seq_of_token, const int* page_table, int max_pages,
+                          int page_size, int n_pages, int ntok, int nq, int nkv, int d, float scale, int window,
+                          int splits, int* status, cudaStream_t stream) {
+    if (ntok <= 0) return 0;
+    if (page_size != PAGE || nq <= 0 || nkv <= 0 || nq % nkv || nq / nkv > 16 || (d != 64 && d != 128) || splits < 1 ||
+        nkv > 65535 || splits > 65535 || n_pages <= 0 || status == nullptr)
+        return GG_ERR_ARG;
+    if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return GG_ERR_ARG;
+    if ((((uintptr_t)k_pool) & 15) || (((uintptr_t)v_pool) & 15)) return GG_ERR_ARG;
+    CUtensorMap tk, tv;
+    const unsigned long long rows = (unsigned long long)n_pages * nkv * PAGE;
+    int rc;
+    if ((rc = tma::make_map_bf16(&tk, k_pool, rows, d, d, PAGE)) != 0) return rc;
+    if ((rc = tma::make_map_bf16(&tv, v_pool, rows, d, d, PAGE)) != 0) return rc;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    if (d == 128)
+        rc = launch_decode_tma<128, 3>(tk, tv, q, out, part_o, part_ml, positions, seq_of_token, page_table, max_pages, ntok,
+                                       nq, nkv, scale_log2, window, splits, status, stream);
+    else
+        rc = launch_decode_tma<64, 4>(tk, tv, q, out, part_o, part_ml, positions, seq_of_token, page_table, max_pages, ntok,
+                                      nq, nkv, scale_log2, window, splits, status, stream);
+    if (rc != 0 || splits == 1) return rc;
+    if (d == 128) attn_combine_kernel<128><<<ntok * nq, 128, 0, stream>>>(part_o, part_ml, (bf16*)out, splits);
+    else attn_combine_kernel<64><<<ntok * nq, 64, 0, stream>>>(part_o, part_ml, (bf16*)out, splits);
     return gg_last_error();
 }

@@ -53,6 +53,7 @@ MODULES: Dict[str, str] = {
 _HEADERS = ["common.cuh"]
 # further files a module's source includes (they take part in its hash)
 _INCLUDES: Dict[str, List[str]] = {
+    "attention_fast.cu": ["tma_util.cuh"],
     "gemm_tcgen05_static.cu": ["gemm_tcgen05.cu", "gemm_tcgen05_static.h"],
 }
 

@@ -330,25 +330,29 @@ def test_attention_decode_tensor_cores(nq, nkv, d, window, ctxs):
     scale = 1.0 / math.sqrt(d)
     qr = torch.cat([q[:1], q[2:]])
     want = attention_reference(qr, ks, vs, seqs, nq, nkv, scale, window)
+    from gogguf_b200.csrc import tcgen05_gemm as tc
     for max_ctx in (max(ctxs), 8192):
-        splits = fa.decode_splits(T, nkv, max_ctx)
-        po = torch.empty(T * nq * splits * d, device=DEV)
-        pm = torch.empty(T * nq * splits * 2, device=DEV)
-        out = torch.full((T, nq, d), float("nan"), device=DEV, dtype=dt)
-        fa.attn_decode(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window, splits, po, pm)
-        got = torch.cat([out[:1], out[2:]])
-        assert rel(got, want) < 8e-3, (splits,)
-        assert float(out[1].float().abs().sum()) == 0.0
+        for form in ("direct", "tma"):
+            splits = (fa.decode_splits if form == "direct" else fa.decode_tma_splits)(T, nkv, max_ctx)
+            po = torch.empty(T * nq * splits * d, device=DEV)
+            pm = torch.empty(T * nq * splits * 2, device=DEV)
+            out = torch.full((T, nq, d), float("nan"), device=DEV, dtype=dt)
+            fn = fa.attn_decode if form == "direct" else fa.attn_decode_tma
+            fn(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window, splits, po, pm)
+            tc.check_status(DEV)
+            got = torch.cat([out[:1], out[2:]])
+            assert rel(got, want) < 8e-3, (form, splits)
+            assert float(out[1].float().abs().sum()) == 0.0
 
 
-@pytest.mark.parametrize("kind", ["plain_f32", "plain_bf16", "decode", "prefill"])
+@pytest.mark.parametrize("kind", ["plain_f32", "plain_bf16", "decode", "decode_tma", "prefill"])
 def test_attention_finds_a_far_key_and_respects_the_window_edge(kind):
     """Random numbers hide a key that is skipped among hundreds.  Here one far key (and, for the
     window, the keys just inside and just outside its edge) is scaled so that it takes all the weight."""
     from gogguf_b200.csrc import fast_attention as fa
     dt = torch.float32 if kind == "plain_f32" else torch.bfloat16
     nq, nkv, d, ctx = 8, 2, 128, 900
-    n_new = 1 if kind == "decode" else 130
+    n_new = 1 if kind.startswith("decode") else 130
     seqs = [(ctx, n_new)]
     scale = 1.0 / math.sqrt(d)
     for window, hot in ((0, 3), (0, 447), (200, ctx - 200), (200, ctx - 201)):
@@ -369,6 +373,10 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge(kind):
             splits = fa.decode_splits(T, nkv, 1024)
             po = torch.empty(T * nq * splits * d, device=DEV); pm = torch.empty(T * nq * splits * 2, device=DEV)
             fa.attn_decode(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window, splits, po, pm)
+        elif kind == "decode_tma":
+            splits = fa.decode_tma_splits(T, nkv, 1024)
+            po = torch.empty(T * nq * splits * d, device=DEV); pm = torch.empty(T * nq * splits * 2, device=DEV)
+            fa.attn_decode_tma(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window, splits, po, pm)
         else:
             fa.attn_prefill(q, kp, vp, out, cu, cl, sot, table, 64, 1, T // 64 + 1, nq, nkv, d, scale, window)
         last = out[-1].float()
