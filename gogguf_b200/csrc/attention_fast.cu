@@ -42,6 +42,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ uint4 ldg16(const bf16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 
 // ------------------------------------------------------------------------------------------- decode
@@ -429,7 +437,7 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
     const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int nq, int nkv, float scale_log2, int window, int nsplit,
-    int* __restrict__ status) {
+    int cluster_reduce, int* __restrict__ status) {
     constexpr int HALVES = D / 64;
     constexpr int BOX_BYTES = 64 * 64 * 2;                 // 8 KB
     constexpr int STAGE_BYTES = 2 * HALVES * BOX_BYTES;    // K halves then V halves
@@ -569,6 +577,8 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
     }
     float* sm_o = reinterpret_cast<float*>(smem);                 // [4][16][D]
     float* sm_ml = sm_o + 4 * 16 * D;                             // [4][16][2]
+    float* res_o = sm_ml + 4 * 16 * 2;                            // [16][D]  this CTA's merged output (cluster form)
+    float* res_ml = res_o + 16 * D;                               // [16][2]
     if (warp < 4) {
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -603,31 +613,87 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
         const int head = kvh * G + r;
         if (nsplit == 1) {
             out[((size_t)tok * nq + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else if (cluster_reduce) {
+            res_o[r * D + c] = acc;
+            if (c == 0) { res_ml[r * 2] = M; res_ml[r * 2 + 1] = L; }
         } else {
             const size_t pi = ((size_t)tok * nq + head) * nsplit + split;
             part_o[pi * D + c] = acc;
             if (c == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
         }
     }
+    if (cluster_reduce) {
+        // The splits of one (token, kv head) form a cluster: every CTA merges a slice of the G x D outputs
+        // over all ranks through distributed shared memory, in rank order.
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const uint32_t ro = tma::smem_u32(res_o), rm = tma::smem_u32(res_ml);
+        for (int idx = split * blockDim.x + threadIdx.x; idx < G * D; idx += nsplit * blockDim.x) {
+            const int r = idx / D, c = idx - r * D;
+            float ms[8], ls[8], as[8];
+            float M = -INFINITY;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (k < nsplit) {
+                    ms[k] = ld_dsmem_f32(rm + 4u * (r * 2), k);
+                    ls[k] = ld_dsmem_f32(rm + 4u * (r * 2 + 1), k);
+                    as[k] = ld_dsmem_f32(ro + 4u * idx, k);
+                } else { ms[k] = -INFINITY; ls[k] = 0.f; as[k] = 0.f; }
+                M = fmaxf(M, ms[k]);
+            }
+            float L = 0.f, acc = 0.f;
+            if (M != -INFINITY) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float f = fast_exp2(ms[k] - M);
+                    L += ls[k] * f;
+                    acc += as[k] * f;
+                }
+            }
+            out[((size_t)tok * nq + kvh * G + r) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
 }
 
 template <int D, int STAGES>
 int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* q, void* out, float* part_o, float* part_ml,
                       const int* positions, const int* seq_of_token, const int* page_table, int max_pages, int ntok,
-                      int nq, int nkv, float scale_log2, int window, int splits, int* status, cudaStream_t stream) {
+                      int nq, int nkv, float scale_log2, int window, int splits, bool cluster, int* status,
+                      cudaStream_t stream) {
     constexpr int ring = STAGES * 4 * (D / 64) * 64 * 64;     // bytes: STAGES * 2 * HALVES * 8 KB
-    constexpr int merge = (4 * 16 * D + 4 * 16 * 2) * 4;
+    constexpr int merge = (5 * 16 * D + 5 * 16 * 2) * 4;
     constexpr int smem = (ring > merge ? ring : merge) + 1024 + 256;
     static bool configured = false;
+    auto kern = attn_decode_tma_kernel<D, STAGES>;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(ntok, nkv, splits);
-    attn_decode_tma_kernel<D, STAGES><<<grid, 160, smem, stream>>>(tk, tv, (const bf16*)q, (bf16*)out, part_o, part_ml, positions,
-                                                                   seq_of_token, page_table, max_pages, nq, nkv, scale_log2,
-                                                                   window, splits, status);
+    const int cl = (cluster && splits > 1) ? 1 : 0;
+    if (!cl) {
+        kern<<<grid, 160, smem, stream>>>(tk, tv, (const bf16*)q, (bf16*)out, part_o, part_ml, positions, seq_of_token,
+                                          page_table, max_pages, nq, nkv, scale_log2, window, splits, 0, status);
+        return gg_last_error();
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(160);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tk, tv, (const bf16*)q, (bf16*)out, part_o, part_ml, positions,
+                                       seq_of_token, page_table, max_pages, nq, nkv, scale_log2, window, splits, 1, status);
+    if (e != cudaSuccess) return (int)e;
     return gg_last_error();
 }
 
@@ -705,30 +771,34 @@ GG_API gg_attn_prefill(const void* q, const void* k_pool, const void* v_pool, vo
     return gg_last_error();
 }
 
-// Splits for the TMA form: whole pages per CTA, about four waves of two CTAs per SM.
-GG_API gg_attn_decode_tma_splits(int ntok, int nkv, int max_ctx) {
+// Splits for the TMA form: whole pages per CTA.  use_cluster != 0: the splits of one (token, kv head)
+// form a thread-block cluster (at most 8) and are merged through distributed shared memory; no scratch.
+GG_API gg_attn_decode_tma_splits(int ntok, int nkv, int max_ctx, int use_cluster) {
     if (ntok <= 0 || nkv <= 0) return 1;
     const long long pairs = (long long)ntok * nkv;
-    int splits = (int)((4 * 296 + pairs - 1) / pairs);
+    int splits = use_cluster ? (int)((592 + pairs / 2) / pairs) : (int)((4 * 296 + pairs - 1) / pairs);
     const int pages = (max_ctx + PAGE - 1) / PAGE;
     if (splits > pages / 2) splits = pages / 2;       // at least two pages per CTA
-    if (splits > 64) splits = 64;
+    const int most = use_cluster ? 8 : 64;
+    if (splits > most) splits = most;
     if (splits < 1) splits = 1;
     return splits;
 }
 
 // As gg_attn_decode, with the cache streamed by TMA.  n_pages is the number of pages in the pools
-// (their first dimension); splits must be what gg_attn_decode_tma_splits returned; status as in the
-// tensor-core product (codes 11 producer, 12 consumer).
+// (their first dimension); splits must be what gg_attn_decode_tma_splits returned for the same
+// use_cluster; status as in the tensor-core product (codes 11 producer, 12 consumer).
 GG_API gg_attn_decode_tma(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_o, float* part_ml,
                           const int* positions, const int* seq_of_token, const int* page_table, int max_pages,
                           int page_size, int n_pages, int ntok, int nq, int nkv, int d, float scale, int window,
-                          int splits, int* status, cudaStream_t stream) {
+                          int splits, int use_cluster, int* status, cudaStream_t stream) {
     if (ntok <= 0) return 0;
     if (page_size != PAGE || nq <= 0 || nkv <= 0 || nq % nkv || nq / nkv > 16 || (d != 64 && d != 128) || splits < 1 ||
         nkv > 65535 || splits > 65535 || n_pages <= 0 || status == nullptr)
         return GG_ERR_ARG;
-    if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return GG_ERR_ARG;
+    const bool cluster = use_cluster != 0;
+    if (cluster && splits > 8) return GG_ERR_ARG;
+    if (splits > 1 && !cluster && (part_o == nullptr || part_ml == nullptr)) return GG_ERR_ARG;
     if ((((uintptr_t)k_pool) & 15) || (((uintptr_t)v_pool) & 15)) return GG_ERR_ARG;
     CUtensorMap tk, tv;
     const unsigned long long rows = (unsigned long long)n_pages * nkv * PAGE;
@@ -738,11 +808,11 @@ GG_API gg_attn_decode_tma(const void* q, const void* k_pool, const void* v_pool,
     const float scale_log2 = scale * 1.4426950408889634f;
     if (d == 128)
         rc = launch_decode_tma<128, 3>(tk, tv, q, out, part_o, part_ml, positions, seq_of_token, page_table, max_pages, ntok,
-                                       nq, nkv, scale_log2, window, splits, status, stream);
+                                       nq, nkv, scale_log2, window, splits, cluster, status, stream);
     else
         rc = launch_decode_tma<64, 4>(tk, tv, q, out, part_o, part_ml, positions, seq_of_token, page_table, max_pages, ntok,
-                                      nq, nkv, scale_log2, window, splits, status, stream);
-    if (rc != 0 || splits == 1) return rc;
+                                      nq, nkv, scale_log2, window, splits, cluster, status, stream);
+    if (rc != 0 || splits == 1 || cluster) return rc;
     if (d == 128) attn_combine_kernel<128><<<ntok * nq, 128, 0, stream>>>(part_o, part_ml, (bf16*)out, splits);
     else attn_combine_kernel<64><<<ntok * nq, 64, 0, stream>>>(part_o, part_ml, (bf16*)out, splits);
     return gg_last_error();

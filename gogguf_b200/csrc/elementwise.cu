@@ -224,6 +224,89 @@ __global__ void qk_norm_rope_cache_kernel(
     }
 }
 
+// bfloat16 form for a full rotation (rot == d) and d = 64 * VPL / 2 ... : each lane owns VPL pairs
+// (i, i + d/2) with i = lane * VPL .. +VPL, so both halves of a pair sit in the same thread, every
+// access is VPL * 2 bytes wide and no shared memory is needed.  VPL = d / 64 (d = 64: 1, 128: 2, 256: 4).
+template <int VPL>
+__global__ void __launch_bounds__(128) qk_norm_rope_cache_vec_kernel(
+    const bf16* __restrict__ qkv, bf16* __restrict__ q_out,
+    const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+    const float* __restrict__ cosv, const float* __restrict__ sinv,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+    const int* __restrict__ page_table, int max_pages, int page_size,
+    bf16* __restrict__ k_pool, bf16* __restrict__ v_pool, int ntok, int nq, int nkv) {
+    constexpr int D = 64 * VPL, HALF = D / 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nheads = nq + 2 * nkv;
+    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (wid >= (long long)ntok * nheads) return;
+    const int t = (int)(wid / nheads), h = (int)(wid - (long long)t * nheads);
+    const int b = seq_of_token[t];
+    const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+    if (!is_q && (k_pool == nullptr || b < 0)) return;
+    const bf16* src = qkv + ((size_t)t * nheads + h) * D;
+    bf16* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * nq + h) * D;
+    } else {
+        const int pos = positions[t];
+        const int page = page_table[(size_t)b * max_pages + pos / page_size];
+        const int kvh = is_k ? h - nq : h - nq - nkv;
+        dst = (is_k ? k_pool : v_pool) + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * D;
+    }
+    const int i0 = lane * VPL;          // first index of this lane in the low half
+    bf16 lo[VPL], hi[VPL];
+    if (VPL == 1) {
+        lo[0] = src[i0]; hi[0] = src[i0 + HALF];
+    } else if (VPL == 2) {
+        *reinterpret_cast<uint32_t*>(lo) = *reinterpret_cast<const uint32_t*>(src + i0);
+        *reinterpret_cast<uint32_t*>(hi) = *reinterpret_cast<const uint32_t*>(src + i0 + HALF);
+    } else {
+        *reinterpret_cast<uint2*>(lo) = *reinterpret_cast<const uint2*>(src + i0);
+        *reinterpret_cast<uint2*>(hi) = *reinterpret_cast<const uint2*>(src + i0 + HALF);
+    }
+    if (!is_q && !is_k) {               // value head: plain copy
+        if (VPL == 1) { dst[i0] = lo[0]; dst[i0 + HALF] = hi[0]; }
+        else if (VPL == 2) {
+            *reinterpret_cast<uint32_t*>(dst + i0) = *reinterpret_cast<uint32_t*>(lo);
+            *reinterpret_cast<uint32_t*>(dst + i0 + HALF) = *reinterpret_cast<uint32_t*>(hi);
+        } else {
+            *reinterpret_cast<uint2*>(dst + i0) = *reinterpret_cast<uint2*>(lo);
+            *reinterpret_cast<uint2*>(dst + i0 + HALF) = *reinterpret_cast<uint2*>(hi);
+        }
+        return;
+    }
+    const float* w = is_q ? qw : kw;
+    float a[VPL], c[VPL], ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        a[k] = __bfloat162float(lo[k]); c[k] = __bfloat162float(hi[k]);
+        ss = fmaf(a[k], a[k], ss); ss = fmaf(c[k], c[k], ss);
+    }
+    float scale = 1.f;
+    if (w != nullptr) {
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)D + eps);
+    }
+    const float* cs = cosv + (size_t)t * HALF + i0;
+    const float* sn = sinv + (size_t)t * HALF + i0;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const float x0 = a[k] * scale * (w ? w[i0 + k] : 1.f);
+        const float x1 = c[k] * scale * (w ? w[i0 + HALF + k] : 1.f);
+        lo[k] = __float2bfloat16_rn(x0 * cs[k] - x1 * sn[k]);
+        hi[k] = __float2bfloat16_rn(x0 * sn[k] + x1 * cs[k]);
+    }
+    if (VPL == 1) { dst[i0] = lo[0]; dst[i0 + HALF] = hi[0]; }
+    else if (VPL == 2) {
+        *reinterpret_cast<uint32_t*>(dst + i0) = *reinterpret_cast<uint32_t*>(lo);
+        *reinterpret_cast<uint32_t*>(dst + i0 + HALF) = *reinterpret_cast<uint32_t*>(hi);
+    } else {
+        *reinterpret_cast<uint2*>(dst + i0) = *reinterpret_cast<uint2*>(lo);
+        *reinterpret_cast<uint2*>(dst + i0 + HALF) = *reinterpret_cast<uint2*>(hi);
+    }
+}
+
 GG_API gg_qk_norm_rope_cache(const void* qkv, int dtype, void* q_out, const float* qw, const float* kw, float eps,
                              const float* cosv, const float* sinv, const int* positions, const int* seq_of_token,
                              const int* page_table, int max_pages, int page_size, void* k_pool, void* v_pool,
@@ -233,6 +316,15 @@ GG_API gg_qk_norm_rope_cache(const void* qkv, int dtype, void* q_out, const floa
     const int warps = 4;
     const long long total = (long long)ntok * (nq + 2 * nkv);
     const unsigned grid = (unsigned)((total + warps - 1) / warps);
+    const bool al = ((((uintptr_t)qkv) | ((uintptr_t)q_out) | ((uintptr_t)k_pool) | ((uintptr_t)v_pool)) & 15) == 0;
+    if (dtype == GG_BF16 && rot == d && al && (d == 64 || d == 128 || d == 256)) {
+#define GG_QK_VEC(V) qk_norm_rope_cache_vec_kernel<V><<<grid, warps * 32, 0, stream>>>( \
+            (const bf16*)qkv, (bf16*)q_out, qw, kw, eps, cosv, sinv, positions, seq_of_token, page_table, max_pages, \
+            page_size, (bf16*)k_pool, (bf16*)v_pool, ntok, nq, nkv)
+        if (d == 64) GG_QK_VEC(1); else if (d == 128) GG_QK_VEC(2); else GG_QK_VEC(4);
+#undef GG_QK_VEC
+        return gg_last_error();
+    }
     const size_t smem = (size_t)warps * d * sizeof(float);
     GG_DISPATCH_DTYPE(dtype, T,
         qk_norm_rope_cache_kernel<T><<<grid, warps * 32, smem, stream>>>(
@@ -254,10 +346,39 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, lon
     out[idx] = from_f<T>(g / (1.0f + expf(-g)) * u);
 }
 
+// Eight elements per thread with 16-byte accesses (rows of I elements, I a multiple of 8).
+__global__ void swiglu_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long long nvec, int I8) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= nvec) return;
+    const long long t = idx / I8;
+    const int c = (int)(idx - t * I8);
+    const uint4 gv = *reinterpret_cast<const uint4*>(gu + (t * 2 * I8 + c) * 8);
+    const uint4 uv = *reinterpret_cast<const uint4*>(gu + (t * 2 * I8 + I8 + c) * 8);
+    const uint32_t* gw = reinterpret_cast<const uint32_t*>(&gv);
+    const uint32_t* uw = reinterpret_cast<const uint32_t*>(&uv);
+    uint32_t ow[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gw[k]);
+        const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(&uw[k]);
+        const float g0 = __low2float(g2), g1 = __high2float(g2);
+        const float r0 = g0 / (1.0f + expf(-g0)) * __low2float(u2);
+        const float r1 = g1 / (1.0f + expf(-g1)) * __high2float(u2);
+        const __nv_bfloat162 r = __floats2bfloat162_rn(r0, r1);
+        ow[k] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+    *reinterpret_cast<uint4*>(out + idx * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
 GG_API gg_swiglu(const void* gu, int dtype, void* out, int ntok, int I, cudaStream_t stream) {
     if (ntok <= 0) return 0;
     if (I <= 0) return GG_ERR_ARG;
     const long long n = (long long)ntok * I;
+    if (dtype == GG_BF16 && I % 8 == 0 && ((((uintptr_t)gu) | ((uintptr_t)out)) & 15) == 0) {
+        const long long nvec = n / 8;
+        swiglu_vec8_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>((const bf16*)gu, (bf16*)out, nvec, I / 8);
+        return gg_last_error();
+    }
     GG_DISPATCH_DTYPE(dtype, T,
         swiglu_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const T*)gu, (T*)out, n, I));
     return gg_last_error();

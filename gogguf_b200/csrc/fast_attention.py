@@ -23,19 +23,21 @@ def attn_decode(q, k_pool, v_pool, out, positions, seq_of_token, table, page_siz
         n_tokens, nq, nkv, d, float(scale), int(window), int(splits), torch.cuda.current_stream().cuda_stream)
 
 
-def decode_tma_splits(n_tokens: int, nkv: int, max_ctx: int) -> int:
-    return int(module("attention_fast").lib.gg_attn_decode_tma_splits(int(n_tokens), int(nkv), int(max_ctx)))
+def decode_tma_splits(n_tokens: int, nkv: int, max_ctx: int, cluster: bool = False) -> int:
+    return int(module("attention_fast").lib.gg_attn_decode_tma_splits(int(n_tokens), int(nkv), int(max_ctx),
+                                                                      int(bool(cluster))))
 
 
 def attn_decode_tma(q, k_pool, v_pool, out, positions, seq_of_token, table, page_size, n_tokens, nq, nkv, d,
-                    scale, window, splits, part_o=None, part_ml=None) -> None:
-    """Decode attention with the cache streamed through a TMA ring (pools: [page][nkv][64][d])."""
+                    scale, window, splits, part_o=None, part_ml=None, cluster: bool = False) -> None:
+    """Decode attention with the cache streamed through a TMA ring (pools: [page][nkv][64][d]).
+    cluster=True merges the splits inside thread-block clusters (no scratch, no second kernel)."""
     from .tcgen05_gemm import status_word
     kernel("attention_fast", "gg_attn_decode_tma")(
         q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
         part_o.data_ptr() if part_o is not None else 0, part_ml.data_ptr() if part_ml is not None else 0,
         positions.data_ptr(), seq_of_token.data_ptr(), table.data_ptr(), table.shape[-1], page_size,
-        k_pool.shape[0], n_tokens, nq, nkv, d, float(scale), int(window), int(splits),
+        k_pool.shape[0], n_tokens, nq, nkv, d, float(scale), int(window), int(splits), int(bool(cluster)),
         status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
 
 
@@ -61,13 +63,9 @@ def try_make(nq: int, nkv: int, d: int, scale: float, window: int) -> Optional[C
                               T, nq, nkv, d, scale, window)
             return
         if ctx.decode:
-            splits = decode_tma_splits(T, nkv, ctx.max_ctx)
-            po = pm = None
-            if splits > 1:
-                po = ctx.ws.get("attn_part_o", (T * nq * splits * d,), torch.float32)
-                pm = ctx.ws.get("attn_part_ml", (T * nq * splits * 2,), torch.float32)
+            splits = decode_tma_splits(T, nkv, ctx.max_ctx, cluster=True)
             attn_decode_tma(q, k_pool, v_pool, out, ctx.positions, ctx.seq_of_token, table, page_size, T, nq, nkv, d,
-                            scale, window, splits, po, pm)
+                            scale, window, splits, cluster=True)
         else:
             max_tiles = T // 64 + ctx.n_seqs
             attn_prefill(q, k_pool, v_pool, out, ctx.cu_seqlens, ctx.ctx_lens, ctx.seq_of_token, table, page_size,

@@ -332,13 +332,20 @@ def test_attention_decode_tensor_cores(nq, nkv, d, window, ctxs):
     want = attention_reference(qr, ks, vs, seqs, nq, nkv, scale, window)
     from gogguf_b200.csrc import tcgen05_gemm as tc
     for max_ctx in (max(ctxs), 8192):
-        for form in ("direct", "tma"):
-            splits = (fa.decode_splits if form == "direct" else fa.decode_tma_splits)(T, nkv, max_ctx)
+        for form in ("direct", "tma", "tma_cluster"):
+            if form == "direct":
+                splits = fa.decode_splits(T, nkv, max_ctx)
+            else:
+                splits = fa.decode_tma_splits(T, nkv, max_ctx, cluster=form == "tma_cluster")
             po = torch.empty(T * nq * splits * d, device=DEV)
             pm = torch.empty(T * nq * splits * 2, device=DEV)
             out = torch.full((T, nq, d), float("nan"), device=DEV, dtype=dt)
-            fn = fa.attn_decode if form == "direct" else fa.attn_decode_tma
-            fn(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window, splits, po, pm)
+            if form == "direct":
+                fa.attn_decode(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window, splits, po, pm)
+            elif form == "tma":
+                fa.attn_decode_tma(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window, splits, po, pm)
+            else:
+                fa.attn_decode_tma(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window, splits, cluster=True)
             tc.check_status(DEV)
             got = torch.cat([out[:1], out[2:]])
             assert rel(got, want) < 8e-3, (form, splits)
@@ -374,9 +381,9 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge(kind):
             po = torch.empty(T * nq * splits * d, device=DEV); pm = torch.empty(T * nq * splits * 2, device=DEV)
             fa.attn_decode(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window, splits, po, pm)
         elif kind == "decode_tma":
-            splits = fa.decode_tma_splits(T, nkv, 1024)
-            po = torch.empty(T * nq * splits * d, device=DEV); pm = torch.empty(T * nq * splits * 2, device=DEV)
-            fa.attn_decode_tma(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window, splits, po, pm)
+            splits = fa.decode_tma_splits(T, nkv, 1024, cluster=True)
+            assert splits > 1
+            fa.attn_decode_tma(q, kp, vp, out, pos, sot, table, 64, T, nq, nkv, d, scale, window, splits, cluster=True)
         else:
             fa.attn_prefill(q, kp, vp, out, cu, cl, sot, table, 64, 1, T // 64 + 1, nq, nkv, d, scale, window)
         last = out[-1].float()
