@@ -62,6 +62,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int nq, int nkv, float scale_log2, int window, int nsplit) {
+    pdl_launch();
+    pdl_wait();
     constexpr int NCH = D / 32;      // 32-wide chunks of the head dimension for Q.K^T
     constexpr int NDB = D / 64;      // 64-wide blocks of output columns for P.V
     constexpr int NT = D / 8;        // output n-tiles
@@ -225,6 +227,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
 template <int D>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int nsplit) {
+    pdl_launch();
+    pdl_wait();
     const size_t row = blockIdx.x;         // token * nq + head
     const int c = threadIdx.x;
     float M = -INFINITY;
@@ -267,6 +271,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool, bf16* __restrict__ out,
     const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int n_seqs, int nq, int nkv, float scale_log2, int window) {
+    pdl_launch();
+    pdl_wait();
     constexpr int CH = D / 8;        // 16-byte chunks per row
     constexpr int KS = D / 16;       // k-steps of Q.K^T
     constexpr int NT = D / 8;        // output n-tiles
@@ -438,6 +444,7 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int nq, int nkv, float scale_log2, int window, int nsplit,
     int cluster_reduce, int* __restrict__ status) {
+    pdl_launch();
     constexpr int HALVES = D / 64;
     constexpr int BOX_BYTES = 64 * 64 * 2;                 // 8 KB
     constexpr int STAGE_BYTES = 2 * HALVES * BOX_BYTES;    // K halves then V halves
@@ -452,8 +459,6 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int G = nq / nkv;
-    const int b = seq_of_token[tok];
-    const int pos = b >= 0 ? positions[tok] : -1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { tma::mbar_init(&full[s], 1); tma::mbar_init(&empty[s], 4); }
@@ -463,6 +468,9 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
         tma::prefetch_map(&tmV);
     }
     __syncthreads();
+    pdl_wait();      // everything below reads what earlier kernels of the step wrote (q, the cache, the tables)
+    const int b = seq_of_token[tok];
+    const int pos = b >= 0 ? positions[tok] : -1;
 
     int lo = 0, p_begin = 0, p_end = 0;
     if (b >= 0) {
@@ -674,27 +682,9 @@ int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* 
     }
     dim3 grid(ntok, nkv, splits);
     const int cl = (cluster && splits > 1) ? 1 : 0;
-    if (!cl) {
-        kern<<<grid, 160, smem, stream>>>(tk, tv, (const bf16*)q, (bf16*)out, part_o, part_ml, positions, seq_of_token,
-                                          page_table, max_pages, nq, nkv, scale_log2, window, splits, 0, status);
-        return gg_last_error();
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(160);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = splits;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tk, tv, (const bf16*)q, (bf16*)out, part_o, part_ml, positions,
-                                       seq_of_token, page_table, max_pages, nq, nkv, scale_log2, window, splits, 1, status);
-    if (e != cudaSuccess) return (int)e;
-    return gg_last_error();
+    return gg_launch(kern, grid, dim3(160), smem, stream, cl ? splits : 1, tk, tv, (const bf16*)q, (bf16*)out, part_o,
+                     part_ml, positions, seq_of_token, page_table, max_pages, nq, nkv, scale_log2, window, splits, cl,
+                     status);
 }
 
 }  // namespace
@@ -727,17 +717,17 @@ GG_API gg_attn_decode(const void* q, const void* k_pool, const void* v_pool, voi
     const float scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(ntok, nkv, splits);
     if (d == 128)
-        attn_decode_kernel<128><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
+        gg_launch(attn_decode_kernel<128>, dim3(grid), dim3(128), 0, stream, 1, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
                                                           part_o, part_ml, positions, seq_of_token, page_table, max_pages,
                                                           nq, nkv, scale_log2, window, splits);
     else
-        attn_decode_kernel<64><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
+        gg_launch(attn_decode_kernel<64>, dim3(grid), dim3(128), 0, stream, 1, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
                                                          part_o, part_ml, positions, seq_of_token, page_table, max_pages,
                                                          nq, nkv, scale_log2, window, splits);
     int rc = gg_last_error();
     if (rc != 0 || splits == 1) return rc;
-    if (d == 128) attn_combine_kernel<128><<<ntok * nq, 128, 0, stream>>>(part_o, part_ml, (bf16*)out, splits);
-    else attn_combine_kernel<64><<<ntok * nq, 64, 0, stream>>>(part_o, part_ml, (bf16*)out, splits);
+    if (d == 128) gg_launch(attn_combine_kernel<128>, dim3(ntok * nq), dim3(128), 0, stream, 1, part_o, part_ml, (bf16*)out, splits);
+    else gg_launch(attn_combine_kernel<64>, dim3(ntok * nq), dim3(64), 0, stream, 1, part_o, part_ml, (bf16*)out, splits);
     return gg_last_error();
 }
 
@@ -760,11 +750,11 @@ GG_API gg_attn_prefill(const void* q, const void* k_pool, const void* v_pool, vo
             if (e != cudaSuccess) return (int)e;
             cfg128 = true;
         }
-        attn_prefill_kernel<128><<<grid, 128, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
+        gg_launch(attn_prefill_kernel<128>, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
                                                               cu_seqlens, ctx_lens, seq_of_token, page_table, max_pages, n_seqs,
                                                               nq, nkv, scale_log2, window);
     } else {
-        attn_prefill_kernel<64><<<grid, 128, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
+        gg_launch(attn_prefill_kernel<64>, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
                                                              cu_seqlens, ctx_lens, seq_of_token, page_table, max_pages, n_seqs,
                                                              nq, nkv, scale_log2, window);
     }
@@ -813,7 +803,7 @@ GG_API gg_attn_decode_tma(const void* q, const void* k_pool, const void* v_pool,
         rc = launch_decode_tma<64, 4>(tk, tv, q, out, part_o, part_ml, positions, seq_of_token, page_table, max_pages, ntok,
                                       nq, nkv, scale_log2, window, splits, cluster, status, stream);
     if (rc != 0 || splits == 1 || cluster) return rc;
-    if (d == 128) attn_combine_kernel<128><<<ntok * nq, 128, 0, stream>>>(part_o, part_ml, (bf16*)out, splits);
-    else attn_combine_kernel<64><<<ntok * nq, 64, 0, stream>>>(part_o, part_ml, (bf16*)out, splits);
+    if (d == 128) gg_launch(attn_combine_kernel<128>, dim3(ntok * nq), dim3(128), 0, stream, 1, part_o, part_ml, (bf16*)out, splits);
+    else gg_launch(attn_combine_kernel<64>, dim3(ntok * nq), dim3(64), 0, stream, 1, part_o, part_ml, (bf16*)out, splits);
     return gg_last_error();
 }

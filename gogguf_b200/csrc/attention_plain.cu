@@ -19,6 +19,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_plain_kernel(
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int page_size,
     int nq, int nkv, int d, float scale, int window) {
+    pdl_launch();
+    pdl_wait();
     extern __shared__ float sm[];
     float* qs = sm;                       // [d]
     float* accs = sm + d;                 // [ATT_WARPS][d]
@@ -93,7 +95,7 @@ GG_API gg_attention_plain(const void* q, const void* k_pool, const void* v_pool,
     const size_t smem = ((size_t)(1 + ATT_WARPS) * d + 2 * ATT_WARPS) * sizeof(float);
     dim3 grid(ntok, nq);
     GG_DISPATCH_DTYPE(dtype, T,
-        attention_plain_kernel<T><<<grid, ATT_WARPS * 32, smem, stream>>>(
+        gg_launch(attention_plain_kernel<T>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 1, 
             (const T*)q, (const T*)k_pool, (const T*)v_pool, (T*)out, positions, seq_of_token, page_table,
             max_pages, page_size, nq, nkv, d, scale, window));
     return gg_last_error();

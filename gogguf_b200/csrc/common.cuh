@@ -72,3 +72,53 @@ __device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats o
         else if ((code) == GG_BF16) { typedef bf16 T; __VA_ARGS__; } \
         else return GG_ERR_DTYPE;                             \
     } while (0)
+
+// ----------------------------------------------------------------------------- dependent launches
+// Kernels of a step are launched with programmatic stream serialisation: a kernel may become
+// resident while its predecessor in the stream is still draining, run its prologue (barrier set-up,
+// tensor-memory allocation, loads of weights, which no kernel writes), and must call pdl_wait()
+// before it touches anything a predecessor reads or writes.  Every kernel calls pdl_wait(), so
+// "my predecessor has completed" holds transitively for all earlier kernels.  pdl_launch() lets the
+// successor start early.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <cstdlib>
+static inline bool gg_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("GOGGUF_B200_PDL");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+// Launch `kernel` with the dependent-launch attribute and, when cluster_z > 1, clusters of (1, 1, cluster_z).
+template <typename... KArgs, typename... Args>
+static inline int gg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            int cluster_z, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (gg_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = (unsigned)cluster_z;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) return (int)e;
+    return (int)cudaGetLastError();
+}

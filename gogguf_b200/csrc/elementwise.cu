@@ -12,6 +12,8 @@
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                                     float* __restrict__ out, int H, int V) {
+    pdl_launch();
+    pdl_wait();
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* o = out + (size_t)t * H;
@@ -28,7 +30,7 @@ GG_API gg_embed_gather(const void* table, int table_dtype, const int* tokens, fl
     if (T <= 0) return 0;
     if (H <= 0 || V <= 0) return GG_ERR_ARG;
     GG_DISPATCH_DTYPE(table_dtype, TW,
-        embed_gather_kernel<TW><<<T, 256, 0, stream>>>((const TW*)table, tokens, out, H, V));
+        gg_launch(embed_gather_kernel<TW>, dim3(T), dim3(256), 0, stream, 1, (const TW*)table, tokens, out, H, V));
     return gg_last_error();
 }
 
@@ -38,6 +40,8 @@ GG_API gg_embed_gather(const void* table, int table_dtype, const int* tokens, fl
 template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                const float* __restrict__ w, TO* __restrict__ out, int H, float eps) {
+    pdl_launch();
+    pdl_wait();
     __shared__ float red[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -60,6 +64,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 template <typename TO, int VPT /* float4 per thread */>
 __global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                                           const float* __restrict__ w, TO* __restrict__ out, int H, float eps) {
+    pdl_launch();
+    pdl_wait();
     __shared__ float red[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -115,16 +121,16 @@ GG_API gg_rmsnorm(const float* x, const int* rows, const float* w, void* out, in
     if (aligned && H <= 8192) {
         const int vpt = (H / 4 + 255) / 256;     // 1..8
         GG_DISPATCH_DTYPE(out_dtype, TO, {
-            if (vpt <= 1) rmsnorm_vec_kernel<TO, 1><<<R, 256, 0, stream>>>(x, rows, w, (TO*)out, H, eps);
-            else if (vpt <= 2) rmsnorm_vec_kernel<TO, 2><<<R, 256, 0, stream>>>(x, rows, w, (TO*)out, H, eps);
-            else if (vpt <= 4) rmsnorm_vec_kernel<TO, 4><<<R, 256, 0, stream>>>(x, rows, w, (TO*)out, H, eps);
-            else rmsnorm_vec_kernel<TO, 8><<<R, 256, 0, stream>>>(x, rows, w, (TO*)out, H, eps);
+            if (vpt <= 1) gg_launch(rmsnorm_vec_kernel<TO, 1>, dim3(R), dim3(256), 0, stream, 1, x, rows, w, (TO*)out, H, eps);
+            else if (vpt <= 2) gg_launch(rmsnorm_vec_kernel<TO, 2>, dim3(R), dim3(256), 0, stream, 1, x, rows, w, (TO*)out, H, eps);
+            else if (vpt <= 4) gg_launch(rmsnorm_vec_kernel<TO, 4>, dim3(R), dim3(256), 0, stream, 1, x, rows, w, (TO*)out, H, eps);
+            else gg_launch(rmsnorm_vec_kernel<TO, 8>, dim3(R), dim3(256), 0, stream, 1, x, rows, w, (TO*)out, H, eps);
         });
         return gg_last_error();
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     GG_DISPATCH_DTYPE(out_dtype, TO,
-        rmsnorm_kernel<TO><<<R, threads, 0, stream>>>(x, rows, w, (TO*)out, H, eps));
+        gg_launch(rmsnorm_kernel<TO>, dim3(R), dim3(threads), 0, stream, 1, x, rows, w, (TO*)out, H, eps));
     return gg_last_error();
 }
 
@@ -133,6 +139,8 @@ GG_API gg_rmsnorm(const float* x, const int* rows, const float* w, void* out, in
 // its tables in float64 too, pkg/ops/rope_tables.go:6-20) and stored as float32.
 __global__ void rope_tables_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
                                    float* __restrict__ cosv, float* __restrict__ sinv, int T, int half) {
+    pdl_launch();
+    pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= T * half) return;
     const int t = idx / half, i = idx - t * half;
@@ -148,7 +156,7 @@ GG_API gg_rope_tables(const int* positions, const double* inv_freq, float* cosv,
                       int T, int half, cudaStream_t stream) {
     if (T <= 0 || half <= 0) return 0;
     const int n = T * half;
-    rope_tables_kernel<<<(n + 255) / 256, 256, 0, stream>>>(positions, inv_freq, cosv, sinv, T, half);
+    gg_launch(rope_tables_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, 1, positions, inv_freq, cosv, sinv, T, half);
     return gg_last_error();
 }
 
@@ -170,6 +178,8 @@ __global__ void qk_norm_rope_cache_kernel(
     const int* __restrict__ page_table, int max_pages, int page_size,
     T* __restrict__ k_pool, T* __restrict__ v_pool,
     int ntok, int nq, int nkv, int d, int rot) {
+    pdl_launch();
+    pdl_wait();
     extern __shared__ float sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nheads = nq + 2 * nkv;
@@ -235,6 +245,8 @@ __global__ void __launch_bounds__(128) qk_norm_rope_cache_vec_kernel(
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int page_size,
     bf16* __restrict__ k_pool, bf16* __restrict__ v_pool, int ntok, int nq, int nkv) {
+    pdl_launch();
+    pdl_wait();
     constexpr int D = 64 * VPL, HALF = D / 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nheads = nq + 2 * nkv;
@@ -318,7 +330,7 @@ GG_API gg_qk_norm_rope_cache(const void* qkv, int dtype, void* q_out, const floa
     const unsigned grid = (unsigned)((total + warps - 1) / warps);
     const bool al = ((((uintptr_t)qkv) | ((uintptr_t)q_out) | ((uintptr_t)k_pool) | ((uintptr_t)v_pool)) & 15) == 0;
     if (dtype == GG_BF16 && rot == d && al && (d == 64 || d == 128 || d == 256)) {
-#define GG_QK_VEC(V) qk_norm_rope_cache_vec_kernel<V><<<grid, warps * 32, 0, stream>>>( \
+#define GG_QK_VEC(V) gg_launch(qk_norm_rope_cache_vec_kernel<V>, dim3(grid), dim3(warps * 32), 0, stream, 1,  \
             (const bf16*)qkv, (bf16*)q_out, qw, kw, eps, cosv, sinv, positions, seq_of_token, page_table, max_pages, \
             page_size, (bf16*)k_pool, (bf16*)v_pool, ntok, nq, nkv)
         if (d == 64) GG_QK_VEC(1); else if (d == 128) GG_QK_VEC(2); else GG_QK_VEC(4);
@@ -327,7 +339,7 @@ GG_API gg_qk_norm_rope_cache(const void* qkv, int dtype, void* q_out, const floa
     }
     const size_t smem = (size_t)warps * d * sizeof(float);
     GG_DISPATCH_DTYPE(dtype, T,
-        qk_norm_rope_cache_kernel<T><<<grid, warps * 32, smem, stream>>>(
+        gg_launch(qk_norm_rope_cache_kernel<T>, dim3(grid), dim3(warps * 32), smem, stream, 1, 
             (const T*)qkv, (T*)q_out, qw, kw, eps, cosv, sinv, positions, seq_of_token, page_table, max_pages,
             page_size, (T*)k_pool, (T*)v_pool, ntok, nq, nkv, d, rot));
     return gg_last_error();
@@ -337,6 +349,8 @@ GG_API gg_qk_norm_rope_cache(const void* qkv, int dtype, void* q_out, const floa
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(z) = z / (1 + exp(-z)) (pkg/ops/ops.go:316-318).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long n, int I) {
+    pdl_launch();
+    pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n) return;
     const long long t = idx / I;
@@ -348,6 +362,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, lon
 
 // Eight elements per thread with 16-byte accesses (rows of I elements, I a multiple of 8).
 __global__ void swiglu_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long long nvec, int I8) {
+    pdl_launch();
+    pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= nvec) return;
     const long long t = idx / I8;
@@ -376,11 +392,11 @@ GG_API gg_swiglu(const void* gu, int dtype, void* out, int ntok, int I, cudaStre
     const long long n = (long long)ntok * I;
     if (dtype == GG_BF16 && I % 8 == 0 && ((((uintptr_t)gu) | ((uintptr_t)out)) & 15) == 0) {
         const long long nvec = n / 8;
-        swiglu_vec8_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>((const bf16*)gu, (bf16*)out, nvec, I / 8);
+        gg_launch(swiglu_vec8_kernel, dim3((unsigned)((nvec + 255) / 256)), dim3(256), 0, stream, 1, (const bf16*)gu, (bf16*)out, nvec, I / 8);
         return gg_last_error();
     }
     GG_DISPATCH_DTYPE(dtype, T,
-        swiglu_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const T*)gu, (T*)out, n, I));
+        gg_launch(swiglu_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, (const T*)gu, (T*)out, n, I));
     return gg_last_error();
 }
 
@@ -389,6 +405,8 @@ GG_API gg_swiglu(const void* gu, int dtype, void* out, int ntok, int I, cudaStre
 // this is the stand-alone form (pkg/gpu/cuda/ptx.go:891-924 add_inplace).
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__ delta, long long n) {
+    pdl_launch();
+    pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx < n) x[idx] += to_f<T>(delta[idx]);
 }
@@ -396,6 +414,6 @@ __global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__
 GG_API gg_residual_add(float* x, const void* delta, int dtype, long long n, cudaStream_t stream) {
     if (n <= 0) return 0;
     GG_DISPATCH_DTYPE(dtype, T,
-        residual_add_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, (const T*)delta, n));
+        gg_launch(residual_add_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, x, (const T*)delta, n));
     return gg_last_error();
 }

@@ -17,6 +17,8 @@ template <typename TX, typename TW, typename TO, bool ACC>
 __global__ void __launch_bounds__(256) gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w,
                                                          TO* __restrict__ out, int M, int N, int K,
                                                          long long ldx, long long ldo) {
+    pdl_launch();
+    pdl_wait();
     __shared__ float xs[BK][BM + 1];
     __shared__ float ws[BK][BN + 1];
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -78,11 +80,11 @@ static int launch(const void* x, const void* w, void* out, int out_dtype, int ac
                   int M, int N, int K, long long ldx, long long ldo, cudaStream_t stream) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (out_dtype == GG_F32) {
-        if (accumulate) gemm_plain_kernel<TX, TW, float, true><<<grid, 256, 0, stream>>>((const TX*)x, (const TW*)w, (float*)out, M, N, K, ldx, ldo);
-        else gemm_plain_kernel<TX, TW, float, false><<<grid, 256, 0, stream>>>((const TX*)x, (const TW*)w, (float*)out, M, N, K, ldx, ldo);
+        if (accumulate) gg_launch(gemm_plain_kernel<TX, TW, float, true>, dim3(grid), dim3(256), 0, stream, 1, (const TX*)x, (const TW*)w, (float*)out, M, N, K, ldx, ldo);
+        else gg_launch(gemm_plain_kernel<TX, TW, float, false>, dim3(grid), dim3(256), 0, stream, 1, (const TX*)x, (const TW*)w, (float*)out, M, N, K, ldx, ldo);
     } else if (out_dtype == GG_BF16) {
         if (accumulate) return GG_ERR_DTYPE;  // sums are kept in float32
-        gemm_plain_kernel<TX, TW, bf16, false><<<grid, 256, 0, stream>>>((const TX*)x, (const TW*)w, (bf16*)out, M, N, K, ldx, ldo);
+        gg_launch(gemm_plain_kernel<TX, TW, bf16, false>, dim3(grid), dim3(256), 0, stream, 1, (const TX*)x, (const TW*)w, (bf16*)out, M, N, K, ldx, ldo);
     } else {
         return GG_ERR_DTYPE;
     }

@@ -154,6 +154,7 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     uint32_t* tmem_slot = (uint32_t*)(accum + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
+    pdl_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
     const int num_kb = (K + BK - 1) / BK;
@@ -180,7 +181,22 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < nkb; ++i) {
+            // The weights are written by no kernel: their first tiles stream in while the kernel before
+            // this one is still finishing.  The activations are that kernel's output and wait for it.
+            const int pre = nkb < STAGES ? nkb : STAGES;
+            for (int i = 0; i < pre; ++i) {
+                mbar_expect_tx(&full[i], STAGE_BYTES);
+                uint8_t* sa = smem + i * STAGE_BYTES;
+                if (SWAP) tma_load_2d(sa, &tmA, &full[i], (kb0 + i) * BK, tile_a * BM);
+                else tma_load_2d(sa + A_BYTES, &tmB, &full[i], (kb0 + i) * BK, tile_b * BN);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                uint8_t* sa = smem + i * STAGE_BYTES;
+                if (SWAP) tma_load_2d(sa + A_BYTES, &tmB, &full[i], (kb0 + i) * BK, tile_b * BN);
+                else tma_load_2d(sa, &tmA, &full[i], (kb0 + i) * BK, tile_a * BM);
+            }
+            for (int i = pre; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
                 if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, 1)) break;
@@ -216,6 +232,7 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
         // epilogue: warp w reads tensor-memory lanes 32*(w%4) .. +31 (row i of D is lane i)
         const int q = warp & 3;
         const int row = q * 32 + lane;           // row of the D tile held by this thread
+        pdl_wait();                              // the output may still be in use by earlier kernels
         mbar_wait(accum, 0, abort_flag, status, 3);
         if (!*abort_flag) {
             tc_fence_after();
@@ -352,6 +369,8 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
 // out[m, n] = epilogue( sum over splits of partial[s, m, n] ), splits added in index order.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, int out_mode,
                                      long long ldo, int M, int N, int splits) {
+    pdl_launch();
+    pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long total = (long long)M * N;
     if (idx >= total) return;
@@ -410,25 +429,8 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode
     dim3 grid((RA + BM - 1) / BM, (RB + BN - 1) / BN, splits);
     float* part = (splits > 1 && !cluster) ? partial : nullptr;
     const int cl = (splits > 1 && cluster) ? 1 : 0;
-    if (!cl) {
-        kern<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, out, out_mode, ldo, M, N, K, kb_per_split, part, 0, status);
-        return gg_last_error();
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = splits;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, out, out_mode, ldo, M, N, K, kb_per_split, part, 1, status);
-    if (e != cudaSuccess) return (int)e;
-    return gg_last_error();
+    return gg_launch(kern, grid, dim3(NUM_THREADS), smem, stream, cl ? splits : 1, ta, tb, out, out_mode, ldo, M, N, K,
+                     kb_per_split, part, cl, status);
 }
 
 }  // namespace
@@ -491,8 +493,8 @@ GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, 
     if (rc != 0) return rc;
     if (splits > 1 && !cluster) {
         const long long total = (long long)M * N;
-        splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(scratch, out, out_mode, ldo, M, N, splits);
-        return gg_last_error();
+        return gg_launch(splitk_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, 1,
+                         (const float*)scratch, out, out_mode, ldo, M, N, splits);
     }
     return 0;
 }

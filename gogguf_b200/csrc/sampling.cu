@@ -65,6 +65,8 @@ __device__ __forceinline__ double block_sum_f64(double v, double* red) {
 
 __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __restrict__ logits, long long ld,
                                                                int* __restrict__ out, int V) {
+    pdl_launch();
+    pdl_wait();
     __shared__ MaxIdx red[33];
     const float* x = logits + (size_t)blockIdx.x * ld;
     MaxIdx best{-INFINITY, 0x7fffffff};
@@ -80,6 +82,8 @@ __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __res
 // launch picks among them (ties still go to the smallest index).
 __global__ void __launch_bounds__(SAMP_THREADS) argmax_partial_kernel(const float* __restrict__ logits, long long ld,
                                                                        MaxIdx* __restrict__ part, int V, int chunks) {
+    pdl_launch();
+    pdl_wait();
     __shared__ MaxIdx red[33];
     const int r = blockIdx.x, c = blockIdx.y;
     const float* x = logits + (size_t)r * ld;
@@ -95,6 +99,8 @@ __global__ void __launch_bounds__(SAMP_THREADS) argmax_partial_kernel(const floa
 }
 
 __global__ void argmax_final_kernel(const MaxIdx* __restrict__ part, int* __restrict__ out, int chunks) {
+    pdl_launch();
+    pdl_wait();
     const int r = blockIdx.x;
     MaxIdx best{-INFINITY, 0x7fffffff};
     for (int c = threadIdx.x; c < chunks; c += 32) best = better(best, part[(size_t)r * chunks + c]);
@@ -121,12 +127,12 @@ GG_API gg_argmax(const float* logits, long long ld, int* out, int R, int V, void
         if ((long long)R * chunks * 2 > scratch_words) chunks = 1;
     }
     if (chunks <= 1) {
-        argmax_kernel<<<R, SAMP_THREADS, 0, stream>>>(logits, ld, out, V);
+        gg_launch(argmax_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, 1, logits, ld, out, V);
         return gg_last_error();
     }
     dim3 grid(R, chunks);
-    argmax_partial_kernel<<<grid, SAMP_THREADS, 0, stream>>>(logits, ld, (MaxIdx*)scratch, V, chunks);
-    argmax_final_kernel<<<R, 32, 0, stream>>>((const MaxIdx*)scratch, out, chunks);
+    gg_launch(argmax_partial_kernel, dim3(grid), dim3(SAMP_THREADS), 0, stream, 1, logits, ld, (MaxIdx*)scratch, V, chunks);
+    gg_launch(argmax_final_kernel, dim3(R), dim3(32), 0, stream, 1, (const MaxIdx*)scratch, out, chunks);
     return gg_last_error();
 }
 
@@ -135,6 +141,8 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(const float* __res
                                                                const float* __restrict__ temps,
                                                                const double* __restrict__ uniforms,
                                                                int* __restrict__ out, int V) {
+    pdl_launch();
+    pdl_wait();
     __shared__ MaxIdx red[33];
     __shared__ double dred[33];
     __shared__ double pre[SAMP_THREADS];
@@ -195,6 +203,6 @@ GG_API gg_sample(const float* logits, long long ld, const float* temps, const do
                  int R, int V, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0 || ld < V) return GG_ERR_ARG;
-    sample_kernel<<<R, SAMP_THREADS, 0, stream>>>(logits, ld, temps, uniforms, out, V);
+    gg_launch(sample_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, 1, logits, ld, temps, uniforms, out, V);
     return gg_last_error();
 }
