@@ -443,7 +443,7 @@ GG_API gg_gemm_tc_splits(int M, int N, int K, int use_cluster) {
     if (M > 128) return 1;
     const int num_kb = (K + BK - 1) / BK;
     const int tiles = (N + BM - 1) / BM;
-    const int per_sm = M <= 16 ? 3 : 2;          // CTAs that share an SM in the decode forms
+    const int per_sm = 3;                        // CTAs that share an SM in the decode forms
     int splits = (148 * per_sm + tiles / 2) / tiles;
     if (splits > num_kb / 2) splits = num_kb / 2;  // at least two 64-wide slabs per CTA
     const int most = use_cluster ? MAX_CLUSTER : 16;
@@ -480,9 +480,9 @@ GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, 
         if ((rc = make_map(&ta, w, N, K, K, BM)) != 0) return rc;
         if ((rc = make_map(&tb, x, M, K, ldx, bn)) != 0) return rc;
         if (bn == 16) rc = launch<16, 4, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
-        else if (bn == 32) rc = launch<32, 4, true, 2>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
-        else if (bn == 64) rc = launch<64, 4, true, 2>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
-        else rc = launch<128, 3, true, 2>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
+        else if (bn == 32) rc = launch<32, 3, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
+        else if (bn == 64) rc = launch<64, 3, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
+        else rc = launch<128, 2, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
     } else {
         const int bn = N > 128 ? 256 : 128;
         if ((rc = make_map(&ta, x, M, K, ldx, BM)) != 0) return rc;
