@@ -766,7 +766,8 @@ GG_API gg_attn_prefill(const void* q, const void* k_pool, const void* v_pool, vo
 GG_API gg_attn_decode_tma_splits(int ntok, int nkv, int max_ctx, int use_cluster) {
     if (ntok <= 0 || nkv <= 0) return 1;
     const long long pairs = (long long)ntok * nkv;
-    int splits = use_cluster ? (int)((592 + pairs / 2) / pairs) : (int)((4 * 296 + pairs - 1) / pairs);
+    // cluster form: one wave of CTAs (two share an SM: 296 places); scratch form: about four waves
+    int splits = use_cluster ? (int)(296 / pairs) : (int)((4 * 296 + pairs - 1) / pairs);
     const int pages = (max_ctx + PAGE - 1) / PAGE;
     if (splits > pages / 2) splits = pages / 2;       // at least two pages per CTA
     const int most = use_cluster ? 8 : 64;

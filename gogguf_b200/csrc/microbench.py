@@ -1,0 +1,85 @@
+"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|attn] [--m 1,8,64]
+
+Times single kernels the way a decode step runs them: forty launches captured in a CUDA graph and
+replayed, so that host launch cost is out of the picture and dependent launches overlap as they do
+in a step.  Weights rotate over more than 400 MB so that the 126 MB L2 cannot serve them.  Prints
+one line per (shape, M) with microseconds per launch and the achieved weight or cache bandwidth.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+
+import torch
+
+SHAPES = {"qkv": (6144, 4096), "o": (4096, 4096), "gateup": (24576, 4096), "down": (4096, 12288),
+          "head": (151936, 4096)}
+
+
+def _time_graph(fn, reps: int = 40) -> float:
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(reps):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps * 1e3
+
+
+def gemm(ms) -> None:
+    from . import tcgen05_gemm as tc
+    dev = "cuda:0"
+    for name, (N, K) in SHAPES.items():
+        nbuf = max(2, int(400e6 // (N * K * 2)) + 1)
+        ws = [torch.randn(N, K, device=dev).to(torch.bfloat16) for _ in range(nbuf)]
+        for M in ms:
+            x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+            out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            us = _time_graph(lambda i: tc.gemm_tc(x, ws[i % nbuf], out, cluster=True))
+            print(f"gemm {name:7s} M={M:4d} splits={tc.splits_for(M, N, K, True):2d} {us:8.1f} us "
+                  f"{N * K * 2 / us / 1e6:6.2f} TB/s", flush=True)
+        del ws
+        torch.cuda.empty_cache()
+
+
+def attn(ms, ctx_len: int = 2048, nq: int = 32, nkv: int = 8, d: int = 128) -> None:
+    from . import fast_attention as fa
+    dev = "cuda:0"
+    for B in ms:
+        pages_per = (ctx_len + 63) // 64
+        layers = max(2, int(400e6 // (B * pages_per * nkv * 64 * d * 2 * 2)) + 1)     # rotate over layers' pools
+        kp = [torch.randn(B * pages_per, nkv, 64, d, device=dev).to(torch.bfloat16) for _ in range(layers)]
+        vp = [torch.randn(B * pages_per, nkv, 64, d, device=dev).to(torch.bfloat16) for _ in range(layers)]
+        table = torch.arange(B * pages_per, dtype=torch.int32, device=dev).view(B, pages_per)
+        pos = torch.full((B,), ctx_len - 1, dtype=torch.int32, device=dev)
+        sot = torch.arange(B, dtype=torch.int32, device=dev)
+        q = torch.randn(B, nq, d, device=dev).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        splits = fa.decode_tma_splits(B, nkv, ctx_len, cluster=True)
+        us = _time_graph(lambda i: fa.attn_decode_tma(q, kp[i % layers], vp[i % layers], out, pos, sot, table, 64, B,
+                                                      nq, nkv, d, 1.0 / math.sqrt(d), 0, splits, cluster=True))
+        nbytes = B * ctx_len * nkv * d * 2 * 2
+        print(f"attn decode B={B:4d} ctx={ctx_len} splits={splits} {us:8.1f} us {nbytes / us / 1e6:6.2f} TB/s", flush=True)
+        del kp, vp
+        torch.cuda.empty_cache()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn"])
+    ap.add_argument("--m", default="1,8,64", help="token counts (gemm) or batch sizes (attn)")
+    a = ap.parse_args()
+    ms = [int(x) for x in a.m.split(",")]
+    (gemm if a.what == "gemm" else attn)(ms)
+
+
+if __name__ == "__main__":
+    main()
