@@ -51,6 +51,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -413,6 +416,211 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long long ld, i
     return r == CUDA_SUCCESS ? 0 : GG_ERR_TMAP;
 }
 
+// ------------------------------------------------------------------------------------------- prefill form, persistent
+// One CTA per SM walks over output tiles of 128 x 256 (token rows fastest, so the CTAs that run
+// together share weight tiles in L2).  The shared-memory ring runs on across tile boundaries, and the
+// accumulator is double buffered in tensor memory (2 x 256 columns): while the four epilogue warps
+// drain tile i, the MMA thread already accumulates tile i + 1.
+template <int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_persistent_kernel(
+    const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+    void* __restrict__ out, int out_mode, long long ldo, int M, int N, int K, int* __restrict__ status) {
+    constexpr int BN = 256;
+    constexpr int B_BYTES = BN * BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;       // [2]
+    uint64_t* acc_empty = acc_full + 2;        // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    pdl_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (K + BK - 1) / BK;
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const int total = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool first = true, ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                const int tm = t % tiles_m, tn = t / tiles_m;
+                int kb = 0;
+                if (first) {
+                    // weights of the first tile before the dependency wait (see the decode form)
+                    const int pre = num_kb < STAGES ? num_kb : STAGES;
+                    for (int i = 0; i < pre; ++i) {
+                        mbar_expect_tx(&full[i], STAGE_BYTES);
+                        tma_load_2d(smem + i * STAGE_BYTES + A_BYTES, &tmB, &full[i], i * BK, tn * BN);
+                    }
+                    pdl_wait();
+                    for (int i = 0; i < pre; ++i) tma_load_2d(smem + i * STAGE_BYTES, &tmA, &full[i], i * BK, tm * BM);
+                    kb = pre;
+                    it = pre;
+                    first = false;
+                }
+                for (; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                    if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, 1)) { ok = false; break; }
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    uint8_t* sa = smem + s * STAGE_BYTES;
+                    tma_load_2d(sa, &tmA, &full[s], kb * BK, tm * BM);
+                    tma_load_2d(sa + A_BYTES, &tmB, &full[s], kb * BK, tn * BN);
+                }
+            }
+            if (first) pdl_wait();
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(BM, BN);
+            int it = 0, i = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++i) {
+                const int buf = i & 1;
+                const uint32_t aph = (uint32_t)(i >> 1) & 1u;
+                ok = mbar_wait(&acc_empty[buf], aph ^ 1u, abort_flag, status, 4);     // the epilogue has drained it
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t tacc = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                    ok = mbar_wait(&full[s], ph, abort_flag, status, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t adesc = make_smem_desc(sa);
+                    const uint64_t bdesc = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma(tacc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);
+                }
+                if (ok) umma_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        pdl_wait();
+        int i = 0;
+        for (int t = blockIdx.x; t < total; t += gridDim.x, ++i) {
+            const int tm = t % tiles_m, tn = t / tiles_m;
+            const int buf = i & 1;
+            const uint32_t aph = (uint32_t)(i >> 1) & 1u;
+            if (!mbar_wait(&acc_full[buf], aph, abort_flag, status, 3)) break;
+            tc_fence_after();
+            const int gi = tm * BM + row;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (tn * BN + c0 >= N) break;
+                uint32_t r[16];
+                tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+                tmem_ld_wait();
+                if (gi >= M) continue;
+                const int gj0 = tn * BN + c0;
+                const size_t o = (size_t)gi * ldo + gj0;
+                const bool whole = gj0 + 16 <= N;
+                if (out_mode == OUT_BF16) {
+                    bf16* op = (bf16*)out + o;
+                    if (whole && ((((uintptr_t)op) & 15) == 0)) {
+                        uint32_t pk[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                            pk[j] = *reinterpret_cast<uint32_t*>(&h2);
+                        }
+                        reinterpret_cast<uint4*>(op)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        reinterpret_cast<uint4*>(op)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (gj0 + j < N) op[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    }
+                } else {
+                    float* op = (float*)out + o;
+                    if (whole && ((((uintptr_t)op) & 15) == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                            float4* dst = reinterpret_cast<float4*>(op) + j;
+                            if (out_mode == OUT_F32_ACC) {
+                                const float4 old = *dst;
+                                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                            }
+                            *dst = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (gj0 + j < N) {
+                                if (out_mode == OUT_F32_ACC) op[j] += __uint_as_float(r[j]);
+                                else op[j] = __uint_as_float(r[j]);
+                            }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&acc_empty[buf]);        // 128 arrivals free the accumulator for tile i + 2
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+int launch_persistent(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N,
+                      int K, int* status, cudaStream_t stream) {
+    constexpr int STAGES = 4;
+    constexpr int smem = STAGES * (A_BYTES + 256 * BK * 2) + 1024 + 256;
+    static int sms = 0;
+    auto kern = gemm_tc_persistent_kernel<STAGES>;
+    if (sms == 0) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0, n = 0;
+        if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        sms = n > 0 ? n : 148;
+    }
+    const int total = ((M + BM - 1) / BM) * ((N + 255) / 256);
+    const int grid = total < sms ? total : sms;
+    return gg_launch(kern, dim3(grid), dim3(NUM_THREADS), smem, stream, 1, ta, tb, out, out_mode, ldo, M, N, K, status);
+}
+
 template <int BN, int STAGES, bool SWAP, int MINB>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N, int K,
            int splits, int kb_per_split, float* partial, bool cluster, int* status, cudaStream_t stream) {
@@ -487,7 +695,7 @@ GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, 
         const int bn = N > 128 ? 256 : 128;
         if ((rc = make_map(&ta, x, M, K, ldx, BM)) != 0) return rc;
         if ((rc = make_map(&tb, w, N, K, K, bn)) != 0) return rc;
-        if (bn == 256) rc = launch<256, 4, false, 1>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, false, status, stream);
+        if (bn == 256) rc = launch_persistent(ta, tb, out, out_mode, ldo, M, N, K, status, stream);
         else rc = launch<128, 6, false, 1>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, false, status, stream);
     }
     if (rc != 0) return rc;
