@@ -122,3 +122,31 @@ static inline int gg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();
 }
+
+// As gg_launch, with clusters of (2, 1, 1): pairs of CTAs with consecutive blockIdx.x.
+template <typename... KArgs, typename... Args>
+static inline int gg_launch2(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (gg_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 2;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) return (int)e;
+    return (int)cudaGetLastError();
+}

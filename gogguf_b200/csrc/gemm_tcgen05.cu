@@ -621,6 +621,250 @@ int launch_persistent(const CUtensorMap& ta, const CUtensorMap& tb, void* out, i
     return gg_launch(kern, dim3(grid), dim3(NUM_THREADS), smem, stream, 1, ta, tb, out, out_mode, ldo, M, N, K, status);
 }
 
+// ------------------------------------------------------------------------------------------- prefill form, CTA pairs
+// Two CTAs of a cluster work on one 256 x 256 output tile with tcgen05.mma.cta_group::2: each CTA
+// stages its own 128 rows of A and its own 128 of the 256 B rows, the leader CTA issues the MMAs
+// for both, and each CTA ends up with its 128 rows of the tile in its own tensor memory.  Per CTA
+// and 64-wide K slab that is 32 KB of operands for 128 x 256 x 64 multiply-adds instead of 48 KB,
+// so six stages fit in shared memory and cover the L2 latency that four 48 KB stages do not
+// (the single-CTA form leaves the tensor pipe idle 22 % of the time).  Persistent over tiles, with
+// the accumulator double buffered as in gemm_tc_persistent_kernel.
+//
+// Barriers live at the same shared-memory offsets in both CTAs.  full[s]: in the leader; it expects
+// the bytes of both CTAs' copies (the peer's TMA signals the leader's barrier).  empty[s] and
+// acc_full[b]: in both; the leader's tcgen05.commit arrives on both at once.  acc_empty[b]: in the
+// leader; the 128 epilogue threads of each CTA arrive on it, the peer's through the cluster.
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;
+
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar) & PEER_BIT_MASK), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(rank));
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
+    const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+    void* __restrict__ out, int out_mode, long long ldo, int M, int N, int K, int* __restrict__ status) {
+    constexpr int BN = 256;                     // columns of the pair's tile (each CTA stages 128 of the B rows)
+    constexpr int HALF_B_BYTES = 128 * BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + HALF_B_BYTES;      // per CTA: 32 KB
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    pdl_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int num_kb = (K + BK - 1) / BK;
+    const int tiles_m = (M + 255) / 256, tiles_n = (N + BN - 1) / BN;
+    const int total = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 256); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the peer's barriers exist before anything is signalled across the pair
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool first = true, ok = true;
+            for (int t = pair; t < total && ok; t += num_pairs) {
+                const int tm = t % tiles_m, tn = t / tiles_m;
+                const int arow = tm * 256 + (int)rank * 128, brow = tn * BN + (int)rank * 128;
+                int kb = 0;
+                if (first) {
+                    const int pre = num_kb < STAGES ? num_kb : STAGES;
+                    for (int i = 0; i < pre; ++i) {
+                        if (leader) mbar_expect_tx(&full[i], 2 * STAGE_BYTES);
+                        tma_load_2d_pair(smem + i * STAGE_BYTES + A_BYTES, &tmB, &full[i], i * BK, brow);
+                    }
+                    pdl_wait();
+                    for (int i = 0; i < pre; ++i) tma_load_2d_pair(smem + i * STAGE_BYTES, &tmA, &full[i], i * BK, arow);
+                    kb = pre;
+                    it = pre;
+                    first = false;
+                }
+                for (; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                    if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, 1)) { ok = false; break; }
+                    if (leader) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+                    uint8_t* sa = smem + s * STAGE_BYTES;
+                    tma_load_2d_pair(sa, &tmA, &full[s], kb * BK, arow);
+                    tma_load_2d_pair(sa + A_BYTES, &tmB, &full[s], kb * BK, brow);
+                }
+            }
+            if (first) pdl_wait();
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            const uint32_t idesc = make_idesc(256, BN);
+            int it = 0, i = 0;
+            bool ok = true;
+            for (int t = pair; t < total && ok; t += num_pairs, ++i) {
+                const int buf = i & 1;
+                const uint32_t aph = (uint32_t)(i >> 1) & 1u;
+                ok = mbar_wait(&acc_empty[buf], aph ^ 1u, abort_flag, status, 4);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t tacc = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                    ok = mbar_wait(&full[s], ph, abort_flag, status, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t adesc = make_smem_desc(sa);
+                    const uint64_t bdesc = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_pair(tacc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(&empty[s]);
+                }
+                if (ok) umma_commit_pair(&acc_full[buf]);
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        pdl_wait();
+        int i = 0;
+        for (int t = pair; t < total; t += num_pairs, ++i) {
+            const int tm = t % tiles_m, tn = t / tiles_m;
+            const int buf = i & 1;
+            const uint32_t aph = (uint32_t)(i >> 1) & 1u;
+            if (!mbar_wait(&acc_full[buf], aph, abort_flag, status, 3)) break;
+            tc_fence_after();
+            const int gi = tm * 256 + (int)rank * 128 + row;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (tn * BN + c0 >= N) break;
+                uint32_t r[16];
+                tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+                tmem_ld_wait();
+                if (gi >= M) continue;
+                const int gj0 = tn * BN + c0;
+                const size_t o = (size_t)gi * ldo + gj0;
+                const bool whole = gj0 + 16 <= N;
+                if (out_mode == OUT_BF16) {
+                    bf16* op = (bf16*)out + o;
+                    if (whole && ((((uintptr_t)op) & 15) == 0)) {
+                        uint32_t pk[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                            pk[j] = *reinterpret_cast<uint32_t*>(&h2);
+                        }
+                        reinterpret_cast<uint4*>(op)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        reinterpret_cast<uint4*>(op)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (gj0 + j < N) op[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    }
+                } else {
+                    float* op = (float*)out + o;
+                    if (whole && ((((uintptr_t)op) & 15) == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                            float4* dst = reinterpret_cast<float4*>(op) + j;
+                            if (out_mode == OUT_F32_ACC) {
+                                const float4 old = *dst;
+                                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                            }
+                            *dst = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (gj0 + j < N) {
+                                if (out_mode == OUT_F32_ACC) op[j] += __uint_as_float(r[j]);
+                                else op[j] = __uint_as_float(r[j]);
+                            }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive_cluster(&acc_empty[buf], 0);     // 256 arrivals in the leader free the accumulator pair
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+        __syncthreads();
+    }
+    cluster_sync_all();          // neither CTA leaves while the other may still signal its barriers
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N,
+                int K, int* status, cudaStream_t stream) {
+    constexpr int STAGES = 6;
+    constexpr int smem = STAGES * (A_BYTES + 128 * BK * 2) + 1024 + 256;
+    static int sms = 0;
+    auto kern = gemm_tc_pair_kernel<STAGES>;
+    if (sms == 0) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0, n = 0;
+        if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        sms = n > 0 ? n : 148;
+    }
+    const int total = ((M + 255) / 256) * ((N + 255) / 256);
+    int pairs = sms / 2;
+    if (pairs > total) pairs = total;
+    return gg_launch2(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, stream, ta, tb, out, out_mode, ldo, M, N, K, status);
+}
+
 template <int BN, int STAGES, bool SWAP, int MINB>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N, int K,
            int splits, int kb_per_split, float* partial, bool cluster, int* status, cudaStream_t stream) {
@@ -695,7 +939,13 @@ GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, 
         const int bn = N > 128 ? 256 : 128;
         if ((rc = make_map(&ta, x, M, K, ldx, BM)) != 0) return rc;
         if ((rc = make_map(&tb, w, N, K, K, bn)) != 0) return rc;
-        if (bn == 256) rc = launch_persistent(ta, tb, out, out_mode, ldo, M, N, K, status, stream);
+        static int use_pair = -1;
+        if (use_pair < 0) { const char* e = getenv("GOGGUF_B200_GEMM_PAIR"); use_pair = (e != nullptr && e[0] == '0') ? 0 : 1; }
+        if (bn == 256 && use_pair) {
+            // CTA pairs: A tiles of 128 rows per CTA as before, B staged in halves of 128 rows per CTA
+            if ((rc = make_map(&tb, w, N, K, K, 128)) != 0) return rc;
+            rc = launch_pair(ta, tb, out, out_mode, ldo, M, N, K, status, stream);
+        } else if (bn == 256) rc = launch_persistent(ta, tb, out, out_mode, ldo, M, N, K, status, stream);
         else rc = launch<128, 6, false, 1>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, false, status, stream);
     }
     if (rc != 0) return rc;
