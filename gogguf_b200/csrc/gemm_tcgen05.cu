@@ -41,7 +41,7 @@ constexpr int A_BYTES = BM * BK * 2;
 constexpr int NUM_THREADS = 192;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // about one second
 
-enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2 };
+enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_SWIGLU = 3 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -124,6 +124,103 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+
+// Epilogue of the normal orientation for one thread: its row `gi` of the output, the 256 accumulator
+// columns of tile column `tn` starting at tensor-memory address `taddr` (lane already selected).
+// OUT_SWIGLU: the weight rows were interleaved in blocks of 64 gate rows and 64 up rows, so columns
+// [0,64) and [128,192) of the tile are gates and the 64 columns after each are their ups; the output
+// row has N / 2 columns.
+__device__ __forceinline__ void epilogue_row_256(uint32_t taddr, int gi, int tn, int M, int N, void* __restrict__ out,
+                                                 int out_mode, long long ldo) {
+    constexpr int BN = 256;
+    if (out_mode == OUT_SWIGLU) {
+#pragma unroll 1
+        for (int cb = 0; cb < 2; ++cb) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+                const int gcol = tn * BN + cb * 128 + c0;          // gate column in the interleaved product
+                if (gcol >= N) return;
+                uint32_t g[16], u[16];
+                tmem_ld16(taddr + (uint32_t)(cb * 128 + c0), g);
+                tmem_ld16(taddr + (uint32_t)(cb * 128 + 64 + c0), u);
+                tmem_ld_wait();
+                if (gi >= M) continue;
+                const int ocol = (tn * 2 + cb) * 64 + c0;          // feature index
+                bf16* op = (bf16*)out + (size_t)gi * ldo + ocol;
+                const int nout = N / 2;
+                if (ocol + 16 <= nout && ((((uintptr_t)op) & 15) == 0)) {
+                    uint32_t pk[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(
+                            silu_mul(__uint_as_float(g[2 * j]), __uint_as_float(u[2 * j])),
+                            silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(u[2 * j + 1])));
+                        pk[j] = *reinterpret_cast<uint32_t*>(&h2);
+                    }
+                    reinterpret_cast<uint4*>(op)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    reinterpret_cast<uint4*>(op)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (ocol + j < nout) op[j] = __float2bfloat16_rn(silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j])));
+                }
+            }
+        }
+        return;
+    }
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (tn * BN + c0 >= N) break;
+        uint32_t r[16];
+        tmem_ld16(taddr + (uint32_t)c0, r);
+        tmem_ld_wait();
+        if (gi >= M) continue;
+        const int gj0 = tn * BN + c0;
+        const size_t o = (size_t)gi * ldo + gj0;
+        const bool whole = gj0 + 16 <= N;
+        if (out_mode == OUT_BF16) {
+            bf16* op = (bf16*)out + o;
+            if (whole && ((((uintptr_t)op) & 15) == 0)) {
+                uint32_t pk[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                    pk[j] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                reinterpret_cast<uint4*>(op)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                reinterpret_cast<uint4*>(op)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (gj0 + j < N) op[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+        } else {
+            float* op = (float*)out + o;
+            if (whole && ((((uintptr_t)op) & 15) == 0)) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                           __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                    float4* dst = reinterpret_cast<float4*>(op) + j;
+                    if (out_mode == OUT_F32_ACC) {
+                        const float4 old = *dst;
+                        v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                    }
+                    *dst = v;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (gj0 + j < N) {
+                        if (out_mode == OUT_F32_ACC) op[j] += __uint_as_float(r[j]);
+                        else op[j] = __uint_as_float(r[j]);
+                    }
+            }
+        }
+    }
+}
 
 template <int BN> constexpr int tmem_cols() { return BN < 32 ? 32 : BN; }
 
@@ -247,7 +344,7 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                 uint32_t r[16];
                 tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
                 tmem_ld_wait();
-                if (cluster_reduce) {
+                if (cluster_reduce || out_mode == OUT_SWIGLU) {
                     // own partial sums to own shared memory, [column][row]: the pipeline stages are free now
                     float* stage = reinterpret_cast<float*>(smem);
 #pragma unroll
@@ -329,10 +426,31 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
 
     tc_fence_before();
     __syncthreads();
-    if (cluster_reduce) {
+    if (cluster_reduce || out_mode == OUT_SWIGLU) {
         // Every CTA of the cluster passes both barriers exactly once, whatever happened before.
-        cluster_sync_all();
-        if (!*abort_flag) {
+        if (cluster_reduce) cluster_sync_all();
+        if (!*abort_flag && out_mode == OUT_SWIGLU) {
+            // gate rows 0..63 and up rows 64..127 of this tile give 64 output features (decode form only)
+            const int S = cluster_reduce ? (int)gridDim.z : 1;
+            const int RB = M;
+            const int cols = min(BN, RB - tile_b * BN);
+            const int E = cols * 64;
+            const uint32_t stage = smem_u32(smem);
+            const int nout = N / 2;
+            for (int e = split * NUM_THREADS + threadIdx.x; e < E; e += S * NUM_THREADS) {
+                const int j = e >> 6, i = e & 63;
+                float g = 0.f, u = 0.f;
+#pragma unroll
+                for (int qq = 0; qq < MAX_CLUSTER; ++qq) {
+                    if (qq < S) {
+                        g += ld_cluster_f32(stage + 4u * (j * BM + i), qq);
+                        u += ld_cluster_f32(stage + 4u * (j * BM + 64 + i), qq);
+                    }
+                }
+                const int feat = tile_a * 64 + i, gj = tile_b * BN + j;
+                if (feat < nout) ((bf16*)out)[(size_t)gj * ldo + feat] = __float2bfloat16_rn(silu_mul(g, u));
+            }
+        } else if (!*abort_flag) {
             const int S = gridDim.z;
             const int RA = SWAP ? N : M, RB = SWAP ? M : N;
             const int cols = min(BN, RB - tile_b * BN);
@@ -355,7 +473,7 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                 }
             }
         }
-        cluster_sync_all();     // nobody leaves while its shared memory may still be read
+        if (cluster_reduce) cluster_sync_all();     // nobody leaves while its shared memory may still be read
     }
     if (*abort_flag) {
         // a wait ran out: give copies and instructions in flight time to land before the memory goes away
@@ -534,56 +652,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_persistent_kernel(
             if (!mbar_wait(&acc_full[buf], aph, abort_flag, status, 3)) break;
             tc_fence_after();
             const int gi = tm * BM + row;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (tn * BN + c0 >= N) break;
-                uint32_t r[16];
-                tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0), r);
-                tmem_ld_wait();
-                if (gi >= M) continue;
-                const int gj0 = tn * BN + c0;
-                const size_t o = (size_t)gi * ldo + gj0;
-                const bool whole = gj0 + 16 <= N;
-                if (out_mode == OUT_BF16) {
-                    bf16* op = (bf16*)out + o;
-                    if (whole && ((((uintptr_t)op) & 15) == 0)) {
-                        uint32_t pk[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                            pk[j] = *reinterpret_cast<uint32_t*>(&h2);
-                        }
-                        reinterpret_cast<uint4*>(op)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                        reinterpret_cast<uint4*>(op)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (gj0 + j < N) op[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-                    }
-                } else {
-                    float* op = (float*)out + o;
-                    if (whole && ((((uintptr_t)op) & 15) == 0)) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                            float4* dst = reinterpret_cast<float4*>(op) + j;
-                            if (out_mode == OUT_F32_ACC) {
-                                const float4 old = *dst;
-                                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
-                            }
-                            *dst = v;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (gj0 + j < N) {
-                                if (out_mode == OUT_F32_ACC) op[j] += __uint_as_float(r[j]);
-                                else op[j] = __uint_as_float(r[j]);
-                            }
-                    }
-                }
-            }
+            epilogue_row_256(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN), gi, tn, M, N, out, out_mode, ldo);
             tc_fence_before();
             mbar_arrive(&acc_empty[buf]);        // 128 arrivals free the accumulator for tile i + 2
         }
@@ -776,56 +845,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
             if (!mbar_wait(&acc_full[buf], aph, abort_flag, status, 3)) break;
             tc_fence_after();
             const int gi = tm * 256 + (int)rank * 128 + row;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (tn * BN + c0 >= N) break;
-                uint32_t r[16];
-                tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0), r);
-                tmem_ld_wait();
-                if (gi >= M) continue;
-                const int gj0 = tn * BN + c0;
-                const size_t o = (size_t)gi * ldo + gj0;
-                const bool whole = gj0 + 16 <= N;
-                if (out_mode == OUT_BF16) {
-                    bf16* op = (bf16*)out + o;
-                    if (whole && ((((uintptr_t)op) & 15) == 0)) {
-                        uint32_t pk[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                            pk[j] = *reinterpret_cast<uint32_t*>(&h2);
-                        }
-                        reinterpret_cast<uint4*>(op)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                        reinterpret_cast<uint4*>(op)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (gj0 + j < N) op[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-                    }
-                } else {
-                    float* op = (float*)out + o;
-                    if (whole && ((((uintptr_t)op) & 15) == 0)) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                            float4* dst = reinterpret_cast<float4*>(op) + j;
-                            if (out_mode == OUT_F32_ACC) {
-                                const float4 old = *dst;
-                                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
-                            }
-                            *dst = v;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (gj0 + j < N) {
-                                if (out_mode == OUT_F32_ACC) op[j] += __uint_as_float(r[j]);
-                                else op[j] = __uint_as_float(r[j]);
-                            }
-                    }
-                }
-            }
+            epilogue_row_256(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN), gi, tn, M, N, out, out_mode, ldo);
             tc_fence_before();
             mbar_arrive_cluster(&acc_empty[buf], 0);     // 256 arrivals in the leader free the accumulator pair
         }
@@ -908,7 +928,7 @@ GG_API gg_gemm_tc_splits(int M, int N, int K, int use_cluster) {
 }
 
 // out[M, N] (mode) = x[M, K] (bf16, row stride ldx) * w[N, K]^T (bf16, contiguous).
-// out_mode: 0 bf16 store, 1 float32 store, 2 float32 add (residual).
+// out_mode: 0 bf16 store, 1 float32 store, 2 float32 add (residual), 3 fused SwiGLU (see below).
 // use_cluster != 0: K splits are reduced inside thread-block clusters; scratch is not touched.
 // use_cluster == 0: scratch must hold gg_gemm_tc_splits(M, N, K, 0) * M * N floats when that count is > 1.
 // status: one int on the device, zero-initialised by the caller; a non-zero value after the kernel
@@ -917,10 +937,13 @@ GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, 
                   long long ldo, float* scratch, long long scratch_elems, int use_cluster, int* status,
                   cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || (K % 8) != 0 || (ldx % 8) != 0 || ldx < K || ldo < N) return GG_ERR_ARG;
-    if ((((uintptr_t)x) & 15) || (((uintptr_t)w) & 15) || out_mode < 0 || out_mode > 2 || status == nullptr) return GG_ERR_ARG;
+    if (K <= 0 || (K % 8) != 0 || (ldx % 8) != 0 || ldx < K || out_mode < 0 || out_mode > 3) return GG_ERR_ARG;
+    // out_mode 3: w holds blocks of 64 gate rows and 64 up rows in turn; out[M, N / 2] (bf16) = silu(gate) * up
+    if (out_mode == OUT_SWIGLU ? ((N % 128) != 0 || ldo < N / 2 || (M > 128 && N < 256)) : ldo < N) return GG_ERR_ARG;
+    if ((((uintptr_t)x) & 15) || (((uintptr_t)w) & 15) || status == nullptr) return GG_ERR_ARG;
     const int num_kb = (K + BK - 1) / BK;
     const bool swap = M <= 128;
+    if (out_mode == OUT_SWIGLU) use_cluster = 1;      // the fused activation needs the staged reduction
     const bool cluster = use_cluster != 0;
     int splits = gg_gemm_tc_splits(M, N, K, use_cluster);
     if (splits > 1 && !cluster && (scratch == nullptr || scratch_elems < (long long)splits * M * N)) return GG_ERR_ARG;

@@ -7,7 +7,7 @@ import torch
 
 from .build import KernelError, kernel, module
 
-OUT_BF16, OUT_F32, OUT_F32_ACC = 0, 1, 2
+OUT_BF16, OUT_F32, OUT_F32_ACC, OUT_SWIGLU = 0, 1, 2, 3
 
 _status: Dict[torch.device, torch.Tensor] = {}
 
@@ -38,8 +38,17 @@ def splits_for(M: int, N: int, K: int, cluster: bool = False) -> int:
     return int(raw(int(M), int(N), int(K), int(bool(cluster))))
 
 
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Rows in blocks of 64 gate rows then their 64 up rows: the layout the fused SwiGLU epilogue reads."""
+    I, K = gate.shape
+    if I % 64:
+        raise KernelError("interleave_gate_up: the intermediate size must be a multiple of 64")
+    return torch.stack([gate.view(I // 64, 64, K), up.view(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
-            m: Optional[int] = None, scratch: Optional[torch.Tensor] = None, cluster: bool = False) -> None:
+            m: Optional[int] = None, scratch: Optional[torch.Tensor] = None, cluster: bool = False,
+            swiglu: bool = False) -> None:
     """out[M, N] (+)= x[M, K] @ w[N, K]^T, bfloat16 operands, float32 accumulation on the tensor cores.
 
     Small M splits K.  cluster=True: the partial sums are added inside thread-block clusters (no scratch).
@@ -48,7 +57,11 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     M = x.shape[0] if m is None else m
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tc takes bfloat16 operands")
-    if out.dtype == torch.bfloat16:
+    if swiglu:
+        if out.dtype != torch.bfloat16 or accumulate or out.shape[-1] != N // 2:
+            raise KernelError("gemm_tc: the fused SwiGLU writes bfloat16 [M, N / 2]")
+        mode = OUT_SWIGLU
+    elif out.dtype == torch.bfloat16:
         if accumulate:
             raise KernelError("gemm_tc: sums are kept in float32")
         mode = OUT_BF16
@@ -65,19 +78,24 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
         int(bool(cluster)), st.data_ptr(), torch.cuda.current_stream().cuda_stream)
 
 
-def make_linear(weight: torch.Tensor) -> Optional[Callable]:
+def make_linear(weight: torch.Tensor, swiglu: bool = False) -> Optional[Callable]:
     """A callable f(x, out, accumulate, m, ws) for this weight, or None if its sizes are not taken
-    (K must be a multiple of 8 so that rows start on 16-byte boundaries for TMA)."""
+    (K must be a multiple of 8 so that rows start on 16-byte boundaries for TMA).  swiglu=True: the
+    weight is interleaved gate/up (see `interleave_gate_up`) and out is [M, N / 2]."""
     N, K = weight.shape
     if K % 8 != 0 or weight.data_ptr() % 16 != 0:
+        return None
+    if swiglu and (N % 128 != 0 or N < 256):
         return None
 
     def run(x, out, accumulate, m, ws):
         M = x.shape[0] if m is None else m
         if x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
+            if swiglu:
+                raise KernelError("fused SwiGLU product: activations must be 16-byte aligned rows")
             from . import kernels as Kn
             Kn.gemm_plain(x, weight, out, accumulate, m)
             return
-        gemm_tc(x, weight, out, accumulate, m, None, cluster=True)
+        gemm_tc(x, weight, out, accumulate, m, None, cluster=True, swiglu=swiglu)
 
     return run

@@ -30,15 +30,29 @@ class SwiGLU:
         g, u = rt.matrix(weights["gate_proj.weight"]), rt.matrix(weights["up_proj.weight"])
         if g.dtype != u.dtype:
             g, u = g.float(), u.float()
-        # gate rows first, then up rows: one product for both
-        self.gate_up = Linear(torch.cat([g, u], dim=0), rt)
-        self.down = Linear(weights["down_proj.weight"], rt)
         self.rt = rt
+        self.fused = None
+        if (rt.fast and rt.dtype == torch.bfloat16 and g.dtype == torch.bfloat16 and self.inter % 64 == 0
+                and self.inter >= 128 and self.hidden % 8 == 0):
+            # gate and up rows interleaved in blocks of 64: the product's epilogue applies silu(gate) * up
+            # and writes the activation directly, so the [T, 2 I] intermediate never exists
+            from ..csrc import tcgen05_gemm
+            w = tcgen05_gemm.interleave_gate_up(g, u)
+            self.fused = tcgen05_gemm.make_linear(w, swiglu=True)
+            if self.fused is not None:
+                self.fused_weight = w
+        if self.fused is None:
+            # gate rows first, then up rows: one product for both, then the activation kernel
+            self.gate_up = Linear(torch.cat([g, u], dim=0), rt)
+        self.down = Linear(weights["down_proj.weight"], rt)
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
         T = ctx.n_tokens
-        gu = ctx.ws.get("ffn_gate_up", (T, 2 * self.inter), self.rt.dtype)
         act = ctx.ws.get("ffn_act", (T, self.inter), self.rt.dtype)
-        self.gate_up(h, gu, ws=ctx.ws)
-        K.swiglu(gu, act, T, self.inter)
+        if self.fused is not None and h.dtype == torch.bfloat16:
+            self.fused(h, act, False, None, ctx.ws)
+        else:
+            gu = ctx.ws.get("ffn_gate_up", (T, 2 * self.inter), self.rt.dtype)
+            self.gate_up(h, gu, ws=ctx.ws)
+            K.swiglu(gu, act, T, self.inter)
         self.down(act, residual, accumulate=True, ws=ctx.ws)

@@ -203,6 +203,29 @@ def test_gemm_tcgen05(M, N, K_):
     assert rel(out, twin) < tol
 
 
+@pytest.mark.parametrize("M,I,K_", [(1, 128, 64), (8, 192, 256), (64, 12288, 512), (100, 640, 136), (129, 128, 72),
+                                    (300, 448, 264), (2048, 1024, 1024)])
+def test_gemm_tcgen05_fused_swiglu(M, I, K_):
+    from gogguf_b200.csrc import tcgen05_gemm as tc
+    g = torch.Generator(device=DEV).manual_seed(15)
+    x = torch.randn(M, K_, device=DEV, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(I, K_, device=DEV, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+    wu = (torch.randn(I, K_, device=DEV, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+    w = tc.interleave_gate_up(wg, wu)
+    out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    tc.gemm_tc(x, w, out, cluster=True, swiglu=True)
+    tc.check_status(DEV)
+    gd, ud = x.double() @ wg.double().T, x.double() @ wu.double().T
+    want = gd / (1 + torch.exp(-gd)) * ud
+    assert rel(out, want) < 6e-3
+    # the unfused pair of kernels gives the same to bfloat16 rounding
+    gu = torch.empty(M, 2 * I, device=DEV, dtype=torch.bfloat16)
+    tc.gemm_tc(x, torch.cat([wg, wu]), gu, cluster=True)
+    twin = torch.empty(M, I, device=DEV, dtype=torch.bfloat16)
+    K().swiglu(gu, twin, M, I)
+    assert rel(out, twin) < 1.2e-2
+
+
 def test_gemm_tcgen05_strided_rows_and_padding_rows():
     from gogguf_b200.csrc import tcgen05_gemm as tc
     g = torch.Generator(device=DEV).manual_seed(6)
