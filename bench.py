@@ -243,8 +243,9 @@ def main():
         ctx.generate(prompts, gg.GenerateParams(max_tokens=warmup + steps + 1, stop_token_ids=[], on_token=on_token))
         # stamps[k] is taken when token k of request 0 has reached the host; steps between stamps are decode steps
         dt = stamps[warmup + steps] - stamps[warmup]
-        lay_ints = 3 * batch + 3 * batch + 1 + batch * 64 + 16
-        return {"tok_s": batch * steps / dt, "h2d": lay_ints * 4, "d2h": batch * 4}
+        # bytes per decode step: the packed integer inputs (tokens, positions, slots, lengths, page tables)
+        # copied from pinned host memory, and the sampled ids read back
+        return {"tok_s": batch * steps / dt, "h2d": getattr(ctx.stepper, "last_h2d_bytes", None), "d2h": batch * 4}
 
     def prefill_run():
         cache = model.new_cache(PROMPT_LEN + 64)

@@ -119,5 +119,6 @@ class GraphStepper(Stepper):
         cap.graph.replay()
         self.replays += 1
         self.last_graph_kernels = cap.kernels
+        self.last_h2d_bytes = cap.layout.total * 4
         self.cache.commit(slots, counts)
         return cap.logits[:len(entries)]
