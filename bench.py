@@ -163,7 +163,6 @@ def main():
     from gogguf_b200.csrc import build
     from gogguf_b200.engine import Model, StepEntry
     from gogguf_b200.engine.graphs import GraphStepper
-    from gogguf_b200.engine.generate import GenerateParams, Generator
     from gogguf_b200.csrc import kernels as K
 
     dev = torch.device("cuda:0")

@@ -6,7 +6,6 @@ tensor that is not on a CUDA device, or a missing compiler, raises.
 """
 from __future__ import annotations
 
-import ctypes
 from typing import Optional
 
 import torch

@@ -93,8 +93,8 @@ class Linear:
         self.out_features, self.in_features = self.weight.shape
         self._fast = None
         if rt.fast and rt.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
-            from . import fast_linear
-            self._fast = fast_linear.try_make(self.weight)
+            from ..csrc import tcgen05_gemm
+            self._fast = tcgen05_gemm.make_linear(self.weight)
 
     def __call__(self, x: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
                  m: Optional[int] = None, ws: Optional[Workspace] = None) -> None:

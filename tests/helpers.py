@@ -38,7 +38,14 @@ TINY_M = dict(
     tie_word_embeddings=True, max_position_embeddings=1024,
     sliding_window=90, layer_types=["full_attention", "sliding_attention"],
 )
-TINY = {"M": (TINY_M, 9, 0.04, 0.05), "A": (TINY_A, 0, 0.02, 0.02), "B": (TINY_B, 1, 0.03, 0.05), "W": (TINY_W, 5, 0.05, 0.1)}
+# head size 128, one kv head for four query heads, widths that take the tensor-core products' fused paths
+TINY_L = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=1, head_dim=128,
+    intermediate_size=448, vocab_size=1000, rope_theta=1000000.0, rms_norm_eps=1e-6,
+    tie_word_embeddings=False, max_position_embeddings=2048,
+)
+TINY = {"L": (TINY_L, 11, 0.03, 0.05), "M": (TINY_M, 9, 0.04, 0.05), "A": (TINY_A, 0, 0.02, 0.02), "B": (TINY_B, 1, 0.03, 0.05), "W": (TINY_W, 5, 0.05, 0.1)}
 
 
 def make_folder(tmp, name: str, store_dtype: str = "float32", scale: float = 1.0) -> str:

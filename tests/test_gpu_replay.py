@@ -48,7 +48,7 @@ class Trace:
 
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("W", "float32"),
                                         ("A", "bfloat16"), ("B", "bfloat16"), ("W", "bfloat16"),
-                                        ("M", "bfloat16"), ("M", "float32")])
+                                        ("M", "bfloat16"), ("M", "float32"), ("L", "bfloat16")])
 def test_replay_shapes(tmp_path_factory, tmp_path, name, dtype):
     store = "float32" if dtype == "float32" else "bfloat16"
     folder = make_folder(tmp_path_factory.getbasetemp(), name, store, scale=1.0 if dtype == "float32" else 4.0)

@@ -31,7 +31,7 @@ def test_whole_f32(tmp_path_factory, name, n):
     assert rel_err(got, want) < TOL_F32
 
 
-@pytest.mark.parametrize("name", ["A", "B", "W", "M"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "M", "L"])
 def test_whole_bf16(tmp_path_factory, name):
     folder = make_folder(tmp_path_factory.getbasetemp(), name, "bfloat16", scale=4.0)
     cfg, w = read_folder(folder)
@@ -42,3 +42,37 @@ def test_whole_bf16(tmp_path_factory, name):
     # the plain kernels on the same bfloat16 weights (the twins of the tensor-core kernels) agree too
     twin = engine_whole(folder, "bfloat16", tokens, fast=False)
     assert rel_err(twin, want) < TOL_BF16
+
+
+@pytest.mark.parametrize("name,dtype", [("L", "bfloat16"), ("M", "bfloat16"), ("B", "float32")])
+def test_captured_decode_steps_equal_eager_steps(tmp_path_factory, name, dtype):
+    """The generation path replays decode steps as CUDA graphs, padded to a batch bucket; it must give what
+    the eager stepper gives, for batches that shrink and for sequences that cross page edges."""
+    from gogguf_b200.engine import Model, StepEntry, Stepper
+    from gogguf_b200.engine.graphs import GraphStepper
+    folder = make_folder(tmp_path_factory.getbasetemp(), name, dtype, scale=1.0 if dtype == "float32" else 3.0)
+    cfg, w = read_folder(folder)
+    model = Model.load(folder, dtype=dtype)
+    reqs = [random_tokens(cfg["vocab_size"], n, n) for n in (150, 9, 70)]
+    oracle = [plain.forward(cfg, w, t, wide=True) for t in reqs]
+    tol = TOL_F32 if dtype == "float32" else TOL_BF16
+    results = {}
+    for kind in (Stepper, GraphStepper):
+        cache = model.new_cache(1024)
+        st = kind(model, cache)
+        slots = [cache.open() for _ in reqs]
+        pre = [len(t) - 25 if len(t) > 30 else 2 for t in reqs]
+        st.step([StepEntry(s, t[:p], want=[p - 1]) for s, t, p in zip(slots, reqs, pre)])
+        pos, live, got = list(pre), [0, 1, 2], {}
+        while live:
+            out = st.step([StepEntry(slots[i], [reqs[i][pos[i]]], want=[0]) for i in live]).clone()
+            for j, i in enumerate(live):
+                got[(i, pos[i])] = out[j]
+                assert rel_err(out[j:j + 1], oracle[i][pos[i]:pos[i] + 1]) < tol, (kind.__name__, i, pos[i])
+                pos[i] += 1
+            live = [i for i in live if pos[i] < len(reqs[i])]
+        results[kind.__name__] = got
+        if kind is GraphStepper:
+            assert st.replays > 20 and len(st._graphs) >= 2       # batch 3 (bucket 4, one padding row), then smaller
+    for key, v in results["Stepper"].items():
+        assert rel_err(results["GraphStepper"][key][None], v[None]) < (1e-6 if dtype == "float32" else 2e-2), key
