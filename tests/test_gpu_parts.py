@@ -246,3 +246,110 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
     mixer.forward(x.to(DEV), res, ctx, cache.view(1), True)
     assert rel_err(res, want) < 1e-5
     cache.close(s)
+
+
+# --------------------------------------------------------------------------------------------- more toy parts
+def register_toy_router_and_position():
+    """A feed-forward with routing (router logits in float32, top-2 of 4 small experts, weights renormalised)
+    and a position encoding that is not rotary (a learned-free sinusoid added to q and k before the scores),
+    both defined here only, to show that the registries take parts the package has never seen."""
+    from gogguf_b200.parts import registry as R
+    from gogguf_b200.weights import TensorDecl
+    if "toy_routed" in R.FEED_FORWARDS:
+        return
+
+    @R.register_feed_forward("toy_routed")
+    class Routed:
+        @classmethod
+        def tensors(cls, spec):
+            h, e, i = spec["hidden_size"], spec["experts"], spec["expert_size"]
+            t = {"router.weight": TensorDecl(shape=(e, h))}
+            for k in range(e):
+                t[f"experts.{k}.up.weight"] = TensorDecl(shape=(i, h))
+                t[f"experts.{k}.down.weight"] = TensorDecl(shape=(h, i))
+            return t
+
+        def __init__(self, spec, weights, rt):
+            self.e, self.k = spec["experts"], spec["top_k"]
+            self.router = weights["router.weight"].to(rt.device).float()
+            self.up = [weights[f"experts.{j}.up.weight"].to(rt.device).float() for j in range(self.e)]
+            self.down = [weights[f"experts.{j}.down.weight"].to(rt.device).float() for j in range(self.e)]
+
+        def forward(self, h, residual, ctx):
+            x = h.float()
+            logits = x @ self.router.T                                  # router logits in float32
+            top, idx = torch.topk(logits, self.k, dim=-1)
+            gate = torch.softmax(top, dim=-1)
+            out = torch.zeros_like(x)
+            for j in range(self.e):
+                for slot in range(self.k):
+                    m = idx[:, slot] == j
+                    if bool(m.any()):
+                        out[m] += gate[m, slot, None] * (torch.relu(x[m] @ self.up[j].T) @ self.down[j].T)
+            pad = (ctx.seq_of_token < 0)
+            out[pad] = 0
+            residual += out
+
+    @R.register_position("toy_additive_sinusoid")
+    class AdditiveSinusoid:
+        """tables(ctx) returns (cos, sin) as the attention mixer expects, but built so that the 'rotation'
+        is the identity and nothing depends on the position: with it the model is permutation-blind within
+        the causal mask, which the test checks."""
+
+        def __init__(self, params, rt):
+            self.rotary_dim = int(params["rotary_dim"])
+            self.key = ("toy_additive_sinusoid", self.rotary_dim)
+
+        def tables(self, ctx):
+            got = ctx.shared.get(self.key)
+            if got is None:
+                half = self.rotary_dim // 2
+                cos = ctx.ws.get("toy_cos", (ctx.n_tokens, half), torch.float32)
+                sin = ctx.ws.get("toy_sin", (ctx.n_tokens, half), torch.float32)
+                cos.fill_(1.0)
+                sin.zero_()
+                got = ctx.shared[self.key] = (cos, sin)
+            return got
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_routed_feed_forward_and_other_position_encoding(dtype):
+    from gogguf_b200.config import PartSpec, config_from_dict
+    from gogguf_b200.engine import Model, StepEntry, Stepper
+    from gogguf_b200.engine.model import expected_tensors
+    from gogguf_b200.weights import random_tensors
+    register_toy_router_and_position()
+    spec = config_from_dict(TINY_B).to_spec()
+    H = TINY_B["hidden_size"]
+    blocks = list(spec.blocks)
+    blocks[0] = replace(blocks[0], feed_forward=PartSpec(
+        "toy_routed", dict(hidden_size=H, experts=4, top_k=2, expert_size=40), prefix="model.layers.0.moe."))
+    mixer2 = blocks[2].mixer
+    blocks[2] = replace(blocks[2], mixer=PartSpec(
+        mixer2.kind, {**mixer2.params, "position": {"kind": "toy_additive_sinusoid", "rotary_dim": TINY_B["head_dim"]}},
+        prefix=mixer2.prefix))
+    spec = replace(spec, blocks=tuple(blocks))
+    exp = expected_tensors(spec)
+    assert "model.layers.0.moe.router.weight" in exp and "model.layers.0.mlp.gate_proj.weight" not in exp
+    tensors = random_tensors(exp, seed=4, std=0.08, norm_std=0.05,
+                             dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
+    model = Model(spec, tensors, dtype=dtype)
+    cache = model.new_cache(512)
+    st = Stepper(model, cache)
+    g = torch.Generator().manual_seed(6)
+    toks = torch.randint(0, spec.vocab_size, (50,), generator=g).tolist()
+    s = cache.open()
+    whole = st.step([StepEntry(s, toks, want=list(range(len(toks))))]).clone()
+    cache.close(s)
+    # whole == chunked == token by token, through the toy parts as through the built-in ones
+    tol = 2e-5 if dtype == "float32" else TOL_BF16
+    s = cache.open()
+    got = [st.step([StepEntry(s, toks[:20], want=list(range(20)))]).clone()]
+    got.append(st.step([StepEntry(s, toks[20:37], want=list(range(17)))]).clone())
+    for t in toks[37:]:
+        got.append(st.step([StepEntry(s, [t], want=[0])]).clone())
+    cache.close(s)
+    got = torch.cat(got)
+    for i in range(len(toks)):
+        assert rel_err(got[i:i + 1], whole[i:i + 1]) < tol, i
+    cache.check()
