@@ -164,6 +164,7 @@ def main():
     from gogguf_b200.engine import Model, StepEntry
     from gogguf_b200.engine.graphs import GraphStepper
     from gogguf_b200.csrc import kernels as K
+    from gogguf_b200.csrc import tcgen05_gemm
 
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
@@ -212,6 +213,7 @@ def main():
             toks = nxt.cpu().tolist()          # the next step's input depends on this step's result
         ev1.record()
         torch.cuda.synchronize()
+        tcgen05_gemm.check_status(dev)       # a bounded wait that ran out inside a kernel would invalidate the run
         clocks = sampler.stop()
         ms = ev0.elapsed_time(ev1)
         direct = build.launch_count() - n_launch0

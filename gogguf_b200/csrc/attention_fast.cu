@@ -271,8 +271,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool, bf16* __restrict__ out,
     const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int n_seqs, int nq, int nkv, float scale_log2, int window) {
-    pdl_launch();
-    pdl_wait();
+    pdl_wait();      // no early release of the next kernel: many waves of CTAs that exclude its CTAs from their SMs
     constexpr int CH = D / 8;        // 16-byte chunks per row
     constexpr int KS = D / 16;       // k-steps of Q.K^T
     constexpr int NT = D / 8;        // output n-tiles
@@ -687,6 +686,240 @@ int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* 
                      status);
 }
 
+
+// ------------------------------------------------------------------------------------------- prefill, tcgen05
+// Prefill attention on the 5th-generation tensor cores.  One CTA per (128-query tile of one sequence,
+// query head).  Per 64-key page:  S = Q K^T  (tcgen05.mma 128 x 64 x 16, eight times; Q and K are
+// K-major tiles staged by TMA) lands in tensor memory; the four softmax warps read it, one query row
+// per thread, so the row maximum and sum need no exchange between threads; they write P as bfloat16
+// into shared memory in the K-major swizzled layout, and  O += P V  (128 x D x 16, four times; V is
+// the MN-major operand: one 128-byte row per key) accumulates in tensor memory.  O is rescaled in
+// place only when a row's maximum has grown by more than 2^8 since the scale in use was set (the
+// sums stay exact: P and the row sum use the same stale maximum), so most pages cost no pass over O.
+// Two CTAs share an SM (96 KB of shared memory and 256 tensor-memory columns each): while one runs
+// its softmax the other's MMAs keep the tensor pipe busy.
+template <int D>
+__global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
+    const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+    bf16* __restrict__ out, const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens,
+    const int* __restrict__ seq_of_token, const int* __restrict__ page_table, int max_pages, int n_seqs,
+    int nq, int nkv, float scale_log2, int window, int* __restrict__ status) {
+    constexpr int HALVES = D / 64;
+    constexpr int QBOX = 128 * 64 * 2;              // [64 columns x 128 rows] box of Q: 16 KB
+    constexpr int KBOX = 64 * 64 * 2;               // [64 columns x 64 rows] box of K or V: 8 KB
+    constexpr int Q_BYTES = HALVES * QBOX, K_STAGE = HALVES * KBOX, V_BYTES = HALVES * KBOX, P_BYTES = 128 * 64 * 2;
+    constexpr int TMEM_COLS = 256;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* Qs = smem;
+    uint8_t* Ks = Qs + Q_BYTES;                     // two stages
+    uint8_t* Vs = Ks + 2 * K_STAGE;
+    uint8_t* Ps = Vs + V_BYTES;
+    uint64_t* bars = (uint64_t*)(Ps + P_BYTES);
+    uint64_t* q_full = bars;
+    uint64_t* k_full = bars + 1;                    // [2]
+    uint64_t* k_empty = bars + 3;                   // [2]
+    uint64_t* v_full = bars + 5;
+    uint64_t* v_empty = bars + 6;
+    uint64_t* s_full = bars + 7;
+    uint64_t* p_ready = bars + 8;
+    uint64_t* pv_done = bars + 9;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    // no early release of the next kernel here: see the note on dependent launches in common.cuh
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        tma::mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) { tma::mbar_init(&k_full[i], 1); tma::mbar_init(&k_empty[i], 1); }
+        tma::mbar_init(v_full, 1); tma::mbar_init(v_empty, 1);
+        tma::mbar_init(s_full, 1); tma::mbar_init(p_ready, 128); tma::mbar_init(pv_done, 1);
+        *abort_flag = 0;
+        tma::mbar_fence_init();
+        tma::prefetch_map(&tmQ); tma::prefetch_map(&tmK); tma::prefetch_map(&tmV);
+    }
+    if (warp == 5) tc5::alloc(tmem_slot, TMEM_COLS);
+    tc5::fence_before();
+    __syncthreads();
+    tc5::fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();          // q, the cache and the integer tables come from earlier kernels and copies
+
+    // which (sequence, 128-row query tile)?  heavy tiles (late rows) first
+    int b = -1, tile = (int)gridDim.y - 1 - (int)blockIdx.y, n_new = 0, tok0 = 0;
+    for (int i = 0; i < n_seqs; ++i) {
+        const int a = cu_seqlens[i], e = cu_seqlens[i + 1];
+        if (seq_of_token[a] < 0) continue;
+        const int nt = (e - a + 127) >> 7;
+        if (tile < nt) { b = i; n_new = e - a; tok0 = a; break; }
+        tile -= nt;
+    }
+    const bool active = b >= 0;
+    const int h = blockIdx.x, kvh = active ? h / (nq / nkv) : 0;
+    const int row0 = tile * 128;
+    const int rows = active ? min(128, n_new - row0) : 0;
+    const int pos0 = active ? ctx_lens[b] - n_new + row0 : 0;
+    int lo = 0;
+    if (window > 0 && pos0 - window + 1 > 0) lo = pos0 - window + 1;
+    const int kt_first = lo / PAGE, kt_last = active ? (pos0 + rows - 1) / PAGE : -1;
+    const int ntiles = kt_last - kt_first + 1;
+    const uint32_t S_t = tmem_base, O_t = tmem_base + 64;
+
+    if (warp == 4) {
+        if (lane == 0 && active) {
+            const int* pt = page_table + (size_t)b * max_pages;
+            tma::mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+            for (int hf = 0; hf < HALVES; ++hf) tma::load_2d(Qs + hf * QBOX, &tmQ, q_full, h * D + hf * 64, tok0 + row0);
+            for (int j = 0; j < ntiles; ++j) {
+                const int s = j & 1;
+                const int row = (pt[kt_first + j] * nkv + kvh) * PAGE;
+                if (!tma::mbar_wait(&k_empty[s], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, status, 21)) break;
+                tma::mbar_expect_tx(&k_full[s], K_STAGE);
+#pragma unroll
+                for (int hf = 0; hf < HALVES; ++hf) tma::load_2d(Ks + s * K_STAGE + hf * KBOX, &tmK, &k_full[s], hf * 64, row);
+                if (!tma::mbar_wait(v_empty, (uint32_t)(j & 1) ^ 1u, abort_flag, status, 22)) break;
+                tma::mbar_expect_tx(v_full, V_BYTES);
+#pragma unroll
+                for (int hf = 0; hf < HALVES; ++hf) tma::load_2d(Vs + hf * KBOX, &tmV, v_full, hf * 64, row);
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0 && active) {
+            const uint32_t idesc_qk = tc5::idesc_bf16(128, 64, 0), idesc_pv = tc5::idesc_bf16(128, D, 1);
+            const uint32_t q_a = tma::smem_u32(Qs), k_a = tma::smem_u32(Ks), v_a = tma::smem_u32(Vs), p_a = tma::smem_u32(Ps);
+            bool ok = tma::mbar_wait(q_full, 0, abort_flag, status, 23);
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int s = j & 1;
+                ok = tma::mbar_wait(&k_full[s], (uint32_t)((j >> 1) & 1), abort_flag, status, 24);
+                if (!ok) break;
+                tc5::fence_after();
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint64_t a = tc5::smem_desc(q_a + (ks >> 2) * QBOX + (ks & 3) * 32, 16, 1024);
+                    const uint64_t bb = tc5::smem_desc(k_a + s * K_STAGE + (ks >> 2) * KBOX + (ks & 3) * 32, 16, 1024);
+                    tc5::mma(S_t, a, bb, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                tc5::commit(s_full);
+                tc5::commit(&k_empty[s]);
+                ok = tma::mbar_wait(p_ready, (uint32_t)(j & 1), abort_flag, status, 25);
+                if (!ok) break;
+                ok = tma::mbar_wait(v_full, (uint32_t)(j & 1), abort_flag, status, 26);
+                if (!ok) break;
+                tc5::fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t a = tc5::smem_desc(p_a + kk * 32, 16, 1024);
+                    const uint64_t bb = tc5::smem_desc(v_a + kk * 2048, KBOX, 1024);
+                    tc5::mma(O_t, a, bb, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                tc5::commit(pv_done);
+                tc5::commit(v_empty);
+            }
+        }
+    } else if (active) {
+        const int row = threadIdx.x;                       // query row of the tile = tensor-memory lane
+        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+        const int p = pos0 + row;
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < ntiles; ++j) {
+            if (!tma::mbar_wait(s_full, (uint32_t)(j & 1), abort_flag, status, 27)) { ok = false; break; }
+            tc5::fence_after();
+            uint32_t sr[64];
+            tc5::ld32(S_t + lane_off, sr);
+            tc5::ld32(S_t + lane_off + 32, sr + 32);
+            tc5::wait_ld();
+            const int key0 = (kt_first + j) * PAGE;
+            const bool edge = (key0 + PAGE - 1 > pos0) || (window > 0 && key0 < pos0 + 127 - window + 1);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+                float v = __uint_as_float(sr[c]) * scale_log2;
+                if (edge) {
+                    const int kidx = key0 + c;
+                    bool vis = kidx <= p;
+                    if (window > 0) vis = vis && (kidx > p - window);
+                    v = vis ? v : -INFINITY;
+                }
+                sr[c] = __float_as_uint(v);
+                mx = fmaxf(mx, v);
+            }
+            // the scale in use is kept while the maximum has not grown by more than 2^8
+            const bool grow = mx > m_used + 8.0f || (m_used == -INFINITY && mx != -INFINITY);
+            if (__any_sync(0xffffffffu, grow)) {
+                float corr = 1.0f;
+                if (grow) {
+                    corr = m_used == -INFINITY ? 0.f : fast_exp2(m_used - mx);
+                    m_used = mx;
+                    l *= corr;
+                }
+                if (j > 0) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        uint32_t orow[32];
+                        tc5::ld32(O_t + lane_off + c0, orow);
+                        tc5::wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * corr);
+                        tc5::st32(O_t + lane_off + c0, orow);
+                    }
+                    tc5::wait_st();
+                }
+            }
+            const float mu = m_used == -INFINITY ? 0.f : m_used;
+            uint8_t* prow = Ps + row * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = fast_exp2(__uint_as_float(sr[ch * 8 + 2 * e]) - mu);
+                    const float p1 = fast_exp2(__uint_as_float(sr[ch * 8 + 2 * e + 1]) - mu);
+                    l += p0 + p1;
+                    pk[e] = pack_bf16(p0, p1);
+                }
+                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+            tc5::fence_proxy_async_smem();     // P was written with ordinary stores; the tensor core reads it
+            tc5::fence_before();
+            tma::mbar_arrive(p_ready);
+        }
+        if (ok && tma::mbar_wait(pv_done, (uint32_t)((ntiles - 1) & 1), abort_flag, status, 28)) {
+            tc5::fence_after();
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            bf16* dst = out + ((size_t)(tok0 + row0 + row) * nq + h) * D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t orow[32];
+                tc5::ld32(O_t + lane_off + c0, orow);
+                tc5::wait_ld();
+                if (row < rows) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            pk[e] = pack_bf16(__uint_as_float(orow[c + 2 * e]) * inv, __uint_as_float(orow[c + 2 * e + 1]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                }
+            }
+        }
+    }
+    tc5::fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+        __syncthreads();
+    }
+    if (warp == 5) {
+        tc5::fence_after();
+        tc5::dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
 }  // namespace
 
 // Number of key-range splits the decode launcher uses for this shape; the caller sizes the scratch:
@@ -807,4 +1040,46 @@ GG_API gg_attn_decode_tma(const void* q, const void* k_pool, const void* v_pool,
     if (d == 128) gg_launch(attn_combine_kernel<128>, dim3(ntok * nq), dim3(128), 0, stream, 1, part_o, part_ml, (bf16*)out, splits);
     else gg_launch(attn_combine_kernel<64>, dim3(ntok * nq), dim3(64), 0, stream, 1, part_o, part_ml, (bf16*)out, splits);
     return gg_last_error();
+}
+
+// Prefill attention on tcgen05 (see attn_prefill_tc_kernel).  q and out: [n_tokens, nq, d] bf16, d = 64 or 128;
+// pools [page][nkv][64][d]; max_tiles >= sum over sequences of ceil(new tokens / 128); status as in the
+// tensor-core product (codes 21-28 name the wait that ran out).
+GG_API gg_attn_prefill_tc(const void* q, const void* k_pool, const void* v_pool, void* out, const int* cu_seqlens,
+                          const int* ctx_lens, const int* seq_of_token, const int* page_table, int max_pages,
+                          int page_size, int n_pages, int n_tokens, int n_seqs, int max_tiles, int nq, int nkv, int d,
+                          float scale, int window, int* status, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_tiles <= 0 || n_tokens <= 0) return 0;
+    if (page_size != PAGE || nq <= 0 || nkv <= 0 || nq % nkv || (d != 64 && d != 128) || nq > 65535 || max_tiles > 65535 ||
+        n_pages <= 0 || status == nullptr)
+        return GG_ERR_ARG;
+    if ((((uintptr_t)q) & 15) || (((uintptr_t)k_pool) & 15) || (((uintptr_t)v_pool) & 15) || (((uintptr_t)out) & 15)) return GG_ERR_ARG;
+    CUtensorMap tq, tk, tv;
+    int rc;
+    if ((rc = tma::make_map_bf16(&tq, q, (unsigned long long)n_tokens, nq * d, (long long)nq * d, 128)) != 0) return rc;
+    const unsigned long long rows = (unsigned long long)n_pages * nkv * PAGE;
+    if ((rc = tma::make_map_bf16(&tk, k_pool, rows, d, d, PAGE)) != 0) return rc;
+    if ((rc = tma::make_map_bf16(&tv, v_pool, rows, d, d, PAGE)) != 0) return rc;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    dim3 grid(nq, max_tiles);
+    if (d == 128) {
+        constexpr int smem = 2 * 16384 + 2 * 16384 + 16384 + 16384 + 1024 + 256;
+        static bool cfg = false;
+        if (!cfg) {
+            cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess) return (int)e;
+            cfg = true;
+        }
+        return gg_launch(attn_prefill_tc_kernel<128>, grid, dim3(192), smem, stream, 1, tq, tk, tv, (bf16*)out, cu_seqlens,
+                         ctx_lens, seq_of_token, page_table, max_pages, n_seqs, nq, nkv, scale_log2, window, status);
+    }
+    constexpr int smem = 16384 + 2 * 8192 + 8192 + 16384 + 1024 + 256;
+    static bool cfg64 = false;
+    if (!cfg64) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        cfg64 = true;
+    }
+    return gg_launch(attn_prefill_tc_kernel<64>, grid, dim3(192), smem, stream, 1, tq, tk, tv, (bf16*)out, cu_seqlens,
+                     ctx_lens, seq_of_token, page_table, max_pages, n_seqs, nq, nkv, scale_log2, window, status);
 }

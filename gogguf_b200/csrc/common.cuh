@@ -80,6 +80,14 @@ __device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats o
 // before it touches anything a predecessor reads or writes.  Every kernel calls pdl_wait(), so
 // "my predecessor has completed" holds transitively for all earlier kernels.  pdl_launch() lets the
 // successor start early.  Without the launch attribute both are no-ops.
+//
+// One rule came out of a stall seen on B200: a kernel that runs in many waves of CTAs and whose
+// CTAs cannot share an SM with the CTAs of the kernel after it (both need most of the shared
+// memory) does NOT call pdl_launch().  With the early release, the persistent product that follows
+// prefill attention took over SMs as they came free while attention CTAs were still waiting to be
+// scheduled, and the two kernels waited for each other; the cause inside the scheduler was not
+// established, so such kernels simply release their successor by completing.  Light kernels with
+// many CTAs (norms, rotary) share SMs with whatever follows and keep the early release.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

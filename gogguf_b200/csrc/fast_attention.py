@@ -49,6 +49,17 @@ def attn_prefill(q, k_pool, v_pool, out, cu_seqlens, ctx_lens, seq_of_token, tab
         n_seqs, max_tiles, nq, nkv, d, float(scale), int(window), torch.cuda.current_stream().cuda_stream)
 
 
+def attn_prefill_tc(q, k_pool, v_pool, out, cu_seqlens, ctx_lens, seq_of_token, table, page_size, n_tokens,
+                    n_seqs, max_tiles, nq, nkv, d, scale, window) -> None:
+    """Prefill attention on tcgen05: 128-query tiles, S and O in tensor memory."""
+    from .tcgen05_gemm import status_word
+    kernel("attention_fast", "gg_attn_prefill_tc")(
+        q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), cu_seqlens.data_ptr(),
+        ctx_lens.data_ptr(), seq_of_token.data_ptr(), table.data_ptr(), table.shape[-1], page_size,
+        k_pool.shape[0], n_tokens, n_seqs, max_tiles, nq, nkv, d, float(scale), int(window),
+        status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+
+
 def try_make(nq: int, nkv: int, d: int, scale: float, window: int) -> Optional[Callable]:
     """f(q, k_pool, v_pool, out, ctx, table, page_size) for bfloat16, or None when the sizes are
     outside what the tensor-core kernels take (head size 64 or 128, at most 16 query heads per kv
@@ -66,7 +77,13 @@ def try_make(nq: int, nkv: int, d: int, scale: float, window: int) -> Optional[C
             splits = decode_tma_splits(T, nkv, ctx.max_ctx, cluster=True)
             attn_decode_tma(q, k_pool, v_pool, out, ctx.positions, ctx.seq_of_token, table, page_size, T, nq, nkv, d,
                             scale, window, splits, cluster=True)
+        elif ctx.max_new >= 32:
+            # 128-query tiles on tcgen05 (S and O in tensor memory)
+            max_tiles = T // 128 + ctx.n_seqs
+            attn_prefill_tc(q, k_pool, v_pool, out, ctx.cu_seqlens, ctx.ctx_lens, ctx.seq_of_token, table, page_size,
+                            T, ctx.n_seqs, max_tiles, nq, nkv, d, scale, window)
         else:
+            # a few tokens per sequence: 64-query tiles on mma.sync waste less
             max_tiles = T // 64 + ctx.n_seqs
             attn_prefill(q, k_pool, v_pool, out, ctx.cu_seqlens, ctx.ctx_lens, ctx.seq_of_token, table, page_size,
                          ctx.n_seqs, max_tiles, nq, nkv, d, scale, window)

@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|attn] [--m 1,8,64]
+"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|attn|prefill_attn] [--m 1,8,64]
 
 Times single kernels the way a decode step runs them: forty launches captured in a CUDA graph and
 replayed, so that host launch cost is out of the picture and dependent launches overlap as they do
@@ -72,13 +72,36 @@ def attn(ms, ctx_len: int = 2048, nq: int = 32, nkv: int = 8, d: int = 128) -> N
         torch.cuda.empty_cache()
 
 
+def prefill_attn(lens, nq: int = 32, nkv: int = 8, d: int = 128) -> None:
+    """One sequence of T new tokens from position 0, both prefill kernels."""
+    from . import fast_attention as fa
+    dev = "cuda:0"
+    for T in lens:
+        pages = (T + 63) // 64
+        kp = torch.randn(pages, nkv, 64, d, device=dev).to(torch.bfloat16)
+        vp = torch.randn(pages, nkv, 64, d, device=dev).to(torch.bfloat16)
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        cl = torch.tensor([T], dtype=torch.int32, device=dev)
+        sot = torch.zeros(T, dtype=torch.int32, device=dev)
+        q = torch.randn(T, nq, d, device=dev).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        flops = 4.0 * nq * d * (T * (T + 1) / 2)
+        us = _time_graph(lambda i: fa.attn_prefill(q, kp, vp, out, cu, cl, sot, table, 64, 1, T // 64 + 1, nq, nkv, d,
+                                                   1.0 / math.sqrt(d), 0), reps=10)
+        print(f"attn prefill mma.sync T={T:6d} {us:9.1f} us {flops / us / 1e6:7.1f} TFLOP/s", flush=True)
+        us = _time_graph(lambda i: fa.attn_prefill_tc(q, kp, vp, out, cu, cl, sot, table, 64, T, 1, T // 128 + 1, nq, nkv,
+                                                      d, 1.0 / math.sqrt(d), 0), reps=10)
+        print(f"attn prefill tcgen05  T={T:6d} {us:9.1f} us {flops / us / 1e6:7.1f} TFLOP/s", flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn"])
+    ap.add_argument("what", choices=["gemm", "attn", "prefill_attn"])
     ap.add_argument("--m", default="1,8,64", help="token counts (gemm) or batch sizes (attn)")
     a = ap.parse_args()
     ms = [int(x) for x in a.m.split(",")]
-    (gemm if a.what == "gemm" else attn)(ms)
+    {"gemm": gemm, "attn": attn, "prefill_attn": prefill_attn}[a.what](ms)
 
 
 if __name__ == "__main__":

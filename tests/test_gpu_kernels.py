@@ -334,6 +334,13 @@ def test_attention_prefill_tensor_cores(nq, nkv, d, window, seqs):
     want = attention_reference(q, ks, vs, seqs, nq, nkv, scale, window) if T <= 400 else twin
     assert rel(out, want) < 8e-3
     assert rel(out, twin) < 8e-3
+    # the tcgen05 form (S and O in tensor memory)
+    from gogguf_b200.csrc import tcgen05_gemm as tc
+    out2 = torch.full((T, nq, d), float("nan"), device=DEV, dtype=dt)
+    fa.attn_prefill_tc(q, kp, vp, out2, cu, cl, sot, table, 64, T, len(seqs), T // 128 + len(seqs), nq, nkv, d, scale, window)
+    tc.check_status(DEV)
+    assert rel(out2, want) < 8e-3
+    assert rel(out2, twin) < 8e-3
 
 
 @pytest.mark.parametrize("nq,nkv,d,window,ctxs", [
