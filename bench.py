@@ -163,8 +163,8 @@ def main():
     from gogguf_b200.csrc import build
     from gogguf_b200.engine import Model, StepEntry
     from gogguf_b200.engine.graphs import GraphStepper
-    from gogguf_b200.csrc import kernels as K
     from gogguf_b200.csrc import tcgen05_gemm
+    from gogguf_b200.sampling import Sampler, SamplerConfig
 
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
@@ -193,28 +193,33 @@ def main():
         for i in range(0, batch, chunk):
             ents = [StepEntry(s, rand_tokens(PROMPT_LEN), want=[PROMPT_LEN - 1]) for s in slots[i:i + chunk]]
             logits_last.append(st.step(ents).clone())
-        nxt = torch.empty(batch, dtype=torch.int32, device=dev)
-        K.argmax(torch.cat(logits_last), nxt)
-        toks = nxt.cpu().tolist()
+        # greedy sampling on the device; each step takes its input ids from the device buffer the previous
+        # step's sampling kernel wrote, and the host reads every step's ids (one step behind the device)
+        sampler = Sampler(SamplerConfig())
+        rows = list(range(batch))
+        pending = sampler.sample_async(torch.cat(logits_last), rows, [0] * batch)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        sampler = None
+        clock_sampler = None
         n_launch0 = 0
+        produced = []
         for it in range(warmup + steps):
             if it == warmup:
+                produced.append(pending.tokens())
                 torch.cuda.synchronize()
-                sampler = ClockSampler()
-                sampler.start()
+                clock_sampler = ClockSampler()
+                clock_sampler.start()
                 time.sleep(0.25)
                 n_launch0 = build.launch_count()
                 replay0 = st.replays
                 ev0.record()
-            logits = st.step([StepEntry(s, [t], want=[0]) for s, t in zip(slots, toks)])
-            K.argmax(logits, nxt, batch)
-            toks = nxt.cpu().tolist()          # the next step's input depends on this step's result
+            logits = st.decode_from_device(slots, pending.device_tokens, rows)
+            nxt_pending = sampler.sample_async(logits, rows, [it + 1] * batch)
+            produced.append(pending.tokens())      # device-to-host read of the step's result, every step
+            pending = nxt_pending
         ev1.record()
         torch.cuda.synchronize()
         tcgen05_gemm.check_status(dev)       # a bounded wait that ran out inside a kernel would invalidate the run
-        clocks = sampler.stop()
+        clocks = clock_sampler.stop()
         ms = ev0.elapsed_time(ev1)
         direct = build.launch_count() - n_launch0
         launches = direct + (st.replays - replay0) * getattr(st, "last_graph_kernels", 0)
@@ -237,8 +242,7 @@ def main():
 
         def on_token(i, t):
             if i == 0:
-                torch.cuda.synchronize()
-                stamps.append(time.perf_counter())
+                stamps.append(time.perf_counter())     # the id has just arrived on the host
             return True
 
         ctx.generate(prompts, gg.GenerateParams(max_tokens=warmup + steps + 1, stop_token_ids=[], on_token=on_token))

@@ -417,3 +417,19 @@ GG_API gg_residual_add(float* x, const void* delta, int dtype, long long n, cuda
         gg_launch(residual_add_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, x, (const T*)delta, n));
     return gg_last_error();
 }
+
+// ----------------------------------------------------------------------------- token feed
+// tokens[i] = sampled[src[i]] where src[i] >= 0: lets a decode step take the ids that the previous
+// step's sampling kernel left on the device, without a round trip through the host.
+__global__ void feed_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ src,
+                                   const int* __restrict__ sampled, int n) {
+    pdl_launch();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && src[i] >= 0) tokens[i] = sampled[src[i]];
+}
+
+GG_API gg_feed_tokens(int* tokens, const int* src, const int* sampled, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    return gg_launch(feed_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, 1, tokens, src, sampled, n);
+}

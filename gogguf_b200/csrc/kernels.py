@@ -102,6 +102,14 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
     kernel("elementwise", "gg_residual_add")(_p(x), _p(delta), dtype_code(delta.dtype), x.numel(), _stream())
 
 
+def feed_tokens(tokens: torch.Tensor, src: torch.Tensor, sampled: torch.Tensor, n: int) -> None:
+    """tokens[i] = sampled[src[i]] where src[i] >= 0 (all int32, on the device)."""
+    _need(tokens, torch.int32, "tokens")
+    _need(src, torch.int32, "src")
+    _need(sampled, torch.int32, "sampled")
+    kernel("elementwise", "gg_feed_tokens")(_p(tokens), _p(src), _p(sampled), n, _stream())
+
+
 # ------------------------------------------------------------------------------- matrix product
 def gemm_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
                m: Optional[int] = None) -> None:

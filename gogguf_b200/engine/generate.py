@@ -91,6 +91,21 @@ class Generator:
             self._run_batch(batch, prompts, params, max_new, results)
         return [r for r in results if r is not None]
 
+    def _finish_reason(self, i: int, t: int, prompts, generated, params: GenerateParams, max_new: int,
+                       stop) -> Optional[str]:
+        """Take the sampled token `t` of request i: append it unless it stops the sequence, and say why the
+        sequence ends, if it does (pkg/runtime/session.go:58-72, :143-151)."""
+        if t < 0 or t in stop:
+            return "stop"
+        generated[i].append(int(t))
+        if params.on_token is not None and not params.on_token(i, int(t)):
+            return "callback"
+        if len(generated[i]) >= max_new:
+            return "length"
+        if len(prompts[i]) + len(generated[i]) > self.context:
+            return "length"          # the token's own position would lie outside the context
+        return None
+
     def _run_batch(self, batch: List[int], prompts, params: GenerateParams, max_new: int, results) -> None:
         stop = set(self.default_stop if params.stop_token_ids is None else params.stop_token_ids)
         sampler = Sampler(params.sampler, params.repeat_penalty, params.repeat_last_n)
@@ -101,24 +116,17 @@ class Generator:
         try:
             entries = [StepEntry(slots[i], list(prompts[i]), want=[len(prompts[i]) - 1]) for i in live]
             logits = self.stepper.step(entries)
+            if (hasattr(self.stepper, "decode_from_device") and sampler.device_only
+                    and getattr(logits, "is_cuda", False) and len(live) <= 256):
+                self._decode_one_ahead(live, logits, sampler, slots, generated, prompts, params, max_new, stop, results)
+                return
             while live:
                 hist = [list(prompts[i]) + generated[i] for i in live] if sampler.penalised else None
                 nxt = sampler.sample(logits, streams=live, steps=[len(generated[i]) for i in live],
                                      histories=hist)
                 go_on: List[int] = []
                 for i, t in zip(live, nxt):
-                    reason = None
-                    if t < 0 or t in stop:                              # session.go:58-65
-                        reason = "stop"
-                    else:
-                        generated[i].append(int(t))
-                        if params.on_token is not None and not params.on_token(i, int(t)):
-                            reason = "callback"
-                        elif len(generated[i]) >= max_new:
-                            reason = "length"
-                        elif len(prompts[i]) + len(generated[i]) > self.context:
-                            # the token's own position would lie outside the context (session.go:68-72)
-                            reason = "length"
+                    reason = self._finish_reason(i, t, prompts, generated, params, max_new, stop)
                     if reason is None:
                         go_on.append(i)
                     else:
@@ -133,3 +141,54 @@ class Generator:
             for i, s in list(slots.items()):
                 cache.close(s)
                 slots.pop(i)
+
+    def _decode_one_ahead(self, live, logits, sampler, slots, generated, prompts, params, max_new, stop, results):
+        """The same loop with the device kept busy: while the host reads the ids of step k, step k + 1 is
+        already running on the ids that the sampling kernel left on the device.  A sequence whose id turns
+        out to be a stop token (or whose callback says stop) was then run one step too far; its extra row
+        is dropped and its slot is given back, and nobody else's result depends on it."""
+        cache = self.cache
+        rows = list(live)                                   # requests whose ids are on their way
+        pending = sampler.sample_async(logits, rows, [len(generated[i]) for i in rows])
+        dev_row = {i: r for r, i in enumerate(rows)}        # where each request's id sits in the device buffer
+        while rows:
+            # who certainly goes on after the id that is on its way (its value is not needed for this)?
+            cont = [i for i in rows
+                    if len(generated[i]) + 1 < max_new and len(prompts[i]) + len(generated[i]) + 1 <= self.context]
+            nxt_pending = None
+            if cont:
+                src = [dev_row[i] for i in cont]
+                logits = self.stepper.decode_from_device([slots[i] for i in cont], pending.device_tokens, src)
+                nxt_pending = sampler.sample_async(logits, cont, [len(generated[i]) + 1 for i in cont])
+            ids = pending.tokens()                           # the host catches up with the previous step
+            stopped = set()
+            for i, t in zip(rows, ids):
+                reason = self._finish_reason(i, t, prompts, generated, params, max_new, stop)
+                if reason is not None:
+                    results[i] = GenerationResult(generated[i], reason, len(prompts[i]))
+                    cache.close(slots.pop(i))
+                    stopped.add(i)
+            if nxt_pending is None:
+                break
+            dev_row = {i: r for r, i in enumerate(cont)}
+            if stopped & set(cont):
+                # rows of sequences that have ended are still in the step that is running: take the ids of
+                # the others from their places
+                keep = [i for i in cont if i not in stopped]
+                nxt_pending = _SubsetSample(nxt_pending, [cont.index(i) for i in keep])
+                cont = keep
+            rows, pending = cont, nxt_pending
+
+
+class _SubsetSample:
+    """Some rows of a pending sample: ids of sequences that ended meanwhile are left out."""
+
+    def __init__(self, base, keep_rows):
+        self._base, self._keep = base, list(keep_rows)
+        self.device_tokens = base.device_tokens
+        self.rows = len(self._keep)
+        self.row_map = self._keep
+
+    def tokens(self):
+        ids = self._base.tokens()
+        return [ids[r] for r in self._keep]

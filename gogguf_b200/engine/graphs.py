@@ -41,6 +41,9 @@ class _Captured:
     logits: torch.Tensor
     layout: StepLayout
     kernels: int
+    host2: Optional[torch.Tensor] = None       # second pinned buffer: steps may be enqueued one ahead
+    copied: Optional[list] = None              # events: the copy out of each pinned buffer has been done
+    turn: int = 0
 
 
 class GraphStepper(Stepper):
@@ -84,6 +87,8 @@ class GraphStepper(Stepper):
             x = self.run_layers(ctx)
             cap.logits = self.run_head(ctx, x, rows, bucket)
         cap.kernels = build.launch_count() - n0
+        cap.host2 = torch.empty(lay.total, dtype=torch.int32, pin_memory=True)
+        cap.copied = [None, None]
         return cap
 
     def _context_for_capture(self, entries, cap: _Captured, bucket: int, width: int):
@@ -102,20 +107,48 @@ class GraphStepper(Stepper):
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         decode = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries) and len(entries) > 0
-        bucket = _bucket(len(entries), BATCH_BUCKETS) if decode else None
-        if bucket is None:
+        if not decode or _bucket(len(entries), BATCH_BUCKETS) is None:
             return super().step(entries)
         self._check(entries)
+        return self._enqueue_decode(entries, None, None)
+
+    def decode_from_device(self, slots: Sequence[int], sampled: torch.Tensor, rows: Sequence[int]
+                           ) -> Optional[torch.Tensor]:
+        """Enqueue one decode step whose input tokens are still on the device: sequence i of `slots`
+        takes `sampled[rows[i]]` (an int32 tensor that a sampling kernel wrote earlier on this stream).
+        Nothing is read back and the host does not wait, so the caller may enqueue this step while it
+        is still reading the previous step's ids.  Returns the logits view [len(slots), vocab]."""
+        entries = [StepEntry(s, [0], want=[0]) for s in slots]
+        if _bucket(len(entries), BATCH_BUCKETS) is None:
+            raise ValueError(f"no captured batch size holds {len(entries)} sequences")
+        self._check(entries)
+        return self._enqueue_decode(entries, sampled, list(rows))
+
+    def _enqueue_decode(self, entries, sampled, rows):
         slots = [e.slot for e in entries]
         counts = [1] * len(entries)
+        bucket = _bucket(len(entries), BATCH_BUCKETS)
         self.cache.plan(slots, counts)
         width = self._width_bucket(slots)
         key = (bucket, width)
         cap = self._graphs.get(key)
         if cap is None:
             cap = self._graphs[key] = self._capture(entries, bucket, width)
-        # refill the integer inputs (this also issues the copy to the device) and replay
-        self.build_context(entries, host=cap.host, dev=cap.dev, pad_seqs=bucket, table_width=width, ws=cap.ws)
+        # two pinned buffers in turn: the one filled now was last copied from two steps ago
+        t = cap.turn
+        cap.turn ^= 1
+        host = cap.host if t == 0 else cap.host2
+        if cap.copied[t] is not None:
+            cap.copied[t].synchronize()
+        self.build_context(entries, host=host, dev=cap.dev, pad_seqs=bucket, table_width=width, ws=cap.ws,
+                           token_src=rows, wait_host=False)
+        if cap.copied[t] is None:
+            cap.copied[t] = torch.cuda.Event()
+        cap.copied[t].record()
+        if sampled is not None:
+            from ..csrc import kernels as K
+            lay = cap.layout
+            K.feed_tokens(lay.view(cap.dev, "tokens"), lay.view(cap.dev, "token_src"), sampled, len(entries))
         cap.graph.replay()
         self.replays += 1
         self.last_graph_kernels = cap.kernels

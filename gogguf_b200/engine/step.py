@@ -49,7 +49,7 @@ class StepLayout:
         self.off: Dict[str, Tuple[int, int]] = {}
         for name, n in (("tokens", n_tokens), ("positions", n_tokens), ("seq_of_token", n_tokens),
                         ("cu_seqlens", n_seqs + 1), ("slots", n_seqs), ("ctx_lens", n_seqs),
-                        ("logit_rows", max(n_want, 1))):
+                        ("token_src", n_seqs), ("logit_rows", max(n_want, 1))):
             self.off[name] = (off, n)
             off += _pad4(n)
         for g, w in enumerate(self.group_widths):
@@ -107,7 +107,8 @@ class Stepper:
 
     def build_context(self, entries: Sequence[StepEntry], host: Optional[torch.Tensor] = None,
                       dev: Optional[torch.Tensor] = None, pad_seqs: int = 0, table_width: Optional[int] = None,
-                      ws: Optional[Workspace] = None) -> Tuple[StepContext, StepLayout, torch.Tensor]:
+                      ws: Optional[Workspace] = None, token_src: Optional[Sequence[int]] = None,
+                      wait_host: bool = True) -> Tuple[StepContext, StepLayout, torch.Tensor]:
         """Fill the integer inputs for `entries` (pages must be reserved already) and copy them to the device.
 
         `pad_seqs` > len(entries) pads the batch with empty rows (one padding token each), which the
@@ -124,12 +125,16 @@ class Stepper:
         lay = StepLayout(T, B, max(n_want, pad_seqs), [width] * len(cache.groups))
         if host is None:
             host, dev = self._buffers(lay.total)
-        if self._copied is not None:
+        if self._copied is not None and wait_host:
             self._copied.synchronize()      # the previous step's copy has left the host buffer
         h = host.numpy()
         tok, pos, sot = lay.view(h, "tokens"), lay.view(h, "positions"), lay.view(h, "seq_of_token")
         cu, sl, cl, rows = (lay.view(h, "cu_seqlens"), lay.view(h, "slots"), lay.view(h, "ctx_lens"),
                             lay.view(h, "logit_rows"))
+        src = lay.view(h, "token_src")
+        src[:] = -1
+        if token_src is not None:
+            src[:len(entries)] = np.asarray(token_src, dtype=np.int32)
         r = 0
         cu[0] = 0
         wi = 0

@@ -121,6 +121,17 @@ def sample_host(logits: np.ndarray, cfg: SamplerConfig, u: float) -> int:
     return int(allowed[hit[0]]) if hit.size else int(allowed[-1])
 
 
+class PendingSample:
+    """Ids that a sampling kernel has written on the device and that are on their way to the host."""
+
+    def __init__(self, device_tokens: torch.Tensor, pinned: torch.Tensor, event, rows: int):
+        self.device_tokens, self._pinned, self._event, self.rows = device_tokens, pinned, event, rows
+
+    def tokens(self) -> List[int]:
+        self._event.synchronize()
+        return self._pinned[:self.rows].tolist()
+
+
 class Sampler:
     """Samples one token per row of a [rows, vocab] float32 logits tensor."""
 
@@ -129,6 +140,44 @@ class Sampler:
         self.repeat_penalty = float(repeat_penalty)
         self.repeat_last_n = int(repeat_last_n) if repeat_last_n else 64   # 0 means 64 (session.go:87-91)
         self._out: Optional[torch.Tensor] = None
+        self._outs = None
+        self._turn = 0
+
+    @property
+    def device_only(self) -> bool:
+        """True when every row can be sampled by a kernel and no history is needed."""
+        return self.cfg.on_device and not self.penalised
+
+    def sample_async(self, logits: torch.Tensor, streams: Sequence[int], steps: Sequence[int]) -> PendingSample:
+        """Greedy or temperature sampling on the device without waiting for the result: the ids stay in
+        a device buffer (the next decode step can take them from there) and are copied to pinned host
+        memory behind the kernel.  Two sets of buffers are used in turn, so one sample may be outstanding
+        while the next is enqueued."""
+        if not (logits.is_cuda and self.device_only):
+            raise ValueError("sample_async needs CUDA logits and a sampler configuration that runs on the device")
+        from ..csrc import kernels as K
+        rows = len(streams)
+        cap = max(rows, 64)
+        if self._outs is None or self._outs[0][0].numel() < cap:
+            self._outs = [(torch.empty(cap, dtype=torch.int32, device=logits.device),
+                           torch.empty(cap, dtype=torch.int32, pin_memory=True),
+                           torch.empty(cap, dtype=torch.float64, pin_memory=True),
+                           torch.empty(cap, dtype=torch.float64, device=logits.device),
+                           torch.empty(cap, dtype=torch.float32, device=logits.device)) for _ in range(2)]
+        out, pinned, u_host, u_dev, temps = self._outs[self._turn]
+        self._turn ^= 1
+        if self.cfg.greedy:
+            K.argmax(logits, out, rows)
+        else:
+            u_host[:rows] = torch.tensor([uniform01(self.cfg.seed, s, k) for s, k in zip(streams, steps)],
+                                         dtype=torch.float64)
+            u_dev[:rows].copy_(u_host[:rows], non_blocking=True)
+            temps[:rows].fill_(float(self.cfg.temp))
+            K.sample(logits, temps, u_dev, out, rows)
+        pinned[:rows].copy_(out[:rows], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return PendingSample(out, pinned, ev, rows)
 
     @property
     def penalised(self) -> bool:
