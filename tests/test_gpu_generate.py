@@ -79,3 +79,47 @@ def test_long_decoding_and_first_tokens(tmp_path_factory, dtype):
             assert rel_err(got, oracle[i:i + 1]) < tol, i
     cache.close(s)
     cache.check()
+
+
+def test_one_step_ahead_loop_equals_the_plain_loop(tmp_path_factory):
+    """The entry point keeps the device one step ahead of the host (the next step starts from ids that are
+    still on the device).  Sequences that end on a stop token, on a callback or on the token limit while
+    the step after theirs is already running must give the same tokens as the step-by-step loop."""
+    import gogguf_b200 as gg
+    from gogguf_b200.engine import Model, Stepper
+    from gogguf_b200.engine.generate import Generator
+    folder = make_folder(tmp_path_factory.getbasetemp(), "B", "float32", scale=6.0)
+    cfg, w = read_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], n, 40 + n) for n in (9, 2, 17, 5)]
+    refs = [plain.generate_greedy(cfg, w, p, 14, wide=True) for p in prompts]
+    stop_tok = refs[0][5]
+    engine = gg.load(folder, gg.LoadOptions(dtype="float32", max_tokens=2048))
+    seen = []
+
+    def cb(i, t):
+        seen.append((i, t))
+        return not (i == 2 and len([1 for j, _ in seen if j == 2]) == 4)      # request 2 ends after 4 tokens
+
+    params = gg.GenerateParams(max_tokens=14, stop_token_ids=[stop_tok], on_token=cb)
+    ahead = engine.new_context().generate(prompts, params)
+    # the same requests through the eager stepper, which has no device-side token feed: the plain loop
+    model = engine.model
+    cache = model.new_cache(2048)
+    seen.clear()
+    slow = Generator(Stepper(model, cache), model.spec.vocab_size, model.spec.max_positions).generate(prompts, params)
+    for a, b in zip(ahead, slow):
+        assert a.tokens == b.tokens and a.finish_reason == b.finish_reason
+    # and against the plain implementation
+    def expected(i):
+        out = []
+        for k, t in enumerate(refs[i]):
+            if t == stop_tok:
+                return out, "stop"
+            out.append(t)
+            if i == 2 and len(out) == 4:
+                return out, "callback"
+        return out, "length"
+    for i, r in enumerate(ahead):
+        toks, why = expected(i)
+        assert r.tokens == toks and r.finish_reason == why, i
+    assert cache.live_slots == 0

@@ -76,3 +76,18 @@ def test_captured_decode_steps_equal_eager_steps(tmp_path_factory, name, dtype):
             assert st.replays > 20 and len(st._graphs) >= 2       # batch 3 (bucket 4, one padding row), then smaller
     for key, v in results["Stepper"].items():
         assert rel_err(results["GraphStepper"][key][None], v[None]) < (1e-6 if dtype == "float32" else 2e-2), key
+
+
+def test_bfloat16_run_of_a_folder_stored_in_32_bit(tmp_path_factory):
+    """A tensor stored in 32-bit stays 32-bit: under dtype=bfloat16 the activations are bfloat16 and the
+    products with such matrices run on the mixed-operand kernel.  The result must be as close to the plain
+    implementation as any bfloat16 run."""
+    folder = make_folder(tmp_path_factory.getbasetemp(), "M", "float32")
+    cfg, w = read_folder(folder)
+    tokens = random_tokens(cfg["vocab_size"], 150, seed=8)
+    want = plain.forward(cfg, w, tokens, wide=True)
+    got = engine_whole(folder, "bfloat16", tokens)
+    assert rel_err(got, want) < TOL_BF16
+    from gogguf_b200.engine import Model
+    m = Model.load(folder, dtype="bfloat16")
+    assert m.blocks[0].mixer.qkv.weight.dtype == torch.float32 and m.blocks[0].mixer.qkv._fast is None
