@@ -5,6 +5,7 @@
     gogguf_b200 info -m DIR
     gogguf_b200 inspect DIR
     gogguf_b200 random -c CONFIG.json -o DIR [--seed 0] [--dtype bfloat16] [--std S] [--norm-std S]
+    gogguf_b200 compare A.f32 B.f32 [--tol 1e-4] [--vocab V]
 
 `run` keeps the reference's option names and defaults (cmd/gogguf/run.go:17-34).  A prompt is a list
 of token ids (the tokenizer is outside this library); several -p make a batch.  Dropped: -hf
@@ -107,6 +108,28 @@ def cmd_random(a) -> int:
     return 0
 
 
+def cmd_compare(a) -> int:
+    """Difference of two logits dumps (files of little-endian float32, as trace_run writes them): the
+    figures of the reference's DiffLogits (pkg/debug/diff.go:17-48): max abs, mean abs, rmse, count over
+    a tolerance, and whether the arg-max rows agree."""
+    import numpy as np
+    x = np.fromfile(a.a, dtype="<f4")
+    y = np.fromfile(a.b, dtype="<f4")
+    if x.size != y.size:
+        print(f"sizes differ: {x.size} and {y.size} values", file=sys.stderr)
+        return 1
+    d = np.abs(x.astype(np.float64) - y.astype(np.float64))
+    print(f"values: {x.size}")
+    print(f"max abs diff: {d.max() if d.size else 0.0:.6g}")
+    print(f"mean abs diff: {d.mean() if d.size else 0.0:.6g}")
+    print(f"rmse: {float(np.sqrt((d * d).mean())) if d.size else 0.0:.6g}")
+    print(f"over tolerance {a.tol:g}: {int((d > a.tol).sum())}")
+    if a.vocab and x.size % a.vocab == 0:
+        same = (x.reshape(-1, a.vocab).argmax(1) == y.reshape(-1, a.vocab).argmax(1))
+        print(f"rows with the same arg-max: {int(same.sum())} of {same.size}")
+    return 0 if (d <= a.tol).all() else 2
+
+
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="gogguf_b200", description="Qwen3 inference on B200")
     sub = ap.add_subparsers(dest="cmd")
@@ -141,6 +164,12 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--std", type=float, default=None, help="std of matrices (default: initializer_range)")
     g.add_argument("--norm-std", type=float, default=0.02, help="std of norm weights around 1")
     g.set_defaults(fn=cmd_random)
+    c = sub.add_parser("compare", help="difference of two logits dumps (.f32 files)")
+    c.add_argument("a")
+    c.add_argument("b")
+    c.add_argument("--tol", type=float, default=1e-4)
+    c.add_argument("--vocab", type=int, default=0, help="row length, to compare arg-max per row")
+    c.set_defaults(fn=cmd_compare)
     return ap
 
 

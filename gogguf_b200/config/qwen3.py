@@ -191,6 +191,25 @@ class Qwen3Config:
     def kv_bytes_per_token(self, itemsize: int = 2) -> int:
         return 2 * self.num_hidden_layers * self.kv_width * itemsize
 
+    # -------------------------------------------------------------- aliases
+    def tensor_aliases(self) -> Dict[str, str]:
+        """The reference's GGUF tensor names (pkg/model/qwen3/tensors.go:19-34, norms.go:16-45) mapped to
+        the checkpoint names; a folder may use either."""
+        m = {"token_embd.weight": "model.embed_tokens.weight", "output_norm.weight": "model.norm.weight",
+             "output.weight": "lm_head.weight"}
+        per_layer = {
+            "attn_norm.weight": "input_layernorm.weight", "ffn_norm.weight": "post_attention_layernorm.weight",
+            "attn_q.weight": "self_attn.q_proj.weight", "attn_k.weight": "self_attn.k_proj.weight",
+            "attn_v.weight": "self_attn.v_proj.weight", "attn_output.weight": "self_attn.o_proj.weight",
+            "attn_q_norm.weight": "self_attn.q_norm.weight", "attn_k_norm.weight": "self_attn.k_norm.weight",
+            "ffn_gate.weight": "mlp.gate_proj.weight", "ffn_up.weight": "mlp.up_proj.weight",
+            "ffn_down.weight": "mlp.down_proj.weight",
+        }
+        for i in range(self.num_hidden_layers):
+            for a, b in per_layer.items():
+                m[f"blk.{i}.{a}"] = f"model.layers.{i}.{b}"
+        return m
+
     # ---------------------------------------------------------------- spec
     def to_spec(self) -> ModelSpec:
         """Block structure of the reference's forwardBlock (pkg/model/qwen3/model.go:198-288)."""

@@ -115,3 +115,40 @@ def test_random_mode_is_seeded_and_shaped(tmp_path):
     assert abs(q.std().item() - 0.03) < 0.003 and abs(q.mean().item()) < 0.003
     n = wa["model.layers.1.input_layernorm.weight"]
     assert abs(n.mean().item() - 1.0) < 0.03
+
+
+def test_gguf_style_names_and_sharded_folders(tmp_path):
+    """A folder may name its tensors as the reference's GGUF files do, and may be split into shards."""
+    cfg = config_from_dict(TINY_B)
+    folder = str(tmp_path / "m")
+    write_random_model(cfg, 3, folder, dtype="float32")
+    _, w = read_folder(folder)
+    back = {v: k for k, v in cfg.tensor_aliases().items()}
+    renamed = {back[k]: v for k, v in w.items()}
+    assert "blk.2.attn_q_norm.weight" in renamed and "token_embd.weight" in renamed and "output.weight" in renamed
+    os.remove(os.path.join(folder, "model.safetensors"))
+    names = sorted(renamed)
+    half = len(names) // 2
+    write_safetensors(os.path.join(folder, "model-00001-of-00002.safetensors"), {n: renamed[n] for n in names[:half]})
+    write_safetensors(os.path.join(folder, "model-00002-of-00002.safetensors"), {n: renamed[n] for n in names[half:]})
+    with open(os.path.join(folder, "model.safetensors.index.json"), "w") as f:
+        json.dump({"weight_map": {n: ("model-00001-of-00002.safetensors" if i < half else "model-00002-of-00002.safetensors")
+                                  for i, n in enumerate(names)}}, f)
+    got = load_tensors(folder, expected_tensors(cfg.to_spec()), aliases=cfg.tensor_aliases())
+    assert set(got) == set(w)
+    for k in w:
+        assert torch.equal(got[k], w[k])
+
+
+def test_compare_command(tmp_path, capsys):
+    import numpy as np
+    from gogguf_b200.cli import main
+    a = np.arange(12, dtype="<f4").reshape(3, 4)
+    b = a.copy()
+    b[1, 2] += 0.5
+    a.tofile(tmp_path / "a.f32")
+    b.tofile(tmp_path / "b.f32")
+    assert main(["compare", str(tmp_path / "a.f32"), str(tmp_path / "a.f32")]) == 0
+    assert main(["compare", str(tmp_path / "a.f32"), str(tmp_path / "b.f32"), "--vocab", "4"]) == 2
+    out = capsys.readouterr().out
+    assert "max abs diff: 0.5" in out and "over tolerance 0.0001: 1" in out and "same arg-max: 3 of 3" in out
