@@ -40,6 +40,12 @@ QWEN3_8B = dict(
     intermediate_size=12288, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
     tie_word_embeddings=False, max_position_embeddings=4096, initializer_range=0.02,
 )
+# BASELINE.json configs[3] and configs[4]: the layer sizes of the 14B and 32B shapes (same vocabulary and rotary base)
+SHAPES = {
+    "8b": {},
+    "14b": dict(num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, intermediate_size=17408),
+    "32b": dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, intermediate_size=25600),
+}
 PROMPT_LEN = 2048
 CONTEXT = 4096
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -141,7 +147,8 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes: the 8B shape is the contract's")
+    ap.add_argument("--layers", type=int, default=0,
                     help="fewer layers than the configuration has (same layer sizes); named in config")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
@@ -168,7 +175,10 @@ def main():
 
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
-    cdict = dict(QWEN3_8B, num_hidden_layers=a.layers)
+    base = dict(QWEN3_8B, **SHAPES[a.shape])
+    if a.layers <= 0:
+        a.layers = base["num_hidden_layers"]
+    cdict = dict(base, num_hidden_layers=a.layers)
     cfg = config_from_dict(cdict)
     pk = peaks()
     t0 = time.time()
@@ -291,14 +301,14 @@ def main():
 
     achieved = main_run["bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9
     line = {
-        "metric": "Qwen3-8B bf16 decode tok/s @ batch 8 (points: batch 1/64; prefill tok/s @ 2,048 tokens)",
+        "metric": f"Qwen3-{a.shape.upper()} bf16 decode tok/s @ batch {a.batch} (points: batch 1/64; prefill tok/s @ 2,048 tokens)",
         "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02), norm weights 1",
         "impl": "ours",
         "config": {
-            "model": "Qwen3-8B shape", "layers": a.layers, "layers_of_config": QWEN3_8B["num_hidden_layers"],
+            "model": f"Qwen3-{a.shape.upper()} shape", "layers": a.layers, "layers_of_config": base["num_hidden_layers"],
             "hidden": cdict["hidden_size"], "q_heads": cdict["num_attention_heads"],
             "kv_heads": cdict["num_key_value_heads"], "head_dim": cdict["head_dim"],
             "intermediate": cdict["intermediate_size"], "vocab": cdict["vocab_size"],
