@@ -1,5 +1,5 @@
 // Row-wise and element-wise kernels: embedding gather, RMSNorm, rotary tables,
-// fused per-head QK-norm + rotary + cache write, SwiGLU, residual add.
+// fused per-head QK-norm + rotary + cache write, SwiGLU, residual add, row statistics.
 //
 // They replace the reference's rmsnorm / rope_heads / swiglu / add_inplace PTX
 // kernels (pkg/gpu/cuda/ptx.go:428-496, 498-564, 634-677, 891-924), which run
@@ -131,6 +131,44 @@ GG_API gg_rmsnorm(const float* x, const int* rows, const float* w, void* out, in
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     GG_DISPATCH_DTYPE(out_dtype, TO,
         gg_launch(rmsnorm_kernel<TO>, dim3(R), dim3(threads), 0, stream, 1, x, rows, w, (TO*)out, H, eps));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- row statistics
+// What a product with a folded RMSNorm reads instead of the normalised rows: xhat = bfloat16(x) and,
+// per row, the sums of squares over blocks of 128 columns (ceil(H / 128) partial sums).  The products
+// that add into the residual stream write both themselves; this kernel makes them where no such
+// product came before (after the embedding, after a part that does not emit them).
+__global__ void __launch_bounds__(128) row_stats_kernel(const float* __restrict__ x, bf16* __restrict__ xhat,
+                                                        float* __restrict__ ssq, int H, int parts) {
+    pdl_launch();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int part = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int t = blockIdx.y;
+    if (part >= parts) return;
+    const int c0 = part * 128 + lane * 4;
+    const float* xr = x + (size_t)t * H + c0;
+    bf16* hr = xhat + (size_t)t * H + c0;
+    float ss = 0.f;
+    if (c0 + 4 <= H && ((((uintptr_t)xr) & 15) == 0) && ((((uintptr_t)hr) & 7) == 0)) {
+        const float4 v = *reinterpret_cast<const float4*>(xr);
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2*>(hr) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+    } else {
+        for (int j = 0; j < 4; ++j)
+            if (c0 + j < H) { const float v = xr[j]; ss = fmaf(v, v, ss); hr[j] = __float2bfloat16_rn(v); }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) ssq[(size_t)t * parts + part] = ss;
+}
+
+GG_API gg_row_stats(const float* x, void* xhat, float* ssq, int T, int H, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || T > 65535) return GG_ERR_ARG;
+    const int parts = (H + 127) / 128;
+    gg_launch(row_stats_kernel, dim3((parts + 3) / 4, T), dim3(128), 0, stream, 1, x, (bf16*)xhat, ssq, H, parts);
     return gg_last_error();
 }
 

@@ -127,13 +127,117 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
 
+// RMSNorm folded into the products around it.  The norm's weight is multiplied into the next matrix
+// when the model is built, the activations are the bfloat16 copy of the raw residual, and what is left
+// of the norm is one factor per token, applied to the float32 accumulator:
+//   in_ssq   per token, `in_parts` partial sums of squares of the residual row this product reads;
+//            factor = 1 / sqrt(sum(parts) * in_inv_k + eps).  Null: no factor.
+//   out_ssq  (float32-add output only) after out += product, the partial sums of squares of the updated
+//            rows, one per 128 output columns (ceil(N / 128) per token), and out_xhat, their bfloat16
+//            copy [M, N] (row stride N): what the next product and its factor need.  Null: nothing.
+// Sums are float32 and their order is fixed, so results do not depend on timing.
+struct NormIO {
+    const float* in_ssq;
+    int in_parts;
+    float in_inv_k;
+    float eps;
+    float* out_ssq;
+    bf16* out_xhat;
+};
+
+// One thread computes its token's factor (four running sums keep the loads independent).
+__device__ __forceinline__ float norm_factor(const NormIO& nio, int token) {
+    if (nio.in_ssq == nullptr) return 1.0f;
+    const float* p = nio.in_ssq + (size_t)token * nio.in_parts;
+    float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
+    int i = 0;
+    for (; i + 4 <= nio.in_parts; i += 4) { t0 += p[i]; t1 += p[i + 1]; t2 += p[i + 2]; t3 += p[i + 3]; }
+    for (; i < nio.in_parts; ++i) t0 += p[i];
+    return 1.0f / sqrtf(((t0 + t1) + (t2 + t3)) * nio.in_inv_k + nio.eps);
+}
+// A whole warp computes one token's factor; every lane gets it.
+__device__ __forceinline__ float norm_factor_warp(const NormIO& nio, int token, int lane) {
+    if (nio.in_ssq == nullptr) return 1.0f;
+    const float* p = nio.in_ssq + (size_t)token * nio.in_parts;
+    float t = 0.f;
+    for (int i = lane; i < nio.in_parts; i += 32) t += p[i];
+    t = warp_sum(t);
+    return 1.0f / sqrtf(t * nio.in_inv_k + nio.eps);
+}
+
+// Sixteen consecutive accumulator columns r[0..15] of output row gi, starting at column gj0 (a multiple
+// of 16), already multiplied by the row's factor.  `ss` carries the sum of squares across a 128-column part.
+__device__ __forceinline__ void store_row_chunk16(const uint32_t* r, int gi, int gj0, int N, void* __restrict__ out,
+                                                  int out_mode, long long ldo, const NormIO& nio, float& ss) {
+    const size_t o = (size_t)gi * ldo + gj0;
+    const bool whole = gj0 + 16 <= N;
+    if (out_mode == OUT_BF16) {
+        bf16* op = (bf16*)out + o;
+        if (whole && ((((uintptr_t)op) & 15) == 0)) {
+            uint32_t pk[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                pk[j] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            reinterpret_cast<uint4*>(op)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            reinterpret_cast<uint4*>(op)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (gj0 + j < N) op[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+        }
+        return;
+    }
+    float* op = (float*)out + o;
+    const bool stats = nio.out_ssq != nullptr && out_mode == OUT_F32_ACC;
+    bf16* xp = stats ? nio.out_xhat + (size_t)gi * N + gj0 : nullptr;
+    if (whole && ((((uintptr_t)op) & 15) == 0) && (!stats || (((uintptr_t)xp) & 15) == 0)) {
+        uint32_t pk[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+            float4* dst = reinterpret_cast<float4*>(op) + j;
+            if (out_mode == OUT_F32_ACC) {
+                const float4 old = *dst;
+                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+            }
+            *dst = v;
+            if (stats) {
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+                __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+                pk[2 * j] = *reinterpret_cast<uint32_t*>(&a);
+                pk[2 * j + 1] = *reinterpret_cast<uint32_t*>(&b);
+            }
+        }
+        if (stats) {
+            reinterpret_cast<uint4*>(xp)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            reinterpret_cast<uint4*>(xp)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (gj0 + j < N) {
+                float v = __uint_as_float(r[j]);
+                if (out_mode == OUT_F32_ACC) v += op[j];
+                op[j] = v;
+                if (stats) { ss = fmaf(v, v, ss); xp[j] = __float2bfloat16_rn(v); }
+            }
+    }
+    if (stats && (((gj0 & 127) == 112) || gj0 + 16 >= N)) {
+        nio.out_ssq[(size_t)gi * ((N + 127) / 128) + (gj0 >> 7)] = ss;
+        ss = 0.f;
+    }
+}
+
 // Epilogue of the normal orientation for one thread: its row `gi` of the output, the 256 accumulator
 // columns of tile column `tn` starting at tensor-memory address `taddr` (lane already selected).
 // OUT_SWIGLU: the weight rows were interleaved in blocks of 64 gate rows and 64 up rows, so columns
 // [0,64) and [128,192) of the tile are gates and the 64 columns after each are their ups; the output
 // row has N / 2 columns.
 __device__ __forceinline__ void epilogue_row_256(uint32_t taddr, int gi, int tn, int M, int N, void* __restrict__ out,
-                                                 int out_mode, long long ldo) {
+                                                 int out_mode, long long ldo, const NormIO& nio, float sc) {
     constexpr int BN = 256;
     if (out_mode == OUT_SWIGLU) {
 #pragma unroll 1
@@ -155,8 +259,8 @@ __device__ __forceinline__ void epilogue_row_256(uint32_t taddr, int gi, int tn,
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         __nv_bfloat162 h2 = __floats2bfloat162_rn(
-                            silu_mul(__uint_as_float(g[2 * j]), __uint_as_float(u[2 * j])),
-                            silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(u[2 * j + 1])));
+                            silu_mul(__uint_as_float(g[2 * j]) * sc, __uint_as_float(u[2 * j]) * sc),
+                            silu_mul(__uint_as_float(g[2 * j + 1]) * sc, __uint_as_float(u[2 * j + 1]) * sc));
                         pk[j] = *reinterpret_cast<uint32_t*>(&h2);
                     }
                     reinterpret_cast<uint4*>(op)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
@@ -164,12 +268,13 @@ __device__ __forceinline__ void epilogue_row_256(uint32_t taddr, int gi, int tn,
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (ocol + j < nout) op[j] = __float2bfloat16_rn(silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j])));
+                        if (ocol + j < nout) op[j] = __float2bfloat16_rn(silu_mul(__uint_as_float(g[j]) * sc, __uint_as_float(u[j]) * sc));
                 }
             }
         }
         return;
     }
+    float ss = 0.f;          // running sum of squares of the updated row over 128 columns
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 16) {
         if (tn * BN + c0 >= N) break;
@@ -177,48 +282,11 @@ __device__ __forceinline__ void epilogue_row_256(uint32_t taddr, int gi, int tn,
         tmem_ld16(taddr + (uint32_t)c0, r);
         tmem_ld_wait();
         if (gi >= M) continue;
-        const int gj0 = tn * BN + c0;
-        const size_t o = (size_t)gi * ldo + gj0;
-        const bool whole = gj0 + 16 <= N;
-        if (out_mode == OUT_BF16) {
-            bf16* op = (bf16*)out + o;
-            if (whole && ((((uintptr_t)op) & 15) == 0)) {
-                uint32_t pk[8];
+        if (nio.in_ssq != nullptr) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                    pk[j] = *reinterpret_cast<uint32_t*>(&h2);
-                }
-                reinterpret_cast<uint4*>(op)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                reinterpret_cast<uint4*>(op)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (gj0 + j < N) op[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-            }
-        } else {
-            float* op = (float*)out + o;
-            if (whole && ((((uintptr_t)op) & 15) == 0)) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                           __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                    float4* dst = reinterpret_cast<float4*>(op) + j;
-                    if (out_mode == OUT_F32_ACC) {
-                        const float4 old = *dst;
-                        v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
-                    }
-                    *dst = v;
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (gj0 + j < N) {
-                        if (out_mode == OUT_F32_ACC) op[j] += __uint_as_float(r[j]);
-                        else op[j] = __uint_as_float(r[j]);
-                    }
-            }
+            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * sc);
         }
+        store_row_chunk16(r, gi, tn * BN + c0, N, out, out_mode, ldo, nio, ss);
     }
 }
 
@@ -228,11 +296,12 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local_addr, uint32_t rank) {
     uint32_t remote;
-    float v;
+    float4 v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
     return v;
 }
 
@@ -243,7 +312,7 @@ template <int BN, int STAGES, bool SWAP, int MINB>
 __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
     void* __restrict__ out, int out_mode, long long ldo, int M, int N, int K, int kb_per_split,
-    float* __restrict__ partial, int cluster_reduce, int* __restrict__ status) {
+    float* __restrict__ partial, int cluster_reduce, int* __restrict__ status, const NormIO nio) {
     constexpr int B_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     extern __shared__ uint8_t smem_raw[];
@@ -251,6 +320,11 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* accum = empty + STAGES;
+    // the tile goes through shared memory when K splits are added inside the cluster, for the fused
+    // activation, and (decode form) whenever a norm is folded into this product
+    // (only the decode form splits K or fuses the activation; the launcher sees to that)
+    const bool staged = SWAP && (cluster_reduce || out_mode == OUT_SWIGLU ||
+                                 (partial == nullptr && (nio.in_ssq != nullptr || nio.out_ssq != nullptr)));
     uint32_t* tmem_slot = (uint32_t*)(accum + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
@@ -332,19 +406,21 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
         // epilogue: warp w reads tensor-memory lanes 32*(w%4) .. +31 (row i of D is lane i)
         const int q = warp & 3;
         const int row = q * 32 + lane;           // row of the D tile held by this thread
+        const int gi = tile_a * BM + row;        // global row of D (A side)
+        const int RA = SWAP ? N : M, RB = SWAP ? M : N;
         pdl_wait();                              // the output may still be in use by earlier kernels
+        const float sc = (!SWAP && gi < RA) ? norm_factor(nio, gi) : 1.0f;
         mbar_wait(accum, 0, abort_flag, status, 3);
         if (!*abort_flag) {
             tc_fence_after();
-            const int gi = tile_a * BM + row;    // global row of D (A side)
-            const int RA = SWAP ? N : M, RB = SWAP ? M : N;
+            float ss = 0.f;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 if (tile_b * BN + c0 >= RB) break;          // whole warp agrees: columns beyond the extent
                 uint32_t r[16];
                 tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
                 tmem_ld_wait();
-                if (cluster_reduce || out_mode == OUT_SWIGLU) {
+                if (staged) {
                     // own partial sums to own shared memory, [column][row]: the pipeline stages are free now
                     float* stage = reinterpret_cast<float*>(smem);
 #pragma unroll
@@ -378,47 +454,11 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                     }
                 } else {
                     // out[m = gi][n = gj0 .. gj0+15]: 16 consecutive n per thread
-                    const size_t o = (size_t)gi * ldo + gj0;
-                    const bool whole = gj0 + 16 <= RB;
-                    if (out_mode == OUT_BF16) {
-                        bf16* op = (bf16*)out + o;
-                        if (whole && ((((uintptr_t)op) & 15) == 0)) {
-                            uint32_t pk[8];
+                    if (nio.in_ssq != nullptr) {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                                pk[j] = *reinterpret_cast<uint32_t*>(&h2);
-                            }
-                            reinterpret_cast<uint4*>(op)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                            reinterpret_cast<uint4*>(op)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (gj0 + j < RB) op[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-                        }
-                    } else {
-                        float* op = (float*)out + o;
-                        if (whole && ((((uintptr_t)op) & 15) == 0)) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                                float4* dst = reinterpret_cast<float4*>(op) + j;
-                                if (out_mode == OUT_F32_ACC) {
-                                    const float4 old = *dst;
-                                    v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
-                                }
-                                *dst = v;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (gj0 + j < RB) {
-                                    if (out_mode == OUT_F32_ACC) op[j] += __uint_as_float(r[j]);
-                                    else op[j] = __uint_as_float(r[j]);
-                                }
-                        }
+                        for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * sc);
                     }
+                    store_row_chunk16(r, gi, gj0, N, out, out_mode, ldo, nio, ss);
                 }
             }
         }
@@ -426,50 +466,94 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
 
     tc_fence_before();
     __syncthreads();
-    if (cluster_reduce || out_mode == OUT_SWIGLU) {
+    if (staged) {
         // Every CTA of the cluster passes both barriers exactly once, whatever happened before.
         if (cluster_reduce) cluster_sync_all();
-        if (!*abort_flag && out_mode == OUT_SWIGLU) {
-            // gate rows 0..63 and up rows 64..127 of this tile give 64 output features (decode form only)
+        if (!*abort_flag && SWAP) {
+            // Decode form: a warp per token.  Each lane adds four consecutive features of the 128 of this
+            // tile over the cluster's ranks, in rank order, then the epilogue of the output mode.
             const int S = cluster_reduce ? (int)gridDim.z : 1;
-            const int RB = M;
-            const int cols = min(BN, RB - tile_b * BN);
-            const int E = cols * 64;
+            const int cols = min(BN, M - tile_b * BN);
             const uint32_t stage = smem_u32(smem);
-            const int nout = N / 2;
-            for (int e = split * NUM_THREADS + threadIdx.x; e < E; e += S * NUM_THREADS) {
-                const int j = e >> 6, i = e & 63;
-                float g = 0.f, u = 0.f;
+            constexpr int WARPS = NUM_THREADS / 32;
+            for (int j = split * WARPS + warp; j < cols; j += S * WARPS) {
+                const int gj = tile_b * BN + j;                      // token
+                float4 v[MAX_CLUSTER];
 #pragma unroll
-                for (int qq = 0; qq < MAX_CLUSTER; ++qq) {
-                    if (qq < S) {
-                        g += ld_cluster_f32(stage + 4u * (j * BM + i), qq);
-                        u += ld_cluster_f32(stage + 4u * (j * BM + 64 + i), qq);
+                for (int qq = 0; qq < MAX_CLUSTER; ++qq)
+                    v[qq] = qq < S ? ld_cluster_f32x4(stage + 4u * (uint32_t)(j * BM + 4 * lane), qq)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int qq = 0; qq < MAX_CLUSTER; ++qq) { acc.x += v[qq].x; acc.y += v[qq].y; acc.z += v[qq].z; acc.w += v[qq].w; }
+                if (nio.in_ssq != nullptr) {
+                    const float sc = norm_factor_warp(nio, gj, lane);
+                    acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc;
+                }
+                if (out_mode == OUT_SWIGLU) {
+                    // lanes 0..15 hold gates of 64 features, lanes 16..31 their ups
+                    const float ux = __shfl_down_sync(0xffffffffu, acc.x, 16), uy = __shfl_down_sync(0xffffffffu, acc.y, 16);
+                    const float uz = __shfl_down_sync(0xffffffffu, acc.z, 16), uw = __shfl_down_sync(0xffffffffu, acc.w, 16);
+                    const int feat = tile_a * 64 + 4 * lane;
+                    if (lane < 16 && feat < N / 2) {                 // N / 2 is a multiple of 64 here
+                        bf16* op = (bf16*)out + (size_t)gj * ldo + feat;
+                        __nv_bfloat162 a = __floats2bfloat162_rn(silu_mul(acc.x, ux), silu_mul(acc.y, uy));
+                        __nv_bfloat162 b = __floats2bfloat162_rn(silu_mul(acc.z, uz), silu_mul(acc.w, uw));
+                        if ((((uintptr_t)op) & 7) == 0) {
+                            *reinterpret_cast<uint2*>(op) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+                        } else {
+                            op[0] = a.x; op[1] = a.y; op[2] = b.x; op[3] = b.y;
+                        }
+                    }
+                    continue;
+                }
+                const int gi0 = tile_a * BM + 4 * lane;              // first of this lane's four features
+                const bool stats = nio.out_ssq != nullptr && out_mode == OUT_F32_ACC;
+                float ss = 0.f;
+                if (gi0 < N) {
+                    const bool whole = gi0 + 4 <= N;
+                    const size_t o = (size_t)gj * ldo + gi0;
+                    float f[4] = {acc.x, acc.y, acc.z, acc.w};
+                    if (out_mode == OUT_BF16) {
+                        bf16* op = (bf16*)out + o;
+                        if (whole && (((uintptr_t)op) & 7) == 0) {
+                            __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+                            *reinterpret_cast<uint2*>(op) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+                        } else {
+#pragma unroll
+                            for (int t = 0; t < 4; ++t)
+                                if (gi0 + t < N) op[t] = __float2bfloat16_rn(f[t]);
+                        }
+                    } else {
+                        float* op = (float*)out + o;
+                        bf16* xp = stats ? nio.out_xhat + (size_t)gj * N + gi0 : nullptr;
+                        if (whole && (((uintptr_t)op) & 15) == 0 && (!stats || (((uintptr_t)xp) & 7) == 0)) {
+                            float4 w4 = make_float4(f[0], f[1], f[2], f[3]);
+                            if (out_mode == OUT_F32_ACC) {
+                                const float4 old = *reinterpret_cast<float4*>(op);
+                                w4.x += old.x; w4.y += old.y; w4.z += old.z; w4.w += old.w;
+                            }
+                            *reinterpret_cast<float4*>(op) = w4;
+                            if (stats) {
+                                ss = fmaf(w4.x, w4.x, ss); ss = fmaf(w4.y, w4.y, ss); ss = fmaf(w4.z, w4.z, ss); ss = fmaf(w4.w, w4.w, ss);
+                                __nv_bfloat162 a = __floats2bfloat162_rn(w4.x, w4.y), b = __floats2bfloat162_rn(w4.z, w4.w);
+                                *reinterpret_cast<uint2*>(xp) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+                            }
+                        } else {
+#pragma unroll
+                            for (int t = 0; t < 4; ++t)
+                                if (gi0 + t < N) {
+                                    float val = f[t];
+                                    if (out_mode == OUT_F32_ACC) val += op[t];
+                                    op[t] = val;
+                                    if (stats) { ss = fmaf(val, val, ss); xp[t] = __float2bfloat16_rn(val); }
+                                }
+                        }
                     }
                 }
-                const int feat = tile_a * 64 + i, gj = tile_b * BN + j;
-                if (feat < nout) ((bf16*)out)[(size_t)gj * ldo + feat] = __float2bfloat16_rn(silu_mul(g, u));
-            }
-        } else if (!*abort_flag) {
-            const int S = gridDim.z;
-            const int RA = SWAP ? N : M, RB = SWAP ? M : N;
-            const int cols = min(BN, RB - tile_b * BN);
-            const int E = cols * BM;
-            const uint32_t stage = smem_u32(smem);
-            for (int e = split * NUM_THREADS + threadIdx.x; e < E; e += S * NUM_THREADS) {
-                float v[MAX_CLUSTER];
-#pragma unroll
-                for (int qq = 0; qq < MAX_CLUSTER; ++qq) v[qq] = qq < S ? ld_cluster_f32(stage + 4u * e, qq) : 0.f;
-                float acc = 0.f;
-#pragma unroll
-                for (int qq = 0; qq < MAX_CLUSTER; ++qq) acc += v[qq];      // rank order, fixed
-                const int j = e / BM, i = e - j * BM;
-                const int gi = tile_a * BM + i, gj = tile_b * BN + j;
-                if (gi < RA) {
-                    const size_t o = SWAP ? (size_t)gj * ldo + gi : (size_t)gi * ldo + gj;
-                    if (out_mode == OUT_BF16) ((bf16*)out)[o] = __float2bfloat16_rn(acc);
-                    else if (out_mode == OUT_F32) ((float*)out)[o] = acc;
-                    else ((float*)out)[o] += acc;
+                if (stats) {
+                    ss = warp_sum(ss);                               // one 128-feature part per tile
+                    if (lane == 0) nio.out_ssq[(size_t)gj * ((N + 127) / 128) + tile_a] = ss;
                 }
             }
         }
@@ -542,7 +626,8 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long long ld, i
 template <int STAGES>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_persistent_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-    void* __restrict__ out, int out_mode, long long ldo, int M, int N, int K, int* __restrict__ status) {
+    void* __restrict__ out, int out_mode, long long ldo, int M, int N, int K, int* __restrict__ status,
+    const NormIO nio) {
     constexpr int BN = 256;
     constexpr int B_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -649,10 +734,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_persistent_kernel(
             const int tm = t % tiles_m, tn = t / tiles_m;
             const int buf = i & 1;
             const uint32_t aph = (uint32_t)(i >> 1) & 1u;
+            const int gi = tm * BM + row;
+            const float sc = gi < M ? norm_factor(nio, gi) : 1.0f;      // while the tile is still being multiplied
             if (!mbar_wait(&acc_full[buf], aph, abort_flag, status, 3)) break;
             tc_fence_after();
-            const int gi = tm * BM + row;
-            epilogue_row_256(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN), gi, tn, M, N, out, out_mode, ldo);
+            epilogue_row_256(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN), gi, tn, M, N, out, out_mode, ldo, nio, sc);
             tc_fence_before();
             mbar_arrive(&acc_empty[buf]);        // 128 arrivals free the accumulator for tile i + 2
         }
@@ -672,7 +758,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_persistent_kernel(
 }
 
 int launch_persistent(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N,
-                      int K, int* status, cudaStream_t stream) {
+                      int K, int* status, const NormIO& nio, cudaStream_t stream) {
     constexpr int STAGES = 4;
     constexpr int smem = STAGES * (A_BYTES + 256 * BK * 2) + 1024 + 256;
     static int sms = 0;
@@ -687,7 +773,7 @@ int launch_persistent(const CUtensorMap& ta, const CUtensorMap& tb, void* out, i
     }
     const int total = ((M + BM - 1) / BM) * ((N + 255) / 256);
     const int grid = total < sms ? total : sms;
-    return gg_launch(kern, dim3(grid), dim3(NUM_THREADS), smem, stream, 1, ta, tb, out, out_mode, ldo, M, N, K, status);
+    return gg_launch(kern, dim3(grid), dim3(NUM_THREADS), smem, stream, 1, ta, tb, out, out_mode, ldo, M, N, K, status, nio);
 }
 
 // ------------------------------------------------------------------------------------------- prefill form, CTA pairs
@@ -730,7 +816,8 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t rank
 template <int STAGES>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-    void* __restrict__ out, int out_mode, long long ldo, int M, int N, int K, int* __restrict__ status) {
+    void* __restrict__ out, int out_mode, long long ldo, int M, int N, int K, int* __restrict__ status,
+    const NormIO nio) {
     constexpr int BN = 256;                     // columns of the pair's tile (each CTA stages 128 of the B rows)
     constexpr int HALF_B_BYTES = 128 * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + HALF_B_BYTES;      // per CTA: 32 KB
@@ -842,10 +929,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
             const int tm = t % tiles_m, tn = t / tiles_m;
             const int buf = i & 1;
             const uint32_t aph = (uint32_t)(i >> 1) & 1u;
+            const int gi = tm * 256 + (int)rank * 128 + row;
+            const float sc = gi < M ? norm_factor(nio, gi) : 1.0f;      // while the tile is still being multiplied
             if (!mbar_wait(&acc_full[buf], aph, abort_flag, status, 3)) break;
             tc_fence_after();
-            const int gi = tm * 256 + (int)rank * 128 + row;
-            epilogue_row_256(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN), gi, tn, M, N, out, out_mode, ldo);
+            epilogue_row_256(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN), gi, tn, M, N, out, out_mode, ldo, nio, sc);
             tc_fence_before();
             mbar_arrive_cluster(&acc_empty[buf], 0);     // 256 arrivals in the leader free the accumulator pair
         }
@@ -866,7 +954,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
 }
 
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N,
-                int K, int* status, cudaStream_t stream) {
+                int K, int* status, const NormIO& nio, cudaStream_t stream) {
     constexpr int STAGES = 6;
     constexpr int smem = STAGES * (A_BYTES + 128 * BK * 2) + 1024 + 256;
     static int sms = 0;
@@ -882,12 +970,13 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out
     const int total = ((M + 255) / 256) * ((N + 255) / 256);
     int pairs = sms / 2;
     if (pairs > total) pairs = total;
-    return gg_launch2(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, stream, ta, tb, out, out_mode, ldo, M, N, K, status);
+    return gg_launch2(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, stream, ta, tb, out, out_mode, ldo, M, N, K, status, nio);
 }
 
 template <int BN, int STAGES, bool SWAP, int MINB>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N, int K,
-           int splits, int kb_per_split, float* partial, bool cluster, int* status, cudaStream_t stream) {
+           int splits, int kb_per_split, float* partial, bool cluster, int* status, const NormIO& nio,
+           cudaStream_t stream) {
     constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256;
     static_assert(STAGES * (A_BYTES + BN * BK * 2) >= BN * BM * 4, "the stages must hold a float32 tile");
     static bool configured = false;
@@ -901,8 +990,9 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode
     dim3 grid((RA + BM - 1) / BM, (RB + BN - 1) / BN, splits);
     float* part = (splits > 1 && !cluster) ? partial : nullptr;
     const int cl = (splits > 1 && cluster) ? 1 : 0;
+    if (!SWAP && (cl || out_mode == OUT_SWIGLU)) return GG_ERR_ARG;      // forms the normal orientation does not have
     return gg_launch(kern, grid, dim3(NUM_THREADS), smem, stream, cl ? splits : 1, ta, tb, out, out_mode, ldo, M, N, K,
-                     kb_per_split, part, cl, status);
+                     kb_per_split, part, cl, status, nio);
 }
 
 }  // namespace
@@ -933,9 +1023,9 @@ GG_API gg_gemm_tc_splits(int M, int N, int K, int use_cluster) {
 // use_cluster == 0: scratch must hold gg_gemm_tc_splits(M, N, K, 0) * M * N floats when that count is > 1.
 // status: one int on the device, zero-initialised by the caller; a non-zero value after the kernel
 // means a bounded wait ran out (1 producer, 2 issuer, 3 epilogue).
-GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, int N, int K, long long ldx,
-                  long long ldo, float* scratch, long long scratch_elems, int use_cluster, int* status,
-                  cudaStream_t stream) {
+static int gemm_tc_impl(const void* x, const void* w, void* out, int out_mode, int M, int N, int K, long long ldx,
+                        long long ldo, float* scratch, long long scratch_elems, int use_cluster, int* status,
+                        const NormIO& nio, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K % 8) != 0 || (ldx % 8) != 0 || ldx < K || out_mode < 0 || out_mode > 3) return GG_ERR_ARG;
     // out_mode 3: w holds blocks of 64 gate rows and 64 up rows in turn; out[M, N / 2] (bf16) = silu(gate) * up
@@ -954,10 +1044,10 @@ GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, 
         const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
         if ((rc = make_map(&ta, w, N, K, K, BM)) != 0) return rc;
         if ((rc = make_map(&tb, x, M, K, ldx, bn)) != 0) return rc;
-        if (bn == 16) rc = launch<16, 4, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
-        else if (bn == 32) rc = launch<32, 3, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
-        else if (bn == 64) rc = launch<64, 3, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
-        else rc = launch<128, 2, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, stream);
+        if (bn == 16) rc = launch<16, 4, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, stream);
+        else if (bn == 32) rc = launch<32, 3, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, stream);
+        else if (bn == 64) rc = launch<64, 3, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, stream);
+        else rc = launch<128, 2, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, stream);
     } else {
         const int bn = N > 128 ? 256 : 128;
         if ((rc = make_map(&ta, x, M, K, ldx, BM)) != 0) return rc;
@@ -967,9 +1057,9 @@ GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, 
         if (bn == 256 && use_pair) {
             // CTA pairs: A tiles of 128 rows per CTA as before, B staged in halves of 128 rows per CTA
             if ((rc = make_map(&tb, w, N, K, K, 128)) != 0) return rc;
-            rc = launch_pair(ta, tb, out, out_mode, ldo, M, N, K, status, stream);
-        } else if (bn == 256) rc = launch_persistent(ta, tb, out, out_mode, ldo, M, N, K, status, stream);
-        else rc = launch<128, 6, false, 1>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, false, status, stream);
+            rc = launch_pair(ta, tb, out, out_mode, ldo, M, N, K, status, nio, stream);
+        } else if (bn == 256) rc = launch_persistent(ta, tb, out, out_mode, ldo, M, N, K, status, nio, stream);
+        else rc = launch<128, 6, false, 1>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, false, status, nio, stream);
     }
     if (rc != 0) return rc;
     if (splits > 1 && !cluster) {
@@ -978,4 +1068,27 @@ GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, 
                          (const float*)scratch, out, out_mode, ldo, M, N, splits);
     }
     return 0;
+}
+
+GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, int N, int K, long long ldx,
+                  long long ldo, float* scratch, long long scratch_elems, int use_cluster, int* status,
+                  cudaStream_t stream) {
+    const NormIO none = {nullptr, 0, 0.f, 0.f, nullptr, nullptr};
+    return gemm_tc_impl(x, w, out, out_mode, M, N, K, ldx, ldo, scratch, scratch_elems, use_cluster, status, none, stream);
+}
+
+// The same product with an RMSNorm folded in on either side (K splits always inside clusters).
+//   in_ssq != null: x is the bfloat16 copy of the raw residual rows, w already carries the norm's weight,
+//     in_ssq[M, in_parts] holds partial sums of squares of those rows (in_parts = ceil(K / 128)); every
+//     accumulator row is multiplied by 1 / sqrt(sum / K + eps) before the output mode is applied.
+//   out_ssq != null (out_mode 2 only): after out += product the kernel also writes out_xhat[M, N]
+//     (bfloat16 copy of the updated rows, row stride N) and out_ssq[M, ceil(N / 128)], their partial sums
+//     of squares over blocks of 128 columns: the inputs of the next folded product.
+GG_API gg_gemm_tc_norm(const void* x, const void* w, void* out, int out_mode, int M, int N, int K, long long ldx,
+                       long long ldo, const float* in_ssq, int in_parts, float eps, float* out_ssq, void* out_xhat,
+                       int* status, cudaStream_t stream) {
+    if (in_ssq != nullptr && (in_parts != (K + 127) / 128 || !(eps > 0.f))) return GG_ERR_ARG;
+    if (out_ssq != nullptr && (out_mode != OUT_F32_ACC || out_xhat == nullptr)) return GG_ERR_ARG;
+    const NormIO nio = {in_ssq, in_parts, 1.0f / (float)K, eps, out_ssq, (bf16*)out_xhat};
+    return gemm_tc_impl(x, w, out, out_mode, M, N, K, ldx, ldo, nullptr, 0, 1, status, nio, stream);
 }

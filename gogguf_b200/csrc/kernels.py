@@ -67,6 +67,18 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
                                          R, H, float(eps), _stream())
 
 
+def row_stats(x: torch.Tensor, xhat: torch.Tensor, ssq: torch.Tensor) -> None:
+    """xhat = bfloat16(x) and ssq[t, p] = sum of x[t, 128 p : 128 p + 128]^2 for float32 rows x [T, H]."""
+    _need(x, torch.float32, "x")
+    _need(xhat, torch.bfloat16, "xhat")
+    _need(ssq, torch.float32, "ssq")
+    H = x.shape[-1]
+    T = x.numel() // H
+    if xhat.numel() != T * H or ssq.numel() != T * ((H + 127) // 128):
+        raise KernelError("row_stats: shapes disagree")
+    kernel("elementwise", "gg_row_stats")(_p(x), _p(xhat), _p(ssq), T, H, _stream())
+
+
 def rope_tables(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
     _need(positions, torch.int32, "positions")
     _need(inv_freq, torch.float64, "inv_freq")

@@ -78,24 +78,78 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
         int(bool(cluster)), st.data_ptr(), torch.cuda.current_stream().cuda_stream)
 
 
+def gemm_tc_norm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+                 m: Optional[int] = None, swiglu: bool = False, in_ssq: Optional[torch.Tensor] = None,
+                 eps: float = 0.0, out_ssq: Optional[torch.Tensor] = None,
+                 out_xhat: Optional[torch.Tensor] = None) -> None:
+    """`gemm_tc` with an RMSNorm folded in on either side (K splits inside clusters).
+
+    in_ssq [M, ceil(K / 128)]: x is the bfloat16 copy of raw residual rows and w carries the norm's weight;
+    every output row is multiplied by 1 / sqrt(sum(in_ssq[row]) / K + eps).  out_ssq [M, ceil(N / 128)] and
+    out_xhat [M, N] (accumulate only): the kernel also writes the bfloat16 copy of the updated rows and
+    their partial sums of squares, the inputs of the next folded product."""
+    N, K = w.shape
+    M = x.shape[0] if m is None else m
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc_norm takes bfloat16 operands")
+    if swiglu:
+        if out.dtype != torch.bfloat16 or accumulate or out.shape[-1] != N // 2:
+            raise KernelError("gemm_tc_norm: the fused SwiGLU writes bfloat16 [M, N / 2]")
+        mode = OUT_SWIGLU
+    elif out.dtype == torch.bfloat16:
+        if accumulate:
+            raise KernelError("gemm_tc_norm: sums are kept in float32")
+        mode = OUT_BF16
+    elif out.dtype == torch.float32:
+        mode = OUT_F32_ACC if accumulate else OUT_F32
+    else:
+        raise KernelError(f"gemm_tc_norm: output dtype {out.dtype}")
+    if x.stride(-1) != 1 or out.stride(-1) != 1 or not w.is_contiguous():
+        raise KernelError("gemm_tc_norm: operands must be row-major")
+    in_parts = 0
+    if in_ssq is not None:
+        in_parts = (K + 127) // 128
+        if in_ssq.dtype != torch.float32 or not in_ssq.is_contiguous() or in_ssq.shape[-1] != in_parts \
+                or in_ssq.numel() < M * in_parts:
+            raise KernelError("gemm_tc_norm: in_ssq must be float32 [M, ceil(K / 128)]")
+    if out_ssq is not None:
+        if not accumulate or out_xhat is None:
+            raise KernelError("gemm_tc_norm: row statistics are written by the accumulating form only")
+        if out_ssq.dtype != torch.float32 or out_ssq.shape[-1] != (N + 127) // 128 or not out_ssq.is_contiguous() \
+                or out_xhat.dtype != torch.bfloat16 or not out_xhat.is_contiguous() or out_xhat.shape[-1] != N \
+                or out_ssq.numel() < M * ((N + 127) // 128) or out_xhat.numel() < M * N:
+            raise KernelError("gemm_tc_norm: out_ssq is float32 [M, ceil(N / 128)], out_xhat bfloat16 [M, N]")
+    st = status_word(x.device)
+    kernel("gemm_tcgen05", "gg_gemm_tc_norm")(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), mode, M, N, K, x.stride(0), out.stride(0),
+        in_ssq.data_ptr() if in_ssq is not None else 0, in_parts, float(eps),
+        out_ssq.data_ptr() if out_ssq is not None else 0, out_xhat.data_ptr() if out_xhat is not None else 0,
+        st.data_ptr(), torch.cuda.current_stream().cuda_stream)
+
+
 def make_linear(weight: torch.Tensor, swiglu: bool = False) -> Optional[Callable]:
-    """A callable f(x, out, accumulate, m, ws) for this weight, or None if its sizes are not taken
-    (K must be a multiple of 8 so that rows start on 16-byte boundaries for TMA).  swiglu=True: the
-    weight is interleaved gate/up (see `interleave_gate_up`) and out is [M, N / 2]."""
+    """A callable f(x, out, accumulate, m, ws, in_ssq=None, eps=0.0, out_ssq=None, out_xhat=None) for this
+    weight, or None if its sizes are not taken (K must be a multiple of 8 so that rows start on 16-byte
+    boundaries for TMA).  swiglu=True: the weight is interleaved gate/up (see `interleave_gate_up`) and
+    out is [M, N / 2].  The keyword arguments are those of `gemm_tc_norm`; a call that has to fall back
+    to the plain kernel refuses them."""
     N, K = weight.shape
     if K % 8 != 0 or weight.data_ptr() % 16 != 0:
         return None
     if swiglu and (N % 128 != 0 or N < 256):
         return None
 
-    def run(x, out, accumulate, m, ws):
-        M = x.shape[0] if m is None else m
+    def run(x, out, accumulate, m, ws, in_ssq=None, eps=0.0, out_ssq=None, out_xhat=None):
+        folded = in_ssq is not None or out_ssq is not None
         if x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
-            if swiglu:
-                raise KernelError("fused SwiGLU product: activations must be 16-byte aligned rows")
+            if swiglu or folded:
+                raise KernelError("fused product: activations must be 16-byte aligned rows")
             from . import kernels as Kn
             Kn.gemm_plain(x, weight, out, accumulate, m)
             return
-        gemm_tc(x, weight, out, accumulate, m, None, cluster=True, swiglu=swiglu)
+        if folded:
+            gemm_tc_norm(x, weight, out, accumulate, m, swiglu, in_ssq, eps, out_ssq, out_xhat)
+        else:
+            gemm_tc(x, weight, out, accumulate, m, None, cluster=True, swiglu=swiglu)
 
     return run

@@ -7,6 +7,7 @@ them against what was found, and wires the blocks in schedule order.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Mapping, Optional, Tuple
 
 import torch
@@ -73,11 +74,13 @@ class Model:
     """Embedding, blocks in schedule order, final norm, head."""
 
     def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], dtype="bfloat16",
-                 device="cuda:0", fast: bool = True, config=None):
+                 device="cuda:0", fast: bool = True, config=None, fold_norms: Optional[bool] = None):
         spec.validate()
         self.spec = spec
         self.config = config
-        self.rt = Runtime(dtype=parse_dtype(dtype), device=torch.device(device), fast=fast)
+        if fold_norms is None:      # GOGGUF_B200_FOLD_NORMS=0 keeps every norm a kernel of its own
+            fold_norms = os.environ.get("GOGGUF_B200_FOLD_NORMS", "1") != "0"
+        self.rt = Runtime(dtype=parse_dtype(dtype), device=torch.device(device), fast=fast, fold_norms=fold_norms)
         found = {n: (t.dtype, tuple(t.shape)) for n, t in tensors.items()}
         check_tensors(expected_tensors(spec), found, where="model tensors")
         rt = self.rt
@@ -99,24 +102,26 @@ class Model:
 
     # ------------------------------------------------------------------ constructors
     @classmethod
-    def load(cls, folder: str, dtype="bfloat16", device="cuda:0", fast: bool = True) -> "Model":
+    def load(cls, folder: str, dtype="bfloat16", device="cuda:0", fast: bool = True,
+             fold_norms: Optional[bool] = None) -> "Model":
         """From a model folder: config.json picks the architecture, model.safetensors gives the tensors."""
         cfg = load_config(folder)
         spec = cfg.to_spec()
         aliases = cfg.tensor_aliases() if hasattr(cfg, "tensor_aliases") else None
         tensors = load_tensors(folder, expected_tensors(spec), device=device, aliases=aliases)
-        return cls(spec, tensors, dtype=dtype, device=device, fast=fast, config=cfg)
+        return cls(spec, tensors, dtype=dtype, device=device, fast=fast, config=cfg, fold_norms=fold_norms)
 
     @classmethod
     def random(cls, config, seed: int, dtype="bfloat16", device="cuda:0", fast: bool = True,
-               std: Optional[float] = None, norm_std: float = 0.0, store_dtype=None) -> "Model":
+               std: Optional[float] = None, norm_std: float = 0.0, store_dtype=None,
+               fold_norms: Optional[bool] = None) -> "Model":
         """Random weights made on the device, without a folder (for measurement)."""
         spec = config.to_spec()
         sd = parse_dtype(store_dtype) if store_dtype is not None else parse_dtype(dtype)
         tensors = random_tensors(expected_tensors(spec), seed,
                                  std if std is not None else getattr(config, "initializer_range", 0.02),
                                  norm_std, dtype=sd, device=device)
-        return cls(spec, tensors, dtype=dtype, device=device, fast=fast, config=config)
+        return cls(spec, tensors, dtype=dtype, device=device, fast=fast, config=config, fold_norms=fold_norms)
 
     # ------------------------------------------------------------------ cache
     def cache_requests(self) -> List[Request]:

@@ -193,7 +193,11 @@ class Stepper:
             if prep is not None:
                 prep(ctx)
         for i, e in enumerate(m.spec.schedule):
-            m.blocks[e.block].forward(x, ctx, self.cache.view(i), e.cache_of is None)
+            block = m.blocks[e.block]
+            block.forward(x, ctx, self.cache.view(i), e.cache_of is None)
+            stats = ctx.shared.get("row_stats")
+            if stats is not None and not getattr(block, "keeps_row_stats", False):
+                stats.fresh = False     # an arrangement that does not know of the statistics changed the rows
         return x
 
     def run_head(self, ctx: StepContext, x: torch.Tensor, rows: torch.Tensor, n_rows: int) -> torch.Tensor:

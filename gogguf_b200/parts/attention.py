@@ -78,6 +78,13 @@ class AttentionMixer:
             from ..csrc import fast_attention
             self._fast = fast_attention.try_make(self.nq, self.nkv, self.d, self.scale, self.window)
 
+    def absorb_norm(self, norm) -> bool:
+        """Take the block's pre-norm into the q/k/v projection; `forward` then gets RowStats as `h`."""
+        if not self.qkv.can_fold or norm.size != self.hidden:
+            return False
+        self.qkv.fold_input_norm(norm.weight, norm.eps)
+        return True
+
     def prepare(self, ctx: StepContext) -> None:
         self.position.tables(ctx)
 
@@ -100,4 +107,4 @@ class AttentionMixer:
         else:
             K.attention_plain(q, cache.k, cache.v, o, ctx.positions, ctx.seq_of_token, table,
                               cache.page_size, T, nq, nkv, d, self.scale, self.window)
-        self.o(o, residual, accumulate=True, ws=ctx.ws)
+        self.o(o, residual, accumulate=True, ws=ctx.ws, emit=ctx.shared.get("row_stats"))

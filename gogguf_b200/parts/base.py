@@ -23,6 +23,8 @@ class Runtime:
     dtype: torch.dtype
     device: torch.device
     fast: bool = True
+    # fast bfloat16 path only: a block's pre-norm is folded into the product that follows it (see RowStats)
+    fold_norms: bool = True
 
     def matrix(self, t: torch.Tensor) -> torch.Tensor:
         """A projection matrix as the compute path keeps it: float32 in the 32-bit path; in the
@@ -80,25 +82,84 @@ class StepContext:
     shared: Dict[Any, Any] = field(default_factory=dict)   # per-step values parts share (rotary tables)
 
 
+class RowStats:
+    """The residual stream as a product with a folded RMSNorm reads it.
+
+    RMSNorm(x) W^T = (x / rms(x)) (W diag(w))^T: the norm's weight w goes into the matrix once, when the
+    model is built; the product reads `xhat`, the bfloat16 copy of the raw float32 rows, and multiplies
+    each accumulator row by 1 / sqrt(sum(ssq[row]) / H + eps) in float32.  `ssq` holds, per row, the sums
+    of squares over blocks of 128 columns.  A product that adds into the residual stream can write both
+    for the rows it has just updated (`Linear(..., emit=stats)`), so in a chain of such products no norm
+    kernel runs at all.  `fresh` says whether xhat and ssq describe the residual rows as they are now:
+    a block clears it before a part writes to the residual, a product that emitted sets it, and
+    `ensure` runs the stand-alone kernel when it is not set (after the embedding, after a part that
+    does not emit).
+    """
+
+    def __init__(self, xhat: torch.Tensor, ssq: torch.Tensor):
+        self.xhat, self.ssq = xhat, ssq
+        self.fresh = False
+
+    def ensure(self, x: torch.Tensor) -> "RowStats":
+        if not self.fresh:
+            K.row_stats(x, self.xhat, self.ssq)
+            self.fresh = True
+        return self
+
+
 class Linear:
     """y = x W^T for a weight W[N, K]; float32 accumulation, optional add into a float32 output.
 
     The bfloat16 path uses the tcgen05 tensor-core kernel when the sizes allow it and the plain CUDA
     core kernel otherwise (and always in the 32-bit path and for a matrix stored in 32-bit).
+
+    `fold_input_norm` turns the projection into one that reads `RowStats` instead of normalised rows;
+    `emit=stats` asks an accumulating product to write the statistics of the rows it updates.
     """
 
-    def __init__(self, weight: torch.Tensor, rt: Runtime):
+    def __init__(self, weight: torch.Tensor, rt: Runtime, swiglu: bool = False):
         self.rt = rt
         self.weight = rt.matrix(weight)
         self.out_features, self.in_features = self.weight.shape
+        self.swiglu = swiglu
+        self.folded_eps: Optional[float] = None
         self._fast = None
         if rt.fast and rt.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
             from ..csrc import tcgen05_gemm
-            self._fast = tcgen05_gemm.make_linear(self.weight)
+            self._fast = tcgen05_gemm.make_linear(self.weight, swiglu=swiglu)
+        if swiglu and self._fast is None:
+            raise ValueError("Linear: the fused SwiGLU form needs the tensor-core kernel")
 
-    def __call__(self, x: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
-                 m: Optional[int] = None, ws: Optional[Workspace] = None) -> None:
+    @property
+    def can_fold(self) -> bool:
+        return self._fast is not None and self.rt.fold_norms
+
+    def fold_input_norm(self, norm_weight: torch.Tensor, eps: float) -> None:
+        """Multiply the norm's weight into the columns of this matrix (float32 product, rounded once)."""
+        if not self.can_fold:
+            raise ValueError("Linear: this projection has no tensor-core form to fold a norm into")
+        from ..csrc import tcgen05_gemm
+        w = (self.weight.float() * norm_weight.to(self.weight.device).float()[None, :]).to(torch.bfloat16).contiguous()
+        self.weight = w
+        self._fast = tcgen05_gemm.make_linear(w, swiglu=self.swiglu)
+        self.folded_eps = float(eps)
+
+    def __call__(self, x, out: torch.Tensor, accumulate: bool = False, m: Optional[int] = None,
+                 ws: Optional[Workspace] = None, emit: Optional[RowStats] = None) -> None:
+        kw = {}
+        if self.folded_eps is not None:
+            if not isinstance(x, RowStats):
+                raise TypeError("Linear: a projection with a folded norm reads RowStats, not normalised rows")
+            kw.update(in_ssq=x.ssq, eps=self.folded_eps)
+            x = x.xhat
+        elif isinstance(x, RowStats):
+            raise TypeError("Linear: RowStats given to a projection without a folded norm")
+        if (emit is not None and accumulate and self._fast is not None and x.dtype == torch.bfloat16
+                and x.data_ptr() != emit.xhat.data_ptr() and out.shape[-1] == emit.xhat.shape[-1]
+                and out.is_contiguous()):
+            kw.update(out_ssq=emit.ssq, out_xhat=emit.xhat)
+            emit.fresh = True
         if self._fast is not None and x.dtype == torch.bfloat16:
-            self._fast(x, out, accumulate, m, ws)
+            self._fast(x, out, accumulate, m, ws, **kw)
         else:
             K.gemm_plain(x, self.weight, out, accumulate, m)

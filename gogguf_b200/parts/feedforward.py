@@ -37,22 +37,27 @@ class SwiGLU:
             # gate and up rows interleaved in blocks of 64: the product's epilogue applies silu(gate) * up
             # and writes the activation directly, so the [T, 2 I] intermediate never exists
             from ..csrc import tcgen05_gemm
-            w = tcgen05_gemm.interleave_gate_up(g, u)
-            self.fused = tcgen05_gemm.make_linear(w, swiglu=True)
-            if self.fused is not None:
-                self.fused_weight = w
+            self.fused = Linear(tcgen05_gemm.interleave_gate_up(g, u), rt, swiglu=True)
         if self.fused is None:
             # gate rows first, then up rows: one product for both, then the activation kernel
             self.gate_up = Linear(torch.cat([g, u], dim=0), rt)
         self.down = Linear(weights["down_proj.weight"], rt)
 
-    def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
+    def absorb_norm(self, norm) -> bool:
+        """Take the block's pre-norm into the gate/up projection; `forward` then gets RowStats as `h`."""
+        first = self.fused if self.fused is not None else self.gate_up
+        if not first.can_fold or norm.size != self.hidden:
+            return False
+        first.fold_input_norm(norm.weight, norm.eps)
+        return True
+
+    def forward(self, h, residual: torch.Tensor, ctx: StepContext) -> None:
         T = ctx.n_tokens
         act = ctx.ws.get("ffn_act", (T, self.inter), self.rt.dtype)
-        if self.fused is not None and h.dtype == torch.bfloat16:
-            self.fused(h, act, False, None, ctx.ws)
+        if self.fused is not None:
+            self.fused(h, act, ws=ctx.ws)
         else:
             gu = ctx.ws.get("ffn_gate_up", (T, 2 * self.inter), self.rt.dtype)
             self.gate_up(h, gu, ws=ctx.ws)
             K.swiglu(gu, act, T, self.inter)
-        self.down(act, residual, accumulate=True, ws=ctx.ws)
+        self.down(act, residual, accumulate=True, ws=ctx.ws, emit=ctx.shared.get("row_stats"))

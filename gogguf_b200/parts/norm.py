@@ -14,6 +14,10 @@ from .registry import register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm:
+    # out = x / rms(x) * weight: a projection after it can take `weight` into its columns and apply
+    # 1 / rms(x) to its own output rows (parts.base.RowStats)
+    foldable = True
+
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
         return {"weight": TensorDecl(shape=(spec["size"],), init="ones_normal")}

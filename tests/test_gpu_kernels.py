@@ -242,6 +242,96 @@ def test_gemm_tcgen05_strided_rows_and_padding_rows():
     assert float(outbig[24:].abs().sum()) == 0 and float(outbig[:, 200:].abs().sum()) == 0
 
 
+def plain_row_stats(x):
+    """bfloat16 copy and per-128-column sums of squares of float32 rows (the plain statement of row_stats)."""
+    T, H = x.shape
+    parts = (H + 127) // 128
+    pad = torch.zeros(T, parts * 128, dtype=torch.float64, device=x.device)
+    pad[:, :H] = x.double()
+    return x.to(torch.bfloat16), (pad * pad).view(T, parts, 128).sum(-1)
+
+
+@pytest.mark.parametrize("T,H", [(1, 128), (5, 200), (64, 4096), (300, 1000), (3, 5128)])
+def test_row_stats(T, H):
+    g = torch.Generator(device=DEV).manual_seed(31)
+    x = torch.randn(T, H, device=DEV, generator=g) * 3
+    xh = torch.empty(T, H, device=DEV, dtype=torch.bfloat16)
+    ssq = torch.full((T, (H + 127) // 128), float("nan"), device=DEV)
+    K().row_stats(x, xh, ssq)
+    wh, ws = plain_row_stats(x)
+    assert torch.equal(xh, wh)
+    assert rel(ssq, ws) < 1e-6
+
+
+NORM_SHAPES = [(1, 128, 128), (8, 256, 512), (8, 4096, 4096), (17, 384, 1000), (64, 1000, 520), (128, 768, 2048),
+               (129, 256, 136), (300, 520, 264), (1024, 1024, 4096), (70, 96, 72), (5, 331, 104), (1000, 72, 48),
+               (260, 200, 64)]
+
+
+@pytest.mark.parametrize("M,N,K_", NORM_SHAPES)
+def test_gemm_tcgen05_with_folded_norm(M, N, K_):
+    """The product that reads raw rows and applies 1/rms in its epilogue, and the accumulating product that
+    also writes the next product's inputs; against the plain statement in float64."""
+    from gogguf_b200.csrc import tcgen05_gemm as tc
+    g = torch.Generator(device=DEV).manual_seed(33)
+    eps = 3e-5
+    resid = torch.randn(M, K_, device=DEV, generator=g) * torch.linspace(0.2, 5.0, M, device=DEV)[:, None]
+    w = (torch.randn(N, K_, device=DEV, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+    xh, ssq = plain_row_stats(resid)
+    ssq = ssq.float().contiguous()
+    factor = 1.0 / torch.sqrt((resid.double() ** 2).mean(-1, keepdim=True) + eps)
+    want = (xh.double() @ w.double().T) * factor
+    tol = 3e-6 + 2e-7 * math.sqrt(K_)
+    # (1) factor on the way in, each output mode
+    out = torch.full((M, N), float("nan"), device=DEV)
+    tc.gemm_tc_norm(xh, w, out, in_ssq=ssq, eps=eps)
+    tc.check_status(DEV)
+    assert rel(out, want) < tol
+    ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    tc.gemm_tc_norm(xh, w, ob, in_ssq=ssq, eps=eps)
+    assert rel(ob, want) < 5e-3
+    # (2) accumulate and emit the statistics of the updated rows
+    res = torch.randn(M, N, device=DEV, generator=g)
+    acc = res.clone()
+    oh = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    oss = torch.full((M, (N + 127) // 128), float("nan"), device=DEV)
+    tc.gemm_tc_norm(xh, w, acc, accumulate=True, in_ssq=ssq, eps=eps, out_ssq=oss, out_xhat=oh)
+    tc.check_status(DEV)
+    assert rel(acc, res.double() + want) < tol
+    wh, ws = plain_row_stats(acc)
+    assert torch.equal(oh, wh)
+    assert rel(oss, ws) < 1e-6
+    # (3) emit without a factor on the way in (the projection after attention)
+    acc2 = res.clone()
+    oh.fill_(float("nan")); oss.fill_(float("nan"))
+    tc.gemm_tc_norm(xh, w, acc2, accumulate=True, out_ssq=oss, out_xhat=oh)
+    assert rel(acc2, res.double() + xh.double() @ w.double().T) < tol
+    wh, ws = plain_row_stats(acc2)
+    assert torch.equal(oh, wh) and rel(oss, ws) < 1e-6
+    # same bits on a second call
+    again = torch.empty(M, N, device=DEV)
+    tc.gemm_tc_norm(xh, w, again, in_ssq=ssq, eps=eps)
+    assert torch.equal(again, out)
+
+
+@pytest.mark.parametrize("M,I,K_", [(1, 128, 128), (8, 12288, 512), (100, 640, 136), (300, 448, 264), (520, 1024, 1024)])
+def test_gemm_tcgen05_fused_swiglu_with_folded_norm(M, I, K_):
+    from gogguf_b200.csrc import tcgen05_gemm as tc
+    g = torch.Generator(device=DEV).manual_seed(35)
+    eps = 1e-6
+    resid = torch.randn(M, K_, device=DEV, generator=g) * 4
+    wg = (torch.randn(I, K_, device=DEV, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+    wu = (torch.randn(I, K_, device=DEV, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+    w = tc.interleave_gate_up(wg, wu)
+    xh, ssq = plain_row_stats(resid)
+    factor = 1.0 / torch.sqrt((resid.double() ** 2).mean(-1, keepdim=True) + eps)
+    out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    tc.gemm_tc_norm(xh, w, out, swiglu=True, in_ssq=ssq.float().contiguous(), eps=eps)
+    tc.check_status(DEV)
+    gd, ud = (xh.double() @ wg.double().T) * factor, (xh.double() @ wu.double().T) * factor
+    assert rel(out, gd / (1 + torch.exp(-gd)) * ud) < 6e-3
+
+
 # ------------------------------------------------------------------------------------------ attention
 def make_paged(seqs, nkv, d, dt, seed, n_pages=None, ps=64):
     """seqs: list of (context length after the step, new tokens).  Returns pools, table and per-sequence K, V."""

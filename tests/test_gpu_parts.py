@@ -89,7 +89,6 @@ def test_mixer_feed_forward_and_block_alone(dtype, cfg):
     mixer, ffn = mcls(b.mixer, mw, rt), fcls(b.feed_forward, fw, rt)
     norm1 = R.NORMS["rmsnorm"](b.mixer_norm, nw, rt)
     norm2 = R.NORMS["rmsnorm"](b.feed_forward_norm, nw, rt)
-    block = R.ARRANGEMENTS[b.arrangement](b, mixer, ffn, norm1, norm2, rt)
 
     cache = SequenceCache([mcls.cache_request(b.mixer)], [None], 1024, dtype=dtype, device=DEV)
     lens = [70, 3]
@@ -116,7 +115,10 @@ def test_mixer_feed_forward_and_block_alone(dtype, cfg):
     wantf = plain.swiglu_ffn(h.float(), fw["gate_proj.weight"].float(), fw["up_proj.weight"].float(),
                              fw["down_proj.weight"].float(), wide=True)
     assert rel_err(res.cpu().double() - x0.double(), wantf) < tol
-    # the whole block (same positions, so the cache rows are simply written again)
+    # the whole block (same positions, so the cache rows are simply written again); on the fast path the
+    # arrangement hands its norms to the parts, which from then on read the raw rows and their statistics
+    block = R.ARRANGEMENTS[b.arrangement](b, mixer, ffn, norm1, norm2, rt)
+    assert block.mixer_folded == block.feed_forward_folded == (dtype == torch.bfloat16)
     xb = x0.clone().to(DEV)
     block.forward(xb, ctx, cache.view(0), True)
     allw = {f"model.layers.{layer}.self_attn.{k}": v.float() for k, v in mw.items()}

@@ -8,9 +8,9 @@ from helpers import TINY, TOL_BF16, TOL_F32, make_folder, random_tokens, read_fo
 pytestmark = pytest.mark.gpu
 
 
-def engine_whole(folder, dtype, tokens, fast=True):
+def engine_whole(folder, dtype, tokens, fast=True, fold_norms=None):
     from gogguf_b200.engine import Model, StepEntry, Stepper
-    model = Model.load(folder, dtype=dtype, fast=fast)
+    model = Model.load(folder, dtype=dtype, fast=fast, fold_norms=fold_norms)
     cache = model.new_cache(max_tokens=1024)
     st = Stepper(model, cache)
     slot = cache.open()
@@ -42,6 +42,30 @@ def test_whole_bf16(tmp_path_factory, name):
     # the plain kernels on the same bfloat16 weights (the twins of the tensor-core kernels) agree too
     twin = engine_whole(folder, "bfloat16", tokens, fast=False)
     assert rel_err(twin, want) < TOL_BF16
+    # and the tensor-core path with every norm as a kernel of its own instead of folded into the products
+    unfolded = engine_whole(folder, "bfloat16", tokens, fold_norms=False)
+    assert rel_err(unfolded, want) < TOL_BF16
+    assert not torch.equal(unfolded, got)        # the two really are different routes
+
+
+def test_norms_are_folded_into_the_products_on_the_fast_path(tmp_path_factory):
+    from gogguf_b200.csrc import build
+    from gogguf_b200.engine import Model, StepEntry, Stepper
+    folder = make_folder(tmp_path_factory.getbasetemp(), "M", "bfloat16", scale=4.0)
+    counts = {}
+    for fold in (True, False):
+        model = Model.load(folder, dtype="bfloat16", fold_norms=fold)
+        assert all(b.mixer_folded == fold and b.feed_forward_folded == fold for b in model.blocks)
+        cache = model.new_cache(256)
+        st = Stepper(model, cache)
+        slot = cache.open()
+        st.step([StepEntry(slot, [1, 2, 3], want=[2])])
+        n0 = build.launch_count()
+        st.step([StepEntry(slot, [4], want=[0])])
+        counts[fold] = build.launch_count() - n0
+        cache.close(slot)
+    layers = len(model.blocks)
+    assert counts[False] - counts[True] == 2 * layers - 1      # two norms a layer less, one statistics kernel more
 
 
 @pytest.mark.parametrize("name,dtype", [("L", "bfloat16"), ("M", "bfloat16"), ("B", "float32")])
