@@ -245,6 +245,11 @@ def main():
         """The same through the generation loop of the entry point: host ids in, host ids out."""
         import gogguf_b200 as gg
         engine = gg.Engine(model, gg.LoadOptions(dtype="bfloat16", max_batch=batch))
+        # The prompts of the whole batch are prefilled in one step right before decoding starts, and the
+        # first decode steps after that burst run at a lower clock (under the power cap) for some tens of
+        # milliseconds; they are warm-up here, so that the timed steps are steady-state decoding as in
+        # `decode_run`, which pauses between its prefill and its timed region.
+        warmup = max(warmup, 32)
         room = PROMPT_LEN + warmup + steps + 8
         ctx = engine.new_context(max_tokens=batch * (-(-room // 64) * 64), max_batch=batch)
         prompts = [rand_tokens(PROMPT_LEN) for _ in range(batch)]
