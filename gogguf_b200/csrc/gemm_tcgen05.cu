@@ -41,7 +41,7 @@ constexpr int A_BYTES = BM * BK * 2;
 constexpr int NUM_THREADS = 192;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // about one second
 
-enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_SWIGLU = 3 };
+enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_SWIGLU = 3, OUT_QKV = 4 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -143,6 +143,29 @@ struct NormIO {
     float eps;
     float* out_ssq;
     bf16* out_xhat;
+};
+
+// The q/k/v projection of an attention layer with what follows it fused into the epilogue (decode form,
+// head size 128 = one head per 128-row weight tile): per-head RMSNorm of q and k with one shared weight
+// each, rotation of pairs (i, i + 64) by the step's cos/sin tables, q to its buffer, k (normed, rotated)
+// and v (raw) into the paged cache at the token's position.  Padding tokens (seq_of_token < 0) write
+// nothing to the cache; k_pool == null writes no cache at all.
+struct QkvIO {
+    bf16* q_out;                 // [M, nq * 128]
+    const float* qw;             // [128] or null: no norm
+    const float* kw;
+    float eps;
+    const float* cosv;           // [M, 64]
+    const float* sinv;
+    const int* positions;        // [M]
+    const int* seq_of_token;     // [M]
+    const int* page_table;       // [sequences, max_pages]
+    int max_pages;
+    int page_size;
+    bf16* k_pool;                // [pages, nkv, page_size, 128] of this layer
+    bf16* v_pool;
+    int nq;
+    int nkv;
 };
 
 // One thread computes its token's factor (four running sums keep the loads independent).
@@ -312,7 +335,7 @@ template <int BN, int STAGES, bool SWAP, int MINB>
 __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
     void* __restrict__ out, int out_mode, long long ldo, int M, int N, int K, int kb_per_split,
-    float* __restrict__ partial, int cluster_reduce, int* __restrict__ status, const NormIO nio) {
+    float* __restrict__ partial, int cluster_reduce, int* __restrict__ status, const NormIO nio, const QkvIO qio) {
     constexpr int B_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     extern __shared__ uint8_t smem_raw[];
@@ -323,7 +346,7 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     // the tile goes through shared memory when K splits are added inside the cluster, for the fused
     // activation, and (decode form) whenever a norm is folded into this product
     // (only the decode form splits K or fuses the activation; the launcher sees to that)
-    const bool staged = SWAP && (cluster_reduce || out_mode == OUT_SWIGLU ||
+    const bool staged = SWAP && (cluster_reduce || out_mode == OUT_SWIGLU || out_mode == OUT_QKV ||
                                  (partial == nullptr && (nio.in_ssq != nullptr || nio.out_ssq != nullptr)));
     uint32_t* tmem_slot = (uint32_t*)(accum + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
@@ -505,6 +528,47 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                             op[0] = a.x; op[1] = a.y; op[2] = b.x; op[3] = b.y;
                         }
                     }
+                    continue;
+                }
+                if (out_mode == OUT_QKV) {
+                    // this tile is head `tile_a` of token gj; the lane holds features 4 lane .. 4 lane + 3
+                    const int h = tile_a;
+                    const bool is_q = h < qio.nq, is_k = !is_q && h < qio.nq + qio.nkv;
+                    const int b = qio.seq_of_token[gj];
+                    if (!is_q && (qio.k_pool == nullptr || b < 0)) continue;
+                    float f[4] = {acc.x, acc.y, acc.z, acc.w};
+                    if (is_q || is_k) {
+                        const float* w = is_q ? qio.qw : qio.kw;
+                        if (w != nullptr) {
+                            float ss = fmaf(f[0], f[0], fmaf(f[1], f[1], fmaf(f[2], f[2], f[3] * f[3])));
+                            ss = warp_sum(ss);
+                            const float scale = 1.0f / sqrtf(ss * (1.0f / 128.0f) + qio.eps);
+                            const float4 w4 = *reinterpret_cast<const float4*>(w + 4 * lane);
+                            f[0] *= scale * w4.x; f[1] *= scale * w4.y; f[2] *= scale * w4.z; f[3] *= scale * w4.w;
+                        }
+                        const int i0 = 4 * (lane & 15);
+                        const float4 c4 = *reinterpret_cast<const float4*>(qio.cosv + (size_t)gj * 64 + i0);
+                        const float4 s4 = *reinterpret_cast<const float4*>(qio.sinv + (size_t)gj * 64 + i0);
+                        const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            const float p = __shfl_xor_sync(0xffffffffu, f[t], 16);      // the other half of the pair
+                            f[t] = lane < 16 ? f[t] * cs[t] - p * sn[t] : p * sn[t] + f[t] * cs[t];
+                        }
+                    }
+                    bf16* dst;
+                    if (is_q) {
+                        dst = qio.q_out + ((size_t)gj * qio.nq + h) * 128;
+                    } else {
+                        const int pos = qio.positions[gj];
+                        const int page = qio.page_table[(size_t)b * qio.max_pages + pos / qio.page_size];
+                        const int kvh = is_k ? h - qio.nq : h - qio.nq - qio.nkv;
+                        dst = (is_k ? qio.k_pool : qio.v_pool) +
+                              (((size_t)page * qio.nkv + kvh) * qio.page_size + (pos % qio.page_size)) * 128;
+                    }
+                    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), bb = __floats2bfloat162_rn(f[2], f[3]);
+                    *reinterpret_cast<uint2*>(dst + 4 * lane) =
+                        make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&bb));
                     continue;
                 }
                 const int gi0 = tile_a * BM + 4 * lane;              // first of this lane's four features
@@ -976,7 +1040,7 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out
 template <int BN, int STAGES, bool SWAP, int MINB>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N, int K,
            int splits, int kb_per_split, float* partial, bool cluster, int* status, const NormIO& nio,
-           cudaStream_t stream) {
+           const QkvIO& qio, cudaStream_t stream) {
     constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256;
     static_assert(STAGES * (A_BYTES + BN * BK * 2) >= BN * BM * 4, "the stages must hold a float32 tile");
     static bool configured = false;
@@ -990,9 +1054,9 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode
     dim3 grid((RA + BM - 1) / BM, (RB + BN - 1) / BN, splits);
     float* part = (splits > 1 && !cluster) ? partial : nullptr;
     const int cl = (splits > 1 && cluster) ? 1 : 0;
-    if (!SWAP && (cl || out_mode == OUT_SWIGLU)) return GG_ERR_ARG;      // forms the normal orientation does not have
+    if (!SWAP && (cl || out_mode == OUT_SWIGLU || out_mode == OUT_QKV)) return GG_ERR_ARG;      // forms the normal orientation does not have
     return gg_launch(kern, grid, dim3(NUM_THREADS), smem, stream, cl ? splits : 1, ta, tb, out, out_mode, ldo, M, N, K,
-                     kb_per_split, part, cl, status, nio);
+                     kb_per_split, part, cl, status, nio, qio);
 }
 
 }  // namespace
@@ -1025,9 +1089,21 @@ GG_API gg_gemm_tc_splits(int M, int N, int K, int use_cluster) {
 // means a bounded wait ran out (1 producer, 2 issuer, 3 epilogue).
 static int gemm_tc_impl(const void* x, const void* w, void* out, int out_mode, int M, int N, int K, long long ldx,
                         long long ldo, float* scratch, long long scratch_elems, int use_cluster, int* status,
-                        const NormIO& nio, cudaStream_t stream) {
+                        const NormIO& nio, const QkvIO& qio, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || (K % 8) != 0 || (ldx % 8) != 0 || ldx < K || out_mode < 0 || out_mode > 3) return GG_ERR_ARG;
+    if (K <= 0 || (K % 8) != 0 || (ldx % 8) != 0 || ldx < K || out_mode < 0 || out_mode > 4) return GG_ERR_ARG;
+    if (out_mode == OUT_QKV) {
+        // decode form only, one 128-wide head per weight tile; `out` is not used
+        if (M > 128 || qio.nq <= 0 || qio.nkv <= 0 || N != (qio.nq + 2 * qio.nkv) * 128 || qio.q_out == nullptr ||
+            qio.cosv == nullptr || qio.sinv == nullptr || qio.positions == nullptr || qio.seq_of_token == nullptr ||
+            (qio.k_pool != nullptr && (qio.v_pool == nullptr || qio.page_table == nullptr || qio.page_size <= 0)))
+            return GG_ERR_ARG;
+        const uintptr_t al = (uintptr_t)qio.q_out | (uintptr_t)qio.k_pool | (uintptr_t)qio.v_pool | (uintptr_t)qio.cosv |
+                             (uintptr_t)qio.sinv | (uintptr_t)qio.qw | (uintptr_t)qio.kw;
+        if (al & 15) return GG_ERR_ARG;
+        ldo = N;
+        use_cluster = 1;
+    }
     // out_mode 3: w holds blocks of 64 gate rows and 64 up rows in turn; out[M, N / 2] (bf16) = silu(gate) * up
     if (out_mode == OUT_SWIGLU ? ((N % 128) != 0 || ldo < N / 2 || (M > 128 && N < 256)) : ldo < N) return GG_ERR_ARG;
     if ((((uintptr_t)x) & 15) || (((uintptr_t)w) & 15) || status == nullptr) return GG_ERR_ARG;
@@ -1044,10 +1120,10 @@ static int gemm_tc_impl(const void* x, const void* w, void* out, int out_mode, i
         const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
         if ((rc = make_map(&ta, w, N, K, K, BM)) != 0) return rc;
         if ((rc = make_map(&tb, x, M, K, ldx, bn)) != 0) return rc;
-        if (bn == 16) rc = launch<16, 4, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, stream);
-        else if (bn == 32) rc = launch<32, 3, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, stream);
-        else if (bn == 64) rc = launch<64, 3, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, stream);
-        else rc = launch<128, 2, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, stream);
+        if (bn == 16) rc = launch<16, 4, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, qio, stream);
+        else if (bn == 32) rc = launch<32, 3, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, qio, stream);
+        else if (bn == 64) rc = launch<64, 3, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, qio, stream);
+        else rc = launch<128, 2, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, qio, stream);
     } else {
         const int bn = N > 128 ? 256 : 128;
         if ((rc = make_map(&ta, x, M, K, ldx, BM)) != 0) return rc;
@@ -1059,7 +1135,7 @@ static int gemm_tc_impl(const void* x, const void* w, void* out, int out_mode, i
             if ((rc = make_map(&tb, w, N, K, K, 128)) != 0) return rc;
             rc = launch_pair(ta, tb, out, out_mode, ldo, M, N, K, status, nio, stream);
         } else if (bn == 256) rc = launch_persistent(ta, tb, out, out_mode, ldo, M, N, K, status, nio, stream);
-        else rc = launch<128, 6, false, 1>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, false, status, nio, stream);
+        else rc = launch<128, 6, false, 1>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, false, status, nio, qio, stream);
     }
     if (rc != 0) return rc;
     if (splits > 1 && !cluster) {
@@ -1073,8 +1149,10 @@ static int gemm_tc_impl(const void* x, const void* w, void* out, int out_mode, i
 GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, int N, int K, long long ldx,
                   long long ldo, float* scratch, long long scratch_elems, int use_cluster, int* status,
                   cudaStream_t stream) {
+    if (out_mode == OUT_QKV) return GG_ERR_ARG;
     const NormIO none = {nullptr, 0, 0.f, 0.f, nullptr, nullptr};
-    return gemm_tc_impl(x, w, out, out_mode, M, N, K, ldx, ldo, scratch, scratch_elems, use_cluster, status, none, stream);
+    const QkvIO noq = {};
+    return gemm_tc_impl(x, w, out, out_mode, M, N, K, ldx, ldo, scratch, scratch_elems, use_cluster, status, none, noq, stream);
 }
 
 // The same product with an RMSNorm folded in on either side (K splits always inside clusters).
@@ -1089,6 +1167,25 @@ GG_API gg_gemm_tc_norm(const void* x, const void* w, void* out, int out_mode, in
                        int* status, cudaStream_t stream) {
     if (in_ssq != nullptr && (in_parts != (K + 127) / 128 || !(eps > 0.f))) return GG_ERR_ARG;
     if (out_ssq != nullptr && (out_mode != OUT_F32_ACC || out_xhat == nullptr)) return GG_ERR_ARG;
+    if (out_mode == OUT_QKV) return GG_ERR_ARG;
     const NormIO nio = {in_ssq, in_parts, 1.0f / (float)K, eps, out_ssq, (bf16*)out_xhat};
-    return gemm_tc_impl(x, w, out, out_mode, M, N, K, ldx, ldo, nullptr, 0, 1, status, nio, stream);
+    const QkvIO noq = {};
+    return gemm_tc_impl(x, w, out, out_mode, M, N, K, ldx, ldo, nullptr, 0, 1, status, nio, noq, stream);
+}
+
+// The q/k/v projection of a decode step (M <= 128 tokens, head size 128) with the per-head q/k RMSNorm,
+// the rotation and the cache write in its epilogue: x[M, K] * w[(nq + 2 nkv) * 128, K]^T, rows of w being
+// all q heads, then all k heads, then all v heads.  See QkvIO for the outputs; in_ssq / in_parts / in_eps
+// as in gg_gemm_tc_norm (null: x is already normalised).  qw / kw null: no q/k norm.
+GG_API gg_gemm_tc_qkv_rope(const void* x, const void* w, int M, int K, long long ldx, const float* in_ssq, int in_parts,
+                           float in_eps, void* q_out, const float* qw, const float* kw, float eps, const float* cosv,
+                           const float* sinv, const int* positions, const int* seq_of_token, const int* page_table,
+                           int max_pages, int page_size, void* k_pool, void* v_pool, int nq, int nkv, int* status,
+                           cudaStream_t stream) {
+    if (in_ssq != nullptr && (in_parts != (K + 127) / 128 || !(in_eps > 0.f))) return GG_ERR_ARG;
+    const NormIO nio = {in_ssq, in_parts, K > 0 ? 1.0f / (float)K : 0.f, in_eps, nullptr, nullptr};
+    const QkvIO qio = {(bf16*)q_out, qw, kw, eps, cosv, sinv, positions, seq_of_token, page_table, max_pages, page_size,
+                       (bf16*)k_pool, (bf16*)v_pool, nq, nkv};
+    const int N = (nq + 2 * nkv) * 128;
+    return gemm_tc_impl(x, w, q_out, OUT_QKV, M, N, K, ldx, N, nullptr, 0, 1, status, nio, qio, stream);
 }

@@ -127,6 +127,40 @@ def gemm_tc_norm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate
         st.data_ptr(), torch.cuda.current_stream().cuda_stream)
 
 
+def gemm_tc_qkv_rope(x: torch.Tensor, w: torch.Tensor, m: int, q_out: torch.Tensor, qw: Optional[torch.Tensor],
+                     kw: Optional[torch.Tensor], eps: float, cos: torch.Tensor, sin: torch.Tensor,
+                     positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor, page_size: int,
+                     k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], nq: int, nkv: int,
+                     in_ssq: Optional[torch.Tensor] = None, in_eps: float = 0.0) -> None:
+    """The q/k/v projection of a decode step (m <= 128 tokens, head size 128) with the per-head q/k RMSNorm,
+    the rotation and the cache write in the product's epilogue (csrc/gemm_tcgen05.cu, gg_gemm_tc_qkv_rope)."""
+    N, K = w.shape
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc_qkv_rope takes bfloat16 operands")
+    if N != (nq + 2 * nkv) * 128 or m > 128 or q_out.numel() < m * nq * 128 or not q_out.is_contiguous():
+        raise KernelError("gemm_tc_qkv_rope: head size 128, at most 128 tokens, q_out [m, nq * 128]")
+    if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape[-1] != 64 or sin.shape[-1] != 64 \
+            or not cos.is_contiguous() or not sin.is_contiguous():
+        raise KernelError("gemm_tc_qkv_rope: cos and sin are float32 [m, 64]")
+    for t in (positions, seq_of_token, page_table):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError("gemm_tc_qkv_rope: integer inputs are contiguous int32")
+    for t in (qw, kw):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != 128):
+            raise KernelError("gemm_tc_qkv_rope: norm weights are float32 [128]")
+    if k_pool is not None and (k_pool.dtype != torch.bfloat16 or v_pool is None or v_pool.dtype != torch.bfloat16):
+        raise KernelError("gemm_tc_qkv_rope: the cache pools are bfloat16")
+    in_parts = (K + 127) // 128 if in_ssq is not None else 0
+    st = status_word(x.device)
+    kernel("gemm_tcgen05", "gg_gemm_tc_qkv_rope")(
+        x.data_ptr(), w.data_ptr(), m, K, x.stride(0), in_ssq.data_ptr() if in_ssq is not None else 0, in_parts,
+        float(in_eps), q_out.data_ptr(), qw.data_ptr() if qw is not None else 0, kw.data_ptr() if kw is not None else 0,
+        float(eps), cos.data_ptr(), sin.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(),
+        page_table.data_ptr(), page_table.shape[-1], int(page_size),
+        k_pool.data_ptr() if k_pool is not None else 0, v_pool.data_ptr() if v_pool is not None else 0,
+        nq, nkv, st.data_ptr(), torch.cuda.current_stream().cuda_stream)
+
+
 def make_linear(weight: torch.Tensor, swiglu: bool = False) -> Optional[Callable]:
     """A callable f(x, out, accumulate, m, ws, in_ssq=None, eps=0.0, out_ssq=None, out_xhat=None) for this
     weight, or None if its sizes are not taken (K must be a multiple of 8 so that rows start on 16-byte

@@ -9,6 +9,7 @@ Score scale is 1/sqrt(head_dim) unless the spec gives `scale` (pkg/ops/attention
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Optional
 
 import torch
@@ -77,6 +78,10 @@ class AttentionMixer:
         if rt.fast and rt.dtype == torch.bfloat16:
             from ..csrc import fast_attention
             self._fast = fast_attention.try_make(self.nq, self.nkv, self.d, self.scale, self.window)
+        # head size 128 with a full rotation by cos/sin tables: the decode form of the q/k/v product can do
+        # the per-head work itself (one head per 128-row weight tile)
+        self._fused_rope = (self.qkv.tensor_core and self.d == 128 and self.rot == self.d
+                            and os.environ.get("GOGGUF_B200_FUSE_QKV_ROPE", "1") != "0")
 
     def absorb_norm(self, norm) -> bool:
         """Take the block's pre-norm into the q/k/v projection; `forward` then gets RowStats as `h`."""
@@ -92,16 +97,23 @@ class AttentionMixer:
                 writes_cache: bool = True) -> None:
         T, nq, nkv, d = ctx.n_tokens, self.nq, self.nkv, self.d
         dt = self.rt.dtype
-        qkv = ctx.ws.get("attn_qkv", (T, (nq + 2 * nkv) * d), dt)
         q = ctx.ws.get("attn_q", (T, nq * d), dt)
         o = ctx.ws.get("attn_out", (T, nq * d), dt)
-        self.qkv(h, qkv, ws=ctx.ws)
         cos, sin = self.position.tables(ctx)
         table = ctx.page_tables[cache.group]
-        K.qk_norm_rope_cache(qkv, q, self.q_norm, self.k_norm, self.eps, cos, sin, ctx.positions,
-                             ctx.seq_of_token, table, cache.page_size,
-                             cache.k if writes_cache else None, cache.v if writes_cache else None,
-                             T, nq, nkv, d, self.rot)
+        if self._fused_rope and T <= 128:
+            # few tokens (decode): norm, rotation and cache write happen in the projection's epilogue
+            self.qkv.qkv_rope(h, T, q_out=q, qw=self.q_norm, kw=self.k_norm, eps=self.eps, cos=cos, sin=sin,
+                              positions=ctx.positions, seq_of_token=ctx.seq_of_token, page_table=table,
+                              page_size=cache.page_size, k_pool=cache.k if writes_cache else None,
+                              v_pool=cache.v if writes_cache else None, nq=nq, nkv=nkv)
+        else:
+            qkv = ctx.ws.get("attn_qkv", (T, (nq + 2 * nkv) * d), dt)
+            self.qkv(h, qkv, ws=ctx.ws)
+            K.qk_norm_rope_cache(qkv, q, self.q_norm, self.k_norm, self.eps, cos, sin, ctx.positions,
+                                 ctx.seq_of_token, table, cache.page_size,
+                                 cache.k if writes_cache else None, cache.v if writes_cache else None,
+                                 T, nq, nkv, d, self.rot)
         if self._fast is not None:
             self._fast(q, cache.k, cache.v, o, ctx, table, cache.page_size)
         else:

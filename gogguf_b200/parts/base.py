@@ -144,6 +144,21 @@ class Linear:
         self._fast = tcgen05_gemm.make_linear(w, swiglu=self.swiglu)
         self.folded_eps = float(eps)
 
+    @property
+    def tensor_core(self) -> bool:
+        return self._fast is not None
+
+    def qkv_rope(self, x, m: int, **outputs) -> None:
+        """This projection as the q/k/v projection of a decode step, with q/k norm, rotation and cache write
+        in its epilogue (`csrc.tcgen05_gemm.gemm_tc_qkv_rope`, whose keyword arguments `outputs` are)."""
+        from ..csrc import tcgen05_gemm
+        if self.folded_eps is not None:
+            if not isinstance(x, RowStats):
+                raise TypeError("Linear: a projection with a folded norm reads RowStats, not normalised rows")
+            outputs.update(in_ssq=x.ssq, in_eps=self.folded_eps)
+            x = x.xhat
+        tcgen05_gemm.gemm_tc_qkv_rope(x, self.weight, m, **outputs)
+
     def __call__(self, x, out: torch.Tensor, accumulate: bool = False, m: Optional[int] = None,
                  ws: Optional[Workspace] = None, emit: Optional[RowStats] = None) -> None:
         kw = {}

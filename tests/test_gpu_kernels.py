@@ -332,6 +332,73 @@ def test_gemm_tcgen05_fused_swiglu_with_folded_norm(M, I, K_):
     assert rel(out, gd / (1 + torch.exp(-gd)) * ud) < 6e-3
 
 
+@pytest.mark.parametrize("M,nq,nkv,K_,norm,fold", [(1, 2, 1, 128, True, False), (8, 8, 2, 512, True, True),
+                                                   (37, 3, 3, 264, False, True), (128, 4, 1, 1024, True, False)])
+def test_gemm_tcgen05_qkv_with_norm_rope_and_cache_write(M, nq, nkv, K_, norm, fold):
+    """The decode form of the q/k/v product with the per-head work in its epilogue, against the unfused pair
+    (product, then the qk_norm_rope_cache kernel), and against the plain statement."""
+    from gogguf_b200.csrc import tcgen05_gemm as tc
+    d, ps = 128, 64
+    g = torch.Generator(device=DEV).manual_seed(41)
+    resid = torch.randn(M, K_, device=DEV, generator=g) * 2
+    w = (torch.randn((nq + 2 * nkv) * d, K_, device=DEV, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+    xh, ssq = plain_row_stats(resid)
+    ssq = ssq.float().contiguous()
+    eps_in, eps = 2e-6, 1e-5
+    qw = (1 + 0.2 * torch.randn(d, device=DEV, generator=g)) if norm else None
+    kw = (1 + 0.2 * torch.randn(d, device=DEV, generator=g)) if norm else None
+    # tokens: sequence b holds a few tokens at positions that cross a page edge; one padding token at the end
+    nseq = max(1, M // 5)
+    seq_of = torch.tensor([min(t % nseq, nseq - 1) for t in range(M)], dtype=torch.int32)
+    pos = torch.tensor([60 + t // nseq for t in range(M)], dtype=torch.int32)
+    if M > 1:
+        seq_of[-1] = -1
+    pages_per = 3
+    table = torch.randperm(nseq * pages_per, generator=torch.Generator().manual_seed(1)).to(torch.int32).view(nseq, pages_per)
+    seq_of, pos, table = seq_of.to(DEV), pos.to(DEV), table.to(DEV)
+    inv = torch.pow(torch.tensor(1e4, dtype=torch.float64), -2.0 * torch.arange(64, dtype=torch.float64) / d).to(DEV)
+    cos, sin = torch.empty(M, 64, device=DEV), torch.empty(M, 64, device=DEV)
+    K().rope_tables(pos, inv, cos, sin)
+    npages = nseq * pages_per
+
+    def pools():
+        return (torch.full((npages, nkv, ps, d), 7.0, device=DEV, dtype=torch.bfloat16),
+                torch.full((npages, nkv, ps, d), 7.0, device=DEV, dtype=torch.bfloat16))
+
+    # unfused twin
+    qkv = torch.empty(M, (nq + 2 * nkv) * d, device=DEV, dtype=torch.bfloat16)
+    if fold:
+        tc.gemm_tc_norm(xh, w, qkv, in_ssq=ssq, eps=eps_in)
+    else:
+        tc.gemm_tc(xh, w, qkv, cluster=True)
+    q1 = torch.empty(M, nq * d, device=DEV, dtype=torch.bfloat16)
+    k1, v1 = pools()
+    K().qk_norm_rope_cache(qkv, q1, qw, kw, eps, cos, sin, pos, seq_of, table, ps, k1, v1, M, nq, nkv, d, d)
+    # fused
+    q2 = torch.full((M, nq * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    k2, v2 = pools()
+    tc.gemm_tc_qkv_rope(xh, w, M, q2, qw, kw, eps, cos, sin, pos, seq_of, table, ps, k2, v2, nq, nkv,
+                        in_ssq=ssq if fold else None, in_eps=eps_in)
+    tc.check_status(DEV)
+    assert rel(q2, q1) < 1e-2 and rel(k2, k1) < 1e-2 and rel(v2, v1) < 1e-2
+    # the same cache rows were written, and no others
+    assert torch.equal(k2 == 7.0, k1 == 7.0) and torch.equal(v2 == 7.0, v1 == 7.0)
+    # plain statement in float64 (the fused epilogue does not round q/k/v to bfloat16 before the norm)
+    factor = 1.0 / torch.sqrt((resid.double() ** 2).mean(-1, keepdim=True) + eps_in) if fold else 1.0
+    full = (xh.double() @ w.double().T) * factor
+    qd = full[:, :nq * d].view(M, nq, d)
+    if norm:
+        qd = qd / torch.sqrt((qd ** 2).mean(-1, keepdim=True) + eps) * qw.double()
+    c, s_ = cos.double()[:, None, :], sin.double()[:, None, :]
+    want = torch.cat([qd[..., :64] * c - qd[..., 64:] * s_, qd[..., :64] * s_ + qd[..., 64:] * c], dim=-1).view(M, nq * d)
+    assert rel(q2, want) < 6e-3
+    # writes_cache False: only q is written
+    q3 = torch.empty_like(q2)
+    tc.gemm_tc_qkv_rope(xh, w, M, q3, qw, kw, eps, cos, sin, pos, seq_of, table, ps, None, None, nq, nkv,
+                        in_ssq=ssq if fold else None, in_eps=eps_in)
+    assert torch.equal(q3, q2)
+
+
 # ------------------------------------------------------------------------------------------ attention
 def make_paged(seqs, nkv, d, dt, seed, n_pages=None, ps=64):
     """seqs: list of (context length after the step, new tokens).  Returns pools, table and per-sequence K, V."""

@@ -115,3 +115,23 @@ def test_bfloat16_run_of_a_folder_stored_in_32_bit(tmp_path_factory):
     from gogguf_b200.engine import Model
     m = Model.load(folder, dtype="bfloat16")
     assert m.blocks[0].mixer.qkv.weight.dtype == torch.float32 and m.blocks[0].mixer.qkv._fast is None
+
+
+def test_decode_projection_does_the_per_head_work_when_the_head_size_is_128(tmp_path_factory, monkeypatch):
+    from gogguf_b200.csrc import build
+    from gogguf_b200.engine import Model, StepEntry, Stepper
+    folder = make_folder(tmp_path_factory.getbasetemp(), "L", "bfloat16", scale=4.0)
+    counts, logits = {}, {}
+    for fuse in ("1", "0"):
+        monkeypatch.setenv("GOGGUF_B200_FUSE_QKV_ROPE", fuse)
+        model = Model.load(folder, dtype="bfloat16")
+        cache = model.new_cache(256)
+        st = Stepper(model, cache)
+        slot = cache.open()
+        st.step([StepEntry(slot, list(range(1, 70)), want=[68])])
+        n0 = build.launch_count()
+        logits[fuse] = st.step([StepEntry(slot, [4], want=[0])]).clone()
+        counts[fuse] = build.launch_count() - n0
+        cache.close(slot)
+    assert counts["0"] - counts["1"] == len(model.blocks)       # one kernel a layer less
+    assert rel_err(logits["1"], logits["0"]) < 2e-2
