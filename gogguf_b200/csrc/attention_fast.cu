@@ -58,7 +58,7 @@ __device__ __forceinline__ uint4 ldg16(const bf16* p) { return __ldg(reinterpret
 // C regs c0,c1 = row g, cols 2t, 2t+1; c2,c3 = row g+8.
 template <int D>
 __global__ void __launch_bounds__(128) attn_decode_kernel(
-    const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+    const bf16* q, const bf16* k_pool, const bf16* v_pool,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int nq, int nkv, float scale_log2, int window, int nsplit) {
@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
 }
 
 template <int D>
-__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+__global__ void attn_combine_kernel(const float* part_o, const float* part_ml,
                                     bf16* __restrict__ out, int nsplit) {
     pdl_launch();
     pdl_wait();
@@ -268,7 +268,7 @@ template <int D> __device__ __forceinline__ bf16* sw(bf16* tile, int row, int ch
 
 template <int D>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(
-    const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool, bf16* __restrict__ out,
+    const bf16* q, const bf16* k_pool, const bf16* v_pool, bf16* __restrict__ out,
     const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int n_seqs, int nq, int nkv, float scale_log2, int window) {
     pdl_wait();      // no early release of the next kernel: many waves of CTAs that exclude its CTAs from their SMs
@@ -439,7 +439,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
 template <int D, int STAGES>
 __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-    const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+    const bf16* q, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int nq, int nkv, float scale_log2, int window, int nsplit,
     int cluster_reduce, int* __restrict__ status) {
@@ -467,7 +467,11 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
         tma::prefetch_map(&tmV);
     }
     __syncthreads();
-    pdl_wait();      // everything below reads what earlier kernels of the step wrote (q, the cache, the tables)
+    // The step's integer inputs (positions, sequence rows, page tables) were copied to the device before the
+    // step's first kernel started.  Of the cache, the kernels of this step write only position `pos` (one new
+    // token per sequence), which lies in page pos / 64; every earlier page was written by earlier steps.  So
+    // the producer starts streaming those pages while the projection before this kernel is still finishing,
+    // and waits for it only before the page that holds the new token; the consumers wait before they read q.
     const int b = seq_of_token[tok];
     const int pos = b >= 0 ? positions[tok] : -1;
 
@@ -489,9 +493,12 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
     if (warp == 4) {
         if (lane == 0) {
             const int* pt = page_table + (size_t)b * max_pages;
+            const int newest = pos / PAGE;
+            bool waited = false;
             for (int i = 0; i < npg; ++i) {
                 const int s = i % STAGES;
                 const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+                if (!waited && p_begin + i >= newest) { pdl_wait(); waited = true; }
                 if (!tma::mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, 11)) break;
                 tma::mbar_expect_tx(&full[s], STAGE_BYTES);
                 const int row = (pt[p_begin + i] * nkv + kvh) * PAGE;
@@ -506,6 +513,7 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
     } else if (npg > 0) {
         // Q fragments in the standard A layout: row = head of the group, k = head dimension
         uint32_t qa[KS][4];
+        pdl_wait();
         {
             const bf16* q0 = q + ((size_t)tok * nq + (size_t)kvh * G) * D;
 #pragma unroll
@@ -576,6 +584,7 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
             if (lane == 0) tma::mbar_arrive(&empty[s]);
         }
     }
+    pdl_wait();               // (returns at once where it was already called) the output buffer is free from here
     __syncthreads();          // all pages consumed (or the CTA gave up): the ring can be reused for the merge
     if (*abort_flag) {
         const long long t0 = clock64();

@@ -15,7 +15,7 @@
 
 template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attention_plain_kernel(
-    const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool, T* __restrict__ out,
+    const T* q, const T* k_pool, const T* v_pool, T* __restrict__ out,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int page_size,
     int nq, int nkv, int d, float scale, int window) {

@@ -88,6 +88,14 @@ __device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats o
 // scheduled, and the two kernels waited for each other; the cause inside the scheduler was not
 // established, so such kernels simply release their successor by completing.  Light kernels with
 // many CTAs (norms, rotary) share SMs with whatever follows and keep the early release.
+//
+// A second rule, for the compiler: a pointer to data that an earlier kernel of the same step writes
+// (activations, the residual stream, q, the cache, rotary tables, logits, partial results) is never
+// declared `const ... __restrict__`.  Loads through such a pointer are invariant loads (ld.global.nc)
+// that the compiler may move above griddepcontrol.wait, "memory" clobber or not; that happened to the
+// q loads of decode attention, which then read the previous layer's q.  Weights and the step's integer
+// inputs (copied to the device before the step's first kernel) do not change while a step runs and
+// keep the qualifier.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

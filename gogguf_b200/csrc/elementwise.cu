@@ -10,7 +10,7 @@
 
 // ----------------------------------------------------------------------------- embedding
 template <typename TW>
-__global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
+__global__ void embed_gather_kernel(const TW* __restrict__ table, const int* tokens,
                                     float* __restrict__ out, int H, int V) {
     pdl_launch();
     pdl_wait();
@@ -38,7 +38,7 @@ GG_API gg_embed_gather(const void* table, int table_dtype, const int* tokens, fl
 // out[r,:] = x[src(r),:] * (1/sqrt(mean(x^2)+eps)) * w ; src(r) = rows ? rows[r] : r.
 // x is the float32 residual stream.  A negative source row gives a zero row.
 template <typename TO>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+__global__ void rmsnorm_kernel(const float* x, const int* __restrict__ rows,
                                const float* __restrict__ w, TO* __restrict__ out, int H, float eps) {
     pdl_launch();
     pdl_wait();
@@ -62,7 +62,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 // 16-byte loads that are all in flight together and kept in registers for the second pass.  In a
 // decode step only a few rows exist, so the kernel's time is one memory latency, not two loops of them.
 template <typename TO, int VPT /* float4 per thread */>
-__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* x, const int* __restrict__ rows,
                                                           const float* __restrict__ w, TO* __restrict__ out, int H, float eps) {
     pdl_launch();
     pdl_wait();
@@ -139,7 +139,7 @@ GG_API gg_rmsnorm(const float* x, const int* rows, const float* w, void* out, in
 // per row, the sums of squares over blocks of 128 columns (ceil(H / 128) partial sums).  The products
 // that add into the residual stream write both themselves; this kernel makes them where no such
 // product came before (after the embedding, after a part that does not emit them).
-__global__ void __launch_bounds__(128) row_stats_kernel(const float* __restrict__ x, bf16* __restrict__ xhat,
+__global__ void __launch_bounds__(128) row_stats_kernel(const float* x, bf16* __restrict__ xhat,
                                                         float* __restrict__ ssq, int H, int parts) {
     pdl_launch();
     pdl_wait();
@@ -209,9 +209,9 @@ GG_API gg_rope_tables(const int* positions, const double* inv_freq, float* cosv,
 // layer's cache writes none); then k and v heads are skipped.
 template <typename T>
 __global__ void qk_norm_rope_cache_kernel(
-    const T* __restrict__ qkv, T* __restrict__ q_out,
+    const T* qkv, T* __restrict__ q_out,
     const float* __restrict__ qw, const float* __restrict__ kw, float eps,
-    const float* __restrict__ cosv, const float* __restrict__ sinv,
+    const float* cosv, const float* sinv,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int page_size,
     T* __restrict__ k_pool, T* __restrict__ v_pool,
@@ -277,9 +277,9 @@ __global__ void qk_norm_rope_cache_kernel(
 // access is VPL * 2 bytes wide and no shared memory is needed.  VPL = d / 64 (d = 64: 1, 128: 2, 256: 4).
 template <int VPL>
 __global__ void __launch_bounds__(128) qk_norm_rope_cache_vec_kernel(
-    const bf16* __restrict__ qkv, bf16* __restrict__ q_out,
+    const bf16* qkv, bf16* __restrict__ q_out,
     const float* __restrict__ qw, const float* __restrict__ kw, float eps,
-    const float* __restrict__ cosv, const float* __restrict__ sinv,
+    const float* cosv, const float* sinv,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int page_size,
     bf16* __restrict__ k_pool, bf16* __restrict__ v_pool, int ntok, int nq, int nkv) {
@@ -386,7 +386,7 @@ GG_API gg_qk_norm_rope_cache(const void* qkv, int dtype, void* q_out, const floa
 // ----------------------------------------------------------------------------- SwiGLU
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(z) = z / (1 + exp(-z)) (pkg/ops/ops.go:316-318).
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long n, int I) {
+__global__ void swiglu_kernel(const T* gu, T* __restrict__ out, long long n, int I) {
     pdl_launch();
     pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -399,7 +399,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, lon
 }
 
 // Eight elements per thread with 16-byte accesses (rows of I elements, I a multiple of 8).
-__global__ void swiglu_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long long nvec, int I8) {
+__global__ void swiglu_vec8_kernel(const bf16* gu, bf16* __restrict__ out, long long nvec, int I8) {
     pdl_launch();
     pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -442,7 +442,7 @@ GG_API gg_swiglu(const void* gu, int dtype, void* out, int ntok, int I, cudaStre
 // x (float32) += delta.  The fast path folds this into the producing product's epilogue;
 // this is the stand-alone form (pkg/gpu/cuda/ptx.go:891-924 add_inplace).
 template <typename T>
-__global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__ delta, long long n) {
+__global__ void residual_add_kernel(float* __restrict__ x, const T* delta, long long n) {
     pdl_launch();
     pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -460,7 +460,7 @@ GG_API gg_residual_add(float* x, const void* delta, int dtype, long long n, cuda
 // tokens[i] = sampled[src[i]] where src[i] >= 0: lets a decode step take the ids that the previous
 // step's sampling kernel left on the device, without a round trip through the host.
 __global__ void feed_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ src,
-                                   const int* __restrict__ sampled, int n) {
+                                   const int* sampled, int n) {
     pdl_launch();
     pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;

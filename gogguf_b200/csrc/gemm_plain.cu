@@ -14,7 +14,7 @@
 #define BK 16
 
 template <typename TX, typename TW, typename TO, bool ACC>
-__global__ void __launch_bounds__(256) gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w,
+__global__ void __launch_bounds__(256) gemm_plain_kernel(const TX* x, const TW* __restrict__ w,
                                                          TO* __restrict__ out, int M, int N, int K,
                                                          long long ldx, long long ldo) {
     pdl_launch();

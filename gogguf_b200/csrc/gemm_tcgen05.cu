@@ -636,7 +636,7 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
 }
 
 // out[m, n] = epilogue( sum over splits of partial[s, m, n] ), splits added in index order.
-__global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, int out_mode,
+__global__ void splitk_reduce_kernel(const float* partial, void* __restrict__ out, int out_mode,
                                      long long ldo, int M, int N, int splits) {
     pdl_launch();
     pdl_wait();

@@ -63,7 +63,7 @@ __device__ __forceinline__ double block_sum_f64(double v, double* red) {
     return red[32];
 }
 
-__global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __restrict__ logits, long long ld,
+__global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* logits, long long ld,
                                                                int* __restrict__ out, int V) {
     pdl_launch();
     pdl_wait();
@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __res
 
 // Two-stage form for a few long rows: `chunks` blocks per row each find the best of their slice, a second
 // launch picks among them (ties still go to the smallest index).
-__global__ void __launch_bounds__(SAMP_THREADS) argmax_partial_kernel(const float* __restrict__ logits, long long ld,
+__global__ void __launch_bounds__(SAMP_THREADS) argmax_partial_kernel(const float* logits, long long ld,
                                                                        MaxIdx* __restrict__ part, int V, int chunks) {
     pdl_launch();
     pdl_wait();
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(SAMP_THREADS) argmax_partial_kernel(const floa
     if (threadIdx.x == 0) part[(size_t)r * chunks + c] = best;
 }
 
-__global__ void argmax_final_kernel(const MaxIdx* __restrict__ part, int* __restrict__ out, int chunks) {
+__global__ void argmax_final_kernel(const MaxIdx* part, int* __restrict__ out, int chunks) {
     pdl_launch();
     pdl_wait();
     const int r = blockIdx.x;
@@ -137,7 +137,7 @@ GG_API gg_argmax(const float* logits, long long ld, int* out, int R, int V, void
 }
 
 // One block per row.  temps[r] <= 0 means greedy for that row.
-__global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(const float* __restrict__ logits, long long ld,
+__global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(const float* logits, long long ld,
                                                                const float* __restrict__ temps,
                                                                const double* __restrict__ uniforms,
                                                                int* __restrict__ out, int V) {
