@@ -1120,10 +1120,19 @@ static int gemm_tc_impl(const void* x, const void* w, void* out, int out_mode, i
         const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
         if ((rc = make_map(&ta, w, N, K, K, BM)) != 0) return rc;
         if ((rc = make_map(&tb, x, M, K, ldx, bn)) != 0) return rc;
-        if (bn == 16) rc = launch<16, 4, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, qio, stream);
-        else if (bn == 32) rc = launch<32, 3, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, qio, stream);
-        else if (bn == 64) rc = launch<64, 3, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, qio, stream);
-        else rc = launch<128, 2, true, 3>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, cluster, status, nio, qio, stream);
+        // A grid that fits two CTAs per SM (296 places) gets the deeper ring; a larger one needs three per SM
+        // to run as one wave.  GOGGUF_B200_GEMM_DEEP=0 always takes the three-per-SM forms.
+        static int deep_ok = -1;
+        if (deep_ok < 0) { const char* e = getenv("GOGGUF_B200_GEMM_DEEP"); deep_ok = (e != nullptr && e[0] == '0') ? 0 : 1; }
+        const long long ctas = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn) * splits;
+        const bool deep = deep_ok && ctas <= 296 && bn <= 32;    // measured in whole steps: a gain up to 32 tokens only
+#define GG_DECODE(BN_, ST_, MINB_) launch<BN_, ST_, true, MINB_>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, \
+                                                                 cluster, status, nio, qio, stream)
+        if (bn == 16) rc = deep ? GG_DECODE(16, 6, 2) : GG_DECODE(16, 4, 3);
+        else if (bn == 32) rc = deep ? GG_DECODE(32, 5, 2) : GG_DECODE(32, 3, 3);
+        else if (bn == 64) rc = deep ? GG_DECODE(64, 4, 2) : GG_DECODE(64, 3, 3);
+        else rc = deep ? GG_DECODE(128, 3, 2) : GG_DECODE(128, 2, 3);
+#undef GG_DECODE
     } else {
         const int bn = N > 128 ? 256 : 128;
         if ((rc = make_map(&ta, x, M, K, ldx, BM)) != 0) return rc;
