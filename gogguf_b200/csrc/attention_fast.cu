@@ -436,6 +436,10 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
 // consumer warps take 16 keys of each page, read fragments with ldmatrix and keep their own running
 // maximum, sum and output; they are merged at the end as in the other kernel.  The copy engine
 // decouples the loads from the arithmetic, which a warp that loads and computes in turn cannot.
+// Largest cluster of splits: 8 is what every device takes; 16 needs the non-portable opt-in, which the
+// launcher asks for once and falls back from (attn_max_cluster).
+constexpr int MAX_ATT_CLUSTER = 16;
+
 template <int D, int STAGES>
 __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -646,10 +650,10 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
         const uint32_t ro = tma::smem_u32(res_o), rm = tma::smem_u32(res_ml);
         for (int idx = split * blockDim.x + threadIdx.x; idx < G * D; idx += nsplit * blockDim.x) {
             const int r = idx / D, c = idx - r * D;
-            float ms[8], ls[8], as[8];
+            float ms[MAX_ATT_CLUSTER], ls[MAX_ATT_CLUSTER], as[MAX_ATT_CLUSTER];
             float M = -INFINITY;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
+            for (int k = 0; k < MAX_ATT_CLUSTER; ++k) {
                 if (k < nsplit) {
                     ms[k] = ld_dsmem_f32(rm + 4u * (r * 2), k);
                     ls[k] = ld_dsmem_f32(rm + 4u * (r * 2 + 1), k);
@@ -660,7 +664,7 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
             float L = 0.f, acc = 0.f;
             if (M != -INFINITY) {
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
+                for (int k = 0; k < MAX_ATT_CLUSTER; ++k) {
                     const float f = fast_exp2(ms[k] - M);
                     L += ls[k] * f;
                     acc += as[k] * f;
@@ -674,13 +678,48 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
 }
 
 template <int D, int STAGES>
+constexpr int decode_tma_smem() {
+    constexpr int ring = STAGES * 4 * (D / 64) * 64 * 64;     // bytes: STAGES * 2 * HALVES * 8 KB
+    constexpr int merge = (5 * 16 * D + 5 * 16 * 2) * 4;
+    return (ring > merge ? ring : merge) + 1024 + 256;
+}
+
+// 16 if this device co-schedules clusters of 16 CTAs of both decode kernels (opt-in), else 8.
+int attn_max_cluster() {
+    static int v = 0;
+    if (v != 0) return v;
+    v = 8;
+    const char* env = getenv("GOGGUF_B200_ATTN_CLUSTER16");
+    if (env != nullptr && env[0] == '0') return v;
+    bool ok = true;
+    auto probe = [&](auto kern, int smem) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+            cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) { ok = false; return; }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, 1, 16);
+        cfg.blockDim = dim3(160);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 16;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 8) ok = false;
+    };
+    probe(attn_decode_tma_kernel<128, 3>, decode_tma_smem<128, 3>());
+    probe(attn_decode_tma_kernel<64, 4>, decode_tma_smem<64, 4>());
+    cudaGetLastError();
+    if (ok) v = 16;
+    return v;
+}
+
+template <int D, int STAGES>
 int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* q, void* out, float* part_o, float* part_ml,
                       const int* positions, const int* seq_of_token, const int* page_table, int max_pages, int ntok,
                       int nq, int nkv, float scale_log2, int window, int splits, bool cluster, int* status,
                       cudaStream_t stream) {
-    constexpr int ring = STAGES * 4 * (D / 64) * 64 * 64;     // bytes: STAGES * 2 * HALVES * 8 KB
-    constexpr int merge = (5 * 16 * D + 5 * 16 * 2) * 4;
-    constexpr int smem = (ring > merge ? ring : merge) + 1024 + 256;
+    constexpr int smem = decode_tma_smem<D, STAGES>();
     static bool configured = false;
     auto kern = attn_decode_tma_kernel<D, STAGES>;
     if (!configured) {
@@ -1012,9 +1051,18 @@ GG_API gg_attn_decode_tma_splits(int ntok, int nkv, int max_ctx, int use_cluster
     int splits = use_cluster ? (int)(296 / pairs) : (int)((4 * 296 + pairs - 1) / pairs);
     const int pages = (max_ctx + PAGE - 1) / PAGE;
     if (splits > pages / 2) splits = pages / 2;       // at least two pages per CTA
-    const int most = use_cluster ? 8 : 64;
+    // Clusters of 16 (where the device takes them) pay off for the fewest sequences and long contexts only
+    // (measured: 28 against 41 us for one sequence at 32K positions; slower than 8 from two sequences on).
+    int most = 64;
+    if (use_cluster) most = (pairs * 16 <= 148 && pages >= 64) ? attn_max_cluster() : 8;
     if (splits > most) splits = most;
     if (splits < 1) splits = 1;
+    if (use_cluster) {
+        // powers of two only: clusters of 5, 6, 7 or 12 CTAs ran 30-50 % slower than the next smaller power
+        int p = 1;
+        while (p * 2 <= splits) p *= 2;
+        splits = p;
+    }
     return splits;
 }
 
@@ -1030,7 +1078,7 @@ GG_API gg_attn_decode_tma(const void* q, const void* k_pool, const void* v_pool,
         nkv > 65535 || splits > 65535 || n_pages <= 0 || status == nullptr)
         return GG_ERR_ARG;
     const bool cluster = use_cluster != 0;
-    if (cluster && splits > 8) return GG_ERR_ARG;
+    if (cluster && splits > attn_max_cluster()) return GG_ERR_ARG;
     if (splits > 1 && !cluster && (part_o == nullptr || part_ml == nullptr)) return GG_ERR_ARG;
     if ((((uintptr_t)k_pool) & 15) || (((uintptr_t)v_pool) & 15)) return GG_ERR_ARG;
     CUtensorMap tk, tv;

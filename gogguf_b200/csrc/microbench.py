@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|attn|prefill_attn] [--m 1,8,64]
+"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|attn|prefill_attn] [--m 1,8,64] [--ctx 2048,8192]
 
 Times single kernels the way a decode step runs them: forty launches captured in a CUDA graph and
 replayed, so that host launch cost is out of the picture and dependent launches overlap as they do
@@ -50,7 +50,7 @@ def gemm(ms) -> None:
         torch.cuda.empty_cache()
 
 
-def attn(ms, ctx_len: int = 2048, nq: int = 32, nkv: int = 8, d: int = 128) -> None:
+def attn(ms, ctx_len: int = 2048, nq: int = 32, nkv: int = 8, d: int = 128, cluster: bool = True) -> None:
     from . import fast_attention as fa
     dev = "cuda:0"
     for B in ms:
@@ -63,11 +63,14 @@ def attn(ms, ctx_len: int = 2048, nq: int = 32, nkv: int = 8, d: int = 128) -> N
         sot = torch.arange(B, dtype=torch.int32, device=dev)
         q = torch.randn(B, nq, d, device=dev).to(torch.bfloat16)
         out = torch.empty_like(q)
-        splits = fa.decode_tma_splits(B, nkv, ctx_len, cluster=True)
+        splits = fa.decode_tma_splits(B, nkv, ctx_len, cluster=cluster)
+        po = torch.empty(B * nq * splits * d, device=dev) if not cluster else None
+        pm = torch.empty(B * nq * splits * 2, device=dev) if not cluster else None
         us = _time_graph(lambda i: fa.attn_decode_tma(q, kp[i % layers], vp[i % layers], out, pos, sot, table, 64, B,
-                                                      nq, nkv, d, 1.0 / math.sqrt(d), 0, splits, cluster=True))
+                                                      nq, nkv, d, 1.0 / math.sqrt(d), 0, splits, po, pm, cluster=cluster))
         nbytes = B * ctx_len * nkv * d * 2 * 2
-        print(f"attn decode B={B:4d} ctx={ctx_len} splits={splits} {us:8.1f} us {nbytes / us / 1e6:6.2f} TB/s", flush=True)
+        form = f"cluster of {splits}" if cluster else f"{splits} splits + combine"
+        print(f"attn decode B={B:4d} ctx={ctx_len:6d} {form:22s} {us:8.1f} us {nbytes / us / 1e6:6.2f} TB/s", flush=True)
         del kp, vp
         torch.cuda.empty_cache()
 
@@ -98,10 +101,16 @@ def prefill_attn(lens, nq: int = 32, nkv: int = 8, d: int = 128) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["gemm", "attn", "prefill_attn"])
-    ap.add_argument("--m", default="1,8,64", help="token counts (gemm) or batch sizes (attn)")
+    ap.add_argument("--m", default="1,8,64", help="token counts (gemm), batch sizes (attn) or prompt lengths (prefill_attn)")
+    ap.add_argument("--ctx", default="2048", help="attn: cached positions per sequence (comma separated)")
+    ap.add_argument("--scratch", action="store_true", help="attn: splits merged by a second kernel instead of inside clusters")
     a = ap.parse_args()
     ms = [int(x) for x in a.m.split(",")]
-    {"gemm": gemm, "attn": attn, "prefill_attn": prefill_attn}[a.what](ms)
+    if a.what == "attn":
+        for c in a.ctx.split(","):
+            attn(ms, ctx_len=int(c), cluster=not a.scratch)
+    else:
+        {"gemm": gemm, "prefill_attn": prefill_attn}[a.what](ms)
 
 
 if __name__ == "__main__":
