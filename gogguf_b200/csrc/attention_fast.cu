@@ -42,6 +42,49 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Pairs of float32 in one 64-bit register for the packed arithmetic of sm_100 (two results per issue slot).
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// 2^x for two arguments x <= 0 (minus infinity included) on the FMA pipe instead of the special-function
+// unit: x = n + f with n the nearest integer and f in [-0.5, 0.5] (the magic-number addition leaves n in the
+// low mantissa bits of t), 2^f by a cubic whose relative error is below 7.5e-5 (the results are rounded to
+// bfloat16, 3.9e-3), and n added to the exponent field.  Prefill attention computes a third of its
+// exponentials this way: the special-function unit (16 results per clock and SM) is what bounds its softmax.
+__device__ __forceinline__ void exp2_poly2(float x0, float x1, float& r0, float& r1) {
+    const float MAGIC = 12582912.0f;                        // 1.5 * 2^23
+    x0 = fmaxf(x0, -126.0f);
+    x1 = fmaxf(x1, -126.0f);
+    const unsigned long long x = pack2(x0, x1);
+    const unsigned long long t = add2(x, pack2(MAGIC, MAGIC));
+    const unsigned long long n = add2(t, pack2(-MAGIC, -MAGIC));
+    const unsigned long long f = fma2(n, pack2(-1.0f, -1.0f), x);
+    unsigned long long p = fma2(pack2(0.0551716685f, 0.0551716685f), f, pack2(0.2426111251f, 0.2426111251f));
+    p = fma2(p, f, pack2(0.6932609677f, 0.6932609677f));
+    p = fma2(p, f, pack2(0.9999280572f, 0.9999280572f));
+    float p0, p1, t0, t1;
+    unpack2(p, p0, p1);
+    unpack2(t, t0, t1);
+    r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+    r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank) {
     uint32_t remote;
     float v;
@@ -746,6 +789,9 @@ int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* 
 // sums stay exact: P and the row sum use the same stale maximum), so most pages cost no pass over O.
 // Two CTAs share an SM (96 KB of shared memory and 256 tensor-memory columns each): while one runs
 // its softmax the other's MMAs keep the tensor pipe busy.
+// Every POLY_EVERY-th pair of exponentials of the softmax is computed by exp2_poly2.
+constexpr int POLY_EVERY = 3;
+
 template <int D>
 __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -757,22 +803,23 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
     constexpr int KBOX = 64 * 64 * 2;               // [64 columns x 64 rows] box of K or V: 8 KB
     constexpr int Q_BYTES = HALVES * QBOX, K_STAGE = HALVES * KBOX, V_BYTES = HALVES * KBOX, P_BYTES = 128 * 64 * 2;
     constexpr int TMEM_COLS = 256;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // The dynamic segment is the only shared memory of this kernel and is asked to start on a 1024-byte
+    // boundary (the swizzled tiles need it); there is no slack to round up in: two CTAs of 112.25 KB share an SM.
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* Qs = smem;
     uint8_t* Ks = Qs + Q_BYTES;                     // two stages
-    uint8_t* Vs = Ks + 2 * K_STAGE;
-    uint8_t* Ps = Vs + V_BYTES;
+    uint8_t* Vs = Ks + 2 * K_STAGE;                 // two stages
+    uint8_t* Ps = Vs + 2 * V_BYTES;
     uint64_t* bars = (uint64_t*)(Ps + P_BYTES);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;                    // [2]
     uint64_t* k_empty = bars + 3;                   // [2]
-    uint64_t* v_full = bars + 5;
-    uint64_t* v_empty = bars + 6;
-    uint64_t* s_full = bars + 7;
-    uint64_t* p_ready = bars + 8;
-    uint64_t* pv_done = bars + 9;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+    uint64_t* v_full = bars + 5;                    // [2]
+    uint64_t* v_empty = bars + 7;                   // [2]
+    uint64_t* s_full = bars + 9;                    // [2]
+    uint64_t* p_ready = bars + 11;
+    uint64_t* pv_done = bars + 12;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 13);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     // no early release of the next kernel here: see the note on dependent launches in common.cuh
@@ -780,8 +827,8 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
     if (threadIdx.x == 0) {
         tma::mbar_init(q_full, 1);
         for (int i = 0; i < 2; ++i) { tma::mbar_init(&k_full[i], 1); tma::mbar_init(&k_empty[i], 1); }
-        tma::mbar_init(v_full, 1); tma::mbar_init(v_empty, 1);
-        tma::mbar_init(s_full, 1); tma::mbar_init(p_ready, 128); tma::mbar_init(pv_done, 1);
+        for (int i = 0; i < 2; ++i) { tma::mbar_init(&v_full[i], 1); tma::mbar_init(&v_empty[i], 1); }
+        tma::mbar_init(&s_full[0], 1); tma::mbar_init(&s_full[1], 1); tma::mbar_init(p_ready, 128); tma::mbar_init(pv_done, 1);
         *abort_flag = 0;
         tma::mbar_fence_init();
         tma::prefetch_map(&tmQ); tma::prefetch_map(&tmK); tma::prefetch_map(&tmV);
@@ -802,7 +849,10 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
         if (tile < nt) { b = i; n_new = e - a; tok0 = a; break; }
         tile -= nt;
     }
-    const bool active = b >= 0;
+    // (a shared-memory base off the 1024-byte boundary would corrupt the swizzled tiles: refuse and say so)
+    const bool aligned = (tma::smem_u32(smem) & 1023u) == 0;
+    if (!aligned && threadIdx.x == 0) atomicCAS(status, 0, 29);
+    const bool active = b >= 0 && aligned;
     const int h = blockIdx.x, kvh = active ? h / (nq / nkv) : 0;
     const int row0 = tile * 128;
     const int rows = active ? min(128, n_new - row0) : 0;
@@ -811,7 +861,9 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
     if (window > 0 && pos0 - window + 1 > 0) lo = pos0 - window + 1;
     const int kt_first = lo / PAGE, kt_last = active ? (pos0 + rows - 1) / PAGE : -1;
     const int ntiles = kt_last - kt_first + 1;
-    const uint32_t S_t = tmem_base, O_t = tmem_base + 64;
+    // tensor memory: two score buffers of 64 columns (the scores of page j + 1 are computed while the softmax
+    // of page j runs), then the output accumulator
+    const uint32_t S_t = tmem_base, O_t = tmem_base + 128;
 
     if (warp == 4) {
         if (lane == 0 && active) {
@@ -826,10 +878,10 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
                 tma::mbar_expect_tx(&k_full[s], K_STAGE);
 #pragma unroll
                 for (int hf = 0; hf < HALVES; ++hf) tma::load_2d(Ks + s * K_STAGE + hf * KBOX, &tmK, &k_full[s], hf * 64, row);
-                if (!tma::mbar_wait(v_empty, (uint32_t)(j & 1) ^ 1u, abort_flag, status, 22)) break;
-                tma::mbar_expect_tx(v_full, V_BYTES);
+                if (!tma::mbar_wait(&v_empty[s], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, status, 22)) break;
+                tma::mbar_expect_tx(&v_full[s], V_BYTES);
 #pragma unroll
-                for (int hf = 0; hf < HALVES; ++hf) tma::load_2d(Vs + hf * KBOX, &tmV, v_full, hf * 64, row);
+                for (int hf = 0; hf < HALVES; ++hf) tma::load_2d(Vs + s * V_BYTES + hf * KBOX, &tmV, &v_full[s], hf * 64, row);
             }
         }
     } else if (warp == 5) {
@@ -837,32 +889,42 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
             const uint32_t idesc_qk = tc5::idesc_bf16(128, 64, 0), idesc_pv = tc5::idesc_bf16(128, D, 1);
             const uint32_t q_a = tma::smem_u32(Qs), k_a = tma::smem_u32(Ks), v_a = tma::smem_u32(Vs), p_a = tma::smem_u32(Ps);
             bool ok = tma::mbar_wait(q_full, 0, abort_flag, status, 23);
-            for (int j = 0; j < ntiles && ok; ++j) {
+            // scores of page j into buffer j & 1
+            auto issue_scores = [&](int j) -> bool {
                 const int s = j & 1;
-                ok = tma::mbar_wait(&k_full[s], (uint32_t)((j >> 1) & 1), abort_flag, status, 24);
-                if (!ok) break;
+                if (!tma::mbar_wait(&k_full[s], (uint32_t)((j >> 1) & 1), abort_flag, status, 24)) return false;
                 tc5::fence_after();
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint64_t a = tc5::smem_desc(q_a + (ks >> 2) * QBOX + (ks & 3) * 32, 16, 1024);
                     const uint64_t bb = tc5::smem_desc(k_a + s * K_STAGE + (ks >> 2) * KBOX + (ks & 3) * 32, 16, 1024);
-                    tc5::mma(S_t, a, bb, idesc_qk, ks > 0 ? 1u : 0u);
+                    tc5::mma(S_t + (uint32_t)(s * 64), a, bb, idesc_qk, ks > 0 ? 1u : 0u);
                 }
-                tc5::commit(s_full);
+                tc5::commit(&s_full[s]);
                 tc5::commit(&k_empty[s]);
+                return true;
+            };
+            if (ok && ntiles > 0) ok = issue_scores(0);
+            for (int j = 0; j < ntiles && ok; ++j) {
+                // The next page's scores do not wait for this page's softmax: their buffer was last read by the
+                // softmax of page j - 1, whose p_ready this thread has already seen.
+                if (j + 1 < ntiles) {
+                    ok = issue_scores(j + 1);
+                    if (!ok) break;
+                }
                 ok = tma::mbar_wait(p_ready, (uint32_t)(j & 1), abort_flag, status, 25);
                 if (!ok) break;
-                ok = tma::mbar_wait(v_full, (uint32_t)(j & 1), abort_flag, status, 26);
+                ok = tma::mbar_wait(&v_full[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, status, 26);
                 if (!ok) break;
                 tc5::fence_after();
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     const uint64_t a = tc5::smem_desc(p_a + kk * 32, 16, 1024);
-                    const uint64_t bb = tc5::smem_desc(v_a + kk * 2048, KBOX, 1024);
+                    const uint64_t bb = tc5::smem_desc(v_a + (j & 1) * V_BYTES + kk * 2048, KBOX, 1024);
                     tc5::mma(O_t, a, bb, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 tc5::commit(pv_done);
-                tc5::commit(v_empty);
+                tc5::commit(&v_empty[j & 1]);
             }
         }
     } else if (active) {
@@ -872,27 +934,40 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < ntiles; ++j) {
-            if (!tma::mbar_wait(s_full, (uint32_t)(j & 1), abort_flag, status, 27)) { ok = false; break; }
+            if (!tma::mbar_wait(&s_full[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, status, 27)) { ok = false; break; }
             tc5::fence_after();
             uint32_t sr[64];
-            tc5::ld32(S_t + lane_off, sr);
-            tc5::ld32(S_t + lane_off + 32, sr + 32);
+            tc5::ld32(S_t + lane_off + (uint32_t)((j & 1) * 64), sr);
+            tc5::ld32(S_t + lane_off + (uint32_t)((j & 1) * 64) + 32, sr + 32);
             tc5::wait_ld();
             const int key0 = (kt_first + j) * PAGE;
             const bool edge = (key0 + PAGE - 1 > pos0) || (window > 0 && key0 < pos0 + 127 - window + 1);
-            float mx = -INFINITY;
+            // the maximum of the raw scores (the scale is positive); masked keys become minus infinity first
+            float mraw = -INFINITY;
+            if (edge) {
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                float v = __uint_as_float(sr[c]) * scale_log2;
-                if (edge) {
+                for (int c = 0; c < 64; ++c) {
                     const int kidx = key0 + c;
                     bool vis = kidx <= p;
                     if (window > 0) vis = vis && (kidx > p - window);
-                    v = vis ? v : -INFINITY;
+                    if (!vis) sr[c] = 0xff800000u;
                 }
-                sr[c] = __float_as_uint(v);
-                mx = fmaxf(mx, v);
             }
+            {
+                // eight independent running maxima: one chain of 64 dependent operations would cost more
+                // than the exponentials (only two softmax warps share a scheduler)
+                float m8[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) m8[k] = __uint_as_float(sr[k]);
+#pragma unroll
+                for (int c = 8; c < 64; ++c) m8[c & 7] = fmaxf(m8[c & 7], __uint_as_float(sr[c]));
+                mraw = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+            }
+            const float mx = mraw * scale_log2;
+            // P V of the page before must be complete before O is rescaled and before P is overwritten (its
+            // scores were issued ahead of it, so s_full does not say so any more).  The exponentials do not
+            // depend on it: they are computed into registers first, and the wait comes as late as it can.
+            bool pv_seen = j == 0;
             // the scale in use is kept while the maximum has not grown by more than 2^8
             const bool grow = mx > m_used + 8.0f || (m_used == -INFINITY && mx != -INFINITY);
             if (__any_sync(0xffffffffu, grow)) {
@@ -903,6 +978,9 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
                     l *= corr;
                 }
                 if (j > 0) {
+                    if (!tma::mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag, status, 28)) { ok = false; break; }
+                    tc5::fence_after();
+                    pv_seen = true;
 #pragma unroll 1
                     for (int c0 = 0; c0 < D; c0 += 32) {
                         uint32_t orow[32];
@@ -916,19 +994,36 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
                 }
             }
             const float mu = m_used == -INFINITY ? 0.f : m_used;
+            const unsigned long long sc2 = pack2(scale_log2, scale_log2), nmu2 = pack2(-mu, -mu);
+            unsigned long long l4[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
+            uint32_t pk[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                // exponent of the pair: score * scale - maximum in use, one packed multiply-add
+                float x0, x1, p0, p1;
+                unpack2(fma2(pack2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1])), sc2, nmu2), x0, x1);
+                if (e % POLY_EVERY == 0) {
+                    exp2_poly2(x0, x1, p0, p1);
+                } else {
+                    p0 = fast_exp2(x0);
+                    p1 = fast_exp2(x1);
+                }
+                l4[e & 3] = add2(l4[e & 3], pack2(p0, p1));
+                pk[e] = pack_bf16(p0, p1);
+            }
+            {
+                float la, lb;
+                unpack2(add2(add2(l4[0], l4[1]), add2(l4[2], l4[3])), la, lb);
+                l += la + lb;
+            }
+            if (!pv_seen) {
+                if (!tma::mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag, status, 28)) { ok = false; break; }
+            }
             uint8_t* prow = Ps + row * 128;
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-                uint32_t pk[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = fast_exp2(__uint_as_float(sr[ch * 8 + 2 * e]) - mu);
-                    const float p1 = fast_exp2(__uint_as_float(sr[ch * 8 + 2 * e + 1]) - mu);
-                    l += p0 + p1;
-                    pk[e] = pack_bf16(p0, p1);
-                }
-                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            }
+            for (int ch = 0; ch < 8; ++ch)
+                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) =
+                    make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
             tc5::fence_proxy_async_smem();     // P was written with ordinary stores; the tensor core reads it
             tc5::fence_before();
             tma::mbar_arrive(p_ready);
@@ -1120,7 +1215,7 @@ GG_API gg_attn_prefill_tc(const void* q, const void* k_pool, const void* v_pool,
     const float scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(nq, max_tiles);
     if (d == 128) {
-        constexpr int smem = 2 * 16384 + 2 * 16384 + 16384 + 16384 + 1024 + 256;
+        constexpr int smem = 2 * 16384 + 2 * 16384 + 2 * 16384 + 16384 + 256;       // Q, K x 2, V x 2, P, barriers
         static bool cfg = false;
         if (!cfg) {
             cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -1130,7 +1225,7 @@ GG_API gg_attn_prefill_tc(const void* q, const void* k_pool, const void* v_pool,
         return gg_launch(attn_prefill_tc_kernel<128>, grid, dim3(192), smem, stream, 1, tq, tk, tv, (bf16*)out, cu_seqlens,
                          ctx_lens, seq_of_token, page_table, max_pages, n_seqs, nq, nkv, scale_log2, window, status);
     }
-    constexpr int smem = 16384 + 2 * 8192 + 8192 + 16384 + 1024 + 256;
+    constexpr int smem = 16384 + 2 * 8192 + 2 * 8192 + 16384 + 256;
     static bool cfg64 = false;
     if (!cfg64) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
