@@ -192,7 +192,7 @@ def main():
     def rand_tokens(n):
         return torch.randint(0, V, (n,), generator=g).tolist()
 
-    def decode_run(batch, steps, warmup):
+    def decode_run(batch, steps, warmup, sampler_cfg=None):
         """Prefill `batch` prompts of PROMPT_LEN tokens, then time `steps` greedy decode steps on the device."""
         room = PROMPT_LEN + warmup + steps + 8
         cache = model.new_cache(batch * (-(-room // 64) * 64))
@@ -205,7 +205,7 @@ def main():
             logits_last.append(st.step(ents).clone())
         # greedy sampling on the device; each step takes its input ids from the device buffer the previous
         # step's sampling kernel wrote, and the host reads every step's ids (one step behind the device)
-        sampler = Sampler(SamplerConfig())
+        sampler = Sampler(sampler_cfg if sampler_cfg is not None else SamplerConfig())
         rows = list(range(batch))
         pending = sampler.sample_async(torch.cat(logits_last), rows, [0] * batch)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -303,6 +303,13 @@ def main():
             points[f"decode_b{b}"] = r["tok_s"]
             points[f"decode_b{b}_hbm_frac"] = r["bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"]
             print(f"[bench] decode batch {b}: {r['tok_s']:.1f} tok/s, {r['ms_per_step']:.3f} ms/step", file=sys.stderr)
+
+    if not a.no_points:
+        # the same steps with the sampling chain a chat deployment of this architecture uses, all of it on the device
+        r = decode_run(a.batch, max(8, min(a.steps, 32)), 3, SamplerConfig(temp=0.6, top_k=20, top_p=0.95, seed=1))
+        points[f"decode_b{a.batch}_temp0.6_top_k20_top_p0.95"] = r["tok_s"]
+        print(f"[bench] decode batch {a.batch}, temp 0.6 / top-k 20 / top-p 0.95 on the device: {r['tok_s']:.1f} tok/s, "
+              f"{r['ms_per_step']:.3f} ms/step", file=sys.stderr)
 
     achieved = main_run["bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9
     line = {

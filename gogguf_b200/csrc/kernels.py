@@ -164,6 +164,28 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None) 
                                      _p(scratch), scratch.numel(), _stream())
 
 
+TOPK_MAX = 1024      # largest top-k the on-device chain takes (csrc/sampling.cu)
+
+
+_topk_scratch = {}
+
+
+def sample_topk(logits: torch.Tensor, temp: float, top_k: int, top_p: float, min_p: float, uniforms: torch.Tensor,
+                out: torch.Tensor, rows: Optional[int] = None) -> None:
+    """The sampling chain with a top-k on the device: temperature, top-k, min-p, softmax, top-p, draw."""
+    _need(logits, torch.float32, "logits")
+    _need(uniforms, torch.float64, "uniforms")
+    _need(out, torch.int32, "out")
+    R = logits.shape[0] if rows is None else rows
+    V = logits.shape[1]
+    words = -(-V // 8192) * min(int(top_k), V) * R          # what gg_sample_topk_scratch_words says
+    buf = _topk_scratch.get(logits.device)
+    if buf is None or buf.numel() < words:
+        buf = _topk_scratch[logits.device] = torch.empty(max(words, 1 << 16), dtype=torch.int64, device=logits.device)
+    kernel("sampling", "gg_sample_topk")(_p(logits), logits.stride(0), float(temp), int(top_k), float(top_p),
+                                          float(min_p), _p(uniforms), _p(out), R, V, _p(buf), buf.numel(), _stream())
+
+
 def sample(logits: torch.Tensor, temps: torch.Tensor, uniforms: torch.Tensor, out: torch.Tensor,
            rows: Optional[int] = None) -> None:
     _need(logits, torch.float32, "logits")

@@ -1,4 +1,5 @@
-// On-device sampling from float32 logits: greedy and temperature.
+// On-device sampling from float32 logits: greedy, temperature, and the whole chain of masks when a
+// top-k is set (temperature, top-k, min-p, softmax, top-p, draw: pkg/sampler/chain.go:34-68).
 //
 // greedy: the first index of the maximum (strict '>', pkg/sampler/greedy.go:4-17).
 // temperature: x = float32(float64(logit) / temp) (pkg/sampler/probs.go:40-49); softmax with
@@ -205,4 +206,251 @@ GG_API gg_sample(const float* logits, long long ld, const float* temps, const do
     if (V <= 0 || ld < V) return GG_ERR_ARG;
     gg_launch(sample_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, 1, logits, ld, temps, uniforms, out, V);
     return gg_last_error();
+}
+
+
+// ----------------------------------------------------------------------------- the chain with a top-k
+// (1) x = float32(float64(logit) / temp) when temp > 0 and != 1.  (2) The k largest x, ties to the lower id
+// (the reference sorts, chain.go:77-103).  Value and id make one 64-bit key, larger = better and no two equal,
+// so "the k best" is a threshold on that key; the k-th largest key of a set is found four bits at a time with
+// per-thread counters (no atomics).  Stage one: every block holds a slice of 8,192 logits of one row in
+// registers and leaves its k best keys in scratch (a row's k best are among its slices' k best).  Stage two:
+// one block per row selects the k best of those and runs (3) on them, in float64 as the reference: min-p
+// against the row maximum (penalties.go:35-54), softmax, top-p over the values in descending order
+// (chain.go:105-133: keep until the running sum reaches p - 1e-6, the element that crosses included), and the
+// draw in id order with the caller's uniform number (chain.go:135-166).  k is at most SAMP_TOPK_MAX.
+#define SAMP_TOPK_MAX 1024
+#define SAMP_SLICE 8192          // logits per block in stage one: eight per thread
+
+__device__ __forceinline__ uint32_t order_key(float f) {
+    // unsigned keys that order like the floats
+    const uint32_t b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t key) {
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+__device__ __forceinline__ unsigned long long best_key(float x, int id) {
+    return ((unsigned long long)order_key(x) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)id);
+}
+
+// The k-th largest of the keys that `key_of(j)`, j < n_mine, gives this thread (0 = no key), over the whole
+// block; k >= 1.  Returns 0 when the block holds fewer than k keys (then every key is among the k best).
+// Four bits per pass: every thread counts its keys per digit in sixteen 16-bit counters packed into four
+// 64-bit words (so a block may hold at most 65,535 keys), a warp adds them with shuffles, lane 0 adds the
+// warp's words into one of three rotating sets in shared memory, and after one barrier every thread reads
+// the totals and takes the same decision.  The low 32 bits (the ids) are only walked when the k-th place
+// falls among equal values.
+template <typename KeyOf>
+__device__ unsigned long long block_kth_largest(int n_mine, KeyOf key_of, int k, unsigned long long (*tot)[4]) {
+    const int lane = threadIdx.x & 31;
+    unsigned long long prefix = 0;
+    int above = 0;
+    if (threadIdx.x < 4) tot[0][threadIdx.x] = 0ull;
+    __syncthreads();
+    for (int pass = 0; pass < 16; ++pass) {
+        // passes 0-7 walk the high word (the value), 8-15 the low word (the id) of keys whose value is the threshold's
+        const int shift = 28 - 4 * (pass & 7);
+        const uint32_t p_hi = (uint32_t)(prefix >> 32), p_lo = (uint32_t)prefix;
+        const uint32_t p_word = pass < 8 ? p_hi : p_lo;
+        const uint32_t mask_above = shift == 28 ? 0u : (0xffffffffu << (shift + 4));     // the digits decided in this word
+        if (threadIdx.x < 4) tot[(pass + 1) % 3][threadIdx.x] = 0ull;     // last read two passes ago
+        unsigned long long c4[4] = {0ull, 0ull, 0ull, 0ull};
+        for (int j = 0; j < n_mine; ++j) {
+            const unsigned long long key = key_of(j);
+            const uint32_t hi = (uint32_t)(key >> 32), lo = (uint32_t)key;
+            const uint32_t word = pass < 8 ? hi : lo;
+            bool in = key != 0ull && ((word ^ p_word) & mask_above) == 0u;
+            if (pass >= 8) in = in && hi == p_hi;
+            const int b = (int)(word >> shift) & 15;
+            const unsigned long long inc = in ? (1ull << (16 * (b & 3))) : 0ull;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) c4[q] += (q == (b >> 2)) ? inc : 0ull;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) c4[q] += __shfl_xor_sync(0xffffffffu, c4[q], o);
+            // (two 32-bit additions: no 16-bit field overflows, so no carry crosses the halves)
+            if (lane == 0 && c4[q] != 0ull) {
+                uint32_t* t32 = reinterpret_cast<uint32_t*>(&tot[pass % 3][q]);
+                if ((uint32_t)c4[q] != 0u) atomicAdd(t32, (uint32_t)c4[q]);
+                if ((uint32_t)(c4[q] >> 32) != 0u) atomicAdd(t32 + 1, (uint32_t)(c4[q] >> 32));
+            }
+        }
+        __syncthreads();
+        int cum = above, bin = -1, at_bin = 0;
+#pragma unroll
+        for (int b = 15; b >= 0; --b) {
+            const int t = (int)((tot[pass % 3][b >> 2] >> (16 * (b & 3))) & 0xffffull);
+            if (bin < 0) {
+                if (cum + t >= k) { bin = b; at_bin = t; }
+                else cum += t;
+            }
+        }
+        if (bin < 0) return 0ull;                     // fewer than k keys in the block
+        prefix |= (unsigned long long)bin << (shift + (pass < 8 ? 32 : 0));
+        above = cum;
+        // all values decided and every key with the threshold value fits: the ids need not be walked
+        if (pass == 7 && above + at_bin <= k) return prefix;
+    }
+    return prefix;
+}
+
+// Stage one: grid (slices, rows).  cand[(row * slices + slice) * k + j]: the slice's k best keys (0 = none).
+__global__ void __launch_bounds__(SAMP_THREADS) topk_slice_kernel(const float* logits, long long ld, int V, float temp,
+                                                                  int k, unsigned long long* __restrict__ cand) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ unsigned long long tot[3][4];
+    __shared__ int n_out;
+    const int row = blockIdx.y, slice = blockIdx.x, tid = threadIdx.x;
+    const float* x = logits + (size_t)row * ld;
+    const bool scale = temp > 0.f && temp != 1.f;
+    const double inv_temp = scale ? 1.0 / (double)temp : 1.0;
+    unsigned long long keys[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int i = slice * SAMP_SLICE + u * SAMP_THREADS + tid;
+        float v = i < V ? x[i] : 0.f;
+        if (scale) v = (float)((double)v * inv_temp);
+        keys[u] = i < V ? best_key(v, i) : 0ull;
+    }
+    if (tid == 0) n_out = 0;
+    const unsigned long long thr = block_kth_largest(8, [&](int j) { return keys[j]; }, k, tot);
+    unsigned long long* dst = cand + ((size_t)row * gridDim.x + slice) * k;
+    for (int j = tid; j < k; j += SAMP_THREADS) dst[j] = 0ull;
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+        if (keys[u] != 0ull && keys[u] >= thr) dst[atomicAdd(&n_out, 1)] = keys[u];
+}
+
+// Stage two: one block per row over its slices * k candidate keys (dynamic shared memory holds them).
+__global__ void __launch_bounds__(SAMP_THREADS) sample_topk_kernel(
+    const unsigned long long* cand, int n_cand_keys, int top_k, float top_p, float min_p,
+    const double* __restrict__ uniforms, int* __restrict__ out) {
+    pdl_launch();
+    pdl_wait();
+    extern __shared__ unsigned long long ckeys[];
+    __shared__ unsigned long long tot[3][4];
+    __shared__ float cand_x[SAMP_TOPK_MAX];
+    __shared__ int cand_i[SAMP_TOPK_MAX];
+    __shared__ double cand_e[SAMP_TOPK_MAX];
+    __shared__ int by_value[SAMP_TOPK_MAX];      // candidate slots in descending order of x (ties: lower id)
+    __shared__ int by_id[SAMP_TOPK_MAX];         // candidate slots in ascending order of id
+    __shared__ unsigned char keep[SAMP_TOPK_MAX];
+    __shared__ int n_sel;
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const unsigned long long* src = cand + (size_t)row * n_cand_keys;
+    for (int j = tid; j < n_cand_keys; j += SAMP_THREADS) ckeys[j] = src[j];
+    if (tid == 0) n_sel = 0;
+    __syncthreads();
+    const int mine = (n_cand_keys - tid + SAMP_THREADS - 1) / SAMP_THREADS;
+    const unsigned long long thr = block_kth_largest(mine, [&](int j) { return ckeys[tid + j * SAMP_THREADS]; }, top_k, tot);
+    for (int j = tid; j < n_cand_keys; j += SAMP_THREADS) {
+        const unsigned long long key = ckeys[j];
+        if (key != 0ull && key >= thr) {
+            const int s = atomicAdd(&n_sel, 1);
+            cand_x[s] = key_value((uint32_t)(key >> 32));
+            cand_i[s] = (int)(0xffffffffu - (uint32_t)key);
+        }
+    }
+    __syncthreads();
+    const int n = n_sel;                          // min(top_k, V)
+    // ---- orders: by value (descending, ties to the lower id) and by id, by counting
+    for (int a = tid; a < n; a += SAMP_THREADS) {
+        const float xa = cand_x[a];
+        const int ia = cand_i[a];
+        int rv = 0, ri = 0;
+        for (int b = 0; b < n; ++b) {
+            const float xb = cand_x[b];
+            const int ib = cand_i[b];
+            rv += (xb > xa) || (xb == xa && ib < ia);
+            ri += ib < ia;
+        }
+        by_value[rv] = a;
+        by_id[ri] = a;
+    }
+    __syncthreads();
+    const float xmax = cand_x[by_value[0]];
+    // ---- min-p and the exponentials (the maximum of the whole row is among the candidates)
+    for (int a = tid; a < n; a += SAMP_THREADS) {
+        const double e = exp((double)(cand_x[a] - xmax));
+        const bool ok = !(min_p > 0.f && e < (double)min_p);     // p < min_p * p_max with p_max = e(0) / Z
+        keep[a] = ok ? 1 : 0;
+        cand_e[a] = ok ? e : 0.0;
+    }
+    __syncthreads();
+    // ---- top-p and the draw: a few hundred values at most, one thread
+    if (tid == 0) {
+        double Z = 0.0;
+        for (int r = 0; r < n; ++r) Z += cand_e[by_id[r]];
+        if (top_p > 0.f && top_p < 1.f) {
+            const double thr_p = (double)top_p - 1e-6;
+            double cum = 0.0;
+            bool cut = false;
+            for (int r = 0; r < n; ++r) {
+                const int a = by_value[r];
+                if (!keep[a]) continue;
+                if (cut) { keep[a] = 0; continue; }
+                cum += cand_e[a] / Z;
+                if (cum >= thr_p) cut = true;                // the element that crosses stays
+            }
+        }
+        double total = 0.0;
+        for (int r = 0; r < n; ++r) { const int a = by_id[r]; if (keep[a]) total += cand_e[a] / Z; }
+        int pick = -1, last = -1;
+        if (total > 0.0) {
+            const double target = uniforms[row] * total;
+            double run = 0.0;
+            for (int r = 0; r < n; ++r) {
+                const int a = by_id[r];
+                if (!keep[a]) continue;
+                last = cand_i[a];
+                run += cand_e[a] / Z;
+                if (target - run <= 0.0) { pick = cand_i[a]; break; }
+            }
+            if (pick < 0) pick = last;
+        } else {
+            pick = cand_i[by_value[0]];
+        }
+        out[row] = pick;
+    }
+}
+
+// Scratch that gg_sample_topk needs for R rows of V logits with this top-k, in 64-bit words.
+GG_API gg_sample_topk_scratch_words(int R, int V, int top_k, long long* words) {
+    if (R <= 0 || V <= 0 || top_k < 1 || words == nullptr) return GG_ERR_ARG;
+    const int k = top_k < V ? top_k : V;
+    const long long slices = (V + SAMP_SLICE - 1) / SAMP_SLICE;
+    *words = (long long)R * slices * k;
+    return 0;
+}
+
+// out[r] = the reference's sampling chain on row r with a top-k (1 <= min(top_k, V) <= 1024).  temp <= 0 or
+// == 1: no scaling; top_p outside (0, 1) and min_p <= 0: off.  uniforms[r] in [0, 1).  scratch: what
+// gg_sample_topk_scratch_words says.
+GG_API gg_sample_topk(const float* logits, long long ld, float temp, int top_k, float top_p, float min_p,
+                      const double* uniforms, int* out, int R, int V, void* scratch, long long scratch_words,
+                      cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (V <= 0 || ld < V || top_k < 1 || R > 65535) return GG_ERR_ARG;
+    const int k = top_k < V ? top_k : V;
+    const int slices = (V + SAMP_SLICE - 1) / SAMP_SLICE;
+    const long long per_row = (long long)slices * k;
+    if (k > SAMP_TOPK_MAX || scratch == nullptr || scratch_words < per_row * R) return GG_ERR_ARG;
+    const size_t smem = (size_t)per_row * sizeof(unsigned long long);
+    if (smem > 160 * 1024) return GG_ERR_ARG;          // 1,024 best of 20 slices still fit
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(sample_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    int rc = gg_launch(topk_slice_kernel, dim3(slices, R), dim3(SAMP_THREADS), 0, stream, 1, logits, ld, V, temp, k,
+                       (unsigned long long*)scratch);
+    if (rc != 0) return rc;
+    return gg_launch(sample_topk_kernel, dim3(R), dim3(SAMP_THREADS), smem, stream, 1,
+                     (const unsigned long long*)scratch, (int)per_row, k, top_p, min_p, uniforms, out);
 }

@@ -2,9 +2,10 @@
 
 Options and their meaning follow the reference's sampler (pkg/sampler/chain.go:9-70):
 `temp` 0 = greedy; `top_k` 0 = off; `top_p` 1 = off; `min_p` 0 = off; `seed` seeds the draws.
-Greedy and plain temperature sampling run on the GPU (csrc/sampling.cu) over the whole batch; the
-other options run this module's host chain on the logits of the rows that need them, in the
-reference's order: temperature, top-k, min-p, mask to -1e10, softmax, top-p, draw.
+Greedy sampling, plain temperature sampling, and the whole chain whenever a top-k of at most 1,024 is
+set run on the GPU (csrc/sampling.cu) over the whole batch; what is left (top-p or min-p without a
+top-k, a repeat penalty) runs this module's host chain on the logits of the rows that need it.  The
+order is the reference's: temperature, top-k, min-p, mask to -1e10, softmax, top-p, draw.
 
 Random draws are counter based: u = uniform01(seed, stream, step) with `stream` the request's index
 and `step` the number of tokens it has generated, so a sequence's draws do not depend on what else
@@ -52,9 +53,15 @@ class SamplerConfig:
         return self.temp <= 0 and self.top_k <= 0 and (self.top_p <= 0 or self.top_p >= 1)
 
     @property
+    def device_chain(self) -> bool:
+        """The chain with a top-k has a kernel (any top-p and min-p with it)."""
+        return 0 < self.top_k <= 1024
+
+    @property
     def on_device(self) -> bool:
-        """Greedy and plain temperature sampling have kernels; the masks run on the host."""
-        return self.greedy or (self.top_k <= 0 and (self.top_p <= 0 or self.top_p >= 1) and self.min_p <= 0)
+        """Greedy, plain temperature and top-k chains have kernels; top-p or min-p without a top-k run on the host."""
+        return self.greedy or self.device_chain or \
+            (self.top_k <= 0 and (self.top_p <= 0 or self.top_p >= 1) and self.min_p <= 0)
 
 
 def greedy(logits: Sequence[float]) -> int:
@@ -172,8 +179,11 @@ class Sampler:
             u_host[:rows] = torch.tensor([uniform01(self.cfg.seed, s, k) for s, k in zip(streams, steps)],
                                          dtype=torch.float64)
             u_dev[:rows].copy_(u_host[:rows], non_blocking=True)
-            temps[:rows].fill_(float(self.cfg.temp))
-            K.sample(logits, temps, u_dev, out, rows)
+            if self.cfg.device_chain:
+                K.sample_topk(logits, self.cfg.temp, self.cfg.top_k, self.cfg.top_p, self.cfg.min_p, u_dev, out, rows)
+            else:
+                temps[:rows].fill_(float(self.cfg.temp))
+                K.sample(logits, temps, u_dev, out, rows)
         pinned[:rows].copy_(out[:rows], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
@@ -197,9 +207,12 @@ class Sampler:
             if self.cfg.greedy:
                 K.argmax(logits, out, rows)
             else:
-                temps = torch.full((rows,), float(self.cfg.temp), dtype=torch.float32).to(logits.device, non_blocking=True)
                 uni = torch.tensor(us, dtype=torch.float64).to(logits.device, non_blocking=True)
-                K.sample(logits, temps, uni, out, rows)
+                if self.cfg.device_chain:
+                    K.sample_topk(logits, self.cfg.temp, self.cfg.top_k, self.cfg.top_p, self.cfg.min_p, uni, out, rows)
+                else:
+                    temps = torch.full((rows,), float(self.cfg.temp), dtype=torch.float32).to(logits.device, non_blocking=True)
+                    K.sample(logits, temps, uni, out, rows)
             return out.cpu().tolist()
         host = logits[:rows].detach().to("cpu", torch.float32).numpy()
         res = []

@@ -47,7 +47,17 @@ def test_temperature_sampling_follows_the_plain_sampler(tmp_path_factory):
             logits = plain.forward(cfg, w, seq, wide=True)[-1].float().tolist()
             assert tok == plain.sample(logits, 0.8, 0, 1.0, 0.0, plain.uniform01(123, i, k)), (i, k)
             seq.append(tok)
-    # the masked options run the host chain on the same logits
+    # a top-k chain runs on the device too (one step ahead of the host, like greedy)
+    sc = gg.SamplerConfig(temp=0.7, top_k=6, top_p=0.85, min_p=0.02, seed=9)
+    assert sc.on_device and sc.device_chain
+    out = engine.new_context().generate(prompts, gg.GenerateParams(max_tokens=5, sampler=sc, stop_token_ids=[]))
+    for i, (p, r) in enumerate(zip(prompts, out)):
+        seq = list(p)
+        for k, tok in enumerate(r.tokens):
+            logits = plain.forward(cfg, w, seq, wide=True)[-1].float().tolist()
+            assert tok == plain.sample(logits, 0.7, 6, 0.85, 0.02, plain.uniform01(9, i, k)), (i, k)
+            seq.append(tok)
+    # with a repeat penalty the host chain runs on the same logits
     params = gg.GenerateParams(max_tokens=4, sampler=gg.SamplerConfig(temp=0.9, top_k=7, top_p=0.9, seed=5),
                                repeat_penalty=1.3, stop_token_ids=[])
     out = engine.new_context().generate(prompts[:1], params)

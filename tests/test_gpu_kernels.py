@@ -579,3 +579,33 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge(kind):
             assert float((last - 5.0).abs().max()) < 0.05, (window, hot)     # all weight on the hot key
         else:
             assert float(last.abs().max()) < 4.0, (window, hot)              # the hot key is outside the window
+
+
+# ------------------------------------------------------------------------------------------ sampling chain
+@pytest.mark.parametrize("temp,top_k,top_p,min_p", [(0.8, 20, 0.95, 0.0), (0.0, 3, 1.0, 0.0), (1.0, 1, 0.5, 0.0),
+                                                     (1.3, 40, 0.6, 0.1), (0.6, 1000, 0.9, 0.0), (2.5, 64, 1.0, 0.3),
+                                                     (0.7, 5000, 0.8, 0.0)])
+def test_sampling_chain_with_top_k_on_device(temp, top_k, top_p, min_p):
+    """The device chain against the host chain (which tests/test_sampling.py holds to the plain sampler),
+    on rows with distinct values and on rows made of a few values only, so that the k-th place falls among
+    equal logits and the lower ids must win."""
+    import numpy as np
+    from gogguf_b200.sampling.sampler import SamplerConfig, sample_host, uniform01
+    V = 4099 if top_k <= 1024 else 600
+    if top_k > 1024:
+        top_k = 1024                                   # with V = 600: every id survives the top-k
+    rows = 16
+    g = torch.Generator().manual_seed(7)
+    logits = torch.randn(rows, V, generator=g) * 4
+    logits[4:8] = torch.round(logits[4:8] * 2) / 2      # many ties
+    logits[8:10] = torch.round(logits[8:10])            # a handful of values
+    logits[10] = 1.5                                    # all equal
+    logits[11, ::7] = 30.0                              # equal maxima
+    cfg = SamplerConfig(temp=temp, top_k=top_k, top_p=top_p, min_p=min_p, seed=3)
+    assert cfg.device_chain
+    for step in range(3):
+        us = [uniform01(3, r, step) for r in range(rows)]
+        out = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+        K().sample_topk(logits.to(DEV), temp, top_k, top_p, min_p, torch.tensor(us, dtype=torch.float64, device=DEV), out)
+        want = [sample_host(logits[r].numpy(), cfg, us[r]) for r in range(rows)]
+        assert out.cpu().tolist() == want, step
