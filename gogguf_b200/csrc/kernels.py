@@ -168,6 +168,7 @@ TOPK_MAX = 1024      # largest top-k the on-device chain takes (csrc/sampling.cu
 
 
 _topk_scratch = {}
+_sample_scratch = {}
 
 
 def sample_topk(logits: torch.Tensor, temp: float, top_k: int, top_p: float, min_p: float, uniforms: torch.Tensor,
@@ -193,5 +194,10 @@ def sample(logits: torch.Tensor, temps: torch.Tensor, uniforms: torch.Tensor, ou
     _need(uniforms, torch.float64, "uniforms")
     _need(out, torch.int32, "out")
     R = logits.shape[0] if rows is None else rows
-    kernel("sampling", "gg_sample")(_p(logits), logits.stride(0), _p(temps), _p(uniforms), _p(out), R,
-                                     logits.shape[1], _stream())
+    V = logits.shape[1]
+    words = R * 128 + 2 * R * (-(-V // 8192))
+    scratch = _sample_scratch.get(logits.device)
+    if scratch is None or scratch.numel() < words:
+        scratch = _sample_scratch[logits.device] = torch.empty(max(words, 1 << 14), dtype=torch.int32, device=logits.device)
+    kernel("sampling", "gg_sample")(_p(logits), logits.stride(0), _p(temps), _p(uniforms), _p(out), R, V,
+                                     _p(scratch), scratch.numel(), _stream())

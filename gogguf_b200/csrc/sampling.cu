@@ -200,12 +200,140 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(const float* logit
     if (threadIdx.x == 0) out[r] = found == 0x7fffffff ? V - 1 : found;
 }
 
+// The same draw for long rows, spread over blocks: out[r] holds the row's first maximum (gg_argmax ran before);
+// stage one sums exp(x - max) over slices of 8,192 ids (eight consecutive ids per thread), stage two finds the
+// slice in which the running sum reaches the target and walks it.  The sums are float64 and their order is
+// fixed (thread, warp, block, slice), though not the order of the one-block kernel above.
+#define SAMP_SLICE_IDS 8192
+
+__global__ void __launch_bounds__(SAMP_THREADS) sample_slice_sum_kernel(const float* logits, long long ld,
+                                                                         const float* __restrict__ temps,
+                                                                         const int* best, double* __restrict__ zs, int V) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ double dred[33];
+    const int r = blockIdx.y, slice = blockIdx.x;
+    const float temp = temps[r];
+    if (temp <= 0.f) return;
+    const float* x = logits + (size_t)r * ld;
+    const bool scaled = temp != 1.f;
+    const double inv_t = scaled ? 1.0 / (double)temp : 1.0;
+    const float raw_max = x[best[r]];
+    const float mx = scaled ? (float)((double)raw_max * inv_t) : raw_max;
+    const int lo = slice * SAMP_SLICE_IDS + threadIdx.x * 8;
+    double local = 0.0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int i = lo + u;
+        if (i < V) {
+            const float v = scaled ? (float)((double)x[i] * inv_t) : x[i];
+            local += exp((double)(v - mx));
+        }
+    }
+    const double total = block_sum_f64(local, dred);
+    if (threadIdx.x == 0) zs[(size_t)r * gridDim.x + slice] = total;
+}
+
+__global__ void __launch_bounds__(SAMP_THREADS) sample_pick_kernel(const float* logits, long long ld,
+                                                                    const float* __restrict__ temps,
+                                                                    const double* __restrict__ uniforms, const double* zs,
+                                                                    int slices, int* out, int V) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ double pre[SAMP_THREADS];
+    __shared__ double sh[3];          // 1 / Z, running sum before the slice, target
+    __shared__ int sh_slice, found;
+    const int r = blockIdx.x;
+    const float temp = temps[r];
+    if (temp <= 0.f) return;          // greedy row: out[r] already holds the first maximum
+    const float* x = logits + (size_t)r * ld;
+    const bool scaled = temp != 1.f;
+    const double inv_t = scaled ? 1.0 / (double)temp : 1.0;
+    const float raw_max = x[out[r]];
+    const float mx = scaled ? (float)((double)raw_max * inv_t) : raw_max;
+    __syncthreads();                  // every thread has read out[r] before it is overwritten
+    if (threadIdx.x == 0) {
+        double Z = 0.0;
+        for (int s = 0; s < slices; ++s) Z += zs[(size_t)r * slices + s];
+        const double inv = 1.0 / Z;
+        double norm = 0.0;
+        for (int s = 0; s < slices; ++s) norm += zs[(size_t)r * slices + s] * inv;
+        const double target = uniforms[r] * norm;
+        double run = 0.0;
+        int pick = -1;
+        for (int s = 0; s < slices; ++s) {
+            const double p = zs[(size_t)r * slices + s] * inv;
+            if (target - (run + p) <= 0.0) { pick = s; break; }
+            run += p;
+        }
+        sh[0] = inv; sh[1] = run; sh[2] = target;
+        sh_slice = pick;
+        found = 0x7fffffff;
+    }
+    __syncthreads();
+    const int slice = sh_slice;
+    if (slice < 0) {                  // rounding left the target above the total: the last id
+        if (threadIdx.x == 0) out[r] = V - 1;
+        return;
+    }
+    const double inv = sh[0], target = sh[2];
+    const int lo = slice * SAMP_SLICE_IDS + threadIdx.x * 8;
+    double e[8], local = 0.0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int i = lo + u;
+        e[u] = 0.0;
+        if (i < V) {
+            const float v = scaled ? (float)((double)x[i] * inv_t) : x[i];
+            e[u] = exp((double)(v - mx)) * inv;
+        }
+        local += e[u];
+    }
+    pre[threadIdx.x] = local;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double run = sh[1];
+        for (int t = 0; t < SAMP_THREADS; ++t) { const double c = pre[t]; pre[t] = run; run += c; }
+    }
+    __syncthreads();
+    double run = pre[threadIdx.x];
+    if (run < target + 1e-300) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (lo + u < V) {
+                run += e[u];
+                if (target - run <= 0.0) { atomicMin(&found, lo + u); break; }
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // the slice's own sum said the target is reached inside it; if the walk's rounding disagrees, its last id
+        const int last = min(V, (slice + 1) * SAMP_SLICE_IDS) - 1;
+        out[r] = found == 0x7fffffff ? last : found;
+    }
+}
+
+// scratch (optional): R * 128 four-byte words for the two-stage maximum, then R * ceil(V / 8192) doubles; with
+// it, rows of 16,384 ids or more are spread over blocks.  Null: one block per row.
 GG_API gg_sample(const float* logits, long long ld, const float* temps, const double* uniforms, int* out,
-                 int R, int V, cudaStream_t stream) {
+                 int R, int V, void* scratch, long long scratch_words, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0 || ld < V) return GG_ERR_ARG;
-    gg_launch(sample_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, 1, logits, ld, temps, uniforms, out, V);
-    return gg_last_error();
+    const int slices = (V + SAMP_SLICE_IDS - 1) / SAMP_SLICE_IDS;
+    const long long need = (long long)R * 128 + 2LL * R * slices;
+    if (scratch == nullptr || V < 16384 || scratch_words < need || R > 65535 || (((uintptr_t)scratch) & 7)) {
+        gg_launch(sample_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, 1, logits, ld, temps, uniforms, out, V);
+        return gg_last_error();
+    }
+    int rc = gg_argmax(logits, ld, out, R, V, scratch, (long long)R * 128, stream);
+    if (rc != 0) return rc;
+    double* zs = reinterpret_cast<double*>(reinterpret_cast<int*>(scratch) + (size_t)R * 128);
+    rc = gg_launch(sample_slice_sum_kernel, dim3(slices, R), dim3(SAMP_THREADS), 0, stream, 1, logits, ld, temps,
+                   (const int*)out, zs, V);
+    if (rc != 0) return rc;
+    return gg_launch(sample_pick_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, 1, logits, ld, temps, uniforms,
+                     (const double*)zs, slices, out, V);
 }
 
 

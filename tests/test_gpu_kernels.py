@@ -591,7 +591,7 @@ def test_sampling_chain_with_top_k_on_device(temp, top_k, top_p, min_p):
     equal logits and the lower ids must win."""
     import numpy as np
     from gogguf_b200.sampling.sampler import SamplerConfig, sample_host, uniform01
-    V = 4099 if top_k <= 1024 else 600
+    V = (20011 if top_k in (20, 40) else 4099) if top_k <= 1024 else 600     # 20011: three slices in stage one
     if top_k > 1024:
         top_k = 1024                                   # with V = 600: every id survives the top-k
     rows = 16
@@ -609,3 +609,24 @@ def test_sampling_chain_with_top_k_on_device(temp, top_k, top_p, min_p):
         K().sample_topk(logits.to(DEV), temp, top_k, top_p, min_p, torch.tensor(us, dtype=torch.float64, device=DEV), out)
         want = [sample_host(logits[r].numpy(), cfg, us[r]) for r in range(rows)]
         assert out.cpu().tolist() == want, step
+
+
+@pytest.mark.parametrize("V", [331, 5000, 40000])
+def test_temperature_sampling_and_argmax_on_device(V):
+    """One block per row for short rows, several blocks per row from 16,384 ids on; both against the host chain.
+    A row with temperature 0 is greedy: the first maximum."""
+    from gogguf_b200.sampling.sampler import SamplerConfig, sample_host, uniform01
+    rows = 9
+    g = torch.Generator().manual_seed(11)
+    logits = torch.randn(rows, V, generator=g) * 3
+    logits[3, V // 2] = logits[3, V - 5] = 25.0            # equal maxima: greedy takes the first
+    temps = [0.7, 1.0, 1.9, 0.0, 0.3, 5.0, 0.0, 1.2, 0.05]
+    for step in range(4):
+        us = [uniform01(5, r, step) for r in range(rows)]
+        out = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+        K().sample(logits.to(DEV), torch.tensor(temps, device=DEV), torch.tensor(us, dtype=torch.float64, device=DEV), out)
+        want = [sample_host(logits[r].numpy(), SamplerConfig(temp=temps[r]), us[r]) for r in range(rows)]
+        assert out.cpu().tolist() == want, step
+    am = torch.empty(rows, dtype=torch.int32, device=DEV)
+    K().argmax(logits.to(DEV), am)
+    assert am.cpu().tolist() == logits.argmax(dim=1).tolist() and am[3].item() == V // 2
