@@ -425,9 +425,13 @@ __device__ unsigned long long block_kth_largest(int n_mine, KeyOf key_of, int k,
     return prefix;
 }
 
-// Stage one: grid (slices, rows).  cand[(row * slices + slice) * k + j]: the slice's k best keys (0 = none).
-__global__ void __launch_bounds__(SAMP_THREADS) topk_slice_kernel(const float* logits, long long ld, int V, float temp,
-                                                                  int k, unsigned long long* __restrict__ cand) {
+// Stage one: grid (slices, rows), 256 threads with 32 logits each (the per-pass cost of a thread is mostly fixed:
+// shuffles, the barrier, the decision).  cand[(row * slices + slice) * k + j]: the slice's k best keys (0 = none).
+#define SAMP_SLICE_THREADS 256
+#define SAMP_SLICE_PER (SAMP_SLICE / SAMP_SLICE_THREADS)
+
+__global__ void __launch_bounds__(SAMP_SLICE_THREADS) topk_slice_kernel(const float* logits, long long ld, int V, float temp,
+                                                                        int k, unsigned long long* __restrict__ cand) {
     pdl_launch();
     pdl_wait();
     __shared__ unsigned long long tot[3][4];
@@ -436,21 +440,21 @@ __global__ void __launch_bounds__(SAMP_THREADS) topk_slice_kernel(const float* l
     const float* x = logits + (size_t)row * ld;
     const bool scale = temp > 0.f && temp != 1.f;
     const double inv_temp = scale ? 1.0 / (double)temp : 1.0;
-    unsigned long long keys[8];
+    unsigned long long keys[SAMP_SLICE_PER];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-        const int i = slice * SAMP_SLICE + u * SAMP_THREADS + tid;
+    for (int u = 0; u < SAMP_SLICE_PER; ++u) {
+        const int i = slice * SAMP_SLICE + u * SAMP_SLICE_THREADS + tid;
         float v = i < V ? x[i] : 0.f;
         if (scale) v = (float)((double)v * inv_temp);
         keys[u] = i < V ? best_key(v, i) : 0ull;
     }
     if (tid == 0) n_out = 0;
-    const unsigned long long thr = block_kth_largest(8, [&](int j) { return keys[j]; }, k, tot);
+    const unsigned long long thr = block_kth_largest(SAMP_SLICE_PER, [&](int j) { return keys[j]; }, k, tot);
     unsigned long long* dst = cand + ((size_t)row * gridDim.x + slice) * k;
-    for (int j = tid; j < k; j += SAMP_THREADS) dst[j] = 0ull;
+    for (int j = tid; j < k; j += SAMP_SLICE_THREADS) dst[j] = 0ull;
     __syncthreads();
 #pragma unroll
-    for (int u = 0; u < 8; ++u)
+    for (int u = 0; u < SAMP_SLICE_PER; ++u)
         if (keys[u] != 0ull && keys[u] >= thr) dst[atomicAdd(&n_out, 1)] = keys[u];
 }
 
@@ -576,7 +580,7 @@ GG_API gg_sample_topk(const float* logits, long long ld, float temp, int top_k, 
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    int rc = gg_launch(topk_slice_kernel, dim3(slices, R), dim3(SAMP_THREADS), 0, stream, 1, logits, ld, V, temp, k,
+    int rc = gg_launch(topk_slice_kernel, dim3(slices, R), dim3(SAMP_SLICE_THREADS), 0, stream, 1, logits, ld, V, temp, k,
                        (unsigned long long*)scratch);
     if (rc != 0) return rc;
     return gg_launch(sample_topk_kernel, dim3(R), dim3(SAMP_THREADS), smem, stream, 1,
