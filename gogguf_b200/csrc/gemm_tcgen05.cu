@@ -313,6 +313,79 @@ __device__ __forceinline__ void epilogue_row_256(uint32_t taddr, int gi, int tn,
     }
 }
 
+// The end of a decode-style epilogue: a warp holds one token's 128 consecutive accumulator columns
+// [128 tile_a, 128 tile_a + 128), four per lane, already summed over the K splits and multiplied by the folded
+// norm's factor, and applies the output mode (bf16 or float32 store, float32 add with the row statistics of the
+// updated rows, or SwiGLU over interleaved gate/up blocks).  All 32 lanes call it.
+__device__ __forceinline__ void finish_token_block(float4 acc, int gj, int tile_a, int lane, void* __restrict__ out,
+                                                   int out_mode, long long ldo, int N, const NormIO& nio) {
+    if (out_mode == OUT_SWIGLU) {
+        // lanes 0..15 hold gates of 64 features, lanes 16..31 their ups
+        const float ux = __shfl_down_sync(0xffffffffu, acc.x, 16), uy = __shfl_down_sync(0xffffffffu, acc.y, 16);
+        const float uz = __shfl_down_sync(0xffffffffu, acc.z, 16), uw = __shfl_down_sync(0xffffffffu, acc.w, 16);
+        const int feat = tile_a * 64 + 4 * lane;
+        if (lane < 16 && feat < N / 2) {                 // N / 2 is a multiple of 64 here
+            bf16* op = (bf16*)out + (size_t)gj * ldo + feat;
+            __nv_bfloat162 a = __floats2bfloat162_rn(silu_mul(acc.x, ux), silu_mul(acc.y, uy));
+            __nv_bfloat162 b = __floats2bfloat162_rn(silu_mul(acc.z, uz), silu_mul(acc.w, uw));
+            if ((((uintptr_t)op) & 7) == 0) {
+                *reinterpret_cast<uint2*>(op) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+            } else {
+                op[0] = a.x; op[1] = a.y; op[2] = b.x; op[3] = b.y;
+            }
+        }
+        return;
+    }
+    const int gi0 = tile_a * BM + 4 * lane;              // first of this lane's four features
+    const bool stats = nio.out_ssq != nullptr && out_mode == OUT_F32_ACC;
+    float ss = 0.f;
+    if (gi0 < N) {
+        const bool whole = gi0 + 4 <= N;
+        const size_t o = (size_t)gj * ldo + gi0;
+        float f[4] = {acc.x, acc.y, acc.z, acc.w};
+        if (out_mode == OUT_BF16) {
+            bf16* op = (bf16*)out + o;
+            if (whole && (((uintptr_t)op) & 7) == 0) {
+                __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+                *reinterpret_cast<uint2*>(op) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+            } else {
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+                    if (gi0 + t < N) op[t] = __float2bfloat16_rn(f[t]);
+            }
+        } else {
+            float* op = (float*)out + o;
+            bf16* xp = stats ? nio.out_xhat + (size_t)gj * N + gi0 : nullptr;
+            if (whole && (((uintptr_t)op) & 15) == 0 && (!stats || (((uintptr_t)xp) & 7) == 0)) {
+                float4 w4 = make_float4(f[0], f[1], f[2], f[3]);
+                if (out_mode == OUT_F32_ACC) {
+                    const float4 old = *reinterpret_cast<float4*>(op);
+                    w4.x += old.x; w4.y += old.y; w4.z += old.z; w4.w += old.w;
+                }
+                *reinterpret_cast<float4*>(op) = w4;
+                if (stats) {
+                    ss = fmaf(w4.x, w4.x, ss); ss = fmaf(w4.y, w4.y, ss); ss = fmaf(w4.z, w4.z, ss); ss = fmaf(w4.w, w4.w, ss);
+                    __nv_bfloat162 a = __floats2bfloat162_rn(w4.x, w4.y), b = __floats2bfloat162_rn(w4.z, w4.w);
+                    *reinterpret_cast<uint2*>(xp) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+                }
+            } else {
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+                    if (gi0 + t < N) {
+                        float val = f[t];
+                        if (out_mode == OUT_F32_ACC) val += op[t];
+                        op[t] = val;
+                        if (stats) { ss = fmaf(val, val, ss); xp[t] = __float2bfloat16_rn(val); }
+                    }
+            }
+        }
+    }
+    if (stats) {
+        ss = warp_sum(ss);                               // one 128-feature part per tile
+        if (lane == 0) nio.out_ssq[(size_t)gj * ((N + 127) / 128) + tile_a] = ss;
+    }
+}
+
 template <int BN> constexpr int tmem_cols() { return BN < 32 ? 32 : BN; }
 
 __device__ __forceinline__ void cluster_sync_all() {
@@ -513,23 +586,6 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                     const float sc = norm_factor_warp(nio, gj, lane);
                     acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc;
                 }
-                if (out_mode == OUT_SWIGLU) {
-                    // lanes 0..15 hold gates of 64 features, lanes 16..31 their ups
-                    const float ux = __shfl_down_sync(0xffffffffu, acc.x, 16), uy = __shfl_down_sync(0xffffffffu, acc.y, 16);
-                    const float uz = __shfl_down_sync(0xffffffffu, acc.z, 16), uw = __shfl_down_sync(0xffffffffu, acc.w, 16);
-                    const int feat = tile_a * 64 + 4 * lane;
-                    if (lane < 16 && feat < N / 2) {                 // N / 2 is a multiple of 64 here
-                        bf16* op = (bf16*)out + (size_t)gj * ldo + feat;
-                        __nv_bfloat162 a = __floats2bfloat162_rn(silu_mul(acc.x, ux), silu_mul(acc.y, uy));
-                        __nv_bfloat162 b = __floats2bfloat162_rn(silu_mul(acc.z, uz), silu_mul(acc.w, uw));
-                        if ((((uintptr_t)op) & 7) == 0) {
-                            *reinterpret_cast<uint2*>(op) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-                        } else {
-                            op[0] = a.x; op[1] = a.y; op[2] = b.x; op[3] = b.y;
-                        }
-                    }
-                    continue;
-                }
                 if (out_mode == OUT_QKV) {
                     // this tile is head `tile_a` of token gj; the lane holds features 4 lane .. 4 lane + 3
                     const int h = tile_a;
@@ -571,54 +627,7 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                         make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&bb));
                     continue;
                 }
-                const int gi0 = tile_a * BM + 4 * lane;              // first of this lane's four features
-                const bool stats = nio.out_ssq != nullptr && out_mode == OUT_F32_ACC;
-                float ss = 0.f;
-                if (gi0 < N) {
-                    const bool whole = gi0 + 4 <= N;
-                    const size_t o = (size_t)gj * ldo + gi0;
-                    float f[4] = {acc.x, acc.y, acc.z, acc.w};
-                    if (out_mode == OUT_BF16) {
-                        bf16* op = (bf16*)out + o;
-                        if (whole && (((uintptr_t)op) & 7) == 0) {
-                            __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
-                            *reinterpret_cast<uint2*>(op) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-                        } else {
-#pragma unroll
-                            for (int t = 0; t < 4; ++t)
-                                if (gi0 + t < N) op[t] = __float2bfloat16_rn(f[t]);
-                        }
-                    } else {
-                        float* op = (float*)out + o;
-                        bf16* xp = stats ? nio.out_xhat + (size_t)gj * N + gi0 : nullptr;
-                        if (whole && (((uintptr_t)op) & 15) == 0 && (!stats || (((uintptr_t)xp) & 7) == 0)) {
-                            float4 w4 = make_float4(f[0], f[1], f[2], f[3]);
-                            if (out_mode == OUT_F32_ACC) {
-                                const float4 old = *reinterpret_cast<float4*>(op);
-                                w4.x += old.x; w4.y += old.y; w4.z += old.z; w4.w += old.w;
-                            }
-                            *reinterpret_cast<float4*>(op) = w4;
-                            if (stats) {
-                                ss = fmaf(w4.x, w4.x, ss); ss = fmaf(w4.y, w4.y, ss); ss = fmaf(w4.z, w4.z, ss); ss = fmaf(w4.w, w4.w, ss);
-                                __nv_bfloat162 a = __floats2bfloat162_rn(w4.x, w4.y), b = __floats2bfloat162_rn(w4.z, w4.w);
-                                *reinterpret_cast<uint2*>(xp) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-                            }
-                        } else {
-#pragma unroll
-                            for (int t = 0; t < 4; ++t)
-                                if (gi0 + t < N) {
-                                    float val = f[t];
-                                    if (out_mode == OUT_F32_ACC) val += op[t];
-                                    op[t] = val;
-                                    if (stats) { ss = fmaf(val, val, ss); xp[t] = __float2bfloat16_rn(val); }
-                                }
-                        }
-                    }
-                }
-                if (stats) {
-                    ss = warp_sum(ss);                               // one 128-feature part per tile
-                    if (lane == 0) nio.out_ssq[(size_t)gj * ((N + 127) / 128) + tile_a] = ss;
-                }
+                finish_token_block(acc, gj, tile_a, lane, out, out_mode, ldo, N, nio);
             }
         }
         if (cluster_reduce) cluster_sync_all();     // nobody leaves while its shared memory may still be read
@@ -881,7 +890,7 @@ template <int STAGES>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
     void* __restrict__ out, int out_mode, long long ldo, int M, int N, int K, int* __restrict__ status,
-    const NormIO nio) {
+    const NormIO nio, int splits, int kb_per_split, float* __restrict__ partial) {
     constexpr int BN = 256;                     // columns of the pair's tile (each CTA stages 128 of the B rows)
     constexpr int HALF_B_BYTES = 128 * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + HALF_B_BYTES;      // per CTA: 32 KB
@@ -902,7 +911,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     const int num_kb = (K + BK - 1) / BK;
     const int tiles_m = (M + 255) / 256, tiles_n = (N + BN - 1) / BN;
-    const int total = tiles_m * tiles_n;
+    // With few tiles (prompts of a few hundred tokens) the K range of every tile is split over `splits` work
+    // items, so that all pairs have work; the items leave float32 partial tiles in `partial`
+    // [splits][M][N] and gemm_splitk_finish_kernel adds them and applies the output mode.
+    const int tiles = tiles_m * tiles_n;
+    const int total = tiles * splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -928,22 +941,24 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
             int it = 0;
             bool first = true, ok = true;
             for (int t = pair; t < total && ok; t += num_pairs) {
-                const int tm = t % tiles_m, tn = t / tiles_m;
+                const int tile = t % tiles, split = t / tiles;
+                const int tm = tile % tiles_m, tn = tile / tiles_m;
                 const int arow = tm * 256 + (int)rank * 128, brow = tn * BN + (int)rank * 128;
-                int kb = 0;
+                const int kb0 = split * kb_per_split, kb1 = min(num_kb, kb0 + kb_per_split);
+                int kb = kb0;
                 if (first) {
-                    const int pre = num_kb < STAGES ? num_kb : STAGES;
+                    const int pre = kb1 - kb0 < STAGES ? kb1 - kb0 : STAGES;
                     for (int i = 0; i < pre; ++i) {
                         if (leader) mbar_expect_tx(&full[i], 2 * STAGE_BYTES);
-                        tma_load_2d_pair(smem + i * STAGE_BYTES + A_BYTES, &tmB, &full[i], i * BK, brow);
+                        tma_load_2d_pair(smem + i * STAGE_BYTES + A_BYTES, &tmB, &full[i], (kb0 + i) * BK, brow);
                     }
                     pdl_wait();
-                    for (int i = 0; i < pre; ++i) tma_load_2d_pair(smem + i * STAGE_BYTES, &tmA, &full[i], i * BK, arow);
-                    kb = pre;
+                    for (int i = 0; i < pre; ++i) tma_load_2d_pair(smem + i * STAGE_BYTES, &tmA, &full[i], (kb0 + i) * BK, arow);
+                    kb = kb0 + pre;
                     it = pre;
                     first = false;
                 }
-                for (; kb < num_kb; ++kb, ++it) {
+                for (; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                     if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, 1)) { ok = false; break; }
@@ -967,7 +982,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t tacc = tmem_base + (uint32_t)(buf * BN);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int split = t / tiles;
+                const int kb0 = split * kb_per_split, kb1 = min(num_kb, kb0 + kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                     ok = mbar_wait(&full[s], ph, abort_flag, status, 2);
@@ -978,7 +995,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
                     const uint64_t bdesc = make_smem_desc(sa + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_pair(tacc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_pair(tacc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     umma_commit_pair(&empty[s]);
                 }
                 if (ok) umma_commit_pair(&acc_full[buf]);
@@ -990,14 +1007,38 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
         pdl_wait();
         int i = 0;
         for (int t = pair; t < total; t += num_pairs, ++i) {
-            const int tm = t % tiles_m, tn = t / tiles_m;
+            const int tile = t % tiles, split = t / tiles;
+            const int tm = tile % tiles_m, tn = tile / tiles_m;
             const int buf = i & 1;
             const uint32_t aph = (uint32_t)(i >> 1) & 1u;
             const int gi = tm * 256 + (int)rank * 128 + row;
-            const float sc = gi < M ? norm_factor(nio, gi) : 1.0f;      // while the tile is still being multiplied
+            const float sc = (gi < M && partial == nullptr) ? norm_factor(nio, gi) : 1.0f;   // while the tile is still being multiplied
             if (!mbar_wait(&acc_full[buf], aph, abort_flag, status, 3)) break;
             tc_fence_after();
-            epilogue_row_256(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN), gi, tn, M, N, out, out_mode, ldo, nio, sc);
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+            if (partial != nullptr) {
+                // the raw sums of this K range: row gi of split's [M][N] float32 tile
+                float* prow = partial + ((size_t)split * M + gi) * N + tn * BN;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    if (tn * BN + c0 >= N) break;
+                    uint32_t r[16];
+                    tmem_ld16(taddr + (uint32_t)c0, r);
+                    tmem_ld_wait();
+                    if (gi >= M) continue;
+                    if (tn * BN + c0 + 16 <= N && ((((uintptr_t)(prow + c0)) & 15) == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            reinterpret_cast<float4*>(prow + c0)[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (tn * BN + c0 + j < N) prow[c0 + j] = __uint_as_float(r[j]);
+                    }
+                }
+            } else
+            epilogue_row_256(taddr, gi, tn, M, N, out, out_mode, ldo, nio, sc);
             tc_fence_before();
             mbar_arrive_cluster(&acc_empty[buf], 0);     // 256 arrivals in the leader free the accumulator pair
         }
@@ -1017,8 +1058,61 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
     }
 }
 
+// out (mode) = sum over splits of partial[s], scaled by the folded norm's factor: a warp per (token, block of 128
+// columns), the epilogue of the decode form.
+__global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* partial, int splits, void* __restrict__ out,
+                                                                 int out_mode, long long ldo, int M, int N, const NormIO nio) {
+    pdl_launch();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int gj = blockIdx.y * 8 + (threadIdx.x >> 5);          // token
+    const int tile_a = blockIdx.x;                               // block of 128 columns
+    if (gj >= M) return;
+    const int c0 = tile_a * 128 + 4 * lane;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c0 + 4 <= N && (N & 3) == 0) {
+        for (int s = 0; s < splits; ++s) {
+            const float4 v = *reinterpret_cast<const float4*>(partial + ((size_t)s * M + gj) * N + c0);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+    } else {
+        float f[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < splits; ++s)
+            for (int t = 0; t < 4; ++t)
+                if (c0 + t < N) f[t] += partial[((size_t)s * M + gj) * N + c0 + t];
+        acc = make_float4(f[0], f[1], f[2], f[3]);
+    }
+    if (nio.in_ssq != nullptr) {
+        const float sc = norm_factor_warp(nio, gj, lane);
+        acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc;
+    }
+    finish_token_block(acc, gj, tile_a, lane, out, out_mode, ldo, N, nio);
+}
+
+// K splits of the CTA-pair form for a product with few tiles: the count that fills the 74 pairs best, as long as
+// every split keeps eight 64-wide slabs and the float32 partial tiles (written and read once) cost less than
+// the idle pairs.  1: no split.
+int pair_splits(int M, int N, int K) {
+    const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    const int num_kb = (K + BK - 1) / BK;
+    const int pairs = 74;
+    double best_cost = 1e30;
+    int best = 1;
+    for (int s = 1; s <= 8; ++s) {
+        if (s > 1 && num_kb / s < 8) break;
+        const int items = tiles * s;
+        const int waves = (items + pairs - 1) / pairs;
+        // time of the product in units of "one tile over the whole K", plus the partial tiles' traffic in the same
+        // units (a 256 x 256 x K tile takes about 2 * 256 * 256 * K / (1.3e15 / 74) s; 6e12 bytes/s for the partials)
+        const double tile_s = 2.0 * 256 * 256 * K / (1.3e15 / pairs);
+        const double cost = waves * tile_s / s + (s > 1 ? 2.0 * s * M * (double)N * 4 / 6e12 : 0.0);
+        if (cost < best_cost * 0.97) { best_cost = cost; best = s; }
+    }
+    return best;
+}
+
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N,
-                int K, int* status, const NormIO& nio, cudaStream_t stream) {
+                int K, int* status, const NormIO& nio, int splits, float* partial, cudaStream_t stream) {
     constexpr int STAGES = 6;
     constexpr int smem = STAGES * (A_BYTES + 128 * BK * 2) + 1024 + 256;
     static int sms = 0;
@@ -1031,10 +1125,18 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out
         if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
         sms = n > 0 ? n : 148;
     }
-    const int total = ((M + 255) / 256) * ((N + 255) / 256);
+    const int total = ((M + 255) / 256) * ((N + 255) / 256) * splits;
     int pairs = sms / 2;
     if (pairs > total) pairs = total;
-    return gg_launch2(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, stream, ta, tb, out, out_mode, ldo, M, N, K, status, nio);
+    const int num_kb = (K + BK - 1) / BK;
+    const int per = (num_kb + splits - 1) / splits;
+    const int used = (num_kb + per - 1) / per;           // no empty split
+    if (used == 1) partial = nullptr;
+    int rc = gg_launch2(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, stream, ta, tb, out, out_mode, ldo, M, N, K, status, nio,
+                        used, per, partial);
+    if (rc != 0 || used == 1) return rc;
+    return gg_launch(gemm_splitk_finish_kernel, dim3((N + 127) / 128, (M + 7) / 8), dim3(256), 0, stream, 1,
+                     (const float*)partial, used, out, out_mode, ldo, M, N, nio);
 }
 
 template <int BN, int STAGES, bool SWAP, int MINB>
@@ -1142,7 +1244,9 @@ static int gemm_tc_impl(const void* x, const void* w, void* out, int out_mode, i
         if (bn == 256 && use_pair) {
             // CTA pairs: A tiles of 128 rows per CTA as before, B staged in halves of 128 rows per CTA
             if ((rc = make_map(&tb, w, N, K, K, 128)) != 0) return rc;
-            rc = launch_pair(ta, tb, out, out_mode, ldo, M, N, K, status, nio, stream);
+            int ps = pair_splits(M, N, K);
+            if (scratch == nullptr || scratch_elems < (long long)ps * M * N) ps = 1;     // no room for partial tiles
+            rc = launch_pair(ta, tb, out, out_mode, ldo, M, N, K, status, nio, ps, scratch, stream);
         } else if (bn == 256) rc = launch_persistent(ta, tb, out, out_mode, ldo, M, N, K, status, nio, stream);
         else rc = launch<128, 6, false, 1>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, false, status, nio, qio, stream);
     }
@@ -1168,18 +1272,31 @@ GG_API gg_gemm_tc(const void* x, const void* w, void* out, int out_mode, int M, 
 //   in_ssq != null: x is the bfloat16 copy of the raw residual rows, w already carries the norm's weight,
 //     in_ssq[M, in_parts] holds partial sums of squares of those rows (in_parts = ceil(K / 128)); every
 //     accumulator row is multiplied by 1 / sqrt(sum / K + eps) before the output mode is applied.
+//   scratch: optional room for the float32 partial tiles of a K split at more than 128 tokens
+//     (gg_gemm_tc_pair_scratch_elems).
 //   out_ssq != null (out_mode 2 only): after out += product the kernel also writes out_xhat[M, N]
 //     (bfloat16 copy of the updated rows, row stride N) and out_ssq[M, ceil(N / 128)], their partial sums
 //     of squares over blocks of 128 columns: the inputs of the next folded product.
 GG_API gg_gemm_tc_norm(const void* x, const void* w, void* out, int out_mode, int M, int N, int K, long long ldx,
                        long long ldo, const float* in_ssq, int in_parts, float eps, float* out_ssq, void* out_xhat,
-                       int* status, cudaStream_t stream) {
+                       float* scratch, long long scratch_elems, int* status, cudaStream_t stream) {
     if (in_ssq != nullptr && (in_parts != (K + 127) / 128 || !(eps > 0.f))) return GG_ERR_ARG;
     if (out_ssq != nullptr && (out_mode != OUT_F32_ACC || out_xhat == nullptr)) return GG_ERR_ARG;
     if (out_mode == OUT_QKV) return GG_ERR_ARG;
     const NormIO nio = {in_ssq, in_parts, 1.0f / (float)K, eps, out_ssq, (bf16*)out_xhat};
     const QkvIO noq = {};
-    return gemm_tc_impl(x, w, out, out_mode, M, N, K, ldx, ldo, nullptr, 0, 1, status, nio, noq, stream);
+    return gemm_tc_impl(x, w, out, out_mode, M, N, K, ldx, ldo, scratch, scratch_elems, 1, status, nio, noq, stream);
+}
+
+// Floats of scratch with which a product of more than 128 tokens splits K over CTA pairs (0: it would not split).
+// Without that much scratch the product runs unsplit.
+GG_API gg_gemm_tc_pair_scratch_elems(int M, int N, int K, long long* elems) {
+    if (elems == nullptr) return GG_ERR_ARG;
+    *elems = 0;
+    if (M <= 128 || N <= 128 || K <= 0) return 0;
+    const int ps = pair_splits(M, N, K);
+    if (ps > 1) *elems = (long long)ps * M * N;
+    return 0;
 }
 
 // The q/k/v projection of a decode step (M <= 128 tokens, head size 128) with the per-head q/k RMSNorm,

@@ -38,6 +38,15 @@ def splits_for(M: int, N: int, K: int, cluster: bool = False) -> int:
     return int(raw(int(M), int(N), int(K), int(bool(cluster))))
 
 
+def pair_scratch_elems(M: int, N: int, K: int) -> int:
+    """Floats of scratch with which a product of more than 128 tokens splits K over the CTA pairs (0: no split)."""
+    import ctypes
+    n = ctypes.c_longlong(0)
+    raw = module("gemm_tcgen05").lib.gg_gemm_tc_pair_scratch_elems
+    raw(int(M), int(N), int(K), ctypes.byref(n))
+    return int(n.value)
+
+
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """Rows in blocks of 64 gate rows then their 64 up rows: the layout the fused SwiGLU epilogue reads."""
     I, K = gate.shape
@@ -81,13 +90,14 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
 def gemm_tc_norm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
                  m: Optional[int] = None, swiglu: bool = False, in_ssq: Optional[torch.Tensor] = None,
                  eps: float = 0.0, out_ssq: Optional[torch.Tensor] = None,
-                 out_xhat: Optional[torch.Tensor] = None) -> None:
+                 out_xhat: Optional[torch.Tensor] = None, scratch: Optional[torch.Tensor] = None) -> None:
     """`gemm_tc` with an RMSNorm folded in on either side (K splits inside clusters).
 
     in_ssq [M, ceil(K / 128)]: x is the bfloat16 copy of raw residual rows and w carries the norm's weight;
     every output row is multiplied by 1 / sqrt(sum(in_ssq[row]) / K + eps).  out_ssq [M, ceil(N / 128)] and
     out_xhat [M, N] (accumulate only): the kernel also writes the bfloat16 copy of the updated rows and
-    their partial sums of squares, the inputs of the next folded product."""
+    their partial sums of squares, the inputs of the next folded product.  scratch: room for the partial tiles
+    of a K split at more than 128 tokens (`pair_scratch_elems`); without it the product runs unsplit."""
     N, K = w.shape
     M = x.shape[0] if m is None else m
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -124,6 +134,7 @@ def gemm_tc_norm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate
         x.data_ptr(), w.data_ptr(), out.data_ptr(), mode, M, N, K, x.stride(0), out.stride(0),
         in_ssq.data_ptr() if in_ssq is not None else 0, in_parts, float(eps),
         out_ssq.data_ptr() if out_ssq is not None else 0, out_xhat.data_ptr() if out_xhat is not None else 0,
+        scratch.data_ptr() if scratch is not None else 0, scratch.numel() if scratch is not None else 0,
         st.data_ptr(), torch.cuda.current_stream().cuda_stream)
 
 
@@ -173,6 +184,8 @@ def make_linear(weight: torch.Tensor, swiglu: bool = False) -> Optional[Callable
     if swiglu and (N % 128 != 0 or N < 256):
         return None
 
+    split_room: Dict[int, int] = {}      # tokens -> floats of scratch with which the prefill form splits K
+
     def run(x, out, accumulate, m, ws, in_ssq=None, eps=0.0, out_ssq=None, out_xhat=None):
         folded = in_ssq is not None or out_ssq is not None
         if x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
@@ -181,9 +194,17 @@ def make_linear(weight: torch.Tensor, swiglu: bool = False) -> Optional[Callable
             from . import kernels as Kn
             Kn.gemm_plain(x, weight, out, accumulate, m)
             return
+        M = x.shape[0] if m is None else m
+        scratch = None
+        if M > 128 and ws is not None:
+            need = split_room.get(M)
+            if need is None:
+                need = split_room[M] = pair_scratch_elems(M, N, K)
+            if need:
+                scratch = ws.get("gemm_partial_tiles", (need,), torch.float32)
         if folded:
-            gemm_tc_norm(x, weight, out, accumulate, m, swiglu, in_ssq, eps, out_ssq, out_xhat)
+            gemm_tc_norm(x, weight, out, accumulate, m, swiglu, in_ssq, eps, out_ssq, out_xhat, scratch)
         else:
-            gemm_tc(x, weight, out, accumulate, m, None, cluster=True, swiglu=swiglu)
+            gemm_tc(x, weight, out, accumulate, m, scratch, cluster=True, swiglu=swiglu)
 
     return run

@@ -399,6 +399,55 @@ def test_gemm_tcgen05_qkv_with_norm_rope_and_cache_write(M, nq, nkv, K_, norm, f
     assert torch.equal(q3, q2)
 
 
+@pytest.mark.parametrize("M,N,K_", [(256, 4096, 4096), (300, 520, 2048), (512, 1024, 8192), (200, 264, 1024),
+                                    (1024, 768, 4096)])
+def test_gemm_tcgen05_prefill_form_splits_k_when_it_has_few_tiles(M, N, K_):
+    """A few hundred tokens give the CTA-pair form fewer tiles than there are pairs; with scratch it splits K,
+    leaves float32 partial tiles and a second kernel applies the output mode.  Every mode, against float64."""
+    from gogguf_b200.csrc import tcgen05_gemm as tc
+    g = torch.Generator(device=DEV).manual_seed(43)
+    need = tc.pair_scratch_elems(M, N, K_)
+    assert need > 0 and need % (M * N) == 0, "these shapes are meant to split"
+    scratch = torch.full((need,), float("nan"), device=DEV)
+    resid = torch.randn(M, K_, device=DEV, generator=g) * 2
+    w = (torch.randn(N, K_, device=DEV, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+    xh, ssq = plain_row_stats(resid)
+    ssq = ssq.float().contiguous()
+    eps = 1e-6
+    factor = 1.0 / torch.sqrt((resid.double() ** 2).mean(-1, keepdim=True) + eps)
+    plain_prod = xh.double() @ w.double().T
+    tol = 3e-6 + 2e-7 * math.sqrt(K_)
+    # plain float32 and bfloat16 stores, split against unsplit
+    out = torch.full((M, N), float("nan"), device=DEV)
+    tc.gemm_tc(xh, w, out, scratch=scratch, cluster=True)
+    tc.check_status(DEV)
+    assert rel(out, plain_prod) < tol
+    unsplit = torch.empty(M, N, device=DEV)
+    tc.gemm_tc(xh, w, unsplit, cluster=True)
+    assert rel(out, unsplit) < tol and not torch.equal(out, unsplit)
+    ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    tc.gemm_tc(xh, w, ob, scratch=scratch, cluster=True)
+    assert rel(ob, plain_prod) < 5e-3
+    # folded norm in, residual add with row statistics out
+    res = torch.randn(M, N, device=DEV, generator=g)
+    acc = res.clone()
+    oh = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    oss = torch.full((M, (N + 127) // 128), float("nan"), device=DEV)
+    tc.gemm_tc_norm(xh, w, acc, accumulate=True, in_ssq=ssq, eps=eps, out_ssq=oss, out_xhat=oh, scratch=scratch)
+    tc.check_status(DEV)
+    assert rel(acc, res.double() + plain_prod * factor) < tol
+    wh, ws_ = plain_row_stats(acc)
+    assert torch.equal(oh, wh) and rel(oss, ws_) < 1e-6
+    # fused SwiGLU
+    if N % 128 == 0 and N >= 256:
+        out_s = torch.full((M, N // 2), float("nan"), device=DEV, dtype=torch.bfloat16)
+        tc.gemm_tc_norm(xh, w, out_s, swiglu=True, in_ssq=ssq, eps=eps, scratch=scratch)
+        prod = (plain_prod * factor).view(M, N // 128, 2, 64)
+        gd, ud = prod[:, :, 0], prod[:, :, 1]
+        want = (gd / (1 + torch.exp(-gd)) * ud).reshape(M, N // 2)
+        assert rel(out_s, want) < 6e-3
+
+
 # ------------------------------------------------------------------------------------------ attention
 def make_paged(seqs, nkv, d, dt, seed, n_pages=None, ps=64):
     """seqs: list of (context length after the step, new tokens).  Returns pools, table and per-sequence K, V."""
