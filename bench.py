@@ -153,6 +153,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (for short profiling runs)")
+    ap.add_argument("--prefill-lengths", default="", help="comma separated prompt lengths: time one prefill step of each "
+                    "(printed on stderr, added to the line as prefill_sweep)")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -267,24 +269,24 @@ def main():
         # copied from pinned host memory, and the sampled ids read back
         return {"tok_s": batch * steps / dt, "h2d": getattr(ctx.stepper, "last_h2d_bytes", None), "d2h": batch * 4}
 
-    def prefill_run():
-        cache = model.new_cache(PROMPT_LEN + 64)
+    def prefill_run(prompt_len=PROMPT_LEN):
+        cache = model.new_cache(prompt_len + 64)
         st = GraphStepper(model, cache)
         times = []
         for it in range(4):
             s = cache.open()
-            toks = rand_tokens(PROMPT_LEN)
+            toks = rand_tokens(prompt_len)
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             ev0.record()
-            st.step([StepEntry(s, toks, want=[PROMPT_LEN - 1])])
+            st.step([StepEntry(s, toks, want=[prompt_len - 1])])
             ev1.record()
             torch.cuda.synchronize()
             times.append(ev0.elapsed_time(ev1))
             cache.close(s)
         ms = sorted(times[1:])[len(times[1:]) // 2]
-        fl = prefill_flops(cdict, a.layers, PROMPT_LEN)
-        return {"value": PROMPT_LEN / (ms / 1e3), "tokens": PROMPT_LEN, "ms": ms,
+        fl = prefill_flops(cdict, a.layers, prompt_len)
+        return {"value": prompt_len / (ms / 1e3), "tokens": prompt_len, "ms": ms,
                 "frac": fl / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), "tflops": fl / (ms / 1e3) / 1e12}
 
     main_run = decode_run(a.batch, a.steps, a.warmup)
@@ -310,6 +312,12 @@ def main():
         points[f"decode_b{a.batch}_temp0.6_top_k20_top_p0.95"] = r["tok_s"]
         print(f"[bench] decode batch {a.batch}, temp 0.6 / top-k 20 / top-p 0.95 on the device: {r['tok_s']:.1f} tok/s, "
               f"{r['ms_per_step']:.3f} ms/step", file=sys.stderr)
+
+    sweep = {}
+    for t in [int(x) for x in a.prefill_lengths.split(",") if x.strip()]:
+        r = prefill_run(t)
+        sweep[str(t)] = round(r["ms"], 3)
+        print(f"[bench] prefill of {t} tokens: {r['ms']:.3f} ms, {r['value']:.0f} tok/s, {r['tflops']:.0f} TFLOP/s", file=sys.stderr)
 
     achieved = main_run["bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9
     line = {
@@ -338,6 +346,8 @@ def main():
     if prefill is not None:
         line["prefill"] = {k: prefill[k] for k in ("value", "tokens", "ms", "frac")}
         line["points"] = points
+    if sweep:
+        line["prefill_sweep_ms"] = sweep
     print(json.dumps(line))
     return 0
 
