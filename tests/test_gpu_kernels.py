@@ -448,6 +448,26 @@ def test_gemm_tcgen05_prefill_form_splits_k_when_it_has_few_tiles(M, N, K_):
         assert rel(out_s, want) < 6e-3
 
 
+def test_linear_takes_the_split_scratch_from_the_workspace():
+    from gogguf_b200.csrc import tcgen05_gemm as tc
+    from gogguf_b200.parts.base import Linear, Runtime, Workspace
+    g = torch.Generator(device=DEV).manual_seed(47)
+    M, N, K_ = 300, 4096, 2048
+    w = (torch.randn(N, K_, device=DEV, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+    x = torch.randn(M, K_, device=DEV, generator=g).to(torch.bfloat16)
+    lin = Linear(w, Runtime(dtype=torch.bfloat16, device=torch.device(DEV), fast=True))
+    ws = Workspace(DEV)
+    out = torch.empty(M, N, device=DEV)
+    lin(x, out, ws=ws)
+    tc.check_status(DEV)
+    assert ("gemm_partial_tiles", torch.float32) in ws._bufs and tc.pair_scratch_elems(M, N, K_) > 0
+    assert rel(out, x.double() @ w.double().T) < 3e-6 + 2e-7 * math.sqrt(K_)
+    # without a workspace the same product runs unsplit
+    out2 = torch.empty(M, N, device=DEV)
+    lin(x, out2)
+    assert rel(out2, out) < 1e-5
+
+
 # ------------------------------------------------------------------------------------------ attention
 def make_paged(seqs, nkv, d, dt, seed, n_pages=None, ps=64):
     """seqs: list of (context length after the step, new tokens).  Returns pools, table and per-sequence K, V."""
