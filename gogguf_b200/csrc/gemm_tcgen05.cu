@@ -24,6 +24,12 @@
 // keeps the partial sums in a float32 scratch buffer in global memory and adds them in a second
 // kernel; it serves callers that ask for it and split counts beyond a cluster.)
 //
+// Further down in this file: the persistent prefill forms (one CTA per SM on 128 x 256 tiles, and CTA pairs
+// on 256 x 256 tiles with cta_group::2, which split K over work items when a product has fewer tiles than
+// pairs), and what the epilogues fuse: the residual add, SwiGLU over interleaved gate/up rows, an RMSNorm
+// folded in on either side (NormIO), and for the q/k/v product of a decode step the per-head norm, the
+// rotation and the cache write (QkvIO).
+//
 // Every mbarrier wait is bounded; a wait that runs out records a code in the status word, raises
 // the CTA's abort flag, and all roles fall through to the common exit, which lets copies in flight
 // land and frees the tensor memory.
