@@ -164,6 +164,25 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None) 
                                      _p(scratch), scratch.numel(), _stream())
 
 
+def repeat_penalty(logits: torch.Tensor, hist: torch.Tensor, hist_len: torch.Tensor, ring_rows: torch.Tensor,
+                   penalty: float, rows: int) -> None:
+    """In place on logits[:rows]: every distinct id in the sequences' rings is penalised once."""
+    _need(logits, torch.float32, "logits")
+    for t, n in ((hist, "hist"), (hist_len, "hist_len"), (ring_rows, "ring_rows")):
+        _need(t, torch.int32, n)
+    kernel("sampling", "gg_repeat_penalty")(_p(logits), logits.stride(0), rows, logits.shape[1], _p(hist), _p(hist_len),
+                                             _p(ring_rows), hist.shape[1], float(penalty), _stream())
+
+
+def history_append(tokens: torch.Tensor, ring_rows: torch.Tensor, hist: torch.Tensor, hist_len: torch.Tensor,
+                   hist_pos: torch.Tensor, rows: int) -> None:
+    """Append tokens[r] to the ring of sequence ring_rows[r]."""
+    for t, n in ((tokens, "tokens"), (hist, "hist"), (hist_len, "hist_len"), (hist_pos, "hist_pos"), (ring_rows, "ring_rows")):
+        _need(t, torch.int32, n)
+    kernel("sampling", "gg_history_append")(_p(tokens), _p(ring_rows), _p(hist), _p(hist_len), _p(hist_pos),
+                                             hist.shape[1], rows, _stream())
+
+
 TOPK_MAX = 1024      # largest top-k the on-device chain takes (csrc/sampling.cu)
 
 

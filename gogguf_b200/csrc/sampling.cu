@@ -586,3 +586,61 @@ GG_API gg_sample_topk(const float* logits, long long ld, float temp, int top_k, 
     return gg_launch(sample_topk_kernel, dim3(R), dim3(SAMP_THREADS), smem, stream, 1,
                      (const unsigned long long*)scratch, (int)per_row, k, top_p, min_p, uniforms, out);
 }
+
+
+// ----------------------------------------------------------------------------- repeat penalty on the device
+// The last `last_n` ids of each sequence (prompt and generated) live in a ring per sequence:
+// hist[ring_row][last_n], hist_len[ring_row] ids valid (at most last_n), hist_pos[ring_row] the slot the next
+// id goes to.  Before sampling, every distinct id of the ring is penalised once: logit > 0 ? logit / penalty
+// : logit * penalty (pkg/sampler/penalties.go:5-32); after sampling, the new id is appended, so that the
+// next step, which may already be queued, sees it without the host.
+__global__ void repeat_penalty_kernel(float* logits, long long ld, int V, const int* __restrict__ hist,
+                                      const int* __restrict__ hist_len, const int* __restrict__ ring_rows, int last_n,
+                                      float penalty) {
+    pdl_launch();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int* h = hist + (size_t)ring_rows[r] * last_n;
+    const int n = hist_len[ring_rows[r]];
+    float* x = logits + (size_t)r * ld;
+    for (int t = threadIdx.x; t < n; t += blockDim.x) {
+        const int id = h[t];
+        if (id < 0 || id >= V) continue;
+        bool first = true;                       // each distinct id once: the lowest slot that holds it acts
+        for (int u = 0; u < t; ++u) first = first && (h[u] != id);
+        if (first) {
+            const float v = x[id];
+            x[id] = v > 0.f ? v / penalty : v * penalty;
+        }
+    }
+}
+
+__global__ void history_append_kernel(const int* tokens, const int* __restrict__ ring_rows, int* hist, int* hist_len,
+                                      int* hist_pos, int last_n, int rows) {
+    pdl_launch();
+    pdl_wait();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    const int row = ring_rows[r];
+    const int p = hist_pos[row];
+    hist[(size_t)row * last_n + p] = tokens[r];
+    hist_pos[row] = p + 1 == last_n ? 0 : p + 1;
+    if (hist_len[row] < last_n) hist_len[row] += 1;
+}
+
+GG_API gg_repeat_penalty(float* logits, long long ld, int R, int V, const int* hist, const int* hist_len,
+                         const int* ring_rows, int last_n, float penalty, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (V <= 0 || ld < V || last_n <= 0 || !(penalty > 0.f)) return GG_ERR_ARG;
+    gg_launch(repeat_penalty_kernel, dim3(R), dim3(128), 0, stream, 1, logits, ld, V, hist, hist_len, ring_rows, last_n, penalty);
+    return gg_last_error();
+}
+
+GG_API gg_history_append(const int* tokens, const int* ring_rows, int* hist, int* hist_len, int* hist_pos, int last_n,
+                         int R, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (last_n <= 0) return GG_ERR_ARG;
+    gg_launch(history_append_kernel, dim3((R + 127) / 128), dim3(128), 0, stream, 1, tokens, ring_rows, hist, hist_len,
+              hist_pos, last_n, R);
+    return gg_last_error();
+}

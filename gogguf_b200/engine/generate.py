@@ -116,6 +116,8 @@ class Generator:
         try:
             entries = [StepEntry(slots[i], list(prompts[i]), want=[len(prompts[i]) - 1]) for i in live]
             logits = self.stepper.step(entries)
+            if hasattr(self.stepper, "decode_from_device") and getattr(logits, "is_cuda", False) and len(live) <= 256:
+                sampler.begin(live, [prompts[i] for i in live], logits.device)     # rings for a repeat penalty
             if (hasattr(self.stepper, "decode_from_device") and sampler.device_only
                     and getattr(logits, "is_cuda", False) and len(live) <= 256):
                 self._decode_one_ahead(live, logits, sampler, slots, generated, prompts, params, max_new, stop, results)

@@ -3,9 +3,10 @@
 Options and their meaning follow the reference's sampler (pkg/sampler/chain.go:9-70):
 `temp` 0 = greedy; `top_k` 0 = off; `top_p` 1 = off; `min_p` 0 = off; `seed` seeds the draws.
 Greedy sampling, plain temperature sampling, and the whole chain whenever a top-k of at most 1,024 is
-set run on the GPU (csrc/sampling.cu) over the whole batch; what is left (top-p or min-p without a
-top-k, a repeat penalty) runs this module's host chain on the logits of the rows that need it.  The
-order is the reference's: temperature, top-k, min-p, mask to -1e10, softmax, top-p, draw.
+set run on the GPU (csrc/sampling.cu) over the whole batch, with the repeat penalty too once the
+sequences' last ids have been put on the device (`Sampler.begin`); what is left (top-p or min-p
+without a top-k) runs this module's host chain on the logits of the rows that need it.  The order is
+the reference's: penalty, temperature, top-k, min-p, mask to -1e10, softmax, top-p, draw.
 
 Random draws are counter based: u = uniform01(seed, stream, step) with `stream` the request's index
 and `step` the number of tokens it has generated, so a sequence's draws do not depend on what else
@@ -149,11 +150,32 @@ class Sampler:
         self._out: Optional[torch.Tensor] = None
         self._outs = None
         self._turn = 0
+        self._rings = None        # device rings of the sequences' last ids (repeat penalty on the device)
+        self._ring_of = {}
 
     @property
     def device_only(self) -> bool:
-        """True when every row can be sampled by a kernel and no history is needed."""
-        return self.cfg.on_device and not self.penalised
+        """True when every row can be sampled by kernels alone (with a repeat penalty: after `begin`)."""
+        return self.cfg.on_device and (not self.penalised or self._rings is not None)
+
+    def begin(self, streams: Sequence[int], prompts: Sequence[Sequence[int]], device) -> None:
+        """Put the last `repeat_last_n` ids of each request's prompt on the device, one ring per request, so
+        that the penalty can be applied, and every sampled id appended, without the host.  Only needed (and
+        only done) with a repeat penalty and a configuration whose sampling runs on the device."""
+        if not (self.penalised and self.cfg.on_device):
+            return
+        n, rows = self.repeat_last_n, len(streams)
+        hist = torch.full((rows, n), -1, dtype=torch.int32)
+        lens = torch.zeros(rows, dtype=torch.int32)
+        for r, p in enumerate(prompts):
+            tail = list(p)[-n:]
+            hist[r, :len(tail)] = torch.tensor(tail, dtype=torch.int32)
+            lens[r] = len(tail)
+        pos = lens % n
+        self._rings = (hist.to(device), lens.to(device), pos.to(torch.int32).to(device))
+        self._ring_of = {int(s): r for r, s in enumerate(streams)}
+        self._ring_rows = [(torch.empty(max(rows, 1), dtype=torch.int32, pin_memory=True),
+                            torch.empty(max(rows, 1), dtype=torch.int32, device=device)) for _ in range(2)]
 
     def sample_async(self, logits: torch.Tensor, streams: Sequence[int], steps: Sequence[int]) -> PendingSample:
         """Greedy or temperature sampling on the device without waiting for the result: the ids stay in
@@ -172,6 +194,14 @@ class Sampler:
                            torch.empty(cap, dtype=torch.float64, device=logits.device),
                            torch.empty(cap, dtype=torch.float32, device=logits.device)) for _ in range(2)]
         out, pinned, u_host, u_dev, temps = self._outs[self._turn]
+        ring_rows = None
+        if self.penalised:
+            # the rows' rings: the penalty edits the logits in place before the sampling kernel reads them
+            rr_host, rr_dev = self._ring_rows[self._turn]
+            rr_host[:rows] = torch.tensor([self._ring_of[int(s)] for s in streams], dtype=torch.int32)
+            rr_dev[:rows].copy_(rr_host[:rows], non_blocking=True)
+            ring_rows = rr_dev
+            K.repeat_penalty(logits, self._rings[0], self._rings[1], ring_rows, self.repeat_penalty, rows)
         self._turn ^= 1
         if self.cfg.greedy:
             K.argmax(logits, out, rows)
@@ -184,6 +214,8 @@ class Sampler:
             else:
                 temps[:rows].fill_(float(self.cfg.temp))
                 K.sample(logits, temps, u_dev, out, rows)
+        if ring_rows is not None:
+            K.history_append(out, ring_rows, self._rings[0], self._rings[1], self._rings[2], rows)
         pinned[:rows].copy_(out[:rows], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()

@@ -57,15 +57,28 @@ def test_temperature_sampling_follows_the_plain_sampler(tmp_path_factory):
             logits = plain.forward(cfg, w, seq, wide=True)[-1].float().tolist()
             assert tok == plain.sample(logits, 0.7, 6, 0.85, 0.02, plain.uniform01(9, i, k)), (i, k)
             seq.append(tok)
-    # with a repeat penalty the host chain runs on the same logits
-    params = gg.GenerateParams(max_tokens=4, sampler=gg.SamplerConfig(temp=0.9, top_k=7, top_p=0.9, seed=5),
+    # with a repeat penalty: the last ids of every sequence live in a ring on the device (here a short one, so
+    # that it wraps), the penalty and the append are kernels, and the loop still runs one step ahead
+    for sc, last_n in ((gg.SamplerConfig(temp=0.9, top_k=7, top_p=0.9, seed=5), 64), (gg.SamplerConfig(), 4),
+                       (gg.SamplerConfig(temp=1.1, seed=2), 3)):
+        params = gg.GenerateParams(max_tokens=9, sampler=sc, repeat_penalty=1.3, repeat_last_n=last_n, stop_token_ids=[])
+        out = engine.new_context().generate(prompts, params)
+        for i, (p, r) in enumerate(zip(prompts, out)):
+            seq = list(p)
+            for k, tok in enumerate(r.tokens):
+                logits = plain.forward(cfg, w, seq, wide=True)[-1].float().tolist()
+                plain.repeat_penalty(logits, seq, 1.3, last_n)
+                assert tok == plain.sample(logits, sc.temp, sc.top_k, sc.top_p, sc.min_p, plain.uniform01(sc.seed, i, k)), (i, k)
+                seq.append(tok)
+    # top-p without a top-k has no kernel: the host chain, with the penalty, on the same logits
+    params = gg.GenerateParams(max_tokens=4, sampler=gg.SamplerConfig(temp=0.9, top_p=0.9, seed=5),
                                repeat_penalty=1.3, stop_token_ids=[])
     out = engine.new_context().generate(prompts[:1], params)
     seq = list(prompts[0])
     for k, tok in enumerate(out[0].tokens):
         logits = plain.forward(cfg, w, seq, wide=True)[-1].float().tolist()
         plain.repeat_penalty(logits, seq, 1.3, 64)
-        assert tok == plain.sample(logits, 0.9, 7, 0.9, 0.0, plain.uniform01(5, 0, k))
+        assert tok == plain.sample(logits, 0.9, 0, 0.9, 0.0, plain.uniform01(5, 0, k))
         seq.append(tok)
 
 
