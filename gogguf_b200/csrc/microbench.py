@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|attn|prefill_attn] [--m 1,8,64] [--ctx 2048,8192]
+"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|attn|prefill_attn|sample] [--m 1,8,64] [--ctx 2048,8192]
 
 Times single kernels the way a decode step runs them: forty launches captured in a CUDA graph and
 replayed, so that host launch cost is out of the picture and dependent launches overlap as they do
@@ -98,9 +98,26 @@ def prefill_attn(lens, nq: int = 32, nkv: int = 8, d: int = 128) -> None:
         print(f"attn prefill tcgen05  T={T:6d} {us:9.1f} us {flops / us / 1e6:7.1f} TFLOP/s", flush=True)
 
 
+def sample(ms, V: int = 151936) -> None:
+    """The sampling kernels on [batch, vocabulary] float32 logits: greedy, temperature, and the top-k chain."""
+    from . import kernels as K
+    dev = "cuda:0"
+    for B in ms:
+        logits = torch.randn(B, V, device=dev) * 3
+        out = torch.empty(B, dtype=torch.int32, device=dev)
+        u = torch.rand(B, dtype=torch.float64, device=dev)
+        temps = torch.full((B,), 0.6, device=dev)
+        for name, fn in (("greedy", lambda i: K.argmax(logits, out, B)),
+                         ("temperature 0.6", lambda i: K.sample(logits, temps, u, out, B)),
+                         ("temp 0.6, top-k 20, top-p 0.95", lambda i: K.sample_topk(logits, 0.6, 20, 0.95, 0.0, u, out, B)),
+                         ("temp 0.6, top-k 1000, top-p 0.95", lambda i: K.sample_topk(logits, 0.6, 1000, 0.95, 0.0, u, out, B))):
+            us = _time_graph(fn, reps=10)
+            print(f"sample B={B:4d} V={V} {name:34s} {us:8.1f} us", flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "prefill_attn"])
+    ap.add_argument("what", choices=["gemm", "attn", "prefill_attn", "sample"])
     ap.add_argument("--m", default="1,8,64", help="token counts (gemm), batch sizes (attn) or prompt lengths (prefill_attn)")
     ap.add_argument("--ctx", default="2048", help="attn: cached positions per sequence (comma separated)")
     ap.add_argument("--scratch", action="store_true", help="attn: splits merged by a second kernel instead of inside clusters")
@@ -110,7 +127,7 @@ def main() -> None:
         for c in a.ctx.split(","):
             attn(ms, ctx_len=int(c), cluster=not a.scratch)
     else:
-        {"gemm": gemm, "prefill_attn": prefill_attn}[a.what](ms)
+        {"gemm": gemm, "prefill_attn": prefill_attn, "sample": sample}[a.what](ms)
 
 
 if __name__ == "__main__":
