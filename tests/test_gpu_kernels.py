@@ -1,6 +1,7 @@
 """Each kernel alone against a plain float32/float64 PyTorch reference of the same op, at sizes other
 than the engine's (odd widths, head sizes in steps of 16, vocabularies that are no power of two)."""
 import math
+import os
 
 import pytest
 import torch
@@ -424,7 +425,9 @@ def test_gemm_tcgen05_prefill_form_splits_k_when_it_has_few_tiles(M, N, K_):
     assert rel(out, plain_prod) < tol
     unsplit = torch.empty(M, N, device=DEV)
     tc.gemm_tc(xh, w, unsplit, cluster=True)
-    assert rel(out, unsplit) < tol and not torch.equal(out, unsplit)
+    assert rel(out, unsplit) < tol
+    if os.environ.get("GOGGUF_B200_GEMM_PAIR", "1") != "0":      # (the single-CTA form has no K split)
+        assert not torch.equal(out, unsplit)
     ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
     tc.gemm_tc(xh, w, ob, scratch=scratch, cluster=True)
     assert rel(ob, plain_prod) < 5e-3

@@ -1,4 +1,6 @@
 """Each request alone and whole: the engine's logits at every position against the plain implementation."""
+import os
+
 import pytest
 import torch
 
@@ -45,7 +47,8 @@ def test_whole_bf16(tmp_path_factory, name):
     # and the tensor-core path with every norm as a kernel of its own instead of folded into the products
     unfolded = engine_whole(folder, "bfloat16", tokens, fold_norms=False)
     assert rel_err(unfolded, want) < TOL_BF16
-    assert not torch.equal(unfolded, got)        # the two really are different routes
+    if os.environ.get("GOGGUF_B200_FOLD_NORMS", "1") != "0":
+        assert not torch.equal(unfolded, got)    # the two really are different routes
 
 
 def test_norms_are_folded_into_the_products_on_the_fast_path(tmp_path_factory):
