@@ -144,8 +144,8 @@ __global__ void __launch_bounds__(128) row_stats_kernel(const float* x, bf16* __
     pdl_launch();
     pdl_wait();
     const int lane = threadIdx.x & 31;
-    const int part = blockIdx.x * 4 + (threadIdx.x >> 5);
-    const int t = blockIdx.y;
+    const int part = blockIdx.y * 4 + (threadIdx.x >> 5);
+    const int t = blockIdx.x;
     if (part >= parts) return;
     const int c0 = part * 128 + lane * 4;
     const float* xr = x + (size_t)t * H + c0;
@@ -166,9 +166,9 @@ __global__ void __launch_bounds__(128) row_stats_kernel(const float* x, bf16* __
 
 GG_API gg_row_stats(const float* x, void* xhat, float* ssq, int T, int H, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (H <= 0 || T > 65535) return GG_ERR_ARG;
+    if (H <= 0 || H > 128 * 4 * 65535) return GG_ERR_ARG;
     const int parts = (H + 127) / 128;
-    gg_launch(row_stats_kernel, dim3((parts + 3) / 4, T), dim3(128), 0, stream, 1, x, (bf16*)xhat, ssq, H, parts);
+    gg_launch(row_stats_kernel, dim3(T, (parts + 3) / 4), dim3(128), 0, stream, 1, x, (bf16*)xhat, ssq, H, parts);
     return gg_last_error();
 }
 

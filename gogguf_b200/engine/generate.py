@@ -72,13 +72,39 @@ class Generator:
     """Runs batches of requests on a stepper (anything with `.step(entries)` and `.cache`)."""
 
     def __init__(self, stepper, vocab_size: int, context: int, default_stop: Sequence[int] = (),
-                 max_batch: int = 64):
+                 max_batch: int = 64, prefill_tokens: int = 16384):
         self.stepper = stepper
         self.cache = stepper.cache
         self.vocab_size = vocab_size
         self.context = context
         self.default_stop = tuple(default_stop)
         self.max_batch = max_batch
+        # The prompts of a batch run in as few steps as hold this many tokens each (at least one prompt per
+        # step): the activations of a step grow with its tokens, the time of a token does not shrink beyond this.
+        self.prefill_tokens = prefill_tokens
+
+    def _prefill(self, live: List[int], prompts, slots):
+        """The prompts of the batch, in order; returns the logits of their last tokens, one row per request."""
+        groups: List[List[int]] = []
+        cur: List[int] = []
+        used = 0
+        for i in live:
+            n = len(prompts[i])
+            if cur and used + n > self.prefill_tokens:
+                groups.append(cur)
+                cur, used = [], 0
+            cur.append(i)
+            used += n
+        groups.append(cur)
+        outs = []
+        for g in groups:
+            entries = [StepEntry(slots[i], list(prompts[i]), want=[len(prompts[i]) - 1]) for i in g]
+            logits = self.stepper.step(entries)
+            outs.append(logits if len(groups) == 1 else logits.clone())     # a step's logits live until the next step
+        if len(outs) == 1:
+            return outs[0]
+        import torch
+        return torch.cat(outs, dim=0)
 
     def generate(self, prompts: Sequence[Sequence[int]], params: Optional[GenerateParams] = None
                  ) -> List[GenerationResult]:
@@ -114,8 +140,7 @@ class Generator:
         generated = {i: [] for i in batch}
         live: List[int] = list(batch)
         try:
-            entries = [StepEntry(slots[i], list(prompts[i]), want=[len(prompts[i]) - 1]) for i in live]
-            logits = self.stepper.step(entries)
+            logits = self._prefill(live, prompts, slots)
             if hasattr(self.stepper, "decode_from_device") and getattr(logits, "is_cuda", False) and len(live) <= 256:
                 sampler.begin(live, [prompts[i] for i in live], logits.device)     # rings for a repeat penalty
             if (hasattr(self.stepper, "decode_from_device") and sampler.device_only

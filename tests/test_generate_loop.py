@@ -131,3 +131,19 @@ def test_temperature_draws_do_not_depend_on_the_batch():
     alone = gen(Flat()).generate([[3]], p)[0].tokens
     both = gen(Flat()).generate([[3], [9, 9]], p)
     assert both[0].tokens == alone and both[1].tokens != alone
+
+
+def test_prompts_of_a_large_batch_run_in_several_steps():
+    """The prompts of a batch start together but need not share one step: a step holds at most `prefill_tokens`
+    tokens (and at least one prompt), the results are those of one step, and decoding begins after the last."""
+    prompts = [[1, 2, 3, 4, 5], [7, 8], [2] * 6, [9], [4, 4, 4]]
+    one = ScriptedStepper()
+    want = gen(one).generate(prompts, GenerateParams(max_tokens=3))
+    st = ScriptedStepper()
+    out = gen(st, prefill_tokens=7).generate(prompts, GenerateParams(max_tokens=3))
+    assert [r.tokens for r in out] == [r.tokens for r in want]
+    assert [[n for _, n in step] for step in st.steps[:3]] == [[5, 2], [6, 1], [3]]      # 7, 7 and 3 tokens
+    assert all(n == 1 for step in st.steps[3:] for _, n in step) and len(st.steps[3]) == 5
+    assert one.steps[0] == [(s, n) for s, n in one.steps[0]] and len(one.steps[0]) == 5  # by default: one step
+    st.cache.check()
+    assert st.cache.live_slots == 0
