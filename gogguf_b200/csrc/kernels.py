@@ -206,6 +206,29 @@ def sample_topk(logits: torch.Tensor, temp: float, top_k: int, top_p: float, min
                                           float(min_p), _p(uniforms), _p(out), R, V, _p(buf), buf.numel(), _stream())
 
 
+_nucleus_scratch = {}
+
+
+def sample_nucleus(logits: torch.Tensor, temp: float, top_p: float, min_p: float, uniforms: torch.Tensor,
+                   out: torch.Tensor, flags: torch.Tensor, rows: Optional[int] = None) -> None:
+    """Top-p and / or min-p without a top-k: candidates are each row's 1,024 largest logits, the softmax runs over
+    the whole row; flags[r] = 1 where the answer may lie beyond the candidates (out[r] is then not to be used)."""
+    _need(logits, torch.float32, "logits")
+    _need(uniforms, torch.float64, "uniforms")
+    _need(out, torch.int32, "out")
+    _need(flags, torch.int32, "flags")
+    R = logits.shape[0] if rows is None else rows
+    V = logits.shape[1]
+    slices = -(-V // 8192)
+    nbytes = R * 128 * 4 + R * slices * 8 + R * slices * min(V, 1024) * 8
+    buf = _nucleus_scratch.get(logits.device)
+    if buf is None or buf.numel() * 8 < nbytes:
+        buf = _nucleus_scratch[logits.device] = torch.empty(max(-(-nbytes // 8), 1 << 16), dtype=torch.int64,
+                                                            device=logits.device)
+    kernel("sampling", "gg_sample_nucleus")(_p(logits), logits.stride(0), float(temp), float(top_p), float(min_p),
+                                             _p(uniforms), _p(out), _p(flags), R, V, _p(buf), buf.numel() * 8, _stream())
+
+
 def sample(logits: torch.Tensor, temps: torch.Tensor, uniforms: torch.Tensor, out: torch.Tensor,
            rows: Optional[int] = None) -> None:
     _need(logits, torch.float32, "logits")

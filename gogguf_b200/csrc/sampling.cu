@@ -206,14 +206,29 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(const float* logit
 // fixed (thread, warp, block, slice), though not the order of the one-block kernel above.
 #define SAMP_SLICE_IDS 8192
 
+__device__ __forceinline__ void slice_sum(const float* logits, long long ld, float temp, const int* best,
+                                          double* __restrict__ zs, int V, double* dred);
+
+__global__ void __launch_bounds__(SAMP_THREADS) sample_slice_sum_uniform_kernel(const float* logits, long long ld, float temp,
+                                                                                 const int* best, double* __restrict__ zs, int V) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ double dred[33];
+    slice_sum(logits, ld, temp, best, zs, V, dred);
+}
+
 __global__ void __launch_bounds__(SAMP_THREADS) sample_slice_sum_kernel(const float* logits, long long ld,
                                                                          const float* __restrict__ temps,
                                                                          const int* best, double* __restrict__ zs, int V) {
     pdl_launch();
     pdl_wait();
     __shared__ double dred[33];
+    slice_sum(logits, ld, temps[blockIdx.y], best, zs, V, dred);
+}
+
+__device__ __forceinline__ void slice_sum(const float* logits, long long ld, float temp, const int* best,
+                                          double* __restrict__ zs, int V, double* dred) {
     const int r = blockIdx.y, slice = blockIdx.x;
-    const float temp = temps[r];
     if (temp <= 0.f) return;
     const float* x = logits + (size_t)r * ld;
     const bool scaled = temp != 1.f;
@@ -458,10 +473,43 @@ __global__ void __launch_bounds__(SAMP_SLICE_THREADS) topk_slice_kernel(const fl
         if (keys[u] != 0ull && keys[u] >= thr) dst[atomicAdd(&n_out, 1)] = keys[u];
 }
 
+// Inclusive prefix sums of one double per thread over the block, in thread order; *total gets the block's sum.
+__device__ __forceinline__ double block_scan_f64(double v, double* warp_tot /* 33 */, double* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double y = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += y;
+    }
+    __syncthreads();
+    if (lane == 31) warp_tot[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        double t = lane < nw ? warp_tot[lane] : 0.0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double y = __shfl_up_sync(0xffffffffu, t, o);
+            if (lane >= o) t += y;
+        }
+        if (lane < nw) warp_tot[lane] = t;          // inclusive over warps
+        if (lane == 31) warp_tot[32] = t;
+    }
+    __syncthreads();
+    if (warp > 0) v += warp_tot[warp - 1];
+    *total = warp_tot[32];
+    return v;
+}
+
 // Stage two: one block per row over its slices * k candidate keys (dynamic shared memory holds them).
+// zs == null: the chain with a top-k (the softmax is over the k survivors).  zs != null: top-p and min-p without
+// a top-k, for which the k survivors are only candidates: the softmax is over the whole row, whose sum
+// of exp(x - max) is the sum of zs[row * z_slices ..], and flags[row] is set when the candidates do not hold
+// the whole answer (min-p keeps even the last candidate, or the running sum never reaches top-p): the caller
+// then takes that row through the host chain.
 __global__ void __launch_bounds__(SAMP_THREADS) sample_topk_kernel(
     const unsigned long long* cand, int n_cand_keys, int top_k, float top_p, float min_p,
-    const double* __restrict__ uniforms, int* __restrict__ out) {
+    const double* __restrict__ uniforms, int* __restrict__ out, const double* zs, int z_slices, int* __restrict__ flags,
+    int V) {
     pdl_launch();
     pdl_wait();
     extern __shared__ unsigned long long ckeys[];
@@ -472,7 +520,8 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_topk_kernel(
     __shared__ int by_value[SAMP_TOPK_MAX];      // candidate slots in descending order of x (ties: lower id)
     __shared__ int by_id[SAMP_TOPK_MAX];         // candidate slots in ascending order of id
     __shared__ unsigned char keep[SAMP_TOPK_MAX];
-    __shared__ int n_sel;
+    __shared__ int n_sel, pick_r, last_r;
+    __shared__ double wtot[33], z_row;
     const int row = blockIdx.x, tid = threadIdx.x;
     const unsigned long long* src = cand + (size_t)row * n_cand_keys;
     for (int j = tid; j < n_cand_keys; j += SAMP_THREADS) ckeys[j] = src[j];
@@ -514,40 +563,59 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_topk_kernel(
         cand_e[a] = ok ? e : 0.0;
     }
     __syncthreads();
-    // ---- top-p and the draw: a few hundred values at most, one thread
-    if (tid == 0) {
-        double Z = 0.0;
-        for (int r = 0; r < n; ++r) Z += cand_e[by_id[r]];
-        if (top_p > 0.f && top_p < 1.f) {
-            const double thr_p = (double)top_p - 1e-6;
-            double cum = 0.0;
-            bool cut = false;
-            for (int r = 0; r < n; ++r) {
-                const int a = by_value[r];
-                if (!keep[a]) continue;
-                if (cut) { keep[a] = 0; continue; }
-                cum += cand_e[a] / Z;
-                if (cum >= thr_p) cut = true;                // the element that crosses stays
+    // ---- the softmax's denominator: over the survivors, or over the whole row
+    double Z;
+    {
+        const double mine = tid < n ? cand_e[by_id[tid]] : 0.0;
+        double total;
+        block_scan_f64(mine, wtot, &total);
+        // (min-p masks before the softmax, so with it the denominator is the sum over its survivors, all of
+        // which are candidates unless the row gets flagged)
+        if (zs != nullptr && !(min_p > 0.f)) {
+            if (tid == 0) {
+                double z = 0.0;
+                for (int sl = 0; sl < z_slices; ++sl) z += zs[(size_t)row * z_slices + sl];
+                z_row = z;
             }
+            __syncthreads();
+            total = z_row;
         }
-        double total = 0.0;
-        for (int r = 0; r < n; ++r) { const int a = by_id[r]; if (keep[a]) total += cand_e[a] / Z; }
-        int pick = -1, last = -1;
-        if (total > 0.0) {
-            const double target = uniforms[row] * total;
-            double run = 0.0;
-            for (int r = 0; r < n; ++r) {
-                const int a = by_id[r];
-                if (!keep[a]) continue;
-                last = cand_i[a];
-                run += cand_e[a] / Z;
-                if (target - run <= 0.0) { pick = cand_i[a]; break; }
-            }
-            if (pick < 0) pick = last;
-        } else {
-            pick = cand_i[by_value[0]];
+        Z = total;
+    }
+    bool incomplete = false;
+    if (zs != nullptr && n < V && min_p > 0.f && keep[by_value[n - 1]]) incomplete = true;      // min-p may keep more
+    // ---- top-p: in descending order keep until the running sum reaches p - 1e-6, the crossing element included
+    if (top_p > 0.f && top_p < 1.f) {
+        const double thr_p = (double)top_p - 1e-6;
+        const int a = tid < n ? by_value[tid] : 0;
+        const double p = (tid < n && keep[a]) ? cand_e[a] / Z : 0.0;
+        double total;
+        const double cum = block_scan_f64(p, wtot, &total);
+        if (tid < n && keep[a] && cum - p >= thr_p) keep[a] = 0;
+        if (zs != nullptr && n < V && total < thr_p) incomplete = true;                           // the nucleus goes on
+    }
+    if (tid == 0) { pick_r = 0x7fffffff; last_r = -1; }
+    __syncthreads();
+    // ---- the draw in id order
+    {
+        const int a = tid < n ? by_id[tid] : 0;
+        const bool kept = tid < n && keep[a];
+        const double p = kept ? cand_e[a] / Z : 0.0;
+        double total;
+        const double run = block_scan_f64(p, wtot, &total);
+        const double target = uniforms[row] * total;
+        if (kept) {
+            atomicMax(&last_r, tid);
+            if (target - run <= 0.0) atomicMin(&pick_r, tid);
         }
-        out[row] = pick;
+        __syncthreads();
+        if (tid == 0) {
+            int pick;
+            if (total > 0.0) pick = cand_i[by_id[pick_r != 0x7fffffff ? pick_r : last_r]];
+            else pick = cand_i[by_value[0]];
+            out[row] = pick;
+            if (flags != nullptr) flags[row] = incomplete ? 1 : 0;
+        }
     }
 }
 
@@ -584,8 +652,47 @@ GG_API gg_sample_topk(const float* logits, long long ld, float temp, int top_k, 
                        (unsigned long long*)scratch);
     if (rc != 0) return rc;
     return gg_launch(sample_topk_kernel, dim3(R), dim3(SAMP_THREADS), smem, stream, 1,
-                     (const unsigned long long*)scratch, (int)per_row, k, top_p, min_p, uniforms, out);
+                     (const unsigned long long*)scratch, (int)per_row, k, top_p, min_p, uniforms, out,
+                     (const double*)nullptr, 0, (int*)nullptr, V);
 }
+
+// Top-p and / or min-p without a top-k (temp > 0): the 1,024 largest logits of each row are the candidates, the
+// softmax runs over the whole row, and flags[r] = 1 says that row r's answer may lie beyond the candidates
+// (out[r] is then not to be used).  scratch: R * 128 four-byte words, then R * ceil(V / 8192) doubles, then
+// R * ceil(V / 8192) * min(V, 1024) 64-bit words; all of it 8-byte aligned.
+GG_API gg_sample_nucleus(const float* logits, long long ld, float temp, float top_p, float min_p, const double* uniforms,
+                         int* out, int* flags, int R, int V, void* scratch, long long scratch_bytes, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (V <= 0 || ld < V || R > 65535 || !(temp > 0.f) || flags == nullptr || scratch == nullptr || (((uintptr_t)scratch) & 7))
+        return GG_ERR_ARG;
+    const int k = V < SAMP_TOPK_MAX ? V : SAMP_TOPK_MAX;
+    const int slices = (V + SAMP_SLICE - 1) / SAMP_SLICE;
+    const long long per_row = (long long)slices * k;
+    const long long need = (long long)R * 128 * 4 + (long long)R * slices * 8 + per_row * R * 8;
+    if (scratch_bytes < need) return GG_ERR_ARG;
+    const size_t smem = (size_t)per_row * sizeof(unsigned long long);
+    if (smem > 160 * 1024) return GG_ERR_ARG;
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(sample_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    int* best = out;                                   // the row maxima's ids, overwritten by the samples at the end
+    double* zs = reinterpret_cast<double*>(reinterpret_cast<int*>(scratch) + (size_t)R * 128);
+    unsigned long long* cand = reinterpret_cast<unsigned long long*>(zs + (size_t)R * slices);
+    int rc = gg_argmax(logits, ld, best, R, V, scratch, (long long)R * 128, stream);
+    if (rc != 0) return rc;
+    // every row at this temperature: the slice sums take one temperature per row
+    rc = gg_launch(sample_slice_sum_uniform_kernel, dim3(slices, R), dim3(SAMP_THREADS), 0, stream, 1, logits, ld, temp,
+                   (const int*)best, zs, V);
+    if (rc != 0) return rc;
+    rc = gg_launch(topk_slice_kernel, dim3(slices, R), dim3(SAMP_SLICE_THREADS), 0, stream, 1, logits, ld, V, temp, k, cand);
+    if (rc != 0) return rc;
+    return gg_launch(sample_topk_kernel, dim3(R), dim3(SAMP_THREADS), smem, stream, 1, (const unsigned long long*)cand,
+                     (int)per_row, k, top_p, min_p, uniforms, out, (const double*)zs, slices, flags, V);
+}
+
 
 
 // ----------------------------------------------------------------------------- repeat penalty on the device

@@ -4,8 +4,11 @@ Options and their meaning follow the reference's sampler (pkg/sampler/chain.go:9
 `temp` 0 = greedy; `top_k` 0 = off; `top_p` 1 = off; `min_p` 0 = off; `seed` seeds the draws.
 Greedy sampling, plain temperature sampling, and the whole chain whenever a top-k of at most 1,024 is
 set run on the GPU (csrc/sampling.cu) over the whole batch, with the repeat penalty too once the
-sequences' last ids have been put on the device (`Sampler.begin`); what is left (top-p or min-p
-without a top-k) runs this module's host chain on the logits of the rows that need it.  The order is
+sequences' last ids have been put on the device (`Sampler.begin`).  Top-p or min-p without a top-k
+also has a kernel, which answers from each row's 1,024 largest logits and flags the rows for which
+that may not be the whole answer; the host reads the flags every step (so this configuration does not
+run a step ahead) and takes flagged rows, like everything with a penalty but no kernel path, through
+this module's host chain.  The order is
 the reference's: penalty, temperature, top-k, min-p, mask to -1e10, softmax, top-p, draw.
 
 Random draws are counter based: u = uniform01(seed, stream, step) with `stream` the request's index
@@ -246,6 +249,22 @@ class Sampler:
                     temps = torch.full((rows,), float(self.cfg.temp), dtype=torch.float32).to(logits.device, non_blocking=True)
                     K.sample(logits, temps, uni, out, rows)
             return out.cpu().tolist()
+        if (logits.is_cuda and not self.penalised and self.cfg.temp > 0 and self.cfg.top_k <= 0
+                and logits.dtype == torch.float32 and logits.shape[1] >= 2048):
+            # top-p and / or min-p without a top-k: a kernel answers from each row's 1,024 largest logits and
+            # says for which rows that is not certain to be the whole answer; only those go through the host chain
+            from ..csrc import kernels as K
+            if self._out is None or self._out.numel() < 2 * rows:
+                self._out = torch.empty(2 * max(rows, 64), dtype=torch.int32, device=logits.device)
+            out, flags = self._out[:rows], self._out[rows:2 * rows]
+            uni = torch.tensor(us, dtype=torch.float64).to(logits.device, non_blocking=True)
+            K.sample_nucleus(logits, self.cfg.temp, self.cfg.top_p, self.cfg.min_p, uni, out, flags, rows)
+            both = self._out[:2 * rows].cpu().tolist()
+            res, unsure = both[:rows], both[rows:]
+            for r in range(rows):
+                if unsure[r]:
+                    res[r] = sample_host(logits[r].detach().to("cpu", torch.float32).numpy().copy(), self.cfg, us[r])
+            return res
         host = logits[:rows].detach().to("cpu", torch.float32).numpy()
         res = []
         for r in range(rows):

@@ -702,3 +702,34 @@ def test_temperature_sampling_and_argmax_on_device(V):
     am = torch.empty(rows, dtype=torch.int32, device=DEV)
     K().argmax(logits.to(DEV), am)
     assert am.cpu().tolist() == logits.argmax(dim=1).tolist() and am[3].item() == V // 2
+
+
+@pytest.mark.parametrize("temp,top_p,min_p", [(0.8, 0.9, 0.0), (1.0, 0.5, 0.0), (0.7, 1.0, 0.05), (1.2, 0.95, 0.02),
+                                              (40.0, 0.9, 0.0), (30.0, 1.0, 0.5)])
+def test_top_p_and_min_p_without_top_k_on_device(temp, top_p, min_p):
+    """The kernel answers from the 1,024 largest logits of a row and flags the rows whose answer may lie beyond
+    them (a flat distribution: the last two cases); unflagged rows equal the host chain, and through the sampler
+    every row does."""
+    from gogguf_b200.sampling.sampler import Sampler, SamplerConfig, sample_host, uniform01
+    V, rows = 20011, 12
+    g = torch.Generator().manual_seed(17)
+    logits = torch.randn(rows, V, generator=g) * 3
+    logits[5] = torch.round(logits[5])                  # ties
+    logits[6, 100:140] = 9.0                            # a plateau at the top
+    cfg = SamplerConfig(temp=temp, top_p=top_p, min_p=min_p, seed=8)
+    assert not cfg.on_device
+    dl = logits.to(DEV)
+    for step in range(3):
+        us = [uniform01(8, r, step) for r in range(rows)]
+        out = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+        flags = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+        K().sample_nucleus(dl, temp, top_p, min_p, torch.tensor(us, dtype=torch.float64, device=DEV), out, flags)
+        want = [sample_host(logits[r].numpy(), cfg, us[r]) for r in range(rows)]
+        got, fl = out.cpu().tolist(), flags.cpu().tolist()
+        assert all(f in (0, 1) for f in fl)
+        assert all(g_ == w for g_, w, f in zip(got, want, fl) if not f), step
+        if temp >= 30:
+            assert sum(fl) == rows          # nothing is certain from 1,024 of 20,011 nearly equal probabilities
+        else:
+            assert sum(fl) == 0
+        assert Sampler(cfg).sample(dl, streams=list(range(rows)), steps=[step] * rows) == want
