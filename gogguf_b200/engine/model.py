@@ -66,15 +66,22 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorDecl]:
     return out
 
 
-def _local(tensors: Mapping[str, torch.Tensor], ps: PartSpec, cls) -> Dict[str, torch.Tensor]:
-    return {local: tensors[ps.prefix + local] for local in cls.tensors(ps) if ps.prefix + local in tensors}
+def _local(tensors: Mapping[str, torch.Tensor], ps: PartSpec, cls, consume: bool = False) -> Dict[str, torch.Tensor]:
+    """A part's tensors under their local names.  consume: take them out of `tensors` (a dict the caller gave up),
+    so that a part which builds its own fused copies leaves no second copy of its weights behind while the
+    remaining layers are built."""
+    names = [local for local in cls.tensors(ps) if ps.prefix + local in tensors]
+    if consume:
+        return {local: tensors.pop(ps.prefix + local) for local in names}
+    return {local: tensors[ps.prefix + local] for local in names}
 
 
 class Model:
     """Embedding, blocks in schedule order, final norm, head."""
 
     def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], dtype="bfloat16",
-                 device="cuda:0", fast: bool = True, config=None, fold_norms: Optional[bool] = None):
+                 device="cuda:0", fast: bool = True, config=None, fold_norms: Optional[bool] = None,
+                 consume: bool = False):
         spec.validate()
         self.spec = spec
         self.config = config
@@ -86,19 +93,20 @@ class Model:
         rt = self.rt
 
         ecls = _part_class(R.EMBEDDINGS, spec.embedding, "embedding")
-        self.embedding = ecls(spec.embedding, _local(tensors, spec.embedding, ecls), rt)
+        consume = consume and isinstance(tensors, dict)
+        self.embedding = ecls(spec.embedding, _local(tensors, spec.embedding, ecls, consume), rt)
         self.blocks = []
         self.mixer_classes = []
         for b in spec.blocks:
-            built = [cls(ps, _local(tensors, ps, cls), rt) for ps, cls in _block_parts(b)]
+            built = [cls(ps, _local(tensors, ps, cls, consume), rt) for ps, cls in _block_parts(b)]
             acls = R.lookup(R.ARRANGEMENTS, b.arrangement, "block arrangement")
             self.blocks.append(acls(b, *built, rt))
             self.mixer_classes.append(_part_class(R.MIXERS, b.mixer, "mixer"))
         ncls = _part_class(R.NORMS, spec.final_norm, "norm")
-        self.final_norm = ncls(spec.final_norm, _local(tensors, spec.final_norm, ncls), rt)
+        self.final_norm = ncls(spec.final_norm, _local(tensors, spec.final_norm, ncls, consume), rt)
         hcls = _part_class(R.HEADS, spec.head, "head")
         tied = getattr(self.embedding, "weight", None) if spec.head.get("tied_to") is not None else None
-        self.head = hcls(spec.head, _local(tensors, spec.head, hcls), rt, tied)
+        self.head = hcls(spec.head, _local(tensors, spec.head, hcls, consume), rt, tied)
 
     # ------------------------------------------------------------------ constructors
     @classmethod
@@ -109,7 +117,7 @@ class Model:
         spec = cfg.to_spec()
         aliases = cfg.tensor_aliases() if hasattr(cfg, "tensor_aliases") else None
         tensors = load_tensors(folder, expected_tensors(spec), device=device, aliases=aliases)
-        return cls(spec, tensors, dtype=dtype, device=device, fast=fast, config=cfg, fold_norms=fold_norms)
+        return cls(spec, tensors, dtype=dtype, device=device, fast=fast, config=cfg, fold_norms=fold_norms, consume=True)
 
     @classmethod
     def random(cls, config, seed: int, dtype="bfloat16", device="cuda:0", fast: bool = True,
@@ -121,7 +129,8 @@ class Model:
         tensors = random_tensors(expected_tensors(spec), seed,
                                  std if std is not None else getattr(config, "initializer_range", 0.02),
                                  norm_std, dtype=sd, device=device)
-        return cls(spec, tensors, dtype=dtype, device=device, fast=fast, config=config, fold_norms=fold_norms)
+        return cls(spec, tensors, dtype=dtype, device=device, fast=fast, config=config, fold_norms=fold_norms,
+                   consume=True)
 
     # ------------------------------------------------------------------ cache
     def cache_requests(self) -> List[Request]:
