@@ -648,14 +648,18 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
             l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
             l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
         }
+        // only the G rows that are query heads go on (the MMA tile has 16)
+        if (g < G) {
 #pragma unroll
-        for (int n = 0; n < NT; ++n)
+            for (int n = 0; n < NT; ++n)
+                *reinterpret_cast<float2*>(&sm_o[(warp * 16 + g) * D + n * 8 + 2 * t]) = make_float2(o[n][0], o[n][1]);
+            if (t == 0) { sm_ml[(warp * 16 + g) * 2] = m[0]; sm_ml[(warp * 16 + g) * 2 + 1] = l[0]; }
+        }
+        if (g + 8 < G) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                sm_o[(warp * 16 + g + 8 * (e >> 1)) * D + n * 8 + 2 * t + (e & 1)] = o[n][e];
-        if (t == 0) {
-            sm_ml[(warp * 16 + g) * 2] = m[0]; sm_ml[(warp * 16 + g) * 2 + 1] = l[0];
-            sm_ml[(warp * 16 + g + 8) * 2] = m[1]; sm_ml[(warp * 16 + g + 8) * 2 + 1] = l[1];
+            for (int n = 0; n < NT; ++n)
+                *reinterpret_cast<float2*>(&sm_o[(warp * 16 + g + 8) * D + n * 8 + 2 * t]) = make_float2(o[n][2], o[n][3]);
+            if (t == 0) { sm_ml[(warp * 16 + g + 8) * 2] = m[1]; sm_ml[(warp * 16 + g + 8) * 2 + 1] = l[1]; }
         }
     }
     __syncthreads();
