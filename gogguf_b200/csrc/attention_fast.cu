@@ -85,6 +85,12 @@ __device__ __forceinline__ void exp2_poly2(float x0, float x1, float& r0, float&
     r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
+__device__ __forceinline__ void st_dsmem_f32(uint32_t local_addr, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank) {
     uint32_t remote;
     float v;
@@ -483,6 +489,14 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
 // launcher asks for once and falls back from (attn_max_cluster).
 constexpr int MAX_ATT_CLUSTER = 16;
 
+// What the other CTAs of a cluster push into this one (beyond the ring, so that they need not wait for it): their
+// partial outputs for the slices of 32 this CTA merges, [rank][round][32], and their (max, sum) per query head.
+constexpr int ATT_PUSH_MAX_OUT = 1024;                               // G * D up to which the splits are pushed
+constexpr int ATT_RECV_O = (ATT_PUSH_MAX_OUT + 32 * 16) * 4;         // bytes: rank * rounds * 32 <= G * D + 32 * cs
+constexpr int ATT_RECV_ML = 16 * 16 * 2 * 4;
+constexpr int ATT_RECV_BYTES = ATT_RECV_O + ATT_RECV_ML;
+
+
 template <int D, int STAGES>
 __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -500,6 +514,8 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
     uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
     uint64_t* empty = full + STAGES;
     volatile int* abort_flag = (volatile int*)(empty + STAGES);
+    float* recv_o = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);      // see ATT_RECV_BYTES
+    float* recv_ml = recv_o + ATT_RECV_O / 4;
 
     const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -680,6 +696,18 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
         const int head = kvh * G + r;
         if (nsplit == 1) {
             out[((size_t)tok * nq + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else if (cluster_reduce && G * D <= ATT_PUSH_MAX_OUT) {
+            // straight into the shared memory of the CTA that merges this output (slices of 32 go round the
+            // ranks), and this head's (max, sum) to every CTA: no load has to cross the cluster afterwards
+            const int chunk = idx >> 5, owner = chunk % nsplit, round = chunk / nsplit;
+            const int rounds = ((G * D + 31) / 32 + nsplit - 1) / nsplit;
+            st_dsmem_f32(tma::smem_u32(recv_o + (split * rounds + round) * 32 + (idx & 31)), (uint32_t)owner, acc);
+            if (c == 0) {
+                for (int k = 0; k < nsplit; ++k) {
+                    st_dsmem_f32(tma::smem_u32(recv_ml + (split * 16 + r) * 2), (uint32_t)k, M);
+                    st_dsmem_f32(tma::smem_u32(recv_ml + (split * 16 + r) * 2 + 1), (uint32_t)k, L);
+                }
+            }
         } else if (cluster_reduce) {
             res_o[r * D + c] = acc;
             if (c == 0) { res_ml[r * 2] = M; res_ml[r * 2 + 1] = L; }
@@ -689,9 +717,30 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
             if (c == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
         }
     }
-    if (cluster_reduce) {
-        // The splits of one (token, kv head) form a cluster: every CTA merges a slice of the G x D outputs
-        // over all ranks through distributed shared memory, in rank order.
+    if (cluster_reduce && G * D <= ATT_PUSH_MAX_OUT) {
+        // The splits of one (token, kv head) form a cluster; what the ranks pushed is complete after one barrier,
+        // and every CTA merges its slice of the G x D outputs, in rank order, from its own shared memory.
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const int rounds = ((G * D + 31) / 32 + nsplit - 1) / nsplit;
+        for (int round = warp; round < rounds; round += 5) {
+            const int idx = (round * nsplit + split) * 32 + lane;
+            if (idx >= G * D) continue;
+            const int r = idx / D;
+            float M = -INFINITY;
+            for (int k = 0; k < nsplit; ++k) M = fmaxf(M, recv_ml[(k * 16 + r) * 2]);
+            float L = 0.f, acc = 0.f;
+            if (M != -INFINITY) {
+                for (int k = 0; k < nsplit; ++k) {
+                    const float f = fast_exp2(recv_ml[(k * 16 + r) * 2] - M);
+                    L += recv_ml[(k * 16 + r) * 2 + 1] * f;
+                    acc += recv_o[(k * rounds + round) * 32 + lane] * f;
+                }
+            }
+            out[((size_t)tok * nq + kvh * G) * D + idx] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        }
+    } else if (cluster_reduce) {
+        // (more than 1,024 outputs per kv head do not fit the receive area: the owner pulls instead)
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         const uint32_t ro = tma::smem_u32(res_o), rm = tma::smem_u32(res_ml);
@@ -728,7 +777,7 @@ template <int D, int STAGES>
 constexpr int decode_tma_smem() {
     constexpr int ring = STAGES * 4 * (D / 64) * 64 * 64;     // bytes: STAGES * 2 * HALVES * 8 KB
     constexpr int merge = (5 * 16 * D + 5 * 16 * 2) * 4;
-    return (ring > merge ? ring : merge) + 1024 + 256;
+    return (ring > merge ? ring : merge) + 1024 + 256 + ATT_RECV_BYTES;
 }
 
 // 16 if this device co-schedules clusters of 16 CTAs of both decode kernels (opt-in), else 8.
