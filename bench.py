@@ -273,6 +273,8 @@ def main():
         cache = model.new_cache(prompt_len + 64)
         st = GraphStepper(model, cache)
         times = []
+        torch.cuda.synchronize()
+        time.sleep(0.5)            # as before the timed decode region: start from an idle GPU, not from the previous run's heat
         for it in range(4):
             s = cache.open()
             toks = rand_tokens(prompt_len)
