@@ -33,14 +33,14 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: Qwen3-8B shape
+# the headline configuration: Qwen3-8B shape
 QWEN3_8B = dict(
     architectures=["Qwen3ForCausalLM"], model_type="qwen3",
     num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
     intermediate_size=12288, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
     tie_word_embeddings=False, max_position_embeddings=4096, initializer_range=0.02,
 )
-# BASELINE.json configs[3] and configs[4]: the layer sizes of the 14B and 32B shapes (same vocabulary and rotary base)
+# the layer sizes of the 14B and 32B shapes (same vocabulary and rotary base)
 SHAPES = {
     "8b": {},
     "14b": dict(num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, intermediate_size=17408),
