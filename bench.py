@@ -44,7 +44,8 @@ QWEN3_8B = dict(
 SHAPES = {
     "8b": {},
     "14b": dict(num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, intermediate_size=17408),
-    "32b": dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, intermediate_size=25600),
+    "32b": dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, intermediate_size=25600,
+                max_position_embeddings=8192),      # its request mix has prompts of 4,096 tokens
 }
 PROMPT_LEN = 2048
 CONTEXT = 4096
@@ -153,6 +154,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (for short profiling runs)")
+    ap.add_argument("--workload", action="store_true",
+                    help="also run the shape's own request mix through the entry point (14b: 16 prompts of 128 to 2,048 "
+                    "tokens and 256 new tokens each; 32b: 8 prompts of 4,096 tokens and 128 new tokens; 8b: 8 prompts "
+                    "of 2,048 tokens and 64 new tokens); added to the line as workload")
     ap.add_argument("--prefill-lengths", default="", help="comma separated prompt lengths: time one prefill step of each "
                     "(printed on stderr, added to the line as prefill_sweep)")
     a = ap.parse_args()
@@ -269,6 +274,43 @@ def main():
         # copied from pinned host memory, and the sampled ids read back
         return {"tok_s": batch * steps / dt, "h2d": getattr(ctx.stepper, "last_h2d_bytes", None), "d2h": batch * 4}
 
+    def workload_run():
+        """The request mix named for this shape, through Context.generate: host ids in, host ids out.
+
+        Times the batch's prefill (until every request's first id is on the host) and the decoding after it."""
+        import gogguf_b200 as gg
+        if a.shape == "14b":
+            lens = torch.randint(128, 2049, (16,), generator=torch.Generator().manual_seed(3)).tolist()
+            new = 256
+        elif a.shape == "32b":
+            lens, new = [4096] * 8, 128
+        else:
+            lens, new = [PROMPT_LEN] * 8, 64
+        batch = len(lens)
+        engine = gg.Engine(model, gg.LoadOptions(dtype="bfloat16", max_batch=batch))
+        ctx = engine.new_context(max_tokens=sum(-(-(n + new + 8) // 64) * 64 for n in lens), max_batch=batch)
+        out = None
+        for rep in range(2):                       # the first pass captures the graphs
+            prompts = [rand_tokens(n) for n in lens]
+            first = {}
+
+            def on_token(i, t):
+                if i not in first:
+                    first[i] = time.perf_counter()
+                return True
+
+            torch.cuda.synchronize()
+            t_start = time.perf_counter()
+            res = ctx.generate(prompts, gg.GenerateParams(max_tokens=new, stop_token_ids=[], on_token=on_token))
+            t_end = time.perf_counter()
+            t_first = max(first.values())
+            made = sum(len(r.tokens) for r in res)
+            out = {"requests": batch, "prompt_tokens": sum(lens), "new_tokens": made,
+                   "prefill_ms": (t_first - t_start) * 1e3, "prefill_tok_s": sum(lens) / (t_first - t_start),
+                   "decode_tok_s": (made - batch) / (t_end - t_first), "decode_ms_per_step": (t_end - t_first) * 1e3 / (new - 1),
+                   "total_s": t_end - t_start}
+        return out
+
     def prefill_run(prompt_len=PROMPT_LEN):
         cache = model.new_cache(prompt_len + 64)
         st = GraphStepper(model, cache)
@@ -321,6 +363,11 @@ def main():
         sweep[str(t)] = round(r["ms"], 3)
         print(f"[bench] prefill of {t} tokens: {r['ms']:.3f} ms, {r['value']:.0f} tok/s, {r['tflops']:.0f} TFLOP/s", file=sys.stderr)
 
+    workload = None
+    if a.workload:
+        workload = workload_run()
+        print(f"[bench] workload: {workload}", file=sys.stderr)
+
     achieved = main_run["bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9
     line = {
         "metric": f"Qwen3-{a.shape.upper()} bf16 decode tok/s @ batch {a.batch} (points: batch 1/64; prefill tok/s @ 2,048 tokens)",
@@ -350,6 +397,8 @@ def main():
         line["points"] = points
     if sweep:
         line["prefill_sweep_ms"] = sweep
+    if workload is not None:
+        line["workload"] = workload
     print(json.dumps(line))
     return 0
 
