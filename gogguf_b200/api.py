@@ -73,6 +73,10 @@ class Context:
         res = self.generator.generate([list(prompts)] if single else [list(p) for p in prompts], params)
         return res[0] if single else res
 
+    def new_conversation(self) -> "Conversation":
+        """Context.NewConversation (pkg/runtime/conversation.go:15-17)."""
+        return Conversation(self)
+
     def forward_token_ids(self, tokens: Sequence[int]) -> torch.Tensor:
         """Logits [len(tokens), vocab] of one fresh sequence (float32, on the device)."""
         slot = self.cache.open()
@@ -81,6 +85,80 @@ class Context:
             return out.clone()
         finally:
             self.cache.close(slot)
+
+
+class Conversation:
+    """Several turns in one cache slot (Conversation, pkg/runtime/conversation.go:9-151).
+
+    Every call of `generate` brings the whole conversation so far as token ids, as the reference's
+    takes the whole rendered prompt.  If it goes on from the tokens that the slot holds, only the new
+    ones are run (conversation.go:107-117); if it is shorter or differs somewhere, the slot starts
+    again (`should_reset`, conversation.go:135-137).  After a turn the history is the prompt plus the
+    tokens that were made (`Commit`, conversation.go:36-38); a turn that raises leaves the history as
+    it was (conversation.go:67-70)."""
+
+    def __init__(self, ctx: "Context"):
+        self.ctx = ctx
+        self.tokens: List[int] = []
+        self._slot: Optional[int] = None
+
+    @staticmethod
+    def should_reset(held: Sequence[int], prompt: Sequence[int]) -> bool:
+        """conversation.go:135-151: the held tokens must be a prefix of the prompt."""
+        n = len(held)
+        return n > len(prompt) or list(prompt[:n]) != list(held)
+
+    def token_count(self) -> int:
+        """TokenCount (conversation.go:26-28): prompt and made tokens of the turns so far."""
+        return len(self.tokens)
+
+    def reset(self) -> None:
+        """Reset (conversation.go:20-23): no history, an empty slot."""
+        self.tokens = []
+        if self._slot is not None:
+            self.ctx.cache.restart(self._slot)
+
+    def rollback(self, token_count: int) -> None:
+        """Rollback (conversation.go:40-58): back to the first `token_count` tokens.  The reference runs
+        them again from an empty cache; here the slot is cut where its groups allow it, and only
+        otherwise emptied, in which case the next turn runs the history again."""
+        if token_count < 0 or token_count > len(self.tokens):
+            raise ValueError(f"the conversation holds {len(self.tokens)} tokens, cannot go back to {token_count}")
+        self.tokens = self.tokens[:token_count]
+        if self._slot is not None:
+            cache = self.ctx.cache
+            if not cache.truncate(self._slot, min(cache.length(self._slot), token_count)):
+                cache.restart(self._slot)
+
+    def generate(self, prompt: Sequence[int], params: Optional[GenerateParams] = None) -> GenerationResult:
+        """Generate (conversation.go:60-74)."""
+        prompt = list(prompt)
+        if not prompt:
+            raise ValueError("empty prompt")            # conversation.go:118-119
+        if self._slot is None:
+            self._slot = self.ctx.cache.open()
+        if self.should_reset(self.tokens, prompt):
+            self.reset()
+        cache = self.ctx.cache
+        # the slot may hold fewer tokens than the history (the last made token is not run until it is
+        # needed), never other ones
+        if cache.length(self._slot) > len(self.tokens):
+            if not cache.truncate(self._slot, len(self.tokens)):
+                cache.restart(self._slot)
+        snap = len(self.tokens)
+        try:
+            res = self.ctx.generator.generate([prompt], params, held={0: self._slot})[0]
+        except Exception:
+            self.rollback(snap)
+            raise
+        self.tokens = prompt + list(res.tokens)
+        return res
+
+    def close(self) -> None:
+        if self._slot is not None:
+            self.ctx.cache.close(self._slot)
+            self._slot = None
+        self.tokens = []
 
 
 def load(path: str, options: Optional[LoadOptions] = None) -> Engine:

@@ -90,6 +90,25 @@ class KVGroup:
                 self.pages.give(pg)
                 pl[idx] = -1
 
+    def can_shorten(self, slot: int, length: int) -> bool:
+        """Are the positions that a token at position `length` reads still held?"""
+        w = self.request.window
+        if w is None:
+            return True
+        pl = self.seq_pages.get(slot, [])
+        first_needed = max(0, length - w + 1)
+        last = (length + self.page_size - 1) // self.page_size
+        return all(pg >= 0 for pg in pl[first_needed // self.page_size:last])
+
+    def shorten(self, slot: int, length: int) -> None:
+        """Give back the pages beyond the first `length` positions."""
+        pl = self.seq_pages.get(slot, [])
+        keep = (length + self.page_size - 1) // self.page_size
+        for pg in pl[keep:]:
+            if pg >= 0:
+                self.pages.give(pg)
+        del pl[keep:]
+
     def release(self, slot: int) -> None:
         for pg in self.seq_pages.pop(slot, []):
             if pg >= 0:
@@ -183,6 +202,34 @@ class SequenceCache:
         if not self.slots.is_held(slot):
             raise CacheError(f"slot {slot} is not open")
         return self.lengths[slot]
+
+    def truncate(self, slot: int, length: int) -> bool:
+        """Shorten an open sequence to its first `length` tokens (a conversation that is rolled back,
+        a sequence that ran one step further than its result).  Returns False and changes nothing
+        where that cannot be done: a windowed group has already given back a page that the shorter
+        sequence's next token reads, or a layer keeps a fixed-size state, in which all tokens are
+        folded together.  The caller then starts the sequence again."""
+        cur = self.length(slot)
+        if length < 0 or length > cur:
+            raise CacheError(f"slot {slot} holds {cur} tokens, cannot be cut to {length}")
+        if length == cur:
+            return True
+        if self.states or not all(g.can_shorten(slot, length) for g in self.groups):
+            return False
+        for g in self.groups:
+            g.shorten(slot, length)
+        self.lengths[slot] = length
+        return True
+
+    def restart(self, slot: int) -> None:
+        """An open slot as `open` hands it out: length 0, no pages, state zeroed."""
+        if not self.slots.is_held(slot):
+            raise CacheError(f"slot {slot} is not open")
+        for g in self.groups:
+            g.release(slot)
+        self.lengths[slot] = 0
+        for st in self.states.values():
+            st[slot].zero_()
 
     @property
     def live_slots(self) -> int:

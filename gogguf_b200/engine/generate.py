@@ -83,13 +83,16 @@ class Generator:
         # step): the activations of a step grow with its tokens, the time of a token does not shrink beyond this.
         self.prefill_tokens = prefill_tokens
 
-    def _prefill(self, live: List[int], prompts, slots):
-        """The prompts of the batch, in order; returns the logits of their last tokens, one row per request."""
+    def _prefill(self, live: List[int], prompts, slots, cached=None):
+        """The prompts of the batch, in order; returns the logits of their last tokens, one row per request.
+        `cached[i]` tokens of request i are in its slot already (a conversation's earlier turns): only the
+        rest of its prompt runs."""
+        cached = cached or {}
         groups: List[List[int]] = []
         cur: List[int] = []
         used = 0
         for i in live:
-            n = len(prompts[i])
+            n = len(prompts[i]) - cached.get(i, 0)
             if cur and used + n > self.prefill_tokens:
                 groups.append(cur)
                 cur, used = [], 0
@@ -98,7 +101,10 @@ class Generator:
         groups.append(cur)
         outs = []
         for g in groups:
-            entries = [StepEntry(slots[i], list(prompts[i]), want=[len(prompts[i]) - 1]) for i in g]
+            entries = []
+            for i in g:
+                new = list(prompts[i][cached.get(i, 0):])
+                entries.append(StepEntry(slots[i], new, want=[len(new) - 1]))
             logits = self.stepper.step(entries)
             outs.append(logits if len(groups) == 1 else logits.clone())     # a step's logits live until the next step
         if len(outs) == 1:
@@ -106,16 +112,32 @@ class Generator:
         import torch
         return torch.cat(outs, dim=0)
 
-    def generate(self, prompts: Sequence[Sequence[int]], params: Optional[GenerateParams] = None
-                 ) -> List[GenerationResult]:
+    def generate(self, prompts: Sequence[Sequence[int]], params: Optional[GenerateParams] = None,
+                 held: Optional[dict] = None) -> List[GenerationResult]:
+        """`held` maps a request's index to a slot that is open already and holds the first tokens of its
+        prompt (as many as the cache says): only the rest of the prompt is run, and when the request ends
+        the slot stays open, cut back to the tokens of prompt + result that it holds (a conversation,
+        pkg/runtime/conversation.go:87-133).  A prompt that is wholly in its slot gives its last token
+        back first, so that there are logits to sample from (conversation.go:120-126)."""
         params = params or GenerateParams()
         max_new = params.max_tokens if params.max_tokens > 0 else 128      # session.go:134-137
         results: List[Optional[GenerationResult]] = [None] * len(prompts)
         batches = plan_batches([len(p) for p in prompts], max_new, self.max_batch,
                                self.cache.max_tokens, self.cache.page_size, self.context)
         for batch in batches:
-            self._run_batch(batch, prompts, params, max_new, results)
+            self._run_batch(batch, prompts, params, max_new, results, held or {})
         return [r for r in results if r is not None]
+
+    def _let_go(self, i: int, slots, held, prompts, generated) -> None:
+        """Request i has ended: its slot goes back, unless its owner holds it; then it keeps the tokens of
+        prompt + result that are in it and loses what a step ahead of the host put beyond them."""
+        s = slots.pop(i)
+        if i not in held:
+            self.cache.close(s)
+            return
+        keep = min(self.cache.length(s), len(prompts[i]) + len(generated[i]))
+        if not self.cache.truncate(s, keep):
+            self.cache.restart(s)            # the owner runs the whole history again at its next turn
 
     def _finish_reason(self, i: int, t: int, prompts, generated, params: GenerateParams, max_new: int,
                        stop) -> Optional[str]:
@@ -132,20 +154,33 @@ class Generator:
             return "length"          # the token's own position would lie outside the context
         return None
 
-    def _run_batch(self, batch: List[int], prompts, params: GenerateParams, max_new: int, results) -> None:
+    def _run_batch(self, batch: List[int], prompts, params: GenerateParams, max_new: int, results,
+                   held=None) -> None:
+        held = held or {}
         stop = set(self.default_stop if params.stop_token_ids is None else params.stop_token_ids)
         sampler = Sampler(params.sampler, params.repeat_penalty, params.repeat_last_n)
         cache = self.cache
-        slots = {i: cache.open() for i in batch}
+        slots, cached = {}, {}
         generated = {i: [] for i in batch}
         live: List[int] = list(batch)
         try:
-            logits = self._prefill(live, prompts, slots)
+            for i in batch:
+                if i in held:
+                    slots[i] = held[i]
+                    have = min(cache.length(held[i]), len(prompts[i]) - 1)
+                    if not cache.truncate(held[i], have):
+                        cache.restart(held[i])
+                        have = 0
+                    cached[i] = have
+                else:
+                    slots[i] = cache.open()
+            logits = self._prefill(live, prompts, slots, cached)
             if hasattr(self.stepper, "decode_from_device") and getattr(logits, "is_cuda", False) and len(live) <= 256:
                 sampler.begin(live, [prompts[i] for i in live], logits.device)     # rings for a repeat penalty
             if (hasattr(self.stepper, "decode_from_device") and sampler.device_only
                     and getattr(logits, "is_cuda", False) and len(live) <= 256):
-                self._decode_one_ahead(live, logits, sampler, slots, generated, prompts, params, max_new, stop, results)
+                self._decode_one_ahead(live, logits, sampler, slots, generated, prompts, params, max_new, stop, results,
+                                       held)
                 return
             while live:
                 hist = [list(prompts[i]) + generated[i] for i in live] if sampler.penalised else None
@@ -158,23 +193,22 @@ class Generator:
                         go_on.append(i)
                     else:
                         results[i] = GenerationResult(generated[i], reason, len(prompts[i]))
-                        cache.close(slots.pop(i))
+                        self._let_go(i, slots, held, prompts, generated)
                 live = go_on
                 if not live:
                     break
                 entries = [StepEntry(slots[i], [generated[i][-1]], want=[0]) for i in live]
                 logits = self.stepper.step(entries)
         finally:
-            for i, s in list(slots.items()):
-                cache.close(s)
-                slots.pop(i)
+            for i in list(slots):
+                self._let_go(i, slots, held, prompts, generated)
 
-    def _decode_one_ahead(self, live, logits, sampler, slots, generated, prompts, params, max_new, stop, results):
+    def _decode_one_ahead(self, live, logits, sampler, slots, generated, prompts, params, max_new, stop, results,
+                          held=None):
         """The same loop with the device kept busy: while the host reads the ids of step k, step k + 1 is
         already running on the ids that the sampling kernel left on the device.  A sequence whose id turns
         out to be a stop token (or whose callback says stop) was then run one step too far; its extra row
         is dropped and its slot is given back, and nobody else's result depends on it."""
-        cache = self.cache
         rows = list(live)                                   # requests whose ids are on their way
         pending = sampler.sample_async(logits, rows, [len(generated[i]) for i in rows])
         dev_row = {i: r for r, i in enumerate(rows)}        # where each request's id sits in the device buffer
@@ -193,7 +227,7 @@ class Generator:
                 reason = self._finish_reason(i, t, prompts, generated, params, max_new, stop)
                 if reason is not None:
                     results[i] = GenerationResult(generated[i], reason, len(prompts[i]))
-                    cache.close(slots.pop(i))
+                    self._let_go(i, slots, held or {}, prompts, generated)
                     stopped.add(i)
             if nxt_pending is None:
                 break

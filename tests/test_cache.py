@@ -143,3 +143,39 @@ def test_random_traffic_keeps_the_books():
         c.close(s)
     c.check()
     assert all(g.pages.held_count == 0 for g in c.groups) and c.slots.held_count == 0
+
+
+def test_truncate_gives_pages_back_and_restart_empties_the_slot():
+    c = SequenceCache([KVRequest(1, 4)], [None], 64 * 6, dtype=torch.float32)
+    a, b = c.open(), c.open()
+    c.plan([a, b], [200, 10]); c.commit([a, b], [200, 10])
+    free = c.free_tokens()
+    assert c.truncate(a, 200) and c.free_tokens() == free
+    assert c.truncate(a, 65)
+    assert c.length(a) == 65 and c.free_tokens() == free + 2 * 64
+    c.check()
+    c.plan([a], [64]); c.commit([a], [64])            # grows again from where it was cut
+    assert c.length(a) == 129 and c.free_tokens() == free + 64
+    with pytest.raises(CacheError):
+        c.truncate(a, 130)
+    c.restart(a)
+    assert c.length(a) == 0 and c.length(b) == 10 and c.live_slots == 2
+    c.check()
+    c.close(a); c.close(b)
+    assert c.free_tokens() == 64 * 6
+    c.check()
+
+
+def test_truncate_refuses_what_a_window_or_a_state_has_let_go():
+    c = SequenceCache([KVRequest(1, 4, window=70)], [None], 64 * 8, dtype=torch.float32)
+    s = c.open()
+    c.plan([s], [200]); c.commit([s], [200])          # positions below 131 have left the window: pages 0 and 1 are gone
+    assert c.truncate(s, 199)                         # reads 130..198: page 2 onwards
+    assert not c.truncate(s, 190) and c.length(s) == 199      # would read 121..: page 1 is gone
+    c.check()
+    c2 = SequenceCache([StateRequest((3,))], [None], 64 * 2, dtype=torch.float32, max_slots=2)
+    s2 = c2.open()
+    c2.plan([s2], [5]); c2.commit([s2], [5])
+    assert c2.truncate(s2, 5) and not c2.truncate(s2, 4)
+    c2.restart(s2)
+    assert c2.length(s2) == 0

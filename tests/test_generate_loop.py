@@ -147,3 +147,79 @@ def test_prompts_of_a_large_batch_run_in_several_steps():
     assert one.steps[0] == [(s, n) for s, n in one.steps[0]] and len(one.steps[0]) == 5  # by default: one step
     st.cache.check()
     assert st.cache.live_slots == 0
+
+
+# ----------------------------------------------------------------------------- conversations
+class _Ctx:
+    """What a Conversation needs of a context: a cache and a generator."""
+
+    def __init__(self, stepper, context=1000):
+        self.stepper = stepper
+        self.cache = stepper.cache
+        self.generator = gen(stepper, context)
+
+
+def test_conversation_runs_only_what_is_new():
+    from gogguf_b200.api import Conversation
+    st = ScriptedStepper()
+    conv = Conversation(_Ctx(st))
+    r1 = conv.generate([1, 2, 3], GenerateParams(max_tokens=3))
+    assert r1.tokens == [4, 5, 6]
+    assert conv.token_count() == 6 and conv.tokens == [1, 2, 3, 4, 5, 6]
+    assert st.cache.live_slots == 1 and st.cache.length(conv._slot) == 5       # 6 was sampled, not run
+    n_before = len(st.steps)
+    # the next turn brings the whole conversation plus two new tokens: 6 (not yet run), 9 and 10 are run
+    r2 = conv.generate(conv.tokens + [9, 10], GenerateParams(max_tokens=2))
+    assert r2.tokens == [11, 12] and r2.prompt_tokens == 8
+    assert st.steps[n_before] == [(conv._slot, 3)]
+    assert conv.tokens == [1, 2, 3, 4, 5, 6, 9, 10, 11, 12]
+    # a prompt that is wholly in the slot gives its last token back to have logits (conversation.go:120-126)
+    conv.rollback(8)
+    assert st.cache.length(conv._slot) == 8
+    n_before = len(st.steps)
+    r3 = conv.generate(conv.tokens, GenerateParams(max_tokens=1))
+    assert r3.tokens == [11] and st.steps[n_before] == [(conv._slot, 1)]
+    st.cache.check()
+    conv.close()
+    assert st.cache.live_slots == 0
+    st.cache.check()
+
+
+def test_conversation_starts_again_when_the_prompt_does_not_go_on_from_it():
+    from gogguf_b200.api import Conversation
+    assert Conversation.should_reset([1, 2, 3, 4, 5], [9, 9])                   # shorter (conversation_test.go:24-26)
+    assert not Conversation.should_reset([1, 2, 3, 4, 5], [1, 2, 3, 4, 5, 6])   # goes on (:28-30)
+    assert Conversation.should_reset([1, 2, 3, 4, 5], [1, 2, 9, 4, 5])          # differs (:32-34)
+    st = ScriptedStepper()
+    conv = Conversation(_Ctx(st))
+    conv.generate([1, 2, 3], GenerateParams(max_tokens=2))
+    n_before = len(st.steps)
+    r = conv.generate([7, 8], GenerateParams(max_tokens=2))
+    assert r.tokens == [9, 10] and st.steps[n_before] == [(conv._slot, 2)]
+    assert conv.tokens == [7, 8, 9, 10] and st.cache.length(conv._slot) == 3
+    conv.reset()
+    assert conv.token_count() == 0 and st.cache.length(conv._slot) == 0
+    st.cache.check()
+
+
+def test_conversation_keeps_its_history_when_a_turn_fails():
+    from gogguf_b200.api import Conversation
+    st = ScriptedStepper(max_tokens=64 * 2)
+    conv = Conversation(_Ctx(st))
+    conv.generate([1, 2, 3], GenerateParams(max_tokens=2))
+    held = list(conv.tokens)
+    with pytest.raises(ValueError):
+        conv.generate(held + [5] * 200, GenerateParams(max_tokens=2))          # more than the cache holds
+    assert conv.tokens == held
+    r = conv.generate(held + [1], GenerateParams(max_tokens=1))
+    assert r.tokens == [2]
+    st.cache.check()
+
+
+def test_conversation_stop_token_is_not_in_the_slot():
+    from gogguf_b200.api import Conversation
+    st = ScriptedStepper()
+    conv = Conversation(_Ctx(st))
+    r = conv.generate([1], GenerateParams(max_tokens=8, stop_token_ids=[4]))
+    assert r.tokens == [2, 3] and r.finish_reason == "stop"
+    assert conv.tokens == [1, 2, 3] and st.cache.length(conv._slot) == 3       # 3 was run, 4 was not

@@ -146,3 +146,50 @@ def test_one_step_ahead_loop_equals_the_plain_loop(tmp_path_factory):
         toks, why = expected(i)
         assert r.tokens == toks and r.finish_reason == why, i
     assert cache.live_slots == 0
+
+
+@pytest.mark.parametrize("name,first,back", [("A", 70, 3), ("B", 70, 3), ("W", 130, 50)])
+def test_conversation_turns_equal_whole_histories(tmp_path_factory, name, first, back):
+    """Several turns in one slot: every turn's tokens are those of the plain implementation on the whole
+    history, although only the new tokens are run; a stop token that the device ran one step ahead of the
+    host is cut out of the slot again; a rollback cuts the slot and the next turn goes on from there (with
+    windows, "W", the rollback reaches behind a page that the window has already given back: the slot
+    starts again and the next turn runs the whole history)."""
+    import gogguf_b200 as gg
+    folder = make_folder(tmp_path_factory.getbasetemp(), name, "float32")
+    cfg, w = read_folder(folder)
+    V = cfg["vocab_size"]
+    engine = gg.load(folder, gg.LoadOptions(dtype="float32", max_tokens=2048))
+    ctx = engine.new_context()
+    conv = ctx.new_conversation()
+    p1 = random_tokens(V, first, 5)                            # more than a page
+    r1 = conv.generate(p1, gg.GenerateParams(max_tokens=6, stop_token_ids=[]))
+    assert r1.tokens == plain.generate_greedy(cfg, w, p1, 6, wide=True)
+    assert ctx.cache.length(conv._slot) <= len(p1) + 6 and conv.token_count() == len(p1) + 6
+    # second turn: the history and some new tokens; ends on a stop token, which the device had already run
+    p2 = conv.tokens + random_tokens(V, 9, 6)
+    ref2 = plain.generate_greedy(cfg, w, p2, 10, wide=True)
+    stop = ref2[4] if ref2[4] not in ref2[:4] else None
+    r2 = conv.generate(p2, gg.GenerateParams(max_tokens=10, stop_token_ids=[stop] if stop is not None else []))
+    want2 = ref2[:4] if stop is not None else ref2
+    assert r2.tokens == want2 and r2.prompt_tokens == len(p2)
+    assert conv.tokens == p2 + want2
+    assert ctx.cache.length(conv._slot) <= len(conv.tokens)
+    # third turn after a rollback into the middle of the second
+    conv.rollback(len(p2) - back)
+    assert ctx.cache.length(conv._slot) == (len(p2) - back if name != "W" else 0)
+    p3 = conv.tokens + random_tokens(V, 2, 7)
+    r3 = conv.generate(p3, gg.GenerateParams(max_tokens=5, stop_token_ids=[]))
+    assert r3.tokens == plain.generate_greedy(cfg, w, p3, 5, wide=True)
+    # a prompt that does not go on from the history starts the slot again; other requests run beside it
+    p4 = random_tokens(V, 11, 8)
+    r4 = conv.generate(p4, gg.GenerateParams(max_tokens=4, stop_token_ids=[]))
+    other = ctx.generate([p1[:5]], gg.GenerateParams(max_tokens=4, stop_token_ids=[]))
+    assert r4.tokens == plain.generate_greedy(cfg, w, p4, 4, wide=True)
+    assert other[0].tokens == plain.generate_greedy(cfg, w, p1[:5], 4, wide=True)
+    r5 = conv.generate(conv.tokens + [3], gg.GenerateParams(max_tokens=3, stop_token_ids=[]))
+    assert r5.tokens == plain.generate_greedy(cfg, w, p4 + r4.tokens + [3], 3, wide=True)
+    ctx.cache.check()
+    conv.close()
+    assert ctx.cache.live_slots == 0
+    ctx.cache.check()
