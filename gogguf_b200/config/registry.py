@@ -83,4 +83,28 @@ def load_config(path: str):
             raise ConfigError(f"{p}: not valid JSON: {e}") from None
     if not isinstance(d, dict):
         raise ConfigError(f"{p}: top level must be an object")
+    _merge_generation_config(d, os.path.join(os.path.dirname(p), "generation_config.json"))
     return config_from_dict(d)
+
+
+def _merge_generation_config(d: Dict[str, Any], path: str) -> None:
+    """A model folder may name further end-of-sequence ids in ``generation_config.json`` (a chat
+    model's end-of-turn id beside its end-of-text id); generation stops on any of them, the ones of
+    config.json first.  An unreadable file is an error, a missing one is not."""
+    if not os.path.isfile(path):
+        return
+    with open(path, "r", encoding="utf-8") as f:
+        try:
+            g = json.load(f)
+        except json.JSONDecodeError as e:
+            raise ConfigError(f"{path}: not valid JSON: {e}") from None
+    extra = g.get("eos_token_id") if isinstance(g, dict) else None
+    if extra is None:
+        return
+    def ids(v):
+        return [int(x) for x in v] if isinstance(v, (list, tuple)) else ([] if v is None else [int(v)])
+    merged = ids(d.get("eos_token_id"))
+    for t in ids(extra):
+        if t not in merged:
+            merged.append(t)
+    d["eos_token_id"] = merged if len(merged) != 1 else merged[0]

@@ -97,3 +97,17 @@ def test_schedule_validation():
         replace(spec, schedule=(ScheduleEntry(0), ScheduleEntry(5))).validate()
     with pytest.raises(ValueError):
         replace(spec, schedule=(ScheduleEntry(0, cache_of=0),)).validate()
+
+
+def test_generation_config_adds_stop_ids(tmp_path):
+    import json
+    from gogguf_b200.config import load_config
+    from helpers import TINY_A
+    (tmp_path / "config.json").write_text(json.dumps(dict(TINY_A, eos_token_id=7)))
+    assert load_config(str(tmp_path)).eos_token_ids == (7,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [9, 7], "temperature": 0.6}))
+    cfg = load_config(str(tmp_path))
+    assert cfg.eos_token_ids == (7, 9) and cfg.to_spec().stop_token_ids == (7, 9)
+    (tmp_path / "generation_config.json").write_text("{")
+    with pytest.raises(Exception, match="not valid JSON"):
+        load_config(str(tmp_path))
