@@ -7,9 +7,9 @@
 from . import config  # noqa: F401  (registers architectures)
 from . import parts   # noqa: F401  (registers part kinds)
 from .api import Context, Conversation, Engine, Greedy, LoadOptions, load, new_sampler
-from .engine.generate import GenerateParams, GenerationResult
+from .engine.generate import GenerateParams, GenerationResult, GenerationSession
 from .sampling.sampler import Sampler, SamplerConfig
 
 __version__ = "0.1.0"
 __all__ = ["Context", "Conversation", "Engine", "Greedy", "LoadOptions", "load", "new_sampler", "GenerateParams",
-           "GenerationResult", "Sampler", "SamplerConfig"]
+           "GenerationResult", "GenerationSession", "Sampler", "SamplerConfig"]

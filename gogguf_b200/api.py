@@ -18,7 +18,7 @@ from typing import List, Optional, Sequence, Union
 
 import torch
 
-from .engine.generate import GenerateParams, GenerationResult, Generator
+from .engine.generate import GenerateParams, GenerationResult, GenerationSession, Generator
 from .engine.model import Model
 from .engine.step import StepEntry, Stepper
 from .sampling.sampler import Sampler, SamplerConfig, greedy as Greedy  # noqa: N812
@@ -72,6 +72,14 @@ class Context:
         single = len(prompts) > 0 and isinstance(prompts[0], int)
         res = self.generator.generate([list(prompts)] if single else [list(p) for p in prompts], params)
         return res[0] if single else res
+
+    def start_generation(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
+                         stop_token_ids: Optional[Sequence[int]] = None) -> GenerationSession:
+        """Context.StartGeneration (pkg/runtime/session.go:19-41): the prompts run in one step, then the
+        caller takes one token per `decode_step`.  One prompt (a list of ids) or a batch of them."""
+        single = len(prompts) > 0 and isinstance(prompts[0], int)
+        return GenerationSession(self.generator, [list(prompts)] if single else [list(p) for p in prompts],
+                                 stop_token_ids)
 
     def new_conversation(self) -> "Conversation":
         """Context.NewConversation (pkg/runtime/conversation.go:15-17)."""

@@ -253,3 +253,105 @@ class _SubsetSample:
     def tokens(self):
         ids = self._base.tokens()
         return [ids[r] for r in self._keep]
+
+
+class GenerationSession:
+    """Step-by-step generation after a prefill (GenerationSession, pkg/runtime/session.go:11-81): the
+    caller asks for one token at a time and may change the sampling between steps.
+
+    `start` runs the prompts of a batch in one step (StartGeneration, session.go:19-41) and keeps the
+    logits of their last tokens; `decode_step` samples one token per live sequence from the kept logits,
+    with the repeat penalty over prompt + generated (session.go:83-103), ends the sequences whose token
+    is a stop token or below 0 (neither appended nor run, session.go:58-65) or whose next position lies
+    outside the context (session.go:69-72: an error there, the end of that sequence here, since others
+    may go on), runs the new tokens of the others as one step and keeps their logits.  A sequence that
+    has ended gives -1 from then on and its slot is free at once."""
+
+    def __init__(self, generator: "Generator", prompts: Sequence[Sequence[int]],
+                 stop_token_ids: Optional[Sequence[int]] = None):
+        self._gen = generator
+        self.prompts = [list(p) for p in prompts]
+        n = len(self.prompts)
+        if n == 0 or n > generator.max_batch:
+            raise ValueError(f"a session takes 1 to {generator.max_batch} prompts, not {n}")
+        plan = plan_batches([len(p) for p in self.prompts], 1, generator.max_batch, generator.cache.max_tokens,
+                            generator.cache.page_size, generator.context)
+        if len(plan) != 1:
+            raise ValueError("the prompts of a session must fit the cache together")
+        self.stop = set(generator.default_stop if stop_token_ids is None else stop_token_ids)
+        self.generated: List[List[int]] = [[] for _ in range(n)]
+        self.finish_reason: List[Optional[str]] = [None] * n
+        self._slots = {}
+        self._samplers = {}
+        self._live: List[int] = list(range(n))
+        try:
+            for i in range(n):
+                self._slots[i] = generator.cache.open()
+            self._logits = generator._prefill(self._live, self.prompts, self._slots)
+        except Exception:
+            self.close()
+            raise
+
+    @property
+    def live(self) -> List[int]:
+        """Indices of the requests that have not ended."""
+        return list(self._live)
+
+    def decode_step(self, params: Optional[GenerateParams] = None) -> List[int]:
+        """DecodeStepWith (session.go:50-81) for every request: its next token, or -1 if it has ended."""
+        params = params or GenerateParams()
+        out = [-1] * len(self.prompts)
+        if not self._live:
+            return out
+        key = (params.sampler, params.repeat_penalty, params.repeat_last_n)
+        sampler = self._samplers.get(key)
+        if sampler is None:
+            sampler = self._samplers[key] = Sampler(params.sampler, params.repeat_penalty, params.repeat_last_n)
+        live = self._live
+        hist = [self.prompts[i] + self.generated[i] for i in live] if sampler.penalised else None
+        nxt = sampler.sample(self._logits, streams=live, steps=[len(self.generated[i]) for i in live], histories=hist)
+        go_on: List[int] = []
+        for i, t in zip(live, nxt):
+            t = int(t)
+            if t < 0 or t in self.stop:
+                self._end(i, "stop")
+                continue
+            self.generated[i].append(t)
+            out[i] = t
+            if len(self.prompts[i]) + len(self.generated[i]) > self._gen.context:
+                self._end(i, "length")           # the token's own position would lie outside the context
+                continue
+            go_on.append(i)
+        self._live = go_on
+        if go_on:
+            entries = [StepEntry(self._slots[i], [self.generated[i][-1]], want=[0]) for i in go_on]
+            self._logits = self._gen.stepper.step(entries)
+        return out
+
+    def _end(self, i: int, reason: str) -> None:
+        self.finish_reason[i] = reason
+        self._gen.cache.close(self._slots.pop(i))
+
+    def generated_tokens(self, i: int = 0) -> List[int]:
+        """GeneratedTokens (session.go:106-110)."""
+        return list(self.generated[i])
+
+    def generated_count(self, i: int = 0) -> int:
+        """GeneratedCount (session.go:118-120)."""
+        return len(self.generated[i])
+
+    def prompt_token_count(self, i: int = 0) -> int:
+        """PromptTokenCount (session.go:123-125)."""
+        return len(self.prompts[i])
+
+    def close(self) -> None:
+        """Give back the slots of the requests that are still live."""
+        for i in list(self._slots):
+            self._gen.cache.close(self._slots.pop(i))
+        self._live = []
+
+    def __enter__(self) -> "GenerationSession":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()

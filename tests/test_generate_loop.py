@@ -223,3 +223,36 @@ def test_conversation_stop_token_is_not_in_the_slot():
     r = conv.generate([1], GenerateParams(max_tokens=8, stop_token_ids=[4]))
     assert r.tokens == [2, 3] and r.finish_reason == "stop"
     assert conv.tokens == [1, 2, 3] and st.cache.length(conv._slot) == 3       # 3 was run, 4 was not
+
+
+# ----------------------------------------------------------------------------- step-by-step sessions
+def test_session_gives_one_token_per_step_and_minus_one_after_the_end():
+    from gogguf_b200.engine.generate import GenerationSession
+    st = ScriptedStepper()
+    sess = GenerationSession(gen(st), [[1, 2], [9]], stop_token_ids=[4])
+    assert st.steps == [[(sess._slots[0], 2), (sess._slots[1], 1)]] and sess.live == [0, 1]
+    assert sess.decode_step() == [3, 10]
+    assert sess.decode_step() == [-1, 11]                  # 4 stops the first: not kept, not run
+    assert sess.finish_reason == ["stop", None] and sess.live == [1]
+    assert st.cache.live_slots == 1 and st.steps[-1] == [(sess._slots[1], 1)]
+    assert sess.decode_step(GenerateParams(sampler=SamplerConfig(temp=0.5, seed=3))) == [-1, 12]   # one-hot logits
+    assert sess.generated_tokens(0) == [3] and sess.generated_tokens(1) == [10, 11, 12]
+    assert sess.generated_count(1) == 3 and sess.prompt_token_count(0) == 2
+    sess.close()
+    assert st.cache.live_slots == 0 and sess.decode_step() == [-1, -1]
+    st.cache.check()
+
+
+def test_session_ends_a_sequence_at_the_context_and_frees_slots_on_errors():
+    from gogguf_b200.engine.generate import GenerationSession
+    st = ScriptedStepper()
+    with GenerationSession(gen(st, context=4), [[1, 2, 3]], stop_token_ids=[]) as sess:
+        assert sess.decode_step() == [4]                   # position 3 is the last one
+        assert sess.decode_step() == [5] and sess.finish_reason == ["length"]     # 5 is given, cannot be run
+        assert sess.decode_step() == [-1]
+    assert st.cache.live_slots == 0
+    with pytest.raises(ValueError):
+        GenerationSession(gen(st, context=4), [[1, 2, 3, 4, 5]])
+    with pytest.raises(ValueError):
+        GenerationSession(gen(ScriptedStepper(max_tokens=64)), [[1] * 40, [2] * 40])      # two pages needed, one there
+    assert st.cache.live_slots == 0

@@ -193,3 +193,43 @@ def test_conversation_turns_equal_whole_histories(tmp_path_factory, name, first,
     conv.close()
     assert ctx.cache.live_slots == 0
     ctx.cache.check()
+
+
+def test_step_by_step_session_equals_the_loop(tmp_path_factory):
+    """Context.start_generation + decode_step: the tokens of the plain implementation, a stop token that
+    ends one sequence while the other goes on, sampling changed between steps, slots given back."""
+    import gogguf_b200 as gg
+    folder = make_folder(tmp_path_factory.getbasetemp(), "B", "float32", scale=8.0)
+    cfg, w = read_folder(folder)
+    V = cfg["vocab_size"]
+    prompts = [random_tokens(V, 9, 31), random_tokens(V, 4, 32)]
+    engine = gg.load(folder, gg.LoadOptions(dtype="float32", max_tokens=1024))
+    ctx = engine.new_context()
+    ref = [plain.generate_greedy(cfg, w, p, 6, wide=True) for p in prompts]
+    stop = next(t for t in ref[0][1:] if t not in ref[1])
+    with ctx.start_generation(prompts, stop_token_ids=[stop]) as sess:
+        got = [sess.decode_step() for _ in range(6)]
+    k = ref[0].index(stop)
+    assert [g[0] for g in got] == ref[0][:k] + [-1] * (6 - k)
+    assert [g[1] for g in got] == ref[1]
+    assert sess.finish_reason[0] == "stop" and ctx.cache.live_slots == 0
+    # one prompt; greedy for two steps, then seeded temperature sampling with a repeat penalty
+    sess = ctx.start_generation(prompts[0], stop_token_ids=[])
+    seq = list(prompts[0])
+    for step in range(5):
+        if step < 2:
+            params, want = gg.GenerateParams(), None
+        else:
+            params = gg.GenerateParams(sampler=gg.SamplerConfig(temp=0.8, top_k=5, seed=11), repeat_penalty=1.2)
+        (tok,) = sess.decode_step(params)
+        logits = plain.forward(cfg, w, seq, wide=True)[-1].float().tolist()
+        if step < 2:
+            assert tok == plain.greedy(logits)
+        else:
+            plain.repeat_penalty(logits, seq, 1.2, 64)
+            assert tok == plain.sample(logits, 0.8, 5, 1.0, 0.0, plain.uniform01(11, 0, step))
+        seq.append(tok)
+    assert sess.generated_tokens() == seq[len(prompts[0]):] and sess.prompt_token_count() == 9
+    sess.close()
+    ctx.cache.check()
+    assert ctx.cache.live_slots == 0
