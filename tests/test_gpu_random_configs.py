@@ -39,11 +39,44 @@ def draw_config(seed: int) -> dict:
 
 @pytest.mark.parametrize("seed", list(range(10)))
 def test_a_configuration_nobody_chose(tmp_path, seed):
+    check_configuration(draw_config(seed), seed, tmp_path)
+
+
+def edge_config(d, hidden, inter, vocab, nq=4, nkv=2):
+    return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=hidden,
+                num_attention_heads=nq, num_key_value_heads=nkv, head_dim=d, intermediate_size=inter, vocab_size=vocab,
+                rope_theta=1e4, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=512)
+
+
+@pytest.mark.parametrize("cfg", [
+    edge_config(2, 64, 96, 331), edge_config(24, 64, 96, 331), edge_config(100, 64, 96, 331),
+    edge_config(200, 64, 96, 331),                       # head sizes that are no multiple of 16
+    edge_config(32, 50, 37, 101), edge_config(32, 4, 2, 3), edge_config(32, 1000, 1001, 999),    # widths no multiple of 8
+    edge_config(128, 72, 96, 331, nq=17, nkv=1),         # more query heads per kv head than an MMA tile has rows
+    edge_config(64, 72, 96, 331, nq=33, nkv=11),
+], ids=lambda c: f"d{c['head_dim']}-h{c['hidden_size']}-i{c['intermediate_size']}-v{c['vocab_size']}-q{c['num_attention_heads']}")
+def test_sizes_at_the_edges_of_what_the_kernels_take(tmp_path, cfg):
+    """What the configuration allows and no fast kernel was written for goes to the general kernels, with the
+    same results."""
+    check_configuration(cfg, 3, tmp_path)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_head_size_beyond_the_kernels_is_refused_when_the_model_is_built(tmp_path, dtype):
+    from gogguf_b200.config import config_from_dict
+    from gogguf_b200.engine import Model
+    from gogguf_b200.engine.model import write_random_model
+    folder = os.path.join(str(tmp_path), "m")
+    write_random_model(config_from_dict(edge_config(272, 64, 96, 331)), 0, folder, dtype=dtype)
+    with pytest.raises(ValueError, match="head_dim=272 is not supported"):
+        Model.load(folder, dtype=dtype)
+
+
+def check_configuration(cfg, seed, tmp_path):
     from gogguf_b200.config import config_from_dict
     from gogguf_b200.engine import Model, StepEntry, Stepper
     from gogguf_b200.engine.graphs import GraphStepper
     from gogguf_b200.engine.model import write_random_model
-    cfg = draw_config(seed)
     n = 150
     tokens = random_tokens(cfg["vocab_size"], n, seed)
     for dtype, tol, std in (("float32", TOL_F32, 0.05), ("bfloat16", TOL_BF16, 0.08)):
