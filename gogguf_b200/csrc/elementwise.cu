@@ -272,10 +272,11 @@ __global__ void qk_norm_rope_cache_kernel(
     }
 }
 
-// bfloat16 form for a full rotation (rot == d) and d = 64 * VPL / 2 ... : each lane owns VPL pairs
-// (i, i + d/2) with i = lane * VPL .. +VPL, so both halves of a pair sit in the same thread, every
-// access is VPL * 2 bytes wide and no shared memory is needed.  VPL = d / 64 (d = 64: 1, 128: 2, 256: 4).
-template <int VPL>
+// bfloat16 form for a full rotation (rot == d) and d = 64, 128 or 256.  D / 16 lanes share one head: a lane
+// owns eight pairs (i, i + d/2), i = 8 * sub .. + 8, so both halves of a pair sit in the same thread and
+// every access to the head is 16 bytes wide; a warp handles 32 / (D / 16) heads at once (four of size 128),
+// which keeps 1 KB in flight per warp.  The head's sum of squares is added over its lanes by shuffles.
+template <int D>
 __global__ void __launch_bounds__(128) qk_norm_rope_cache_vec_kernel(
     const bf16* qkv, bf16* __restrict__ q_out,
     const float* __restrict__ qw, const float* __restrict__ kw, float eps,
@@ -285,76 +286,78 @@ __global__ void __launch_bounds__(128) qk_norm_rope_cache_vec_kernel(
     bf16* __restrict__ k_pool, bf16* __restrict__ v_pool, int ntok, int nq, int nkv) {
     pdl_launch();
     pdl_wait();
-    constexpr int D = 64 * VPL, HALF = D / 2;
+    constexpr int HALF = D / 2, LPH = D / 16, HPW = 32 / LPH;      // lanes per head, heads per warp
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nheads = nq + 2 * nkv;
-    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
-    if (wid >= (long long)ntok * nheads) return;
-    const int t = (int)(wid / nheads), h = (int)(wid - (long long)t * nheads);
-    const int b = seq_of_token[t];
+    const long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + warp) * HPW + lane / LPH;
+    const int sub = lane % LPH;
+    const bool in_range = item < (long long)ntok * nheads;
+    const int t = in_range ? (int)(item / nheads) : 0, h = in_range ? (int)(item - (long long)t * nheads) : 0;
+    const int b = in_range ? seq_of_token[t] : -1;
     const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
-    if (!is_q && (k_pool == nullptr || b < 0)) return;
+    const bool live = in_range && (is_q || (k_pool != nullptr && b >= 0));     // every lane stays for the shuffles
     const bf16* src = qkv + ((size_t)t * nheads + h) * D;
-    bf16* dst;
-    if (is_q) {
-        dst = q_out + ((size_t)t * nq + h) * D;
-    } else {
-        const int pos = positions[t];
-        const int page = page_table[(size_t)b * max_pages + pos / page_size];
-        const int kvh = is_k ? h - nq : h - nq - nkv;
-        dst = (is_k ? k_pool : v_pool) + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * D;
-    }
-    const int i0 = lane * VPL;          // first index of this lane in the low half
-    bf16 lo[VPL], hi[VPL];
-    if (VPL == 1) {
-        lo[0] = src[i0]; hi[0] = src[i0 + HALF];
-    } else if (VPL == 2) {
-        *reinterpret_cast<uint32_t*>(lo) = *reinterpret_cast<const uint32_t*>(src + i0);
-        *reinterpret_cast<uint32_t*>(hi) = *reinterpret_cast<const uint32_t*>(src + i0 + HALF);
-    } else {
-        *reinterpret_cast<uint2*>(lo) = *reinterpret_cast<const uint2*>(src + i0);
-        *reinterpret_cast<uint2*>(hi) = *reinterpret_cast<const uint2*>(src + i0 + HALF);
-    }
-    if (!is_q && !is_k) {               // value head: plain copy
-        if (VPL == 1) { dst[i0] = lo[0]; dst[i0 + HALF] = hi[0]; }
-        else if (VPL == 2) {
-            *reinterpret_cast<uint32_t*>(dst + i0) = *reinterpret_cast<uint32_t*>(lo);
-            *reinterpret_cast<uint32_t*>(dst + i0 + HALF) = *reinterpret_cast<uint32_t*>(hi);
+    bf16* dst = nullptr;
+    if (live) {
+        if (is_q) {
+            dst = q_out + ((size_t)t * nq + h) * D;
         } else {
-            *reinterpret_cast<uint2*>(dst + i0) = *reinterpret_cast<uint2*>(lo);
-            *reinterpret_cast<uint2*>(dst + i0 + HALF) = *reinterpret_cast<uint2*>(hi);
+            const int pos = positions[t];
+            const int page = page_table[(size_t)b * max_pages + pos / page_size];
+            const int kvh = is_k ? h - nq : h - nq - nkv;
+            dst = (is_k ? k_pool : v_pool) + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * D;
         }
-        return;
     }
+    const int i0 = sub * 8;             // first index of this lane in the low half
+    uint4 lo4 = make_uint4(0, 0, 0, 0), hi4 = make_uint4(0, 0, 0, 0);
+    if (live) {
+        lo4 = *reinterpret_cast<const uint4*>(src + i0);
+        hi4 = *reinterpret_cast<const uint4*>(src + i0 + HALF);
+    }
+    if (live && !is_q && !is_k) {       // value head: plain copy
+        *reinterpret_cast<uint4*>(dst + i0) = lo4;
+        *reinterpret_cast<uint4*>(dst + i0 + HALF) = hi4;
+    }
+    const bool rotate = live && (is_q || is_k);
     const float* w = is_q ? qw : kw;
-    float a[VPL], c[VPL], ss = 0.f;
+    float4 cs[2], sn[2], wl[2], wh[2];
+    if (rotate) {                       // asked for before the sum of squares is known
+        const float4* cp = reinterpret_cast<const float4*>(cosv + (size_t)t * HALF + i0);
+        const float4* sp = reinterpret_cast<const float4*>(sinv + (size_t)t * HALF + i0);
+        cs[0] = cp[0]; cs[1] = cp[1]; sn[0] = sp[0]; sn[1] = sp[1];
+        if (w != nullptr) {
+            wl[0] = reinterpret_cast<const float4*>(w + i0)[0]; wl[1] = reinterpret_cast<const float4*>(w + i0)[1];
+            wh[0] = reinterpret_cast<const float4*>(w + i0 + HALF)[0]; wh[1] = reinterpret_cast<const float4*>(w + i0 + HALF)[1];
+        }
+    }
+    const bf16* lo = reinterpret_cast<const bf16*>(&lo4);
+    const bf16* hi = reinterpret_cast<const bf16*>(&hi4);
+    float a[8], c[8], ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < VPL; ++k) {
+    for (int k = 0; k < 8; ++k) {
         a[k] = __bfloat162float(lo[k]); c[k] = __bfloat162float(hi[k]);
         ss = fmaf(a[k], a[k], ss); ss = fmaf(c[k], c[k], ss);
     }
-    float scale = 1.f;
-    if (w != nullptr) {
-        ss = warp_sum(ss);
-        scale = 1.0f / sqrtf(ss / (float)D + eps);
-    }
-    const float* cs = cosv + (size_t)t * HALF + i0;
-    const float* sn = sinv + (size_t)t * HALF + i0;
 #pragma unroll
-    for (int k = 0; k < VPL; ++k) {
-        const float x0 = a[k] * scale * (w ? w[i0 + k] : 1.f);
-        const float x1 = c[k] * scale * (w ? w[i0 + HALF + k] : 1.f);
-        lo[k] = __float2bfloat16_rn(x0 * cs[k] - x1 * sn[k]);
-        hi[k] = __float2bfloat16_rn(x0 * sn[k] + x1 * cs[k]);
+    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!rotate) return;
+    const float scale = w != nullptr ? 1.0f / sqrtf(ss / (float)D + eps) : 1.f;
+    const float* csf = reinterpret_cast<const float*>(cs);
+    const float* snf = reinterpret_cast<const float*>(sn);
+    const float* wlf = reinterpret_cast<const float*>(wl);
+    const float* whf = reinterpret_cast<const float*>(wh);
+    uint4 olo, ohi;
+    bf16* ol = reinterpret_cast<bf16*>(&olo);
+    bf16* oh = reinterpret_cast<bf16*>(&ohi);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float x0 = a[k] * scale * (w != nullptr ? wlf[k] : 1.f);
+        const float x1 = c[k] * scale * (w != nullptr ? whf[k] : 1.f);
+        ol[k] = __float2bfloat16_rn(x0 * csf[k] - x1 * snf[k]);
+        oh[k] = __float2bfloat16_rn(x0 * snf[k] + x1 * csf[k]);
     }
-    if (VPL == 1) { dst[i0] = lo[0]; dst[i0 + HALF] = hi[0]; }
-    else if (VPL == 2) {
-        *reinterpret_cast<uint32_t*>(dst + i0) = *reinterpret_cast<uint32_t*>(lo);
-        *reinterpret_cast<uint32_t*>(dst + i0 + HALF) = *reinterpret_cast<uint32_t*>(hi);
-    } else {
-        *reinterpret_cast<uint2*>(dst + i0) = *reinterpret_cast<uint2*>(lo);
-        *reinterpret_cast<uint2*>(dst + i0 + HALF) = *reinterpret_cast<uint2*>(hi);
-    }
+    *reinterpret_cast<uint4*>(dst + i0) = olo;
+    *reinterpret_cast<uint4*>(dst + i0 + HALF) = ohi;
 }
 
 GG_API gg_qk_norm_rope_cache(const void* qkv, int dtype, void* q_out, const float* qw, const float* kw, float eps,
@@ -366,12 +369,15 @@ GG_API gg_qk_norm_rope_cache(const void* qkv, int dtype, void* q_out, const floa
     const int warps = 4;
     const long long total = (long long)ntok * (nq + 2 * nkv);
     const unsigned grid = (unsigned)((total + warps - 1) / warps);
-    const bool al = ((((uintptr_t)qkv) | ((uintptr_t)q_out) | ((uintptr_t)k_pool) | ((uintptr_t)v_pool)) & 15) == 0;
+    const bool al = ((((uintptr_t)qkv) | ((uintptr_t)q_out) | ((uintptr_t)k_pool) | ((uintptr_t)v_pool) |
+                      ((uintptr_t)cosv) | ((uintptr_t)sinv) | ((uintptr_t)qw) | ((uintptr_t)kw)) & 15) == 0;
     if (dtype == GG_BF16 && rot == d && al && (d == 64 || d == 128 || d == 256)) {
-#define GG_QK_VEC(V) gg_launch(qk_norm_rope_cache_vec_kernel<V>, dim3(grid), dim3(warps * 32), 0, stream, 1,  \
+        const int per_block = warps * (32 / (d / 16));          // heads a block of four warps handles
+        const unsigned vgrid = (unsigned)((total + per_block - 1) / per_block);
+#define GG_QK_VEC(D_) gg_launch(qk_norm_rope_cache_vec_kernel<D_>, dim3(vgrid), dim3(warps * 32), 0, stream, 1,  \
             (const bf16*)qkv, (bf16*)q_out, qw, kw, eps, cosv, sinv, positions, seq_of_token, page_table, max_pages, \
             page_size, (bf16*)k_pool, (bf16*)v_pool, ntok, nq, nkv)
-        if (d == 64) GG_QK_VEC(1); else if (d == 128) GG_QK_VEC(2); else GG_QK_VEC(4);
+        if (d == 64) GG_QK_VEC(64); else if (d == 128) GG_QK_VEC(128); else GG_QK_VEC(256);
 #undef GG_QK_VEC
         return gg_last_error();
     }

@@ -304,6 +304,58 @@ __device__ __forceinline__ void epilogue_row_256(uint32_t taddr, int gi, int tn,
         return;
     }
     float ss = 0.f;          // running sum of squares of the updated row over 128 columns
+    if (out_mode == OUT_F32_ACC && tn * BN + BN <= N && ((((uintptr_t)out) | ((uintptr_t)nio.out_xhat)) & 15) == 0 &&
+        (ldo & 3) == 0 && (N & 7) == 0) {
+        // Adding into the residual reads what is there: one thread's 16 columns at a time, every group would
+        // wait a whole trip to L2 for its 64 bytes (about 20 us per tile, in the open after a product's last
+        // tile).  So the old values of 64 columns are asked for at once, before the accumulator is read.
+        const bool stats = nio.out_ssq != nullptr;
+        const bool scaled = nio.in_ssq != nullptr;
+        const bool live = gi < M;
+        float* orow = (float*)out + (size_t)(live ? gi : 0) * ldo + tn * BN;
+        bf16* xrow = stats ? nio.out_xhat + (size_t)(live ? gi : 0) * N + tn * BN : nullptr;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+            float4 old[16];
+            if (live) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) old[j] = reinterpret_cast<const float4*>(orow + c0)[j];
+            }
+            uint32_t r[64];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) tmem_ld16(taddr + (uint32_t)(c0 + 16 * q), r + 16 * q);
+            tmem_ld_wait();
+            if (!live) continue;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t pk[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 o = old[4 * q + j];
+                    float4 v = make_float4(__uint_as_float(r[16 * q + 4 * j]), __uint_as_float(r[16 * q + 4 * j + 1]),
+                                           __uint_as_float(r[16 * q + 4 * j + 2]), __uint_as_float(r[16 * q + 4 * j + 3]));
+                    if (scaled) { v.x *= sc; v.y *= sc; v.z *= sc; v.w *= sc; }
+                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                    reinterpret_cast<float4*>(orow + c0 + 16 * q)[j] = v;
+                    if (stats) {
+                        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+                        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+                        pk[2 * j] = *reinterpret_cast<uint32_t*>(&a);
+                        pk[2 * j + 1] = *reinterpret_cast<uint32_t*>(&b);
+                    }
+                }
+                if (stats) {
+                    reinterpret_cast<uint4*>(xrow + c0 + 16 * q)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    reinterpret_cast<uint4*>(xrow + c0 + 16 * q)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                }
+            }
+            if (stats && (c0 & 64)) {            // a part of 128 columns is complete
+                nio.out_ssq[(size_t)gi * ((N + 127) / 128) + ((tn * BN + c0) >> 7)] = ss;
+                ss = 0.f;
+            }
+        }
+        return;
+    }
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 16) {
         if (tn * BN + c0 >= N) break;

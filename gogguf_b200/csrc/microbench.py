@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|attn|prefill_attn|sample] [--m 1,8,64] [--ctx 2048,8192]
+"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|gemm_layer|attn|prefill_attn|sample] [--m 1,8,64] [--ctx 2048,8192]
 
 Times single kernels the way a decode step runs them: forty launches captured in a CUDA graph and
 replayed, so that host launch cost is out of the picture and dependent launches overlap as they do
@@ -48,6 +48,39 @@ def gemm(ms) -> None:
                   f"{N * K * 2 / us / 1e6:6.2f} TB/s", flush=True)
         del ws
         torch.cuda.empty_cache()
+
+
+def gemm_layer(ms) -> None:
+    """The four products of a layer as the layer runs them: q/k/v and gate-up (+ SwiGLU) with the folded norm on
+    the way in, O and down adding into the residual and writing the next product's row statistics."""
+    from . import tcgen05_gemm as tc
+    dev = "cuda:0"
+    H, QKV, I = 4096, 6144, 12288
+    for M in ms:
+        resid = torch.randn(M, H, device=dev)
+        xh = resid.to(torch.bfloat16)
+        ssq = torch.rand(M, H // 128, device=dev) * 128
+        oss = torch.empty(M, H // 128, device=dev)
+        oxh = torch.empty(M, H, device=dev, dtype=torch.bfloat16)
+        act = torch.randn(M, I, device=dev).to(torch.bfloat16)
+        attn_out = torch.randn(M, H, device=dev).to(torch.bfloat16)
+        cases = (
+            ("qkv    norm in", QKV, H, lambda w, o: tc.gemm_tc_norm(xh, w, o, in_ssq=ssq, eps=1e-6),
+             torch.empty(M, QKV, device=dev, dtype=torch.bfloat16)),
+            ("o      add+stats", H, H, lambda w, o: tc.gemm_tc_norm(attn_out, w, o, accumulate=True, out_ssq=oss, out_xhat=oxh), resid),
+            ("gateup norm in, swiglu", 2 * I, H, lambda w, o: tc.gemm_tc_norm(xh, w, o, swiglu=True, in_ssq=ssq, eps=1e-6),
+             torch.empty(M, I, device=dev, dtype=torch.bfloat16)),
+            ("down   add+stats", H, I, lambda w, o: tc.gemm_tc_norm(act, w, o, accumulate=True, out_ssq=oss, out_xhat=oxh), resid),
+        )
+        for name, N, K, fn, out in cases:
+            nbuf = max(2, int(400e6 // (N * K * 2)) + 1)
+            ws = [(torch.randn(N, K, device=dev) * 0.01).to(torch.bfloat16) for _ in range(nbuf)]
+            us = _time_graph(lambda i: fn(ws[i % nbuf], out))
+            print(f"gemm_layer {name:24s} M={M:5d} {us:8.1f} us {2.0 * M * N * K / us / 1e6:7.1f} TFLOP/s "
+                  f"{N * K * 2 / us / 1e6:6.2f} TB/s", flush=True)
+            del ws
+            torch.cuda.empty_cache()
+        tc.check_status(torch.device(dev))
 
 
 def attn(ms, ctx_len: int = 2048, nq: int = 32, nkv: int = 8, d: int = 128, cluster: bool = True) -> None:
@@ -117,7 +150,7 @@ def sample(ms, V: int = 151936) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "prefill_attn", "sample"])
+    ap.add_argument("what", choices=["gemm", "gemm_layer", "attn", "prefill_attn", "sample"])
     ap.add_argument("--m", default="1,8,64", help="token counts (gemm), batch sizes (attn) or prompt lengths (prefill_attn)")
     ap.add_argument("--ctx", default="2048", help="attn: cached positions per sequence (comma separated)")
     ap.add_argument("--scratch", action="store_true", help="attn: splits merged by a second kernel instead of inside clusters")
@@ -127,7 +160,7 @@ def main() -> None:
         for c in a.ctx.split(","):
             attn(ms, ctx_len=int(c), cluster=not a.scratch)
     else:
-        {"gemm": gemm, "prefill_attn": prefill_attn, "sample": sample}[a.what](ms)
+        {"gemm": gemm, "gemm_layer": gemm_layer, "prefill_attn": prefill_attn, "sample": sample}[a.what](ms)
 
 
 if __name__ == "__main__":
