@@ -2,6 +2,7 @@
 """Measurement: Qwen3-8B-shaped random-weight model, bfloat16, one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+                    [--shape 8b|14b|32b] [--workload] [--prefill-lengths 256,1024]
 
 A "step" is one decode step of a batch: every sequence goes on by one token, sampled greedily on the
 device.  The timed region is exactly K steps after W warm-up steps, timed with CUDA events on the
@@ -16,6 +17,8 @@ launching stream.  One JSON line is printed:
                / time, against the measured HBM copy bandwidth
   points       decode tokens per second at batch 1 and 64
   config       every size, flat
+  workload     (--workload) the shape's own request mix through Context.generate: prefill and decode rates
+  prefill_sweep_ms  (--prefill-lengths) one prefill step per listed prompt length
 
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from the
 fallback figures of an earlier measurement on this pool.  The weights (16 GB) are far larger than
