@@ -371,6 +371,113 @@ __device__ __forceinline__ void epilogue_row_256(uint32_t taddr, int gi, int tn,
     }
 }
 
+// Epilogue of the CTA-pair form for the q/k/v projection of a prefill step (head size 128): the tile's 256
+// columns are heads 2 tn and 2 tn + 1 of token gi, all in this thread's row of tensor memory, so the per-head
+// RMSNorm is a sum over the thread's own columns and the rotation's pairs (i, i + 64) need no exchange.  q
+// goes to its buffer, k (normed, rotated) and v (raw) into the paged cache at the token's position, as in the
+// decode form (QkvIO).  Every thread of the warp reads tensor memory; rows beyond M and tokens of padding
+// write nothing.
+__device__ __forceinline__ void epilogue_row_qkv(uint32_t taddr, int gi, int tn, int M, const QkvIO& qio, float sc) {
+    const bool live = gi < M;
+    const int nheads = qio.nq + 2 * qio.nkv;
+    int b = -1, pos = 0, page = 0;
+    if (live) {
+        b = qio.seq_of_token[gi];
+        if (qio.k_pool != nullptr && b >= 0) {
+            pos = qio.positions[gi];
+            page = qio.page_table[(size_t)b * qio.max_pages + pos / qio.page_size];
+        }
+    }
+    const float* cs = qio.cosv + (size_t)(live ? gi : 0) * 64;
+    const float* sn = qio.sinv + (size_t)(live ? gi : 0) * 64;
+#pragma unroll 1
+    for (int hh = 0; hh < 2; ++hh) {
+        const int h = tn * 2 + hh;
+        if (h >= nheads) break;
+        const bool is_q = h < qio.nq, is_k = !is_q && h < qio.nq + qio.nkv;
+        const uint32_t tcol = taddr + (uint32_t)(hh * 128);
+        bf16* dst = nullptr;
+        if (live) {
+            if (is_q) {
+                dst = qio.q_out + ((size_t)gi * qio.nq + h) * 128;
+            } else if (qio.k_pool != nullptr && b >= 0) {
+                const int kvh = is_k ? h - qio.nq : h - qio.nq - qio.nkv;
+                dst = (is_k ? qio.k_pool : qio.v_pool) +
+                      (((size_t)page * qio.nkv + kvh) * qio.page_size + (pos % qio.page_size)) * 128;
+            }
+        }
+        if (!is_q && !is_k) {                      // value head: the sums as they are
+#pragma unroll 1
+            for (int c = 0; c < 128; c += 16) {
+                uint32_t r[16];
+                tmem_ld16(tcol + (uint32_t)c, r);
+                tmem_ld_wait();
+                if (dst == nullptr) continue;
+                uint32_t pk[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * sc, __uint_as_float(r[2 * j + 1]) * sc);
+                    pk[j] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                reinterpret_cast<uint4*>(dst + c)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                reinterpret_cast<uint4*>(dst + c)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            }
+            continue;
+        }
+        const float* w = is_q ? qio.qw : qio.kw;
+        float scale = sc;
+        if (w != nullptr) {
+            float ss = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 128; c += 16) {
+                uint32_t r[16];
+                tmem_ld16(tcol + (uint32_t)c, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) { const float v = __uint_as_float(r[j]) * sc; ss = fmaf(v, v, ss); }
+            }
+            scale = sc * (1.0f / sqrtf(ss * (1.0f / 128.0f) + qio.eps));
+        }
+#pragma unroll 1
+        for (int c = 0; c < 64; c += 16) {
+            uint32_t lo[16], hi[16];
+            tmem_ld16(tcol + (uint32_t)c, lo);
+            tmem_ld16(tcol + (uint32_t)(64 + c), hi);
+            tmem_ld_wait();
+            if (dst == nullptr) continue;
+            uint32_t pl[8], ph[8];
+#pragma unroll
+            for (int j4 = 0; j4 < 4; ++j4) {
+                const float4 c4 = *reinterpret_cast<const float4*>(cs + c + 4 * j4);
+                const float4 s4 = *reinterpret_cast<const float4*>(sn + c + 4 * j4);
+                float4 wl = make_float4(1.f, 1.f, 1.f, 1.f), wh = wl;
+                if (w != nullptr) {
+                    wl = *reinterpret_cast<const float4*>(w + c + 4 * j4);
+                    wh = *reinterpret_cast<const float4*>(w + 64 + c + 4 * j4);
+                }
+                const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
+                const float wlv[4] = {wl.x, wl.y, wl.z, wl.w}, whv[4] = {wh.x, wh.y, wh.z, wh.w};
+                float ol[4], oh[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const float x0 = __uint_as_float(lo[4 * j4 + t]) * scale * wlv[t];
+                    const float x1 = __uint_as_float(hi[4 * j4 + t]) * scale * whv[t];
+                    ol[t] = x0 * cc[t] - x1 * sv[t];
+                    oh[t] = x1 * cc[t] + x0 * sv[t];
+                }
+                __nv_bfloat162 a = __floats2bfloat162_rn(ol[0], ol[1]), bb = __floats2bfloat162_rn(ol[2], ol[3]);
+                pl[2 * j4] = *reinterpret_cast<uint32_t*>(&a); pl[2 * j4 + 1] = *reinterpret_cast<uint32_t*>(&bb);
+                a = __floats2bfloat162_rn(oh[0], oh[1]); bb = __floats2bfloat162_rn(oh[2], oh[3]);
+                ph[2 * j4] = *reinterpret_cast<uint32_t*>(&a); ph[2 * j4 + 1] = *reinterpret_cast<uint32_t*>(&bb);
+            }
+            reinterpret_cast<uint4*>(dst + c)[0] = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+            reinterpret_cast<uint4*>(dst + c)[1] = make_uint4(pl[4], pl[5], pl[6], pl[7]);
+            reinterpret_cast<uint4*>(dst + 64 + c)[0] = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+            reinterpret_cast<uint4*>(dst + 64 + c)[1] = make_uint4(ph[4], ph[5], ph[6], ph[7]);
+        }
+    }
+}
+
 // The end of a decode-style epilogue: a warp holds one token's 128 consecutive accumulator columns
 // [128 tile_a, 128 tile_a + 128), four per lane, already summed over the K splits and multiplied by the folded
 // norm's factor, and applies the output mode (bf16 or float32 store, float32 add with the row statistics of the
@@ -982,7 +1089,7 @@ template <int STAGES>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
     void* __restrict__ out, int out_mode, long long ldo, int M, int N, int K, int* __restrict__ status,
-    const NormIO nio, int splits, int kb_per_split, float* __restrict__ partial) {
+    const NormIO nio, int splits, int kb_per_split, float* __restrict__ partial, const QkvIO qio) {
     constexpr int BN = 256;                     // columns of the pair's tile (each CTA stages 128 of the B rows)
     constexpr int HALF_B_BYTES = 128 * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + HALF_B_BYTES;      // per CTA: 32 KB
@@ -1129,8 +1236,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
                             if (tn * BN + c0 + j < N) prow[c0 + j] = __uint_as_float(r[j]);
                     }
                 }
-            } else
-            epilogue_row_256(taddr, gi, tn, M, N, out, out_mode, ldo, nio, sc);
+            } else if (out_mode == OUT_QKV)
+                epilogue_row_qkv(taddr, gi, tn, M, qio, sc);
+            else
+                epilogue_row_256(taddr, gi, tn, M, N, out, out_mode, ldo, nio, sc);
             tc_fence_before();
             mbar_arrive_cluster(&acc_empty[buf], 0);     // 256 arrivals in the leader free the accumulator pair
         }
@@ -1204,7 +1313,7 @@ int pair_splits(int M, int N, int K) {
 }
 
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N,
-                int K, int* status, const NormIO& nio, int splits, float* partial, cudaStream_t stream) {
+                int K, int* status, const NormIO& nio, const QkvIO& qio, int splits, float* partial, cudaStream_t stream) {
     constexpr int STAGES = 6;
     constexpr int smem = STAGES * (A_BYTES + 128 * BK * 2) + 1024 + 256;
     static int sms = 0;
@@ -1225,7 +1334,7 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out
     const int used = (num_kb + per - 1) / per;           // no empty split
     if (used == 1) partial = nullptr;
     int rc = gg_launch2(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, stream, ta, tb, out, out_mode, ldo, M, N, K, status, nio,
-                        used, per, partial);
+                        used, per, partial, qio);
     if (rc != 0 || used == 1) return rc;
     return gg_launch(gemm_splitk_finish_kernel, dim3((N + 127) / 128, (M + 7) / 8), dim3(256), 0, stream, 1,
                      (const float*)partial, used, out, out_mode, ldo, M, N, nio);
@@ -1289,8 +1398,8 @@ static int gemm_tc_impl(const void* x, const void* w, void* out, int out_mode, i
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K % 8) != 0 || (ldx % 8) != 0 || ldx < K || out_mode < 0 || out_mode > 4) return GG_ERR_ARG;
     if (out_mode == OUT_QKV) {
-        // decode form only, one 128-wide head per weight tile; `out` is not used
-        if (M > 128 || qio.nq <= 0 || qio.nkv <= 0 || N != (qio.nq + 2 * qio.nkv) * 128 || qio.q_out == nullptr ||
+        // one 128-wide head per weight tile (decode form) or two per tile (CTA-pair form); `out` is not used
+        if (qio.nq <= 0 || qio.nkv <= 0 || N != (qio.nq + 2 * qio.nkv) * 128 || qio.q_out == nullptr ||
             qio.cosv == nullptr || qio.sinv == nullptr || qio.positions == nullptr || qio.seq_of_token == nullptr ||
             (qio.k_pool != nullptr && (qio.v_pool == nullptr || qio.page_table == nullptr || qio.page_size <= 0)))
             return GG_ERR_ARG;
@@ -1340,8 +1449,10 @@ static int gemm_tc_impl(const void* x, const void* w, void* out, int out_mode, i
             if ((rc = make_map(&tb, w, N, K, K, 128)) != 0) return rc;
             int ps = pair_splits(M, N, K);
             if (scratch == nullptr || scratch_elems < (long long)ps * M * N) ps = 1;     // no room for partial tiles
-            rc = launch_pair(ta, tb, out, out_mode, ldo, M, N, K, status, nio, ps, scratch, stream);
-        } else if (bn == 256) rc = launch_persistent(ta, tb, out, out_mode, ldo, M, N, K, status, nio, stream);
+            if (out_mode == OUT_QKV) ps = 1;             // the per-head epilogue needs the whole sums in tensor memory
+            rc = launch_pair(ta, tb, out, out_mode, ldo, M, N, K, status, nio, qio, ps, scratch, stream);
+        } else if (out_mode == OUT_QKV) rc = GG_ERR_ARG;       // only the CTA-pair form has the q/k/v epilogue
+        else if (bn == 256) rc = launch_persistent(ta, tb, out, out_mode, ldo, M, N, K, status, nio, stream);
         else rc = launch<128, 6, false, 1>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, false, status, nio, qio, stream);
     }
     if (rc != 0) return rc;
@@ -1393,7 +1504,7 @@ GG_API gg_gemm_tc_pair_scratch_elems(int M, int N, int K, long long* elems) {
     return 0;
 }
 
-// The q/k/v projection of a decode step (M <= 128 tokens, head size 128) with the per-head q/k RMSNorm,
+// The q/k/v projection of a step (head size 128; more than 128 tokens in the CTA-pair form) with the per-head q/k RMSNorm,
 // the rotation and the cache write in its epilogue: x[M, K] * w[(nq + 2 nkv) * 128, K]^T, rows of w being
 // all q heads, then all k heads, then all v heads.  See QkvIO for the outputs; in_ssq / in_parts / in_eps
 // as in gg_gemm_tc_norm (null: x is already normalised).  qw / kw null: no q/k norm.

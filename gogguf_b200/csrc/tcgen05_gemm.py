@@ -47,6 +47,13 @@ def pair_scratch_elems(M: int, N: int, K: int) -> int:
     return int(n.value)
 
 
+def qkv_rope_takes(m: int) -> bool:
+    """Does `gemm_tc_qkv_rope` take m tokens?  Up to 128 always (decode form); more in the CTA-pair form, which
+    GOGGUF_B200_GEMM_PAIR=0 switches off."""
+    import os
+    return m <= 128 or os.environ.get("GOGGUF_B200_GEMM_PAIR", "1") != "0"
+
+
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """Rows in blocks of 64 gate rows then their 64 up rows: the layout the fused SwiGLU epilogue reads."""
     I, K = gate.shape
@@ -143,13 +150,14 @@ def gemm_tc_qkv_rope(x: torch.Tensor, w: torch.Tensor, m: int, q_out: torch.Tens
                      positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor, page_size: int,
                      k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], nq: int, nkv: int,
                      in_ssq: Optional[torch.Tensor] = None, in_eps: float = 0.0) -> None:
-    """The q/k/v projection of a decode step (m <= 128 tokens, head size 128) with the per-head q/k RMSNorm,
+    """The q/k/v projection of a step (head size 128; any m, see `qkv_rope_takes`) with the per-head q/k RMSNorm,
     the rotation and the cache write in the product's epilogue (csrc/gemm_tcgen05.cu, gg_gemm_tc_qkv_rope)."""
     N, K = w.shape
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16:
         raise KernelError("gemm_tc_qkv_rope takes bfloat16 operands")
-    if N != (nq + 2 * nkv) * 128 or m > 128 or q_out.numel() < m * nq * 128 or not q_out.is_contiguous():
-        raise KernelError("gemm_tc_qkv_rope: head size 128, at most 128 tokens, q_out [m, nq * 128]")
+    if N != (nq + 2 * nkv) * 128 or not qkv_rope_takes(m) or q_out.numel() < m * nq * 128 or not q_out.is_contiguous():
+        raise KernelError("gemm_tc_qkv_rope: head size 128, q_out [m, nq * 128]; more than 128 tokens only in the "
+                          "CTA-pair form")
     if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape[-1] != 64 or sin.shape[-1] != 64 \
             or not cos.is_contiguous() or not sin.is_contiguous():
         raise KernelError("gemm_tc_qkv_rope: cos and sin are float32 [m, 64]")

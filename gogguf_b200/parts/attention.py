@@ -17,6 +17,7 @@ import torch
 from ..cache.sequence_cache import KVRequest, KVView
 from ..config.spec import PartSpec
 from ..csrc import kernels as K
+from ..csrc import tcgen05_gemm
 from ..weights.loader import TensorDecl
 from .base import Linear, Runtime, StepContext
 from .registry import POSITIONS, lookup, register_mixer
@@ -101,8 +102,8 @@ class AttentionMixer:
         o = ctx.ws.get("attn_out", (T, nq * d), dt)
         cos, sin = self.position.tables(ctx)
         table = ctx.page_tables[cache.group]
-        if self._fused_rope and T <= 128:
-            # few tokens (decode): norm, rotation and cache write happen in the projection's epilogue
+        if self._fused_rope and tcgen05_gemm.qkv_rope_takes(T):
+            # norm, rotation and cache write happen in the projection's epilogue
             self.qkv.qkv_rope(h, T, q_out=q, qw=self.q_norm, kw=self.k_norm, eps=self.eps, cos=cos, sin=sin,
                               positions=ctx.positions, seq_of_token=ctx.seq_of_token, page_table=table,
                               page_size=cache.page_size, k_pool=cache.k if writes_cache else None,
