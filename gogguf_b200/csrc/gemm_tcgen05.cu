@@ -27,8 +27,8 @@
 // Further down in this file: the persistent prefill forms (one CTA per SM on 128 x 256 tiles, and CTA pairs
 // on 256 x 256 tiles with cta_group::2, which split K over work items when a product has fewer tiles than
 // pairs), and what the epilogues fuse: the residual add, SwiGLU over interleaved gate/up rows, an RMSNorm
-// folded in on either side (NormIO), and for the q/k/v product of a decode step the per-head norm, the
-// rotation and the cache write (QkvIO).
+// folded in on either side (NormIO), and for the q/k/v product (decode form and CTA pairs) the per-head norm,
+// the rotation and the cache write (QkvIO).
 //
 // Every mbarrier wait is bounded; a wait that runs out records a code in the status word, raises
 // the CTA's abort flag, and all roles fall through to the common exit, which lets copies in flight
@@ -151,8 +151,8 @@ struct NormIO {
     bf16* out_xhat;
 };
 
-// The q/k/v projection of an attention layer with what follows it fused into the epilogue (decode form,
-// head size 128 = one head per 128-row weight tile): per-head RMSNorm of q and k with one shared weight
+// The q/k/v projection of an attention layer with what follows it fused into the epilogue (head size 128:
+// one head per 128-row weight tile of the decode form, two per tile of the CTA-pair form): per-head RMSNorm of q and k with one shared weight
 // each, rotation of pairs (i, i + 64) by the step's cos/sin tables, q to its buffer, k (normed, rotated)
 // and v (raw) into the paged cache at the token's position.  Padding tokens (seq_of_token < 0) write
 // nothing to the cache; k_pool == null writes no cache at all.
