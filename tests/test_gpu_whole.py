@@ -138,3 +138,33 @@ def test_decode_projection_does_the_per_head_work_when_the_head_size_is_128(tmp_
         cache.close(slot)
     assert counts["0"] - counts["1"] == len(model.blocks)       # one kernel a layer less
     assert rel_err(logits["1"], logits["0"]) < 2e-2
+
+
+def test_prefill_projection_does_the_per_head_work_too(tmp_path_factory, monkeypatch):
+    """More than 128 tokens: the CTA-pair form of the q/k/v product has the same epilogue, so a layer of a
+    prompt is five kernels as well; the logits of every position agree with the separate kernel's."""
+    from gogguf_b200.csrc import build
+    from gogguf_b200.engine import Model, StepEntry, Stepper
+    if os.environ.get("GOGGUF_B200_GEMM_PAIR", "1") == "0":
+        pytest.skip("the single-CTA prefill form has no q/k/v epilogue")
+    folder = make_folder(tmp_path_factory.getbasetemp(), "L", "bfloat16", scale=4.0)
+    cfg, w = read_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], n, 60 + n) for n in (300, 131)]
+    counts, logits = {}, {}
+    for fuse in ("1", "0"):
+        monkeypatch.setenv("GOGGUF_B200_FUSE_QKV_ROPE", fuse)
+        model = Model.load(folder, dtype="bfloat16")
+        cache = model.new_cache(1024)
+        st = Stepper(model, cache)
+        slots = [cache.open(), cache.open()]
+        st.step([StepEntry(slots[0], prompts[0][:5], want=[4])])        # position 0 is not where the prompt's rest starts
+        n0 = build.launch_count()
+        logits[fuse] = st.step([StepEntry(slots[0], prompts[0][5:], want=list(range(295))),
+                                StepEntry(slots[1], prompts[1], want=list(range(131)))]).clone()
+        counts[fuse] = build.launch_count() - n0
+        for s_ in slots:
+            cache.close(s_)
+    assert counts["0"] - counts["1"] == len(model.blocks)       # one kernel a layer less
+    assert rel_err(logits["1"], logits["0"]) < 2e-2
+    want = torch.cat([plain.forward(cfg, w, prompts[0], wide=True)[5:], plain.forward(cfg, w, prompts[1], wide=True)])
+    assert rel_err(logits["1"], want) < TOL_BF16
