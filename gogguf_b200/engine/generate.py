@@ -18,7 +18,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence, Tuple
 
-from ..sampling.sampler import Sampler, SamplerConfig
+from ..sampling.sampler import SamplerConfig, make_sampler
 from .step import StepEntry
 
 
@@ -26,7 +26,7 @@ from .step import StepEntry
 class GenerateParams:
     """pkg/runtime GenerateParams as used by session.go:133-159."""
     max_tokens: int = 128
-    sampler: SamplerConfig = field(default_factory=SamplerConfig)
+    sampler: object = field(default_factory=SamplerConfig)   # a SamplerConfig, or a function of a row's logits
     repeat_penalty: float = 1.0
     repeat_last_n: int = 64
     stop_token_ids: Optional[Sequence[int]] = None     # None: the model's own (eos_token_id)
@@ -158,7 +158,7 @@ class Generator:
                    held=None) -> None:
         held = held or {}
         stop = set(self.default_stop if params.stop_token_ids is None else params.stop_token_ids)
-        sampler = Sampler(params.sampler, params.repeat_penalty, params.repeat_last_n)
+        sampler = make_sampler(params.sampler, params.repeat_penalty, params.repeat_last_n)
         cache = self.cache
         slots, cached = {}, {}
         generated = {i: [] for i in batch}
@@ -306,7 +306,7 @@ class GenerationSession:
         key = (params.sampler, params.repeat_penalty, params.repeat_last_n)
         sampler = self._samplers.get(key)
         if sampler is None:
-            sampler = self._samplers[key] = Sampler(params.sampler, params.repeat_penalty, params.repeat_last_n)
+            sampler = self._samplers[key] = make_sampler(params.sampler, params.repeat_penalty, params.repeat_last_n)
         live = self._live
         hist = [self.prompts[i] + self.generated[i] for i in live] if sampler.penalised else None
         nxt = sampler.sample(self._logits, streams=live, steps=[len(self.generated[i]) for i in live], histories=hist)

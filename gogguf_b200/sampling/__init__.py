@@ -1,4 +1,5 @@
 """Sampling: configuration, host chain, device kernels."""
-from .sampler import Sampler, SamplerConfig, apply_repeat_penalty, greedy, sample_host, uniform01
+from .sampler import (FunctionSampler, Sampler, SamplerConfig, apply_repeat_penalty, greedy, make_sampler,
+                      sample_host, uniform01)
 
-__all__ = ["Sampler", "SamplerConfig", "apply_repeat_penalty", "greedy", "sample_host", "uniform01"]
+__all__ = ["FunctionSampler", "Sampler", "SamplerConfig", "make_sampler", "apply_repeat_penalty", "greedy", "sample_host", "uniform01"]

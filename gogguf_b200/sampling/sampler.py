@@ -273,3 +273,45 @@ class Sampler:
                 apply_repeat_penalty(row, histories[r], self.repeat_penalty, self.repeat_last_n)
             res.append(sample_host(row, self.cfg, us[r]))
         return res
+
+
+class FunctionSampler:
+    """A caller's own sampling function in the place of the chain: `fn(logits) -> id`, with the row's float32
+    logits as a numpy array (sampler.Func, pkg/sampler/temperature.go:9; GenerateParams.Sampler,
+    pkg/runtime/context.go:15).  The repeat penalty is applied before the call, as for the chain
+    (session.go:83-96).  The rows come to the host every step, so the loop does not run ahead of it."""
+
+    device_only = False
+
+    def __init__(self, fn, repeat_penalty: float = 1.0, repeat_last_n: int = 64):
+        self.fn = fn
+        self.repeat_penalty = float(repeat_penalty)
+        self.repeat_last_n = int(repeat_last_n) if repeat_last_n else 64
+
+    @property
+    def penalised(self) -> bool:
+        return self.repeat_penalty > 0 and self.repeat_penalty != 1
+
+    def begin(self, streams, prompts, device) -> None:
+        pass
+
+    def sample(self, logits: torch.Tensor, streams: Sequence[int], steps: Sequence[int],
+               histories: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
+        rows = len(streams)
+        host = logits[:rows].detach().to("cpu", torch.float32).numpy()
+        res = []
+        for r in range(rows):
+            row = host[r].copy()
+            if self.penalised and histories is not None:
+                apply_repeat_penalty(row, histories[r], self.repeat_penalty, self.repeat_last_n)
+            res.append(int(self.fn(row)))
+        return res
+
+
+def make_sampler(sampler, repeat_penalty: float = 1.0, repeat_last_n: int = 64):
+    """The sampler of a request: a `SamplerConfig` gives the chain, a function is called as it is."""
+    if isinstance(sampler, SamplerConfig):
+        return Sampler(sampler, repeat_penalty, repeat_last_n)
+    if callable(sampler):
+        return FunctionSampler(sampler, repeat_penalty, repeat_last_n)
+    raise TypeError(f"a sampler is a SamplerConfig or a function of a row of logits, not {type(sampler).__name__}")

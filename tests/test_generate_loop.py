@@ -256,3 +256,40 @@ def test_session_ends_a_sequence_at_the_context_and_frees_slots_on_errors():
     with pytest.raises(ValueError):
         GenerationSession(gen(ScriptedStepper(max_tokens=64)), [[1] * 40, [2] * 40])      # two pages needed, one there
     assert st.cache.live_slots == 0
+
+
+# ----------------------------------------------------------------------------- a caller's own sampler
+def test_a_function_can_take_the_samplers_place():
+    """GenerateParams.sampler may be a function of a row's logits (sampler.Func of the reference): it is
+    called once per live sequence and step, after the repeat penalty, and an id below 0 ends the sequence."""
+    import numpy as np
+    import gogguf_b200 as gg
+    seen = []
+
+    def second_best(row):
+        assert isinstance(row, np.ndarray) and row.dtype == np.float32 and row.shape == (V,)
+        seen.append(int(np.argmax(row)))
+        return int(np.argsort(row)[-2])             # some id whose logit is 0
+
+    st = ScriptedStepper()
+    out = gen(st).generate([[1], [9]], GenerateParams(max_tokens=3, sampler=second_best, stop_token_ids=[]))
+    assert seen[:2] == [2, 10] and len(seen) == 6
+    assert all(len(r.tokens) == 3 for r in out)
+    # gg.Greedy is such a function (gogguf.Greedy)
+    out = gen(ScriptedStepper()).generate([[1]], GenerateParams(max_tokens=3, sampler=gg.Greedy, stop_token_ids=[]))
+    assert out[0].tokens == [2, 3, 4]
+    # the repeat penalty reaches the function's logits: token 2's logit 5.0 is divided by 2.5
+    def look(row):
+        look.row = row.copy()
+        return 7
+    gen(ScriptedStepper()).generate([[3, 1]], GenerateParams(max_tokens=1, sampler=look, repeat_penalty=2.5,
+                                                             stop_token_ids=[]))
+    assert look.row[2] == 5.0                       # 2 is not in the history
+    gen(ScriptedStepper()).generate([[2, 1]], GenerateParams(max_tokens=1, sampler=look, repeat_penalty=2.5,
+                                                             stop_token_ids=[]))
+    assert look.row[2] == 2.0
+    # an id below 0 ends the sequence (session.go:58-60)
+    out = gen(ScriptedStepper()).generate([[1]], GenerateParams(max_tokens=5, sampler=lambda row: -1))
+    assert out[0].tokens == [] and out[0].finish_reason == "stop"
+    with pytest.raises(TypeError):
+        gen(ScriptedStepper()).generate([[1]], GenerateParams(sampler="greedy"))
