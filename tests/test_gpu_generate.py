@@ -29,6 +29,9 @@ def test_greedy_generation_through_the_entry_point(tmp_path_factory):
     # a single prompt gives a single result
     one = ctx.generate(prompts[0], gg.GenerateParams(max_tokens=3, stop_token_ids=[]))
     assert one.tokens == ref0[:3]
+    # a function of the row's logits in the sampler's place (gogguf.Greedy is one)
+    out = ctx.generate(prompts, gg.GenerateParams(max_tokens=4, stop_token_ids=[], sampler=gg.Greedy))
+    assert [r.tokens for r in out] == [ref0[:4], ref1[:4]]
     ctx.cache.check()
     assert ctx.cache.live_slots == 0
 
