@@ -1,7 +1,7 @@
 """Command line, in the manner of the reference's `gogguf` (cmd/gogguf/main.go:21-51):
 
     gogguf_b200 run -m DIR -p "1 2 3" [-p "4 5"] [-n 128] [--temp 0] [--top-k 0] [--top-p 1] [--min-p 0]
-                    [--repeat-penalty 1] [--repeat-last-n 64] [--seed 0] [--dtype bfloat16]
+                    [--repeat-penalty 1] [--repeat-last-n 64] [--seed 0] [--dtype bfloat16] [-i]
     gogguf_b200 info -m DIR
     gogguf_b200 inspect DIR
     gogguf_b200 random -c CONFIG.json -o DIR [--seed 0] [--dtype bfloat16] [--std S] [--norm-std S]
@@ -9,7 +9,8 @@
 
 `run` keeps the reference's option names and defaults (cmd/gogguf/run.go:17-34).  A prompt is a list
 of token ids (the tokenizer is outside this library); several -p make a batch.  Dropped: -hf
-(network), --chat/--thinking/-i (text templates), -ngl (the whole model is always on the GPU).
+(network), --chat/--thinking (text templates), -ngl (the whole model is always on the GPU).  -i is the
+reference's REPL on token ids: one conversation, a line of new ids per turn.
 `info` prints what the reference's info prints (cmd/gogguf/info.go:27-44), `inspect` every
 configuration key and tensor (cmd/gogguf/inspect.go:13-41).  `random` is the random-weights mode.
 """
@@ -39,8 +40,8 @@ def cmd_run(a) -> int:
     if a.prompt_file:
         with open(a.prompt_file) as f:
             prompts += [_ids(line) for line in f if line.strip()]
-    if not prompts:
-        raise SystemExit("give a prompt with -p (token ids) or --prompt-file")
+    if not prompts and not a.i:
+        raise SystemExit("give a prompt with -p (token ids) or --prompt-file, or use -i")
     engine = gg.load(a.m, gg.LoadOptions(dtype=a.dtype, max_tokens=a.cache_tokens, max_batch=a.max_batch))
     ctx = engine.new_context()
     params = gg.GenerateParams(
@@ -48,10 +49,43 @@ def cmd_run(a) -> int:
         sampler=gg.SamplerConfig(temp=a.temp, top_k=a.top_k, top_p=a.top_p, min_p=a.min_p, seed=a.seed),
         repeat_penalty=a.repeat_penalty, repeat_last_n=a.repeat_last_n,
         stop_token_ids=None if a.stop_ids is None else _ids(a.stop_ids))
+    if a.i:
+        return run_interactive(ctx, params, prompts, sys.stdin, sys.stdout)
     for r in ctx.generate(prompts, params):
         print(" ".join(str(t) for t in r.tokens))
         print(f"# prompt {r.prompt_tokens} tokens, generated {len(r.tokens)}, finish: {r.finish_reason}",
               file=sys.stderr)
+    return 0
+
+
+def run_interactive(ctx, params, first: List[List[int]], inp, out) -> int:
+    """The reference's REPL (runInteractive, cmd/gogguf/run.go:115-175) on token ids: every line is the new
+    ids of a turn; they are added to the conversation so far (ids given and ids made), only they are run, and
+    the turn's ids are printed.  An empty line or the end of the input ends it; `/clear` starts the
+    conversation again (run.go:135-140).  A prompt given with -p is the first turn."""
+    print("interactive: a line of token ids per turn; an empty line ends, /clear starts again", file=sys.stderr)
+    conv = ctx.new_conversation()
+    turns = list(first[:1])
+    try:
+        while True:
+            if turns:
+                new = turns.pop(0)
+            else:
+                print("> ", end="", file=sys.stderr, flush=True)
+                line = inp.readline()
+                if not line or not line.strip():
+                    break
+                if line.strip() == "/clear":
+                    conv.reset()
+                    print("conversation cleared", file=sys.stderr)
+                    continue
+                new = _ids(line)
+            r = conv.generate(conv.tokens + new, params)
+            print(" ".join(str(t) for t in r.tokens), file=out, flush=True)
+            print(f"# conversation {conv.token_count()} tokens, generated {len(r.tokens)}, finish: {r.finish_reason}",
+                  file=sys.stderr)
+    finally:
+        conv.close()
     return 0
 
 
@@ -137,6 +171,7 @@ def build_parser() -> argparse.ArgumentParser:
     r.add_argument("-m", help="model folder (config.json + model.safetensors)")
     r.add_argument("-p", action="append", help="prompt as token ids; repeat for a batch")
     r.add_argument("--prompt-file", help="one prompt of token ids per line")
+    r.add_argument("-i", action="store_true", help="interactive: a conversation, one line of token ids per turn")
     r.add_argument("-n", type=int, default=128, help="most new tokens")
     r.add_argument("--temp", type=float, default=0.0, help="temperature (0 = greedy)")
     r.add_argument("--top-k", type=int, default=0, help="top-k sampling (0 = off)")

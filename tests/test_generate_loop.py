@@ -293,3 +293,25 @@ def test_a_function_can_take_the_samplers_place():
     assert out[0].tokens == [] and out[0].finish_reason == "stop"
     with pytest.raises(TypeError):
         gen(ScriptedStepper()).generate([[1]], GenerateParams(sampler="greedy"))
+
+
+def test_interactive_mode_is_one_conversation_with_a_line_of_ids_per_turn():
+    import io
+    from gogguf_b200.api import Conversation
+    from gogguf_b200.cli import run_interactive
+    st = ScriptedStepper()
+
+    class Ctx(_Ctx):
+        def new_conversation(self):
+            return Conversation(self)
+
+    ctx = Ctx(st)
+    out = io.StringIO()
+    inp = io.StringIO("9 10\n/clear\n5\n\n7\n")          # the empty line ends it: "7" is never read
+    rc = run_interactive(ctx, GenerateParams(max_tokens=2, stop_token_ids=[]), [[1, 2, 3]], inp, out)
+    assert rc == 0
+    assert out.getvalue().splitlines() == ["4 5", "11 12", "6 7"]
+    # first turn: the prompt; second: 5 (made, not yet run), 9 and 10; after /clear the slot starts again
+    assert [n for step in st.steps for _, n in step] == [3, 1, 3, 1, 1, 1]
+    assert st.cache.live_slots == 0
+    st.cache.check()
