@@ -21,6 +21,13 @@ slots, pages and groups are this library's own.
 
 Capacity is counted in tokens: `max_tokens` is the most that live sequences may hold, each
 sequence's count rounded up to a whole page.
+
+The kinds of request are an open set.  Each request class is registered with the *store* class that
+holds what it asks for (`register_cache_store`); `SequenceCache` looks the store up by the request's
+type, lets requests with equal `group_key` share one store, and talks to every store through the
+`CacheStore` interface only.  A per-token cache that is not a K/V pair of equal head size subclasses
+`PagedStore` (page bookkeeping, page tables) and allocates its own tensors; a per-sequence state of
+another shape subclasses `CacheStore` directly.
 """
 from __future__ import annotations
 
@@ -47,24 +54,94 @@ class StateRequest:
     dtype: torch.dtype = torch.float32
 
 
-Request = Union[KVRequest, StateRequest, None]
+Request = Optional[object]       # an instance of any registered request class, or None
+
+STORES: Dict[type, type] = {}     # request class -> store class
 
 
-class KVGroup:
-    """Storage and page bookkeeping of the layers that share one `KVRequest`."""
+def register_cache_store(request_cls: type):
+    """Class decorator: instances of `request_cls` are held by the decorated `CacheStore` class."""
+    def deco(store_cls: type) -> type:
+        if request_cls in STORES and STORES[request_cls] is not store_cls:
+            raise ValueError(f"cache requests of type {request_cls.__name__} already have a store")
+        STORES[request_cls] = store_cls
+        return store_cls
+    return deco
 
-    def __init__(self, request: KVRequest, entries: List[int], n_pages: int, page_size: int,
-                 dtype: torch.dtype, device):
+
+class CacheStore:
+    """What the cache asks of the storage behind one kind of request.
+
+    Built as ``Store(request, entries, n_pages=..., page_size=..., max_slots=..., dtype=..., device=...)``
+    for the schedule entries `entries` that share it.  The defaults describe storage that does not
+    grow with the sequence; a paged store overrides the page methods (see `PagedStore`).
+    """
+
+    paged = False                 # True: has `pages`, `seq_pages`, `table_row`; gets a page table every step
+
+    @staticmethod
+    def group_key(request) -> Optional[object]:
+        """Requests with equal keys share one store; None: every entry gets a store of its own."""
+        return None
+
+    def view(self, entry: int):
+        """What the mixer of schedule entry `entry` is handed each step."""
+        raise NotImplementedError
+
+    def open(self, slot: int) -> None:            # a slot starts a new sequence
+        pass
+
+    def release(self, slot: int) -> None:         # the sequence is over (or starts again)
+        pass
+
+    def pages_needed(self, slot: int, new_len: int) -> int:
+        return 0
+
+    def reserve(self, slot: int, new_len: int) -> None:
+        pass
+
+    def trim(self, slot: int, length: int) -> None:   # after a step's commit
+        pass
+
+    def can_shorten(self, slot: int, length: int) -> bool:
+        """Can the sequence be cut back to its first `length` tokens without running them again?"""
+        return True
+
+    def shorten(self, slot: int, length: int) -> None:
+        pass
+
+    def check(self, is_open) -> None:             # bookkeeping invariants, for tests
+        pass
+
+
+class PagedStore(CacheStore):
+    """Page bookkeeping for per-token storage: a free list of pages and, per slot, the pages that hold
+    its positions.  A subclass allocates its tensors (indexed ``[layer_in_store][page]...``) and
+    implements `view`; an optional `window` gives pages back once every position in them has left it."""
+
+    paged = True
+
+    def __init__(self, request, entries: List[int], n_pages: int, page_size: int, window: Optional[int] = None):
         self.request = request
-        self.entries = list(entries)          # schedule entries that own a layer of this group
+        self.entries = list(entries)          # schedule entries that own a layer of this store
         self.page_size = page_size
         self.n_pages = n_pages
-        shape = (len(entries), n_pages, request.num_kv_heads, page_size, request.head_dim)
-        # zero-filled once: a page that is handed out again holds old finite numbers, never NaN patterns
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.window = window
         self.pages = FreeList(n_pages, "page")
         self.seq_pages: Dict[int, List[int]] = {}   # slot -> page id per page index (-1 once given back)
+        self.index = -1                        # position among the cache's paged stores (set by the cache):
+        #                                        a step's page table of this store is ctx.page_tables[index]
+
+    def check(self, is_open) -> None:
+        self.pages.check()
+        held = [p for pl in self.seq_pages.values() for p in pl if p >= 0]
+        if len(held) != len(set(held)):
+            raise CacheError("a page is held by two sequences")
+        if len(held) != self.pages.held_count:
+            raise CacheError(f"{self.pages.held_count} pages are held but sequences list {len(held)}")
+        for s in self.seq_pages:
+            if not is_open(s):
+                raise CacheError(f"pages are listed for slot {s}, which is not open")
 
     def pages_needed(self, slot: int, new_len: int) -> int:
         have = len(self.seq_pages.get(slot, ()))
@@ -78,7 +155,7 @@ class KVGroup:
 
     def trim(self, slot: int, length: int) -> None:
         """Windowed group: give back pages all of whose positions are below length - window + 1."""
-        w = self.request.window
+        w = self.window
         if w is None:
             return
         first_needed = length - w + 1
@@ -92,7 +169,7 @@ class KVGroup:
 
     def can_shorten(self, slot: int, length: int) -> bool:
         """Are the positions that a token at position `length` reads still held?"""
-        w = self.request.window
+        w = self.window
         if w is None:
             return True
         pl = self.seq_pages.get(slot, [])
@@ -122,6 +199,28 @@ class KVGroup:
         return [p if p >= 0 else 0 for p in pl] + [0] * (width - len(pl))
 
 
+
+@register_cache_store(KVRequest)
+class KVGroup(PagedStore):
+    """Storage of the layers that share one `KVRequest`: pools ``k, v [layer][page][kv_head][page_size][head_dim]``."""
+
+    @staticmethod
+    def group_key(request: KVRequest):
+        return request
+
+    def __init__(self, request: KVRequest, entries: List[int], n_pages: int, page_size: int,
+                 dtype: torch.dtype, device, max_slots: int = 0):
+        super().__init__(request, entries, n_pages, page_size, window=request.window)
+        shape = (len(entries), n_pages, request.num_kv_heads, page_size, request.head_dim)
+        # zero-filled once: a page that is handed out again holds old finite numbers, never NaN patterns
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
+
+    def view(self, entry: int) -> "KVView":
+        li = self.entries.index(entry)
+        return KVView(group=self.index, k=self.k[li], v=self.v[li], page_size=self.page_size, request=self.request)
+
+
 @dataclass
 class KVView:
     """What a mixer gets for one scheduled layer: its slices of the group's pools."""
@@ -136,6 +235,28 @@ class KVView:
 class StateView:
     state: torch.Tensor        # [max_slots, *shape]
     request: StateRequest
+
+
+@register_cache_store(StateRequest)
+class StateStore(CacheStore):
+    """A fixed-size state per sequence for one layer: ``[max_slots, *shape]``, zeroed when a slot is
+    opened.  All tokens are folded into it, so a sequence cannot be cut back without running it again."""
+
+    def __init__(self, request: StateRequest, entries: List[int], n_pages: int, page_size: int,
+                 dtype: torch.dtype, device, max_slots: int = 0):
+        self.request = request
+        self.entries = list(entries)
+        self.state = torch.zeros((max_slots,) + tuple(request.shape), dtype=request.dtype, device=device)
+        self._view = StateView(state=self.state, request=request)
+
+    def view(self, entry: int) -> StateView:
+        return self._view
+
+    def open(self, slot: int) -> None:
+        self.state[slot].zero_()
+
+    def can_shorten(self, slot: int, length: int) -> bool:
+        return False
 
 
 class SequenceCache:
@@ -154,26 +275,39 @@ class SequenceCache:
         self.slots = FreeList(self.max_slots, "slot")
         self.lengths: List[int] = [0] * self.max_slots
 
-        self.groups: List[KVGroup] = []
-        self._views: Dict[int, Union[KVView, StateView, None]] = {}
-        by_request: Dict[KVRequest, List[int]] = {}
+        self.stores: List[CacheStore] = []        # every store, paged or not
+        self.groups: List[PagedStore] = []        # the paged ones, in the order of their page tables
+        self._views: Dict[int, object] = {}
+        shared: Dict[Tuple[type, object], List[int]] = {}
+        own: List[Tuple[type, object, List[int]]] = []
         for i, (rq, src) in enumerate(zip(requests, cache_of)):
-            if src is None and isinstance(rq, KVRequest):
-                by_request.setdefault(rq, []).append(i)
-        for rq, entries in by_request.items():
-            g = KVGroup(rq, entries, self.n_pages, page_size, dtype, self.device)
-            gi = len(self.groups)
-            self.groups.append(g)
-            for li, e in enumerate(entries):
-                self._views[e] = KVView(group=gi, k=g.k[li], v=g.v[li], page_size=page_size, request=rq)
-        self.states: Dict[int, torch.Tensor] = {}
-        for i, (rq, src) in enumerate(zip(requests, cache_of)):
-            if src is None and isinstance(rq, StateRequest):
-                st = torch.zeros((self.max_slots,) + tuple(rq.shape), dtype=rq.dtype, device=self.device)
-                self.states[i] = st
-                self._views[i] = StateView(state=st, request=rq)
-            elif src is None and rq is None:
+            if src is not None:
+                continue
+            if rq is None:
                 self._views[i] = None
+                continue
+            store_cls = STORES.get(type(rq))
+            if store_cls is None:
+                raise CacheError(f"schedule entry {i}: no store is registered for cache requests of type "
+                                 f"{type(rq).__name__} (registered: {sorted(c.__name__ for c in STORES)})")
+            key = store_cls.group_key(rq)
+            if key is None:
+                own.append((store_cls, rq, [i]))
+            else:
+                shared.setdefault((store_cls, key), []).append(i)
+        built = [(cls, requests[entries[0]], entries) for (cls, _), entries in shared.items()] + own
+        for store_cls, rq, entries in sorted(built, key=lambda b: b[2][0]):
+            st = store_cls(rq, entries, n_pages=self.n_pages, page_size=page_size, dtype=dtype,
+                           device=self.device, max_slots=self.max_slots)
+            self.stores.append(st)
+            if st.paged:
+                st.index = len(self.groups)
+                self.groups.append(st)
+            for e in entries:
+                self._views[e] = st.view(e)
+        # fixed-size states by schedule entry (kept for callers that look at them directly)
+        self.states: Dict[int, torch.Tensor] = {e: st.state for st in self.stores if isinstance(st, StateStore)
+                                                for e in st.entries}
         for i, src in enumerate(cache_of):
             if src is not None:
                 if self._views.get(src) is None:
@@ -185,16 +319,16 @@ class SequenceCache:
         """A slot for a new sequence: length 0, state zeroed, no pages yet."""
         s = self.slots.take()
         self.lengths[s] = 0
-        for st in self.states.values():
-            st[s].zero_()
+        for st in self.stores:
+            st.open(s)
         return s
 
     def close(self, slot: int) -> None:
         """Give back a sequence's slot and pages.  Nothing is cleared: reads are bounded by lengths."""
         if not self.slots.is_held(slot):
             raise CacheError(f"slot {slot} is not open")
-        for g in self.groups:
-            g.release(slot)
+        for st in self.stores:
+            st.release(slot)
         self.lengths[slot] = 0
         self.slots.give(slot)
 
@@ -214,10 +348,10 @@ class SequenceCache:
             raise CacheError(f"slot {slot} holds {cur} tokens, cannot be cut to {length}")
         if length == cur:
             return True
-        if self.states or not all(g.can_shorten(slot, length) for g in self.groups):
+        if not all(st.can_shorten(slot, length) for st in self.stores):
             return False
-        for g in self.groups:
-            g.shorten(slot, length)
+        for st in self.stores:
+            st.shorten(slot, length)
         self.lengths[slot] = length
         return True
 
@@ -225,11 +359,10 @@ class SequenceCache:
         """An open slot as `open` hands it out: length 0, no pages, state zeroed."""
         if not self.slots.is_held(slot):
             raise CacheError(f"slot {slot} is not open")
-        for g in self.groups:
-            g.release(slot)
+        for st in self.stores:
+            st.release(slot)
+            st.open(slot)
         self.lengths[slot] = 0
-        for st in self.states.values():
-            st[slot].zero_()
 
     @property
     def live_slots(self) -> int:
@@ -258,6 +391,21 @@ class SequenceCache:
             for s, n in zip(slots, counts):
                 g.reserve(s, self.lengths[s] + n)
 
+    def pages_short(self, slots: Sequence[int], counts: Sequence[int]) -> int:
+        """How many pages the fullest group lacks for `counts[i]` new tokens of `slots[i]` (<= 0: it fits)."""
+        short = -self.n_pages
+        for g in self.groups:
+            need = sum(g.pages_needed(s, self.lengths[s] + n) for s, n in zip(slots, counts))
+            short = max(short, need - g.pages.free_count)
+        return short if self.groups else 0
+
+    def unplan(self, slots: Sequence[int]) -> None:
+        """Undo `plan` for a step that did not run to its commit: pages beyond what each sequence's
+        committed length needs go back."""
+        for g in self.groups:
+            for s in slots:
+                g.shorten(s, self.lengths[s])
+
     def commit(self, slots: Sequence[int], counts: Sequence[int]) -> None:
         """Advance the lengths after the last layer of a step; windowed groups drop old pages."""
         for s, n in zip(slots, counts):
@@ -282,13 +430,5 @@ class SequenceCache:
     def check(self) -> None:
         """Bookkeeping invariants (used by tests): nothing lost, nothing held twice."""
         self.slots.check()
-        for g in self.groups:
-            g.pages.check()
-            held = [p for pl in g.seq_pages.values() for p in pl if p >= 0]
-            if len(held) != len(set(held)):
-                raise CacheError("a page is held by two sequences")
-            if len(held) != g.pages.held_count:
-                raise CacheError(f"{g.pages.held_count} pages are held but sequences list {len(held)}")
-            for s in g.seq_pages:
-                if not self.slots.is_held(s):
-                    raise CacheError(f"pages are listed for slot {s}, which is not open")
+        for st in self.stores:
+            st.check(self.slots.is_held)

@@ -1,7 +1,7 @@
 """Model description as data.
 
 A model is described by a `ModelSpec`: a list of `BlockSpec` (each names its
-mixer, feed-forward, norms and their sizes), a *schedule* (the order in which
+arrangement and, by role, its parts - mixer, feed-forward, norms - with their sizes), a *schedule* (the order in which
 blocks run; an entry may name a block twice or let a block read the cache that
 an earlier entry wrote), the embedding / final norm / head description, and the
 tensor-name prefixes under which every part finds its weights.
@@ -19,7 +19,8 @@ is data so that another architecture only adds a config class.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from types import MappingProxyType
+from typing import Any, Dict, List, Mapping, Optional, Tuple
 
 
 @dataclass(frozen=True)
@@ -41,15 +42,54 @@ class PartSpec:
         return self.params[key]
 
 
-@dataclass(frozen=True)
+@dataclass(frozen=True, init=False)
 class BlockSpec:
-    """One layer: arrangement (how the parts are wired) plus its parts."""
+    """One layer: an arrangement (how the parts are wired) and its parts by *role*.
+
+    Which roles a block has is the arrangement's business: the arrangement class declares
+    ``roles = {role: family}`` (family: "mixer", "feed_forward" or "norm", the registry the part's kind
+    is looked up in), and the model builder builds exactly those.  The pre-norm arrangement of this
+    library has the roles mixer, feed_forward, mixer_norm and feed_forward_norm; an arrangement with
+    norms after its parts as well, with one norm shared by parallel parts, or without a feed-forward
+    declares other roles and needs no change here or in the builder.
+
+    ``BlockSpec("pre_norm", mixer=..., feed_forward=..., mixer_norm=..., feed_forward_norm=...)`` and
+    ``BlockSpec("pre_norm", parts={...})`` are the same thing; ``block.mixer`` reads role "mixer".
+    """
 
     arrangement: str  # registry key of the block arrangement, e.g. "pre_norm"
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    parts: Mapping[str, PartSpec]
+
+    def __init__(self, arrangement: str, parts: Optional[Mapping[str, PartSpec]] = None, **roles: PartSpec):
+        merged = dict(parts or {})
+        for role, ps in roles.items():
+            if role in merged:
+                raise ValueError(f"block spec: role {role!r} is given twice")
+            merged[role] = ps
+        for role, ps in merged.items():
+            if not isinstance(ps, PartSpec):
+                raise TypeError(f"block spec: role {role!r} must be a PartSpec, got {type(ps).__name__}")
+        object.__setattr__(self, "arrangement", arrangement)
+        object.__setattr__(self, "parts", MappingProxyType(merged))
+
+    def __getattr__(self, role: str) -> PartSpec:
+        # only reached when normal lookup fails: a role read as an attribute
+        parts = object.__getattribute__(self, "__dict__").get("parts")
+        if parts is not None and role in parts:
+            return parts[role]
+        raise AttributeError(f"block spec has no role {role!r}; its roles are {sorted(parts or ())}")
+
+    def with_part(self, role: str, part: Optional[PartSpec]) -> "BlockSpec":
+        """A copy with one role replaced, added, or (part None) taken out."""
+        merged = dict(self.parts)
+        if part is None:
+            merged.pop(role, None)
+        else:
+            merged[role] = part
+        return BlockSpec(self.arrangement, merged)
+
+    def with_arrangement(self, arrangement: str) -> "BlockSpec":
+        return BlockSpec(arrangement, dict(self.parts))
 
 
 @dataclass(frozen=True)

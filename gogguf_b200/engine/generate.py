@@ -123,10 +123,20 @@ class Generator:
         max_new = params.max_tokens if params.max_tokens > 0 else 128      # session.go:134-137
         results: List[Optional[GenerationResult]] = [None] * len(prompts)
         batches = plan_batches([len(p) for p in prompts], max_new, self.max_batch,
-                               self.cache.max_tokens, self.cache.page_size, self.context)
+                               self._room(held), self.cache.page_size, self.context)
         for batch in batches:
             self._run_batch(batch, prompts, params, max_new, results, held or {})
         return [r for r in results if r is not None]
+
+    def _room(self, held: Optional[dict] = None) -> int:
+        """Tokens this call may plan with: what is free now plus what its own held slots already hold.
+        Pages of other open slots (another conversation, an open session) are not this call's to use, so a
+        request that cannot fit beside them is refused before the first step instead of failing in the
+        middle of decoding."""
+        cache = self.cache
+        ps = cache.page_size
+        own = sum(-(-cache.length(s) // ps) * ps for s in (held or {}).values())
+        return min(cache.max_tokens, cache.free_tokens() + own)
 
     def _let_go(self, i: int, slots, held, prompts, generated) -> None:
         """Request i has ended: its slot goes back, unless its owner holds it; then it keeps the tokens of
@@ -175,10 +185,12 @@ class Generator:
                 else:
                     slots[i] = cache.open()
             logits = self._prefill(live, prompts, slots, cached)
-            if hasattr(self.stepper, "decode_from_device") and getattr(logits, "is_cuda", False) and len(live) <= 256:
+            # a step ahead of the host needs a stepper that replays captured decode steps
+            ahead = (hasattr(self.stepper, "decode_from_device") and getattr(self.stepper, "capturable", True)
+                     and getattr(logits, "is_cuda", False) and len(live) <= 256)
+            if ahead:
                 sampler.begin(live, [prompts[i] for i in live], logits.device)     # rings for a repeat penalty
-            if (hasattr(self.stepper, "decode_from_device") and sampler.device_only
-                    and getattr(logits, "is_cuda", False) and len(live) <= 256):
+            if ahead and sampler.device_only:
                 self._decode_one_ahead(live, logits, sampler, slots, generated, prompts, params, max_new, stop, results,
                                        held)
                 return
@@ -274,7 +286,7 @@ class GenerationSession:
         n = len(self.prompts)
         if n == 0 or n > generator.max_batch:
             raise ValueError(f"a session takes 1 to {generator.max_batch} prompts, not {n}")
-        plan = plan_batches([len(p) for p in self.prompts], 1, generator.max_batch, generator.cache.max_tokens,
+        plan = plan_batches([len(p) for p in self.prompts], 1, generator.max_batch, generator._room(),
                             generator.cache.page_size, generator.context)
         if len(plan) != 1:
             raise ValueError("the prompts of a session must fit the cache together")

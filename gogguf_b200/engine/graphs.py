@@ -52,6 +52,9 @@ class GraphStepper(Stepper):
         self.min_width = min_width
         self._graphs: Dict[Tuple[int, int], _Captured] = {}
         self.replays = 0
+        # a part that reads back to the host or allocates while it runs declares `capturable = False`;
+        # such a model is stepped eagerly, and `decode_from_device` is not offered for it
+        self.capturable = all(getattr(p, "capturable", True) for p in model.parts())
 
     def _width_bucket(self, slots: Sequence[int]) -> int:
         w = max(self.cache.table_width(slots), self.min_width)
@@ -105,11 +108,14 @@ class GraphStepper(Stepper):
             max_new=1, max_ctx=width * self.cache.page_size, decode=True)
         return ctx, lay, lay.view(dev, "logit_rows")
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def _run(self, entries: Sequence[StepEntry], taps=None) -> Optional[torch.Tensor]:
+        """Checked entries: a plain decode step replays its graph, everything else runs eagerly
+        (prompts, several tokens per sequence, other wanted places, a step with layer taps, a model
+        one of whose parts says it cannot be captured)."""
         decode = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries) and len(entries) > 0
-        if not decode or _bucket(len(entries), BATCH_BUCKETS) is None:
-            return super().step(entries)
-        self._check(entries)
+        if (not decode or taps is not None or not self.capturable
+                or _bucket(len(entries), BATCH_BUCKETS) is None):
+            return super()._run(entries, taps)
         return self._enqueue_decode(entries, None, None)
 
     def decode_from_device(self, slots: Sequence[int], sampled: torch.Tensor, rows: Sequence[int]
@@ -119,6 +125,8 @@ class GraphStepper(Stepper):
         Nothing is read back and the host does not wait, so the caller may enqueue this step while it
         is still reading the previous step's ids.  Returns the logits view [len(slots), vocab]."""
         entries = [StepEntry(s, [0], want=[0]) for s in slots]
+        if not self.capturable:
+            raise ValueError("a part of this model cannot be captured in a CUDA graph; step it eagerly")
         if _bucket(len(entries), BATCH_BUCKETS) is None:
             raise ValueError(f"no captured batch size holds {len(entries)} sequences")
         self._check(entries)
@@ -129,6 +137,13 @@ class GraphStepper(Stepper):
         counts = [1] * len(entries)
         bucket = _bucket(len(entries), BATCH_BUCKETS)
         self.cache.plan(slots, counts)
+        try:
+            return self._replay(entries, slots, counts, bucket, sampled, rows)
+        except BaseException:
+            self.cache.unplan(slots)
+            raise
+
+    def _replay(self, entries, slots, counts, bucket, sampled, rows):
         width = self._width_bucket(slots)
         key = (bucket, width)
         cap = self._graphs.get(key)

@@ -37,13 +37,47 @@ def _part_class(table, spec: PartSpec, what: str):
     return R.lookup(table, spec.kind, what)
 
 
-def _block_parts(b: BlockSpec) -> List[Tuple[PartSpec, type]]:
-    return [
-        (b.mixer, _part_class(R.MIXERS, b.mixer, "mixer")),
-        (b.feed_forward, _part_class(R.FEED_FORWARDS, b.feed_forward, "feed-forward")),
-        (b.mixer_norm, _part_class(R.NORMS, b.mixer_norm, "norm")),
-        (b.feed_forward_norm, _part_class(R.NORMS, b.feed_forward_norm, "norm")),
-    ]
+_FAMILIES = {"mixer": (R.MIXERS, "mixer"), "feed_forward": (R.FEED_FORWARDS, "feed-forward"),
+             "norm": (R.NORMS, "norm")}
+
+
+def _block_parts(b: BlockSpec) -> List[Tuple[str, PartSpec, type]]:
+    """(role, spec, class) of every part of a block, in the order of the arrangement's `roles`.
+
+    The arrangement class says which roles a block of its kind has and which family (registry) each
+    role's part comes from; the block spec must name exactly those (roles listed in the arrangement's
+    `optional_roles` may be left out)."""
+    acls = R.lookup(R.ARRANGEMENTS, b.arrangement, "block arrangement")
+    roles = getattr(acls, "roles", None)
+    if roles is None:
+        raise TypeError(f"block arrangement {b.arrangement!r} declares no `roles` (role -> family)")
+    optional = set(getattr(acls, "optional_roles", ()))
+    missing = [r for r in roles if r not in b.parts and r not in optional]
+    extra = [r for r in b.parts if r not in roles]
+    if missing or extra:
+        raise ValueError(f"block arrangement {b.arrangement!r} has the roles {sorted(roles)}"
+                         + (f"; missing: {sorted(missing)}" if missing else "")
+                         + (f"; not known to it: {sorted(extra)}" if extra else ""))
+    out = []
+    for role, family in roles.items():
+        if role not in b.parts:
+            continue
+        if family not in _FAMILIES:
+            raise ValueError(f"block arrangement {b.arrangement!r}: role {role!r} names the unknown family "
+                             f"{family!r} (known: {sorted(_FAMILIES)})")
+        table, what = _FAMILIES[family]
+        out.append((role, b.parts[role], _part_class(table, b.parts[role], what)))
+    return out
+
+
+def _cache_part(b: BlockSpec) -> Optional[Tuple[PartSpec, type]]:
+    """The part of a block that may ask for cache or state: its mixer-family role (at most one)."""
+    acls = R.lookup(R.ARRANGEMENTS, b.arrangement, "block arrangement")
+    mixers = [(ps, cls) for role, ps, cls in _block_parts(b) if acls.roles[role] == "mixer"]
+    if len(mixers) > 1:
+        raise ValueError(f"block arrangement {b.arrangement!r}: a block may hold one mixer, not {len(mixers)} "
+                         "(a schedule entry owns one cache)")
+    return mixers[0] if mixers else None
 
 
 def expected_tensors(spec: ModelSpec) -> Dict[str, TensorDecl]:
@@ -59,7 +93,7 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorDecl]:
 
     add(spec.embedding, _part_class(R.EMBEDDINGS, spec.embedding, "embedding"))
     for b in spec.blocks:
-        for ps, cls in _block_parts(b):
+        for _, ps, cls in _block_parts(b):
             add(ps, cls)
     add(spec.final_norm, _part_class(R.NORMS, spec.final_norm, "norm"))
     add(spec.head, _part_class(R.HEADS, spec.head, "head"))
@@ -96,12 +130,12 @@ class Model:
         consume = consume and isinstance(tensors, dict)
         self.embedding = ecls(spec.embedding, _local(tensors, spec.embedding, ecls, consume), rt)
         self.blocks = []
-        self.mixer_classes = []
+        self._cache_parts = []
         for b in spec.blocks:
-            built = [cls(ps, _local(tensors, ps, cls, consume), rt) for ps, cls in _block_parts(b)]
+            built = {role: cls(ps, _local(tensors, ps, cls, consume), rt) for role, ps, cls in _block_parts(b)}
             acls = R.lookup(R.ARRANGEMENTS, b.arrangement, "block arrangement")
-            self.blocks.append(acls(b, *built, rt))
-            self.mixer_classes.append(_part_class(R.MIXERS, b.mixer, "mixer"))
+            self.blocks.append(acls(b, built, rt))
+            self._cache_parts.append(_cache_part(b))
         ncls = _part_class(R.NORMS, spec.final_norm, "norm")
         self.final_norm = ncls(spec.final_norm, _local(tensors, spec.final_norm, ncls, consume), rt)
         hcls = _part_class(R.HEADS, spec.head, "head")
@@ -116,7 +150,8 @@ class Model:
         cfg = load_config(folder)
         spec = cfg.to_spec()
         aliases = cfg.tensor_aliases() if hasattr(cfg, "tensor_aliases") else None
-        tensors = load_tensors(folder, expected_tensors(spec), device=device, aliases=aliases)
+        tensors = load_tensors(folder, expected_tensors(spec), device=device, aliases=aliases,
+                               compute_dtype=parse_dtype(dtype))
         return cls(spec, tensors, dtype=dtype, device=device, fast=fast, config=cfg, fold_norms=fold_norms, consume=True)
 
     @classmethod
@@ -136,9 +171,17 @@ class Model:
     def cache_requests(self) -> List[Request]:
         out: List[Request] = []
         for e in self.spec.schedule:
-            b = self.spec.blocks[e.block]
-            out.append(self.mixer_classes[e.block].cache_request(b.mixer))
+            cp = self._cache_parts[e.block]
+            out.append(cp[1].cache_request(cp[0]) if cp is not None else None)
         return out
+
+    def parts(self):
+        """Every built part of the model: embedding, the parts of every block, final norm, head."""
+        yield self.embedding
+        for b in self.blocks:
+            yield from getattr(b, "parts", {}).values()
+        yield self.final_norm
+        yield self.head
 
     def new_cache(self, max_tokens: int, max_slots: Optional[int] = None) -> SequenceCache:
         return SequenceCache(self.cache_requests(), [e.cache_of for e in self.spec.schedule], max_tokens,

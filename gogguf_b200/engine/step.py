@@ -9,12 +9,19 @@ separately from its cache counter, pkg/model/qwen3/model.go:112-134, and the two
 pkg/runtime/conversation.go:120-125).  Only the wanted rows go through the final norm and the head
 (the reference computes logits for the last token of a call only, model.go:127).
 
-Everything is checked on the host before the first launch; a refused step leaves the cache as it was.
+Everything is checked on the host before the first launch; a refused step leaves the cache as it was,
+and so does a step that fails between reserving its pages and committing its lengths.  `step` refuses
+the whole step at the first bad entry; `try_step` gives every entry a status of its own and runs the
+others (the reference returns the error of its one sequence, pkg/runtime/session.go:69-72).
+
+`taps` (a `LayerTaps`) hands out the residual rows of the wanted places after the embedding and after
+every scheduled block, as the reference's debug hooks do for its last token
+(pkg/model/qwen3/debug.go:4-9, fired at pkg/model/qwen3/model.go:141-162).
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -25,7 +32,38 @@ from .model import Model
 
 
 class StepError(ValueError):
-    """A step that cannot run: unknown slot, token id out of range, context overflow, bad index."""
+    """A step, or one entry of it, that cannot run.  `code` is one of "empty_step", "duplicate_slot",
+    "unknown_slot", "no_tokens", "bad_token", "bad_want", "context_overflow", "cache_full"."""
+
+    def __init__(self, message: str, code: str = "bad_entry"):
+        super().__init__(message)
+        self.code = code
+
+
+@dataclass
+class LayerTaps:
+    """Per-layer hooks of an eager step, in the manner of the reference's DebugHooks
+    (pkg/model/qwen3/debug.go:4-9).  Every function gets float32 rows on the device, one per wanted
+    place of the step, in the order of the logits: `on_embed(rows[wanted, hidden])` after the embedding,
+    `on_layer(i, rows)` after schedule entry i, `on_layer_logits(i, logits[wanted, vocab])` the final
+    norm and head applied to those rows (computed only if the hook is set), `on_logits(logits)` the
+    step's own result.  The tensors are copies: a hook may keep them."""
+    on_embed: Optional[Callable[[torch.Tensor], None]] = None
+    on_layer: Optional[Callable[[int, torch.Tensor], None]] = None
+    on_layer_logits: Optional[Callable[[int, torch.Tensor], None]] = None
+    on_logits: Optional[Callable[[torch.Tensor], None]] = None
+
+
+@dataclass
+class StepOutcome:
+    """What `try_step` gives back: `status[i]` is None for an entry that ran and the `StepError` that
+    refused it otherwise; `logits` holds the wanted rows of the entries that ran, in their order."""
+    logits: Optional[torch.Tensor]
+    status: List[Optional[StepError]]
+
+    @property
+    def ran(self) -> List[int]:
+        return [i for i, s in enumerate(self.status) if s is None]
 
 
 @dataclass
@@ -74,29 +112,44 @@ class Stepper:
         self._copied: Optional[torch.cuda.Event] = None
 
     # ------------------------------------------------------------------ host side
-    def _check(self, entries: Sequence[StepEntry]) -> None:
-        if not entries:
-            raise StepError("a step needs at least one entry")
+    def _check_entry(self, e: StepEntry, seen: set) -> Optional[StepError]:
+        """Why entry `e` cannot run, or None.  `seen` holds the slots of the entries before it."""
         V = self.model.spec.vocab_size
         limit = self.model.spec.max_positions
-        seen = set()
+        if e.slot in seen:
+            return StepError(f"slot {e.slot} appears twice in one step", "duplicate_slot")
+        if not self.cache.slots.is_held(e.slot):
+            return StepError(f"slot {e.slot} is not open", "unknown_slot")
+        n = len(e.tokens)
+        if n == 0:
+            return StepError(f"slot {e.slot}: no tokens", "no_tokens")
+        try:
+            toks = np.asarray(e.tokens, dtype=np.int64)
+        except (TypeError, ValueError, OverflowError):
+            return StepError(f"slot {e.slot}: token ids must be integers", "bad_token")
+        if toks.ndim != 1:
+            return StepError(f"slot {e.slot}: token ids must be a flat list", "bad_token")
+        bad = np.nonzero((toks < 0) | (toks >= V))[0]
+        if bad.size:
+            return StepError(f"slot {e.slot}: token id {int(toks[bad[0]])} is outside the vocabulary "
+                             f"(0..{V - 1})", "bad_token")
+        for w in e.want:
+            if not (0 <= int(w) < n):
+                return StepError(f"slot {e.slot}: wanted place {w} is outside its {n} tokens", "bad_want")
+        if self.cache.lengths[e.slot] + n > limit:
+            return StepError(f"slot {e.slot}: {self.cache.lengths[e.slot]} cached + {n} new tokens "
+                             f"exceed the model's context of {limit}", "context_overflow")
+        return None
+
+    def _check(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise StepError("a step needs at least one entry", "empty_step")
+        seen: set = set()
         for e in entries:
-            if e.slot in seen:
-                raise StepError(f"slot {e.slot} appears twice in one step")
+            err = self._check_entry(e, seen)
+            if err is not None:
+                raise err
             seen.add(e.slot)
-            if not self.cache.slots.is_held(e.slot):
-                raise StepError(f"slot {e.slot} is not open")
-            if len(e.tokens) == 0:
-                raise StepError(f"slot {e.slot}: no tokens")
-            for t in e.tokens:
-                if not (0 <= int(t) < V):
-                    raise StepError(f"slot {e.slot}: token id {t} is outside the vocabulary (0..{V - 1})")
-            for w in e.want:
-                if not (0 <= int(w) < len(e.tokens)):
-                    raise StepError(f"slot {e.slot}: wanted place {w} is outside its {len(e.tokens)} tokens")
-            if self.cache.lengths[e.slot] + len(e.tokens) > limit:
-                raise StepError(f"slot {e.slot}: {self.cache.lengths[e.slot]} cached + {len(e.tokens)} new tokens "
-                                f"exceed the model's context of {limit}")
 
     def _buffers(self, n: int) -> Tuple[torch.Tensor, torch.Tensor]:
         if self._host is None or self._host.numel() < n:
@@ -183,21 +236,39 @@ class Stepper:
         return ctx, lay, lay.view(dev, "logit_rows")
 
     # ------------------------------------------------------------------ device side
-    def run_layers(self, ctx: StepContext) -> torch.Tensor:
-        """Embedding and all scheduled blocks; returns the float32 residual stream [T, hidden]."""
+    def run_layers(self, ctx: StepContext, taps: Optional[LayerTaps] = None,
+                   tap_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Embedding and all scheduled blocks; returns the float32 residual stream [T, hidden].
+        With `taps`, the rows `tap_rows` of the stream are handed out after the embedding and after
+        every scheduled block (a debugging aid: it copies, and the head runs once more per block if
+        `on_layer_logits` is set)."""
         m = self.model
         x = ctx.ws.get("residual", (ctx.n_tokens, m.spec.hidden_size), torch.float32)
         m.embedding.forward(ctx.tokens, x)
+        tapping = taps is not None and tap_rows is not None and tap_rows.numel() > 0
+        if tapping and taps.on_embed is not None:
+            taps.on_embed(x.index_select(0, tap_rows.long()))
         for b in m.blocks:
-            prep = getattr(b.mixer, "prepare", None)
-            if prep is not None:
-                prep(ctx)
+            for part in getattr(b, "parts", {}).values():
+                prep = getattr(part, "prepare", None)
+                if prep is not None:
+                    prep(ctx)
         for i, e in enumerate(m.spec.schedule):
             block = m.blocks[e.block]
             block.forward(x, ctx, self.cache.view(i), e.cache_of is None)
             stats = ctx.shared.get("row_stats")
             if stats is not None and not getattr(block, "keeps_row_stats", False):
                 stats.fresh = False     # an arrangement that does not know of the statistics changed the rows
+            if tapping:
+                if taps.on_layer is not None:
+                    taps.on_layer(i, x.index_select(0, tap_rows.long()))
+                if taps.on_layer_logits is not None:
+                    n = int(tap_rows.numel())
+                    hn = ctx.ws.get("tap_normed", (n, m.spec.hidden_size), m.rt.dtype)
+                    lg = ctx.ws.get("tap_logits", (n, m.spec.vocab_size), torch.float32)
+                    m.final_norm.forward(x, hn, tap_rows)
+                    m.head.forward(hn, lg, ctx, m=n)
+                    taps.on_layer_logits(i, lg.clone())
         return x
 
     def run_head(self, ctx: StepContext, x: torch.Tensor, rows: torch.Tensor, n_rows: int) -> torch.Tensor:
@@ -209,16 +280,48 @@ class Stepper:
         m.head.forward(hn, logits, ctx, m=n_rows)
         return logits
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], taps: Optional[LayerTaps] = None) -> Optional[torch.Tensor]:
         """Run one step.  Returns float32 logits [wanted, vocab] on the device (None if nothing is
         wanted), in the order of the entries and of their `want`.  The tensor is workspace memory:
-        it is valid until the next step."""
+        it is valid until the next step.  A bad entry refuses the whole step (`StepError`)."""
         self._check(entries)
+        return self._run(entries, taps)
+
+    def try_step(self, entries: Sequence[StepEntry], taps: Optional[LayerTaps] = None) -> StepOutcome:
+        """Run the entries that can run and say, entry by entry, why the others cannot.  An entry that is
+        refused changes nothing: its slot keeps its length and pages.  If the cache cannot hold the
+        step, entries are left out from the end until it can ("cache_full")."""
+        status: List[Optional[StepError]] = []
+        seen: set = set()
+        for e in entries:
+            err = self._check_entry(e, seen)
+            status.append(err)
+            if err is None:
+                seen.add(e.slot)
+        good = [i for i, st in enumerate(status) if st is None]
+        while good:
+            need = self.cache.pages_short([entries[i].slot for i in good], [len(entries[i].tokens) for i in good])
+            if need <= 0:
+                break
+            i = good.pop()
+            status[i] = StepError(f"slot {entries[i].slot}: the cache has no room for its "
+                                  f"{len(entries[i].tokens)} tokens in this step", "cache_full")
+        logits = self._run([entries[i] for i in good], taps) if good else None
+        return StepOutcome(logits=logits, status=status)
+
+    def _run(self, entries: Sequence[StepEntry], taps: Optional[LayerTaps] = None) -> Optional[torch.Tensor]:
+        """The checked entries, eagerly: reserve, pack, launch, commit."""
         slots = [e.slot for e in entries]
         counts = [len(e.tokens) for e in entries]
         self.cache.plan(slots, counts)          # raises before anything ran if the cache is full
-        ctx, lay, rows = self.build_context(entries)
-        x = self.run_layers(ctx)
-        logits = self.run_head(ctx, x, rows, lay.n_want) if lay.n_want else None
+        try:
+            ctx, lay, rows = self.build_context(entries)
+            x = self.run_layers(ctx, taps, rows[:lay.n_want] if lay.n_want else None)
+            logits = self.run_head(ctx, x, rows, lay.n_want) if lay.n_want else None
+        except BaseException:
+            self.cache.unplan(slots)            # the pages reserved for this step go back
+            raise
         self.cache.commit(slots, counts)
+        if taps is not None and taps.on_logits is not None and logits is not None:
+            taps.on_logits(logits.clone())
         return logits

@@ -1,6 +1,8 @@
 """Block arrangements: how a mixer, a feed-forward and their norms are wired around the residual."""
 from __future__ import annotations
 
+from typing import Dict
+
 import torch
 
 from ..config.spec import BlockSpec
@@ -13,9 +15,14 @@ class PreNormBlock:
     """x += mixer(norm1(x)); x += feed_forward(norm2(x)) (pkg/model/qwen3/model.go:198-288).
     The residual stream x is float32; the parts add their outputs into it."""
 
+    # role -> family: what a block of this arrangement is made of (the builder builds exactly these)
+    roles = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
     keeps_row_stats = True      # clears RowStats.fresh itself before each write to the residual
 
-    def __init__(self, spec: BlockSpec, mixer, feed_forward, mixer_norm, feed_forward_norm, rt: Runtime):
+    def __init__(self, spec: BlockSpec, parts: Dict[str, object], rt: Runtime):
+        self.parts = dict(parts)
+        mixer, feed_forward = parts["mixer"], parts["feed_forward"]
+        mixer_norm, feed_forward_norm = parts["mixer_norm"], parts["feed_forward_norm"]
         self.mixer, self.feed_forward = mixer, feed_forward
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
         self.rt = rt

@@ -13,7 +13,11 @@ Interfaces (duck-typed; see `gogguf_b200.parts.base` for the step context they r
 * feed-forward: ``forward(h, residual, ctx)``, same contract.
 * norm:         ``forward(x, out, rows=None)``: `x` float32 rows -> `out` in the compute dtype.
 * position:     built by the mixer that uses it from ``spec["position"]``; ``tables(ctx)``.
-* arrangement:  ``__init__(block_spec, parts...)`` and ``forward(x, ctx, cache, writes_cache)``.
+* arrangement:  class attribute ``roles = {role: family}`` (family "mixer", "feed_forward" or "norm"; optional
+                ``optional_roles``), ``__init__(block_spec, parts, runtime)`` with `parts` the built parts by role,
+                an attribute ``parts`` holding them, and ``forward(x, ctx, cache, writes_cache)``.
+* any part may set ``capturable = False`` if its `forward` reads back to the host or allocates; a model with
+  such a part is stepped eagerly instead of through captured CUDA graphs.
 """
 from __future__ import annotations
 

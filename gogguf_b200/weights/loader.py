@@ -8,9 +8,11 @@ shapes, instead of the reference's first-failure errors
 (pkg/format/reader.go:306-313 "tensor not found"; pkg/model/qwen3/norms.go:16-45
 wraps it with the layer; pkg/model/qwen3/model.go:664-666 checks q/k-norm length).
 
-Storage policy: a tensor stored in bfloat16 stays bfloat16, float16 is widened
-to bfloat16's partner only on request of the compute path, a tensor stored in
-32-bit floating point stays 32-bit, and integer tables become int32.
+Storage policy: a tensor stored in bfloat16 stays bfloat16, a tensor stored in
+32-bit floating point stays 32-bit, and integer tables become int32.  float16
+has no kernel of its own: under the 32-bit compute path it is widened to
+float32, which holds every float16 value exactly, and only under the bfloat16
+path is it rounded to bfloat16.
 """
 from __future__ import annotations
 
@@ -74,12 +76,12 @@ def check_tensors(expected: Mapping[str, TensorDecl],
                        wrong_shape=sorted(wrong))
 
 
-def _stored_to_kept(t: torch.Tensor) -> torch.Tensor:
+def _stored_to_kept(t: torch.Tensor, compute_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """Storage policy of the loader (see module docstring)."""
     if t.dtype in (torch.bfloat16, torch.float32):
         return t
     if t.dtype == torch.float16:
-        return t.to(torch.bfloat16)
+        return t.to(torch.float32 if compute_dtype == torch.float32 else torch.bfloat16)
     if t.dtype == torch.float64:
         return t.to(torch.float32)
     if t.dtype in (torch.int64, torch.int16, torch.int8, torch.uint8, torch.bool, torch.int32):
@@ -88,8 +90,11 @@ def _stored_to_kept(t: torch.Tensor) -> torch.Tensor:
 
 
 def load_tensors(folder: str, expected: Mapping[str, TensorDecl], device: str | torch.device = "cpu",
-                 aliases: Optional[Mapping[str, str]] = None) -> Dict[str, torch.Tensor]:
+                 aliases: Optional[Mapping[str, str]] = None,
+                 compute_dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
     """Read the expected tensors of a model folder onto `device`.
+
+    `compute_dtype` decides only what a float16 tensor becomes (float32 under the 32-bit path).
 
     `aliases` maps an alternative stored name to the expected name (for
     instance the GGUF-style names of pkg/model/qwen3/tensors.go:19-34).
@@ -114,7 +119,7 @@ def load_tensors(folder: str, expected: Mapping[str, TensorDecl], device: str | 
             if name not in source:
                 continue
             f, stored = source[name]
-            t = _stored_to_kept(f.tensor(stored))
+            t = _stored_to_kept(f.tensor(stored), compute_dtype)
             out[name] = t.to(device, copy=True) if torch.device(device).type != "cpu" else t.clone()
         return out
     finally:

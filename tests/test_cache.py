@@ -179,3 +179,59 @@ def test_truncate_refuses_what_a_window_or_a_state_has_let_go():
     assert c2.truncate(s2, 5) and not c2.truncate(s2, 4)
     c2.restart(s2)
     assert c2.length(s2) == 0
+
+
+def test_a_step_that_fails_after_plan_gives_its_pages_back_and_entries_get_a_status_each():
+    """`Stepper` on the CPU with a model stand-in: everything up to the first launch is host code."""
+    from types import SimpleNamespace
+    from gogguf_b200.engine.step import StepEntry, StepError, Stepper
+    cache = SequenceCache([KVRequest(1, 4), KVRequest(1, 4, window=70)], [None, None], 64 * 6, dtype=torch.float32)
+    spec = SimpleNamespace(vocab_size=50, max_positions=200, hidden_size=8, schedule=())
+    model = SimpleNamespace(spec=spec, rt=SimpleNamespace(device=torch.device("cpu"), dtype=torch.float32),
+                            blocks=[], parts=lambda: [])
+    st = Stepper(model, cache)
+    ran = []
+
+    def fake_layers(ctx, taps=None, tap_rows=None):
+        ran.append(int(ctx.n_tokens))
+        if fail[0]:
+            raise RuntimeError("a launcher refused")
+        return torch.zeros(ctx.n_tokens, 8)
+
+    st.run_layers = fake_layers
+    st.run_head = lambda ctx, x, rows, n: torch.zeros(n, 50)
+    fail = [True]
+    a, b = cache.open(), cache.open()
+    st_before = (cache.free_tokens(), list(cache.lengths))
+    with pytest.raises(RuntimeError):
+        st.step([StepEntry(a, [1] * 100, want=[99]), StepEntry(b, [2] * 70)])
+    cache.check()
+    assert (cache.free_tokens(), list(cache.lengths)) == st_before        # nothing stays reserved
+    fail[0] = False
+    # per-entry status: the bad ones are named, the others run
+    c = cache.open()
+    out = st.try_step([StepEntry(a, [1, 2, 3], want=[2]),
+                       StepEntry(b, [1, 99]),                # token outside the vocabulary
+                       StepEntry(7, [1]),                    # not an open slot
+                       StepEntry(a, [4]),                    # the same slot twice
+                       StepEntry(c, [1] * 201),              # longer than the context
+                       StepEntry(c, [5, 6], want=[0, 1])])
+    assert [s.code if s else None for s in out.status] == [None, "bad_token", "unknown_slot", "duplicate_slot",
+                                                           "context_overflow", None]
+    assert out.ran == [0, 5] and out.logits.shape == (3, 50)
+    assert cache.length(a) == 3 and cache.length(b) == 0 and cache.length(c) == 2
+    # the cache holds 6 pages: a and c hold one each; b wants 3, a fourth sequence wants 2 -> left out from the end
+    d = cache.open()
+    out = st.try_step([StepEntry(b, [1] * 150), StepEntry(d, [1] * 100)])
+    assert [s.code if s else None for s in out.status] == [None, "cache_full"]
+    assert cache.length(b) == 150 and cache.length(d) == 0
+    with pytest.raises(CacheFull):                   # the strict form refuses the whole step, cache untouched
+        st.step([StepEntry(d, [1] * 100)])
+    with pytest.raises(StepError):
+        st.step([StepEntry(d, [1]), StepEntry(b, [77])])
+    assert cache.length(d) == 0
+    cache.check()
+    for s in (a, b, c, d):
+        cache.close(s)
+    cache.check()
+    assert cache.free_tokens() == 64 * 6

@@ -315,3 +315,28 @@ def test_interactive_mode_is_one_conversation_with_a_line_of_ids_per_turn():
     assert [n for step in st.steps for _, n in step] == [3, 1, 3, 1, 1, 1]
     assert st.cache.live_slots == 0
     st.cache.check()
+
+
+def test_two_conversations_share_one_cache_and_a_request_that_cannot_fit_beside_them_is_refused():
+    """Batches are planned against what is free now plus what the call's own slot holds, not against the
+    whole cache: pages held by another conversation are not this call's to use."""
+    from gogguf_b200.api import Conversation
+    st = ScriptedStepper(max_tokens=64 * 4)
+    a, b = Conversation(_Ctx(st)), Conversation(_Ctx(st))
+    a.generate(list(range(1, 11)) * 10, GenerateParams(max_tokens=20))       # 100 + 20 tokens: 2 pages held
+    assert st.cache.free_tokens() == 64 * 2
+    # b asks for 3 pages: the whole cache would hold them, what is free does not -> refused before any step
+    n_before = len(st.steps)
+    with pytest.raises(ValueError, match="needs room"):
+        b.generate([1] * 100, GenerateParams(max_tokens=60))
+    assert len(st.steps) == n_before
+    st.cache.check()
+    # what fits beside a runs, and a's slot is untouched by it
+    r = b.generate([1, 2, 3], GenerateParams(max_tokens=4))
+    assert r.tokens == [4, 5, 6, 7] and st.cache.length(a._slot) == 119
+    # a may grow into its own pages and the free ones
+    r = a.generate(a.tokens + [5], GenerateParams(max_tokens=3))
+    assert r.tokens == [6, 7, 8]
+    a.close(); b.close()
+    st.cache.check()
+    assert st.cache.free_tokens() == 64 * 4 and st.cache.live_slots == 0

@@ -117,7 +117,7 @@ def test_mixer_feed_forward_and_block_alone(dtype, cfg):
     assert rel_err(res.cpu().double() - x0.double(), wantf) < tol
     # the whole block (same positions, so the cache rows are simply written again); on the fast path the
     # arrangement hands its norms to the parts, which from then on read the raw rows and their statistics
-    block = R.ARRANGEMENTS[b.arrangement](b, mixer, ffn, norm1, norm2, rt)
+    block = R.ARRANGEMENTS[b.arrangement](b, dict(mixer=mixer, feed_forward=ffn, mixer_norm=norm1, feed_forward_norm=norm2), rt)
     assert block.mixer_folded == block.feed_forward_folded == (dtype == torch.bfloat16)
     xb = x0.clone().to(DEV)
     block.forward(xb, ctx, cache.view(0), True)
@@ -181,7 +181,7 @@ def toy_spec():
     spec = config_from_dict(TINY_B).to_spec()
     H = TINY_B["hidden_size"]
     blocks = list(spec.blocks)
-    blocks[1] = replace(blocks[1], mixer=PartSpec("toy_running_mean", dict(hidden_size=H), prefix="model.layers.1.toy."))
+    blocks[1] = blocks[1].with_part("mixer", PartSpec("toy_running_mean", dict(hidden_size=H), prefix="model.layers.1.toy."))
     # order as data: layer 0, the toy layer, layer 2, then layer 0 again reading the cache its first run wrote
     schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(0, cache_of=0))
     return replace(spec, blocks=tuple(blocks), schedule=schedule)
@@ -324,10 +324,10 @@ def test_toy_routed_feed_forward_and_other_position_encoding(dtype):
     spec = config_from_dict(TINY_B).to_spec()
     H = TINY_B["hidden_size"]
     blocks = list(spec.blocks)
-    blocks[0] = replace(blocks[0], feed_forward=PartSpec(
+    blocks[0] = blocks[0].with_part("feed_forward", PartSpec(
         "toy_routed", dict(hidden_size=H, experts=4, top_k=2, expert_size=40), prefix="model.layers.0.moe."))
     mixer2 = blocks[2].mixer
-    blocks[2] = replace(blocks[2], mixer=PartSpec(
+    blocks[2] = blocks[2].with_part("mixer", PartSpec(
         mixer2.kind, {**mixer2.params, "position": {"kind": "toy_additive_sinusoid", "rotary_dim": TINY_B["head_dim"]}},
         prefix=mixer2.prefix))
     spec = replace(spec, blocks=tuple(blocks))

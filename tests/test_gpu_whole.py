@@ -33,6 +33,24 @@ def test_whole_f32(tmp_path_factory, name, n):
     assert rel_err(got, want) < TOL_F32
 
 
+@pytest.mark.parametrize("name", ["B", "L"])
+def test_float16_folder_is_exact_on_the_32_bit_path(tmp_path, name):
+    """A checkpoint stored in float16: the 32-bit path runs the stored values themselves (float32 holds
+    every float16 exactly), not their bfloat16 rounding; the bfloat16 path rounds them once."""
+    from gogguf_b200.weights.safetensors_io import write_safetensors
+    folder = make_folder(tmp_path, name, "float32", scale=4.0)
+    cfg, w = read_folder(folder)
+    w16 = {k: v.to(torch.float16) for k, v in w.items()}
+    write_safetensors(os.path.join(folder, "model.safetensors"), w16)
+    tokens = random_tokens(cfg["vocab_size"], 90, seed=8)
+    want = plain.forward(cfg, {k: v.float() for k, v in w16.items()}, tokens, wide=True)
+    got = engine_whole(folder, "float32", tokens)
+    assert rel_err(got, want) < TOL_F32
+    rounded = plain.forward(cfg, {k: v.to(torch.bfloat16).float() for k, v in w16.items()}, tokens, wide=True)
+    assert rel_err(rounded, want) > 20 * TOL_F32        # the test can tell the two apart
+    assert rel_err(engine_whole(folder, "bfloat16", tokens), rounded) < TOL_BF16
+
+
 @pytest.mark.parametrize("name", ["A", "B", "W", "M", "L"])
 def test_whole_bf16(tmp_path_factory, name):
     folder = make_folder(tmp_path_factory.getbasetemp(), name, "bfloat16", scale=4.0)

@@ -77,6 +77,13 @@ def test_storage_policy(tmp_path):
     assert got["model.norm.weight"].dtype == torch.float32
     assert got["model.embed_tokens.weight"].dtype == torch.bfloat16
     assert got["model.layers.0.mlp.up_proj.weight"].dtype == torch.bfloat16
+    # float16 has no kernels of its own: rounded to bfloat16 for the bfloat16 path, but widened exactly
+    # for the 32-bit path, whose results must be those of the stored values
+    got32 = load_tensors(folder, expected_tensors(cfg.to_spec()), compute_dtype=torch.float32)
+    up = got32["model.layers.0.mlp.up_proj.weight"]
+    assert up.dtype == torch.float32
+    assert torch.equal(up, w["model.layers.0.mlp.up_proj.weight"].float())
+    assert got32["model.embed_tokens.weight"].dtype == torch.bfloat16
 
 
 def test_truncated_and_broken_files(tmp_path):
