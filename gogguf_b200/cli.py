@@ -6,6 +6,9 @@
     gogguf_b200 inspect DIR
     gogguf_b200 random -c CONFIG.json -o DIR [--seed 0] [--dtype bfloat16] [--std S] [--norm-std S]
     gogguf_b200 compare A.f32 B.f32 [--tol 1e-4] [--vocab V]
+    gogguf_b200 dumplayers -m DIR -p "1 2 3" -o PREFIX [--dtype float32] [--all]
+    gogguf_b200 comparelayers -a A.bin -b B.bin [--tol 1e-4]   |   -m DIR -p "1 2 3" (float32 against bfloat16)
+    gogguf_b200 layerlogits -m DIR -p "1 2 3" [--top 5] [--dtype float32]
 
 `run` keeps the reference's option names and defaults (cmd/gogguf/run.go:17-34).  A prompt is a list
 of token ids (the tokenizer is outside this library); several -p make a batch.  Dropped: -hf
@@ -13,6 +16,9 @@ of token ids (the tokenizer is outside this library); several -p make a batch.  
 reference's REPL on token ids: one conversation, a line of new ids per turn.
 `info` prints what the reference's info prints (cmd/gogguf/info.go:27-44), `inspect` every
 configuration key and tensor (cmd/gogguf/inspect.go:13-41).  `random` is the random-weights mode.
+`dumplayers`, `comparelayers` and `layerlogits` are the reference's layer tools (cmd/tools/dumplayers.go,
+comparelayers.go, layerlogits.go) on the engine's layer taps: hidden states after the embedding and after
+every block, two such dumps compared layer by layer, and the head applied after every layer.
 """
 from __future__ import annotations
 
@@ -164,6 +170,88 @@ def cmd_compare(a) -> int:
     return 0 if (d <= a.tol).all() else 2
 
 
+def _collect_layers(folder: str, dtype: str, prompt: List[int], all_rows: bool, logits: bool = False):
+    """One prompt through an eager step with layer taps (collectLayersDump, cmd/tools/dumplayers.go:55-108):
+    the last token's rows as the reference dumps them, or every token's with `all_rows`."""
+    import gogguf_b200 as gg
+    from .engine.layers_dump import LayerCollector
+    from .engine.step import StepEntry
+    engine = gg.load(folder, gg.LoadOptions(dtype=dtype, max_tokens=len(prompt) + 64, graphs=False))
+    ctx = engine.new_context()
+    taps = LayerCollector(logits=logits)
+    slot = ctx.cache.open()
+    try:
+        want = list(range(len(prompt))) if all_rows else [len(prompt) - 1]
+        ctx.stepper.step([StepEntry(slot, prompt, want=want)], taps)
+    finally:
+        ctx.cache.close(slot)
+    return taps
+
+
+def cmd_dumplayers(a) -> int:
+    """runDumpLayers (cmd/tools/dumplayers.go:16-53): PREFIX.bin and PREFIX.json."""
+    from .engine.layers_dump import save_layers
+    from .sampling.sampler import greedy as greedy_host
+    prompt = _ids(a.p)
+    taps = _collect_layers(a.m, a.dtype, prompt, a.all)
+    dump = taps.dump()
+    save_layers(a.o, dump, model=os.path.basename(os.path.normpath(a.m)), tokens=prompt, dtype=a.dtype,
+                greedy=greedy_host(taps.final_logits[-1].tolist()))
+    print(f"wrote {a.o}.bin / {a.o}.json (embd={dump.hidden} layers={dump.layers.shape[0]} rows={dump.rows})")
+    return 0
+
+
+def cmd_comparelayers(a) -> int:
+    """runCompareLayers (cmd/tools/comparelayers.go:11-84): two dumps, or one model in float32 against
+    bfloat16 (where the reference compares its CPU path with its GPU path).  Prints the reference's lines
+    and, beyond them, rmse per layer and the first layer over the tolerance."""
+    from .engine.layers_dump import diff_layers, read_layers
+    if a.m:
+        prompt = _ids(a.p)
+        x = _collect_layers(a.m, "float32", prompt, a.all).dump()
+        y = _collect_layers(a.m, "bfloat16", prompt, a.all).dump()
+    elif a.a and a.b:
+        x, y = read_layers(a.a), read_layers(a.b)
+    else:
+        raise SystemExit("usage: gogguf_b200 comparelayers -a A.bin -b B.bin | -m DIR -p \"token ids\"")
+    d = diff_layers(x, y, a.tol)
+    e = d.embed
+    print(f"embed: max_abs={e.max_abs:.6g}@{e.max_abs_idx} mean={e.mean_abs:.6g} rmse={e.rmse:.6g} over={e.over_tol}")
+    for i, st in enumerate(d.layers):
+        if st.over_tol > 0 or a.verbose:
+            print(f"layer[{i}]: max_abs={st.max_abs:.6g}@{st.max_abs_idx} rmse={st.rmse:.6g} over={st.over_tol}")
+    w = d.worst_layer
+    total = sum(st.over_tol for st in d.layers)
+    print(f"layers: n={len(d.layers)} worst_max_abs={d.layers[w].max_abs if w >= 0 else 0.0:.6g}@layer{w} "
+          f"total_over_tol={total} (tol={a.tol:g})")
+    if e.over_tol or total:
+        first = d.first_over
+        print(f"FAIL: hidden states differ by more than the tolerance, first at "
+              f"{'the embedding' if first == -1 else f'layer {first}'}")
+        return 2
+    print("OK: hidden states of every layer are within the tolerance")
+    return 0
+
+
+def cmd_layerlogits(a) -> int:
+    """runLayerLogits (cmd/tools/layerlogits.go:31-114): the arg-max and the `--top` largest logits of the
+    last token with the final norm and head applied after every layer, as JSON."""
+    from .sampling.sampler import greedy as greedy_host
+    prompt = _ids(a.p)
+    taps = _collect_layers(a.m, a.dtype, prompt, False, logits=True)
+    case = dict(name="layer_greedy", input=prompt,
+                layer_greedy=[greedy_host(lg[-1].tolist()) for lg in taps.layer_logits])
+    if a.top > 0:
+        tops = []
+        for lg in taps.layer_logits:
+            v, i = lg[-1].topk(min(a.top, lg.shape[-1]))
+            tops.append([dict(id=int(t), logit=float(x)) for x, t in zip(v.tolist(), i.tolist())])
+        case["layer_top_logits"] = tops
+    json.dump(dict(model=os.path.basename(os.path.normpath(a.m)), cases=[case]), sys.stdout, indent=2)
+    print()
+    return 0
+
+
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="gogguf_b200", description="Qwen3 inference on B200")
     sub = ap.add_subparsers(dest="cmd")
@@ -205,6 +293,28 @@ def build_parser() -> argparse.ArgumentParser:
     c.add_argument("--tol", type=float, default=1e-4)
     c.add_argument("--vocab", type=int, default=0, help="row length, to compare arg-max per row")
     c.set_defaults(fn=cmd_compare)
+    d = sub.add_parser("dumplayers", help="hidden states after the embedding and after every layer")
+    d.add_argument("-m", required=True)
+    d.add_argument("-p", required=True, help="prompt as token ids")
+    d.add_argument("-o", required=True, help="output prefix: PREFIX.bin and PREFIX.json")
+    d.add_argument("--dtype", default="float32", choices=["bfloat16", "float32"])
+    d.add_argument("--all", action="store_true", help="every token's rows, not the last token's only")
+    d.set_defaults(fn=cmd_dumplayers)
+    cl = sub.add_parser("comparelayers", help="two layer dumps, or float32 against bfloat16 of one model")
+    cl.add_argument("-a", help="dump A (.bin)")
+    cl.add_argument("-b", help="dump B (.bin)")
+    cl.add_argument("-m", help="model folder: float32 against bfloat16")
+    cl.add_argument("-p", default="1", help="prompt as token ids, for -m")
+    cl.add_argument("--all", action="store_true", help="every token's rows, for -m")
+    cl.add_argument("--tol", type=float, default=1e-4)
+    cl.add_argument("-v", "--verbose", action="store_true", help="print every layer, not only those over the tolerance")
+    cl.set_defaults(fn=cmd_comparelayers)
+    ll = sub.add_parser("layerlogits", help="arg-max and top logits of the last token after every layer")
+    ll.add_argument("-m", required=True)
+    ll.add_argument("-p", required=True, help="prompt as token ids")
+    ll.add_argument("--top", type=int, default=5, help="largest logits per layer (0: arg-max only)")
+    ll.add_argument("--dtype", default="float32", choices=["bfloat16", "float32"])
+    ll.set_defaults(fn=cmd_layerlogits)
     return ap
 
 

@@ -79,38 +79,41 @@ class Generator:
         self.context = context
         self.default_stop = tuple(default_stop)
         self.max_batch = max_batch
-        # The prompts of a batch run in as few steps as hold this many tokens each (at least one prompt per
-        # step): the activations of a step grow with its tokens, the time of a token does not shrink beyond this.
+        # The prompts of a batch run in as few steps as hold this many tokens each (a longer prompt is cut):
+        # the activations of a step grow with its tokens, the time of a token does not shrink beyond this.
         self.prefill_tokens = prefill_tokens
 
     def _prefill(self, live: List[int], prompts, slots, cached=None):
         """The prompts of the batch, in order; returns the logits of their last tokens, one row per request.
         `cached[i]` tokens of request i are in its slot already (a conversation's earlier turns): only the
-        rest of its prompt runs."""
+        rest of its prompt runs.  A step holds at most `prefill_tokens` tokens: the prompts are packed into
+        steps in order, and a prompt that does not fit what is left of a step goes on in the next one (its
+        later tokens read its earlier ones from the cache, as a decode step does)."""
         cached = cached or {}
-        groups: List[List[int]] = []
-        cur: List[int] = []
-        used = 0
+        steps: List[List[Tuple[int, int, int]]] = [[]]      # per step: (request, first token, one past the last)
+        room = self.prefill_tokens
         for i in live:
-            n = len(prompts[i]) - cached.get(i, 0)
-            if cur and used + n > self.prefill_tokens:
-                groups.append(cur)
-                cur, used = [], 0
-            cur.append(i)
-            used += n
-        groups.append(cur)
-        outs = []
-        for g in groups:
-            entries = []
-            for i in g:
-                new = list(prompts[i][cached.get(i, 0):])
-                entries.append(StepEntry(slots[i], new, want=[len(new) - 1]))
+            a, n = cached.get(i, 0), len(prompts[i])
+            while a < n:
+                if room == 0:
+                    steps.append([])
+                    room = self.prefill_tokens
+                take = min(n - a, room)
+                steps[-1].append((i, a, a + take))
+                a += take
+                room -= take
+        outs = {}
+        for st in steps:
+            entries = [StepEntry(slots[i], list(prompts[i][a:e]), want=[e - a - 1] if e == len(prompts[i]) else [])
+                       for i, a, e in st]
             logits = self.stepper.step(entries)
-            outs.append(logits if len(groups) == 1 else logits.clone())     # a step's logits live until the next step
-        if len(outs) == 1:
-            return outs[0]
+            ends = [i for i, a, e in st if e == len(prompts[i])]
+            if len(steps) == 1:
+                return logits
+            for r, i in enumerate(ends):                     # a step's logits live until the next step
+                outs[i] = logits[r:r + 1].clone()
         import torch
-        return torch.cat(outs, dim=0)
+        return torch.cat([outs[i] for i in live], dim=0)
 
     def generate(self, prompts: Sequence[Sequence[int]], params: Optional[GenerateParams] = None,
                  held: Optional[dict] = None) -> List[GenerationResult]:
@@ -168,7 +171,7 @@ class Generator:
                    held=None) -> None:
         held = held or {}
         stop = set(self.default_stop if params.stop_token_ids is None else params.stop_token_ids)
-        sampler = make_sampler(params.sampler, params.repeat_penalty, params.repeat_last_n)
+        sampler = make_sampler(params.sampler, params.repeat_penalty, params.repeat_last_n, self.vocab_size)
         cache = self.cache
         slots, cached = {}, {}
         generated = {i: [] for i in batch}
@@ -318,7 +321,8 @@ class GenerationSession:
         key = (params.sampler, params.repeat_penalty, params.repeat_last_n)
         sampler = self._samplers.get(key)
         if sampler is None:
-            sampler = self._samplers[key] = make_sampler(params.sampler, params.repeat_penalty, params.repeat_last_n)
+            sampler = self._samplers[key] = make_sampler(params.sampler, params.repeat_penalty, params.repeat_last_n,
+                                                         self._gen.vocab_size)
         live = self._live
         hist = [self.prompts[i] + self.generated[i] for i in live] if sampler.penalised else None
         nxt = sampler.sample(self._logits, streams=live, steps=[len(self.generated[i]) for i in live], histories=hist)

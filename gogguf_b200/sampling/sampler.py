@@ -146,8 +146,20 @@ class PendingSample:
 class Sampler:
     """Samples one token per row of a [rows, vocab] float32 logits tensor."""
 
-    def __init__(self, cfg: SamplerConfig, repeat_penalty: float = 1.0, repeat_last_n: int = 64):
+    # what the top-k kernel's shared memory holds: k candidates of each 8,192-logit slice of a row, 8 bytes each
+    TOPK_SLICE, TOPK_SMEM = 8192, 160 * 1024
+
+    def __init__(self, cfg: SamplerConfig, repeat_penalty: float = 1.0, repeat_last_n: int = 64,
+                 vocab_size: Optional[int] = None):
         self.cfg = cfg
+        # The chain with a top-k has a kernel as long as the slices' candidates fit its shared memory (top-k
+        # 1,024 up to a vocabulary of 163,840); beyond that the host chain takes the rows, as it does for
+        # every configuration without a kernel.
+        self.device_chain = cfg.device_chain
+        if self.device_chain and vocab_size:
+            slices = -(-int(vocab_size) // self.TOPK_SLICE)
+            self.device_chain = slices * min(cfg.top_k, int(vocab_size)) * 8 <= self.TOPK_SMEM
+        self.on_device = cfg.on_device and (self.device_chain or not cfg.device_chain)
         self.repeat_penalty = float(repeat_penalty)
         self.repeat_last_n = int(repeat_last_n) if repeat_last_n else 64   # 0 means 64 (session.go:87-91)
         self._out: Optional[torch.Tensor] = None
@@ -159,13 +171,13 @@ class Sampler:
     @property
     def device_only(self) -> bool:
         """True when every row can be sampled by kernels alone (with a repeat penalty: after `begin`)."""
-        return self.cfg.on_device and (not self.penalised or self._rings is not None)
+        return self.on_device and (not self.penalised or self._rings is not None)
 
     def begin(self, streams: Sequence[int], prompts: Sequence[Sequence[int]], device) -> None:
         """Put the last `repeat_last_n` ids of each request's prompt on the device, one ring per request, so
         that the penalty can be applied, and every sampled id appended, without the host.  Only needed (and
         only done) with a repeat penalty and a configuration whose sampling runs on the device."""
-        if not (self.penalised and self.cfg.on_device):
+        if not (self.penalised and self.on_device):
             return
         n, rows = self.repeat_last_n, len(streams)
         hist = torch.full((rows, n), -1, dtype=torch.int32)
@@ -212,7 +224,7 @@ class Sampler:
             u_host[:rows] = torch.tensor([uniform01(self.cfg.seed, s, k) for s, k in zip(streams, steps)],
                                          dtype=torch.float64)
             u_dev[:rows].copy_(u_host[:rows], non_blocking=True)
-            if self.cfg.device_chain:
+            if self.device_chain:
                 K.sample_topk(logits, self.cfg.temp, self.cfg.top_k, self.cfg.top_p, self.cfg.min_p, u_dev, out, rows)
             else:
                 temps[:rows].fill_(float(self.cfg.temp))
@@ -234,7 +246,7 @@ class Sampler:
         `histories[r]`: prompt + generated ids (only read when a repeat penalty is set)."""
         rows = len(streams)
         us = [uniform01(self.cfg.seed, s, k) for s, k in zip(streams, steps)]
-        if logits.is_cuda and self.cfg.on_device and not self.penalised:
+        if logits.is_cuda and self.on_device and not self.penalised:
             from ..csrc import kernels as K
             if self._out is None or self._out.numel() < rows:
                 self._out = torch.empty(max(rows, 64), dtype=torch.int32, device=logits.device)
@@ -243,7 +255,7 @@ class Sampler:
                 K.argmax(logits, out, rows)
             else:
                 uni = torch.tensor(us, dtype=torch.float64).to(logits.device, non_blocking=True)
-                if self.cfg.device_chain:
+                if self.device_chain:
                     K.sample_topk(logits, self.cfg.temp, self.cfg.top_k, self.cfg.top_p, self.cfg.min_p, uni, out, rows)
                 else:
                     temps = torch.full((rows,), float(self.cfg.temp), dtype=torch.float32).to(logits.device, non_blocking=True)
@@ -308,10 +320,11 @@ class FunctionSampler:
         return res
 
 
-def make_sampler(sampler, repeat_penalty: float = 1.0, repeat_last_n: int = 64):
-    """The sampler of a request: a `SamplerConfig` gives the chain, a function is called as it is."""
+def make_sampler(sampler, repeat_penalty: float = 1.0, repeat_last_n: int = 64, vocab_size: Optional[int] = None):
+    """The sampler of a request: a `SamplerConfig` gives the chain, a function is called as it is.
+    `vocab_size`, where known, lets the sampler decide at once which of its kernels take rows of that length."""
     if isinstance(sampler, SamplerConfig):
-        return Sampler(sampler, repeat_penalty, repeat_last_n)
+        return Sampler(sampler, repeat_penalty, repeat_last_n, vocab_size)
     if callable(sampler):
         return FunctionSampler(sampler, repeat_penalty, repeat_last_n)
     raise TypeError(f"a sampler is a SamplerConfig or a function of a row of logits, not {type(sampler).__name__}")

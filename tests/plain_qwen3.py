@@ -116,7 +116,7 @@ def softmax_rows(s: torch.Tensor, wide: bool = False) -> torch.Tensor:
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: Optional[int] = None,
-              wide: bool = False) -> torch.Tensor:
+              wide: bool = False, q_pos: Optional[Sequence[int]] = None) -> torch.Tensor:
     """Causal grouped-query attention over one whole sequence.
 
     q[T, heads, d], k and v [T, kv_heads, d] (k already normed and rotated, v raw).
@@ -124,23 +124,31 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: Optiona
     score = dot(q, k) * float32(1/sqrt(d)) (:24,:33); softmax over the visible keys;
     out = sum_t p_t * v_t (:38-43).  A token sees keys 0..pos, itself included
     (pkg/model/qwen3/model.go:244-246); with a window w only the last w of them.
+
+    `q_pos`: q holds only the queries at these positions (for long sequences of which a few rows are
+    wanted); default: one query per key.  Queries are taken in blocks so that a long sequence fits.
     """
-    T, H, d = q.shape
+    Tk = k.shape[0]
+    Tq, H, d = q.shape
     G = H // k.shape[1]
     dt = torch.float64 if wide else torch.float32
     scale = torch.tensor(1.0 / math.sqrt(d), dtype=dt)
-    i = torch.arange(T)[:, None]
-    j = torch.arange(T)[None, :]
-    visible = j <= i
-    if window is not None:
-        visible &= j > i - window
-    out = torch.empty(T, H, d, dtype=dt)
-    for h in range(H):
-        g = h // G
-        s = (q[:, h, :].to(dt) @ k[:, g, :].to(dt).T) * scale
-        s = s.masked_fill(~visible, float("-inf"))
-        p = softmax_rows(s, wide)
-        out[:, h, :] = p.to(dt) @ v[:, g, :].to(dt)
+    pos = torch.arange(Tk) if q_pos is None else torch.as_tensor(list(q_pos), dtype=torch.long)
+    j = torch.arange(Tk)[None, :]
+    out = torch.empty(Tq, H, d, dtype=dt)
+    kt, vt = k.to(dt), v.to(dt)
+    block = max(1, min(Tq, (1 << 24) // max(Tk, 1)))
+    for a in range(0, Tq, block):
+        i = pos[a:a + block, None]
+        visible = j <= i
+        if window is not None:
+            visible &= j > i - window
+        for h in range(H):
+            g = h // G
+            s = (q[a:a + block, h, :].to(dt) @ kt[:, g, :].T) * scale
+            s = s.masked_fill(~visible, float("-inf"))
+            p = softmax_rows(s, wide)
+            out[a:a + block, h, :] = p.to(dt) @ vt[:, g, :]
     return out
 
 
@@ -159,8 +167,9 @@ def swiglu_ffn(h: torch.Tensor, w_gate, w_up, w_down, wide: bool = False) -> tor
     return (silu(g, wide) * u) @ w_down.to(dt).T
 
 
-def attention_mixer(h, w, prefix, c, positions, window, wide=False):
+def attention_mixer(h, w, prefix, c, positions, window, wide=False, rows=None):
     """q,k,v projections, per-head q/k RMSNorm, rotary, attention, output projection.
+    `rows`: compute the output only for these rows of h (keys and values still come from all rows).
 
     pkg/model/qwen3/model.go:215-260: no bias (:215-225); each head's slice is normed with one
     [d] weight shared by the heads and the model's eps (:227-233, :663-676) BEFORE the rotation
@@ -169,23 +178,31 @@ def attention_mixer(h, w, prefix, c, positions, window, wide=False):
     dt = torch.float64 if wide else torch.float32
     T = h.shape[0]
     d = c["head_dim"]
-    q = (h.to(dt) @ w[prefix + "q_proj.weight"].to(dt).T).reshape(T, c["heads"], d)
+    hq = h if rows is None else h[list(rows)]
+    q = (hq.to(dt) @ w[prefix + "q_proj.weight"].to(dt).T).reshape(hq.shape[0], c["heads"], d)
     k = (h.to(dt) @ w[prefix + "k_proj.weight"].to(dt).T).reshape(T, c["kv_heads"], d)
     v = (h.to(dt) @ w[prefix + "v_proj.weight"].to(dt).T).reshape(T, c["kv_heads"], d)
     q = rms_norm(q, w[prefix + "q_norm.weight"], c["eps"], wide)
     k = rms_norm(k, w[prefix + "k_norm.weight"], c["eps"], wide)
     cos, sin = rope_tables(positions, d, c["theta"])
-    q = rope_neox(q, cos, sin, wide)
     k = rope_neox(k, cos, sin, wide)
-    o = attention(q, k, v, window, wide).reshape(T, c["heads"] * d)
-    return o @ w[prefix + "o_proj.weight"].to(dt).T
+    if rows is None:
+        q = rope_neox(q, cos, sin, wide)
+        o = attention(q, k, v, window, wide)
+    else:
+        idx = list(rows)
+        q = rope_neox(q, cos[idx], sin[idx], wide)
+        o = attention(q, k, v, window, wide, q_pos=[positions[r] for r in idx])
+    return o.reshape(-1, c["heads"] * d) @ w[prefix + "o_proj.weight"].to(dt).T
 
 
-def block(x, w, layer, c, positions, wide=False):
-    """One pre-norm block with two residual adds (pkg/model/qwen3/model.go:198-288)."""
+def block(x, w, layer, c, positions, wide=False, rows=None):
+    """One pre-norm block with two residual adds (pkg/model/qwen3/model.go:198-288).
+    `rows`: return only these rows (the attention still reads every row's keys and values)."""
     p = f"model.layers.{layer}."
     h = rms_norm(x, w[p + "input_layernorm.weight"], c["eps"], wide)
-    x = x + attention_mixer(h, w, p + "self_attn.", c, positions, c["windows"][layer], wide)
+    a = attention_mixer(h, w, p + "self_attn.", c, positions, c["windows"][layer], wide, rows)
+    x = (x if rows is None else x[list(rows)]) + a
     h = rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"], wide)
     x = x + swiglu_ffn(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                        w[p + "mlp.down_proj.weight"], wide)
@@ -193,8 +210,9 @@ def block(x, w, layer, c, positions, wide=False):
 
 
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], wide: bool = False,
-            taps: Optional[list] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence starting at position 0.
+            taps: Optional[list] = None, rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence starting at position 0 (`rows`: only of these positions;
+    the last block and the head then run on those rows alone, which keeps long sequences affordable).
 
     pkg/model/qwen3/model.go:112-167 (embed, blocks in order) and :578-610 (final norm, then
     the head, which is the embedding matrix when no separate head exists, tensors.go:36-48).
@@ -207,7 +225,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], wide: 
         taps.append(x.clone())
     positions = list(range(len(tokens)))
     for layer in range(c["layers"]):
-        x = block(x, w, layer, c, positions, wide)
+        x = block(x, w, layer, c, positions, wide, rows if layer == c["layers"] - 1 else None)
         if taps is not None:
             taps.append(x.clone())
     h = rms_norm(x, w["model.norm.weight"], c["eps"], wide)

@@ -30,7 +30,7 @@ class ScriptedStepper:
                 rows.append(row)
         self.cache.commit(slots, counts)
         self.cache.check()
-        return torch.stack(rows)
+        return torch.stack(rows) if rows else None
 
 
 def gen(stepper, context=1000, **kw):
@@ -135,7 +135,8 @@ def test_temperature_draws_do_not_depend_on_the_batch():
 
 def test_prompts_of_a_large_batch_run_in_several_steps():
     """The prompts of a batch start together but need not share one step: a step holds at most `prefill_tokens`
-    tokens (and at least one prompt), the results are those of one step, and decoding begins after the last."""
+    tokens (a longer prompt is cut and goes on from the cache), the results are those of one step, and decoding
+    begins after the last."""
     prompts = [[1, 2, 3, 4, 5], [7, 8], [2] * 6, [9], [4, 4, 4]]
     one = ScriptedStepper()
     want = gen(one).generate(prompts, GenerateParams(max_tokens=3))
@@ -147,6 +148,16 @@ def test_prompts_of_a_large_batch_run_in_several_steps():
     assert one.steps[0] == [(s, n) for s, n in one.steps[0]] and len(one.steps[0]) == 5  # by default: one step
     st.cache.check()
     assert st.cache.live_slots == 0
+    # prompts longer than a step: 10 and 3 tokens in steps of 4 -> 4 | 4 | 2 + 2 | 1, the logits of each
+    # request taken from the step that holds its last token
+    prompts = [list(range(1, 11)), [5, 6, 7]]
+    st = ScriptedStepper()
+    out = gen(st, prefill_tokens=4).generate(prompts, GenerateParams(max_tokens=2))
+    assert [r.tokens for r in out] == [[11, 12], [8, 9]]
+    assert [[n for _, n in step] for step in st.steps[:4]] == [[4], [4], [2, 2], [1]]
+    assert st.steps[2][0][0] == st.steps[0][0][0] and st.steps[3][0][0] == st.steps[2][1][0]
+    assert [n for _, n in st.steps[4]] == [1, 1]
+    st.cache.check()
 
 
 # ----------------------------------------------------------------------------- conversations

@@ -236,3 +236,68 @@ def test_step_by_step_session_equals_the_loop(tmp_path_factory):
     sess.close()
     ctx.cache.check()
     assert ctx.cache.live_slots == 0
+
+
+@pytest.mark.parametrize("name", ["L", "M"])
+def test_bfloat16_one_step_ahead_loop_on_the_tensor_core_path(tmp_path_factory, name, monkeypatch):
+    """bfloat16 through `Context.generate`: captured decode steps, padded batch buckets, ids fed from the
+    device, sampling kernels.  The ids equal those of the plain loop over the eager stepper on the same model,
+    and the logits the loop sampled from, at every fed position, lie within the bfloat16 bound of the plain
+    implementation on the sequence that was generated."""
+    import gogguf_b200 as gg
+    from gogguf_b200.engine import Stepper
+    from gogguf_b200.engine.generate import Generator
+    from gogguf_b200.sampling.sampler import Sampler
+    folder = make_folder(tmp_path_factory.getbasetemp(), name, "bfloat16", scale=4.0)
+    cfg, w = read_folder(folder)
+    V = cfg["vocab_size"]
+    prompts = [random_tokens(V, n, 70 + n) for n in (140, 3, 66, 31, 9)]       # five rows in a bucket of eight
+    engine = gg.load(folder, gg.LoadOptions(dtype="bfloat16", max_tokens=4096))
+    seen = []
+    real = Sampler.sample_async
+
+    def spy(self, logits, streams, steps):
+        seen.append((list(streams), list(steps), logits[:len(streams)].clone()))
+        return real(self, logits, streams, steps)
+
+    monkeypatch.setattr(Sampler, "sample_async", spy)
+    n_new = 40
+    params = gg.GenerateParams(max_tokens=n_new, stop_token_ids=[])
+    ctx = engine.new_context()
+    ahead = ctx.generate(prompts, params)
+    assert ctx.stepper.replays >= n_new - 1 and len(seen) == n_new
+    monkeypatch.setattr(Sampler, "sample_async", real)
+    model = engine.model
+    slow = Generator(Stepper(model, model.new_cache(4096)), V, model.spec.max_positions).generate(prompts, params)
+    assert [r.tokens for r in ahead] == [r.tokens for r in slow]
+    oracle = [plain.forward(cfg, w, p + r.tokens, wide=True) for p, r in zip(prompts, ahead)]
+    for streams, steps, logits in seen:
+        for row, (i, k) in enumerate(zip(streams, steps)):
+            at = len(prompts[i]) - 1 + k              # the position whose logits the k-th new token was sampled from
+            assert rel_err(logits[row:row + 1], oracle[i][at:at + 1]) < TOL_BF16, (i, k)
+    # a seeded top-k chain with a repeat penalty, all on the device: the same ids from both loops
+    params = gg.GenerateParams(max_tokens=12, stop_token_ids=[], repeat_penalty=1.2,
+                               sampler=gg.SamplerConfig(temp=0.8, top_k=12, top_p=0.9, seed=4))
+    a = engine.new_context().generate(prompts, params)
+    b = Generator(Stepper(model, model.new_cache(4096)), V, model.spec.max_positions).generate(prompts, params)
+    assert [r.tokens for r in a] == [r.tokens for r in b]
+
+
+def test_top_k_beyond_the_kernels_shared_memory_falls_back_to_the_host_chain():
+    """top-k 1,024 over more than 163,840 ids does not fit the top-k kernel: the sampler answers from the host
+    chain instead of raising, id for id what the plain sampler gives."""
+    from gogguf_b200.sampling import Sampler, SamplerConfig
+    V = 170000
+    logits = torch.randn(3, V, generator=torch.Generator().manual_seed(1)) * 3
+    cfg = SamplerConfig(temp=0.9, top_k=1024, top_p=0.95, seed=3)
+    s = Sampler(cfg, vocab_size=V)
+    assert not s.device_chain and not s.device_only
+    got = s.sample(logits.cuda(), [0, 1, 2], [5, 5, 5])
+    for r in range(3):
+        assert got[r] == plain.sample(logits[r].tolist(), 0.9, 1024, 0.95, 0.0, plain.uniform01(3, r, 5))
+    # and within the limit the kernel gives the same ids as the host chain
+    V2 = 163840
+    s2 = Sampler(cfg, vocab_size=V2)
+    assert s2.device_chain
+    l2 = logits[:, :V2].contiguous()
+    assert s2.sample(l2.cuda(), [0, 1, 2], [5, 5, 5]) == Sampler(cfg).sample(l2, [0, 1, 2], [5, 5, 5])

@@ -3,6 +3,8 @@ than the engine's (odd widths, head sizes in steps of 16, vocabularies that are 
 import math
 import os
 
+from types import SimpleNamespace
+
 import pytest
 import torch
 
@@ -660,6 +662,55 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge(kind):
             assert float((last - 5.0).abs().max()) < 0.05, (window, hot)     # all weight on the hot key
         else:
             assert float(last.abs().max()) < 4.0, (window, hot)              # the hot key is outside the window
+
+
+@pytest.mark.parametrize("nq,nkv,d,ctxs", [(8, 2, 128, [20000]), (8, 2, 128, [5000, 9000, 333]), (16, 4, 64, [9000]),
+                                          (32, 8, 128, [20000, 70, 5000]), (4, 1, 128, [40000])])
+def test_attention_decode_reads_every_page_of_a_long_context(nq, nkv, d, ctxs):
+    """Among thousands of random keys a page that is skipped, or read twice, changes the output by less than
+    the bfloat16 bound.  So every query head is given one key that takes all the weight (the key points where
+    the head's query points, sixty times as long), each head its own, and from launch to launch these keys
+    move on so that every page of every sequence is, once, the page that holds a head's only key.  The head's
+    output must then be that position's value row.  Both through the sizes an eager step passes and through
+    the bound a captured step passes (the page-table width rounded up to a power of two)."""
+    from gogguf_b200.csrc import fast_attention as fa
+    from gogguf_b200.csrc import tcgen05_gemm as tc
+    dt = torch.bfloat16
+    seqs = [(c, 1) for c in ctxs]
+    kp, vp, table, ks, vs = make_paged(seqs, nkv, d, dt, seed=21)
+    pos, sot, cu, cl = step_meta(seqs)
+    T, G = len(ctxs), nq // nkv
+    scale = 1.0 / math.sqrt(d)
+    q = torch.randn(T, nq, d, device=DEV, generator=torch.Generator(device=DEV).manual_seed(22)).to(dt)
+    run = fa.try_make(nq, nkv, d, scale, 0)
+    n_pages = [(c + 63) // 64 for c in ctxs]
+    width_bound = 64 * (1 << (max(n_pages) - 1).bit_length())
+    rng = torch.Generator().manual_seed(23)
+    launches = (max(n_pages) + nq - 1) // nq
+    for r in range(launches):
+        saved, expect = [], {}
+        for b, c in enumerate(ctxs):
+            for h in range(nq):
+                pg = (r * nq + h) % n_pages[b]
+                off = int(torch.randint(0, min(64, c - pg * 64), (1,), generator=rng))
+                page = int(table[b, pg])
+                if any(sv[0] == page and sv[1] == h // G and sv[2] == off for sv in saved):
+                    continue                                   # two heads of a group drew the same place: the first keeps it
+                saved.append((page, h // G, off, kp[page, h // G, off].clone()))
+                qh = q[b, h].float()
+                kp[page, h // G, off] = (60.0 * qh / qh.norm()).to(dt)
+                expect[(b, h)] = vp[page, h // G, off].float()
+        for max_ctx in (max(ctxs), width_bound):
+            ctx = SimpleNamespace(n_tokens=T, n_seqs=T, decode=True, max_ctx=max_ctx, max_new=1, positions=pos,
+                                  seq_of_token=sot, cu_seqlens=cu, ctx_lens=cl)
+            out = torch.full((T, nq, d), float("nan"), device=DEV, dtype=dt)
+            run(q, kp, vp, out, ctx, table, 64)
+            tc.check_status(DEV)
+            for (b, h), v in expect.items():
+                err = float((out[b, h].float() - v).abs().max())
+                assert err < 0.05, (r, b, h, max_ctx, err)
+        for page, g, off, old in saved:
+            kp[page, g, off] = old
 
 
 # ------------------------------------------------------------------------------------------ sampling chain

@@ -19,11 +19,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 class Trace:
-    def __init__(self, folder, dtype, out, max_tokens):
+    def __init__(self, folder, dtype, out, max_tokens, extra=()):
         self.out = str(out)
         self.p = subprocess.Popen(
             [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
-             "--out", self.out, "--max-tokens", str(max_tokens)],
+             "--out", self.out, "--max-tokens", str(max_tokens), *extra],
             stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
         self.n = 0
 
@@ -46,10 +46,14 @@ class Trace:
         assert self.p.wait(timeout=60) == 0
 
 
-@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("W", "float32"),
-                                        ("A", "bfloat16"), ("B", "bfloat16"), ("W", "bfloat16"),
-                                        ("M", "bfloat16"), ("M", "float32"), ("L", "bfloat16")])
-def test_replay_shapes(tmp_path_factory, tmp_path, name, dtype):
+# By default replay steps through generation's own stepper, which replays plain decode steps as captured CUDA
+# graphs (padded to a batch bucket, integer inputs in a fixed device buffer); --no-graphs runs every step eagerly.
+@pytest.mark.parametrize("name,dtype,extra", [
+    ("A", "float32", ()), ("B", "float32", ()), ("W", "float32", ()),
+    ("A", "bfloat16", ()), ("B", "bfloat16", ()), ("W", "bfloat16", ()),
+    ("M", "bfloat16", ()), ("M", "float32", ()), ("L", "bfloat16", ()),
+    ("B", "float32", ("--no-graphs",)), ("W", "bfloat16", ("--no-graphs",)), ("L", "bfloat16", ("--no-graphs",))])
+def test_replay_shapes(tmp_path_factory, tmp_path, name, dtype, extra):
     store = "float32" if dtype == "float32" else "bfloat16"
     folder = make_folder(tmp_path_factory.getbasetemp(), name, store, scale=1.0 if dtype == "float32" else 4.0)
     cfg, w = read_folder(folder)
@@ -59,7 +63,7 @@ def test_replay_shapes(tmp_path_factory, tmp_path, name, dtype):
     reqs = {f"r{i}": random_tokens(V, n, seed=10 + i) for i, n in enumerate(lens)}
     oracle = {k: plain.forward(cfg, w, t, wide=True) for k, t in reqs.items()}
     # the cache holds two batches' worth at most: slots and pages must be reused
-    tr = Trace(folder, dtype, tmp_path / "out", max_tokens=3 * 64 + 2 * 64 + 64)
+    tr = Trace(folder, dtype, tmp_path / "out", max_tokens=3 * 64 + 2 * 64 + 64, extra=extra)
     try:
         # (1) each request alone and whole, every position wanted
         for k, t in reqs.items():
@@ -106,3 +110,37 @@ def test_replay_refuses_what_does_not_fit(tmp_path_factory, tmp_path):
                        input=json.dumps({"step": 0, "entries": [{"id": "a", "tokens": [1] * 65, "want": [0]}],
                                          "end": []}) + "\n", capture_output=True, text=True)
     assert p.returncode != 0 and "pages" in p.stderr
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("M", "bfloat16")])
+def test_replay_writes_the_layers_of_the_wanted_places(tmp_path_factory, tmp_path, name, dtype):
+    """--layers: hidden states after the embedding and after every block, beside the logits, for prompts and
+    for decode steps (which then run eagerly), against the plain implementation's taps."""
+    sys.path.insert(0, ROOT)
+    from gogguf_b200.engine.layers_dump import read_layers
+    store = "float32" if dtype == "float32" else "bfloat16"
+    folder = make_folder(tmp_path_factory.getbasetemp(), name, store, scale=1.0 if dtype == "float32" else 4.0)
+    cfg, w = read_folder(folder)
+    tol = TOL_F32 if dtype == "float32" else TOL_BF16
+    toks = {k: random_tokens(cfg["vocab_size"], n, seed=60 + n) for k, n in (("a", 70), ("b", 12))}
+    taps = {}
+    for k, t in toks.items():
+        taps[k] = []
+        plain.forward(cfg, w, t, wide=True, taps=taps[k])
+    tr = Trace(folder, dtype, tmp_path / "out", max_tokens=256, extra=("--layers",))
+    try:
+        tr.step([{"id": "a", "tokens": toks["a"][:-1], "want": [0, 40]}, {"id": "b", "tokens": toks["b"][:-1], "want": [10]}])
+        d = read_layers(os.path.join(tr.out, "0.layers.bin"))
+        assert d.layers.shape == (cfg["num_hidden_layers"], 3, cfg["hidden_size"]) and d.embed.shape == d.layers.shape[1:]
+        for layer in range(-1, cfg["num_hidden_layers"]):
+            got = torch.from_numpy(d.embed if layer < 0 else d.layers[layer])
+            want = torch.stack([taps["a"][layer + 1][0], taps["a"][layer + 1][40], taps["b"][layer + 1][10]])
+            assert rel_err(got, want) < tol, layer
+        tr.step([{"id": "a", "tokens": toks["a"][-1:], "want": [0]}, {"id": "b", "tokens": toks["b"][-1:], "want": [0]}],
+                end=["a", "b"])
+        d = read_layers(os.path.join(tr.out, "1.layers.bin"))
+        for layer in range(cfg["num_hidden_layers"]):
+            want = torch.stack([taps["a"][layer + 1][-1], taps["b"][layer + 1][-1]])
+            assert rel_err(torch.from_numpy(d.layers[layer]), want) < tol, layer
+    finally:
+        tr.close()

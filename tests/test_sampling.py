@@ -64,3 +64,20 @@ def test_repeat_penalty():
     p = x.tolist()
     plain.repeat_penalty(p, [0, 1, 1, 9, -1], 2.0, 64)
     assert p == y.tolist()
+
+
+def test_a_top_k_chain_too_wide_for_the_kernel_goes_to_the_host_chain():
+    """The top-k kernel keeps k candidates per 8,192-logit slice in 160 KB of shared memory: top-k 1,024 fits a
+    vocabulary of up to 163,840 ids.  Beyond that the sampler must not ask the kernel (which refuses) but run
+    the host chain, and say so before the loop decides to stay a step ahead."""
+    from gogguf_b200.sampling import Sampler, SamplerConfig
+    cfg = SamplerConfig(temp=0.7, top_k=1024, seed=1)
+    assert Sampler(cfg, vocab_size=151936).device_chain and Sampler(cfg, vocab_size=151936).device_only
+    wide = Sampler(cfg, vocab_size=163841)
+    assert not wide.device_chain and not wide.on_device and not wide.device_only
+    assert Sampler(SamplerConfig(temp=0.7, top_k=40), vocab_size=400000).device_chain      # 49 slices x 40 fit
+    assert Sampler(SamplerConfig(temp=0.7), vocab_size=400000).on_device                   # plain temperature
+    # on the CPU the host chain answers whatever the sizes
+    import torch
+    logits = torch.randn(2, 300)
+    assert Sampler(cfg, vocab_size=300).sample(logits, [0, 1], [0, 0]) == Sampler(cfg).sample(logits, [0, 1], [0, 0])
