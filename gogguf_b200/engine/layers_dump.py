@@ -89,7 +89,7 @@ def read_layers(path: str) -> LayersDump:
         if magic != MAGIC:
             raise ValueError(f"{path}: not a layers dump (magic {magic!r}, expected {MAGIC!r})")
         hidden, n_layers, rows = struct.unpack("<III", f.read(12))
-        data = np.frombuffer(f.read(), dtype="<f4")
+        data = np.frombuffer(f.read(), dtype="<f4").copy()
     want = (1 + n_layers) * rows * hidden
     if data.size != want:
         raise ValueError(f"{path}: holds {data.size} values, its header says {want}")

@@ -269,18 +269,38 @@ def test_bfloat16_one_step_ahead_loop_on_the_tensor_core_path(tmp_path_factory, 
     monkeypatch.setattr(Sampler, "sample_async", real)
     model = engine.model
     slow = Generator(Stepper(model, model.new_cache(4096)), V, model.spec.max_positions).generate(prompts, params)
-    assert [r.tokens for r in ahead] == [r.tokens for r in slow]
     oracle = [plain.forward(cfg, w, p + r.tokens, wide=True) for p, r in zip(prompts, ahead)]
     for streams, steps, logits in seen:
         for row, (i, k) in enumerate(zip(streams, steps)):
             at = len(prompts[i]) - 1 + k              # the position whose logits the k-th new token was sampled from
             assert rel_err(logits[row:row + 1], oracle[i][at:at + 1]) < TOL_BF16, (i, k)
-    # a seeded top-k chain with a repeat penalty, all on the device: the same ids from both loops
-    params = gg.GenerateParams(max_tokens=12, stop_token_ids=[], repeat_penalty=1.2,
-                               sampler=gg.SamplerConfig(temp=0.8, top_k=12, top_p=0.9, seed=4))
-    a = engine.new_context().generate(prompts, params)
-    b = Generator(Stepper(model, model.new_cache(4096)), V, model.spec.max_positions).generate(prompts, params)
-    assert [r.tokens for r in a] == [r.tokens for r in b]
+            assert ahead[i].tokens[k] == int(logits[row].argmax()), (i, k)
+    # The eager loop runs the same kernels on batches that are not padded and with the true lengths as the bound
+    # of the attention's splits, so its bfloat16 logits differ from the captured steps' in the last bits.  The ids
+    # are the same until two candidates lie that close together; from there the sequences are different texts.
+    for i, (a, b) in enumerate(zip(ahead, slow)):
+        k = next((k for k in range(n_new) if a.tokens[k] != b.tokens[k]), None)
+        if k is None:
+            continue
+        row = oracle[i][len(prompts[i]) - 1 + k]
+        top = float(row.abs().max())
+        assert abs(float(row[a.tokens[k]] - row[b.tokens[k]])) < TOL_BF16 * top, (i, k)
+        assert float(row.max() - row[a.tokens[k]]) < TOL_BF16 * top, (i, k)
+    assert sum(a.tokens == b.tokens for a, b in zip(ahead, slow)) >= 2
+    # a seeded top-k chain with a repeat penalty, all on the device and a step ahead: every id is what the plain
+    # sampler draws from the very logits the kernels saw
+    seen.clear()
+    monkeypatch.setattr(Sampler, "sample_async", spy)
+    sc = gg.SamplerConfig(temp=0.8, top_k=12, top_p=0.9, seed=4)
+    params = gg.GenerateParams(max_tokens=12, stop_token_ids=[], repeat_penalty=1.2, sampler=sc)
+    out = engine.new_context().generate(prompts, params)
+    monkeypatch.setattr(Sampler, "sample_async", real)
+    assert len(seen) == 12
+    for streams, steps, logits in seen:
+        for row, (i, k) in enumerate(zip(streams, steps)):
+            lg = logits[row].float().tolist()
+            plain.repeat_penalty(lg, prompts[i] + out[i].tokens[:k], 1.2, 64)
+            assert out[i].tokens[k] == plain.sample(lg, 0.8, 12, 0.9, 0.0, plain.uniform01(4, i, k)), (i, k)
 
 
 def test_top_k_beyond_the_kernels_shared_memory_falls_back_to_the_host_chain():

@@ -79,12 +79,17 @@ def test_layer_tools_of_the_command_line(tmp_path_factory, tmp_path):
     meta = json.load(open(pa + ".json"))
     assert meta["greedy"] == int(want[-1].argmax()) and meta["tokens"] == toks and len(meta["layer_rms"]) == d.layers.shape[0]
     assert abs(meta["layer_rms"][-1] - float(want_taps[-1][-1].pow(2).mean().sqrt())) < 1e-4
-    # float32 against bfloat16 of the same weights: within a loose tolerance, not within a tight one
+    # float32 against bfloat16 of the same weights: within a tolerance above their largest difference, not
+    # within one below it; the difference itself is small against the hidden states
+    from gogguf_b200.engine.layers_dump import diff_layers
+    dd = diff_layers(d, read_layers(pb + ".bin"), 0.0)
+    worst = max(st.max_abs for st in dd.layers)
+    assert 0 < worst < 0.05 * float(abs(d.layers).max())
     out = io.StringIO()
     with redirect_stdout(out):
-        assert cli.main(["comparelayers", "-a", pa + ".bin", "-b", pb + ".bin", "--tol", "0.5"]) == 0
+        assert cli.main(["comparelayers", "-a", pa + ".bin", "-b", pb + ".bin", "--tol", str(2 * worst)]) == 0
         assert cli.main(["comparelayers", "-a", pa + ".bin", "-b", pb + ".bin", "--tol", "1e-6"]) == 2
-        assert cli.main(["comparelayers", "-m", folder, "-p", ids, "--tol", "0.5", "-v"]) == 0
+        assert cli.main(["comparelayers", "-m", folder, "-p", ids, "--tol", str(2 * worst), "-v"]) == 0
     text = out.getvalue()
     assert "OK: hidden states" in text and "FAIL" in text and "first at layer 0" in text and "layer[2]:" in text
     out = io.StringIO()
