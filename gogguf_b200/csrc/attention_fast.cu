@@ -110,7 +110,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
     const bf16* q, const bf16* k_pool, const bf16* v_pool,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-    const int* __restrict__ page_table, int max_pages, int nq, int nkv, float scale_log2, int window, int nsplit) {
+    const int* __restrict__ page_table, int max_pages, int nq, int nkv, float scale_log2, int window, int nsplit,
+    const PageBounds pb) {
     pdl_launch();
     pdl_wait();
     constexpr int NCH = D / 32;      // 32-wide chunks of the head dimension for Q.K^T
@@ -155,7 +156,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
         const int* pt = page_table + (size_t)b * max_pages;
         for (int kt = t_begin + warp; kt < t_end; kt += 4) {
             const int key0 = kt << 4;
-            const int page = pt[key0 / PAGE];
+            const int page = gg_page(pt, key0 / PAGE, max_pages, pb, 42);
             const size_t base = (((size_t)page * nkv + kvh) * PAGE + (key0 % PAGE)) * D;
             // ---- S = Q K^T for 16 keys (two n-tiles of 8)
             float s[2][4];
@@ -319,7 +320,8 @@ template <int D>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(
     const bf16* q, const bf16* k_pool, const bf16* v_pool, bf16* __restrict__ out,
     const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens, const int* __restrict__ seq_of_token,
-    const int* __restrict__ page_table, int max_pages, int n_seqs, int nq, int nkv, float scale_log2, int window) {
+    const int* __restrict__ page_table, int max_pages, int n_seqs, int nq, int nkv, float scale_log2, int window,
+    const PageBounds pb) {
     pdl_wait();      // no early release of the next kernel: many waves of CTAs that exclude its CTAs from their SMs
     constexpr int CH = D / 8;        // 16-byte chunks per row
     constexpr int KS = D / 16;       // k-steps of Q.K^T
@@ -359,7 +361,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
         else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
     auto load_kv = [&](int kt, int stage) {
-        const size_t base = (((size_t)pt[kt] * nkv + kvh) * PAGE) * D;
+        const size_t base = (((size_t)gg_page(pt, kt, max_pages, pb, 43) * nkv + kvh) * PAGE) * D;
         bf16* kd = Ks + stage * 64 * D;
         bf16* vd = Vs + stage * 64 * D;
         for (int idx = threadIdx.x; idx < 64 * CH; idx += 128) {
@@ -503,8 +505,11 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
     const bf16* q, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int nq, int nkv, float scale_log2, int window, int nsplit,
-    int cluster_reduce, int* __restrict__ status) {
-    pdl_launch();
+    int cluster_reduce, int early_release, int n_pages, int* __restrict__ status) {
+    // A grid that is resident as a whole lets the next kernel's CTAs in at once: they share the SMs' free
+    // shared memory and start fetching weights.  A grid of several waves releases only after its pages (the
+    // rule on dependent launches in common.cuh): until then its own waiting CTAs should get the SMs.
+    if (early_release) pdl_launch();
     constexpr int HALVES = D / 64;
     constexpr int BOX_BYTES = 64 * 64 * 2;                 // 8 KB
     constexpr int STAGE_BYTES = 2 * HALVES * BOX_BYTES;    // K halves then V halves
@@ -564,7 +569,7 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
                 if (!waited && p_begin + i >= newest) { pdl_wait(); waited = true; }
                 if (!tma::mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, 11)) break;
                 tma::mbar_expect_tx(&full[s], STAGE_BYTES);
-                const int row = (pt[p_begin + i] * nkv + kvh) * PAGE;
+                const int row = (gg_page(pt, p_begin + i, max_pages, PageBounds{n_pages, status}, 44) * nkv + kvh) * PAGE;
                 uint8_t* dst = smem + s * STAGE_BYTES;
 #pragma unroll
                 for (int hf = 0; hf < HALVES; ++hf) {
@@ -648,6 +653,7 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
         }
     }
     pdl_wait();               // (returns at once where it was already called) the output buffer is free from here
+    if (!early_release) pdl_launch();
     __syncthreads();          // all pages consumed (or the CTA gave up): the ring can be reused for the merge
     if (*abort_flag) {
         const long long t0 = clock64();
@@ -813,7 +819,7 @@ int attn_max_cluster() {
 template <int D, int STAGES>
 int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* q, void* out, float* part_o, float* part_ml,
                       const int* positions, const int* seq_of_token, const int* page_table, int max_pages, int ntok,
-                      int nq, int nkv, float scale_log2, int window, int splits, bool cluster, int* status,
+                      int nq, int nkv, float scale_log2, int window, int splits, bool cluster, int n_pages, int* status,
                       cudaStream_t stream) {
     constexpr int smem = decode_tma_smem<D, STAGES>();
     static bool configured = false;
@@ -825,9 +831,18 @@ int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* 
     }
     dim3 grid(ntok, nkv, splits);
     const int cl = (cluster && splits > 1) ? 1 : 0;
+    static int places = 0;         // CTAs of this kernel that the device holds at once
+    if (places == 0) {
+        int dev = 0, sms = 0, per_sm = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 160, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+        places = (sms > 0 ? sms : 1) * per_sm;
+    }
+    const int early = (long long)ntok * nkv * splits <= places ? 1 : 0;
     return gg_launch(kern, grid, dim3(160), smem, stream, cl ? splits : 1, tk, tv, (const bf16*)q, (bf16*)out, part_o,
                      part_ml, positions, seq_of_token, page_table, max_pages, nq, nkv, scale_log2, window, splits, cl,
-                     status);
+                     early, n_pages, status);
 }
 
 
@@ -850,7 +865,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
     bf16* __restrict__ out, const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens,
     const int* __restrict__ seq_of_token, const int* __restrict__ page_table, int max_pages, int n_seqs,
-    int nq, int nkv, float scale_log2, int window, int* __restrict__ status) {
+    int nq, int nkv, float scale_log2, int window, int n_pages, int* __restrict__ status) {
     constexpr int HALVES = D / 64;
     constexpr int QBOX = 128 * 64 * 2;              // [64 columns x 128 rows] box of Q: 16 KB
     constexpr int KBOX = 64 * 64 * 2;               // [64 columns x 64 rows] box of K or V: 8 KB
@@ -926,7 +941,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
             for (int hf = 0; hf < HALVES; ++hf) tma::load_2d(Qs + hf * QBOX, &tmQ, q_full, h * D + hf * 64, tok0 + row0);
             for (int j = 0; j < ntiles; ++j) {
                 const int s = j & 1;
-                const int row = (pt[kt_first + j] * nkv + kvh) * PAGE;
+                const int row = (gg_page(pt, kt_first + j, max_pages, PageBounds{n_pages, status}, 45) * nkv + kvh) * PAGE;
                 if (!tma::mbar_wait(&k_empty[s], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, status, 21)) break;
                 tma::mbar_expect_tx(&k_full[s], K_STAGE);
 #pragma unroll
@@ -1136,8 +1151,8 @@ GG_API gg_attn_decode_splits(int ntok, int nkv, int max_ctx) {
 // nq / nkv at most 16, page size 64.  splits must be what gg_attn_decode_splits returned.
 GG_API gg_attn_decode(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_o, float* part_ml,
                       const int* positions, const int* seq_of_token, const int* page_table, int max_pages,
-                      int page_size, int ntok, int nq, int nkv, int d, float scale, int window, int splits,
-                      cudaStream_t stream) {
+                      int page_size, int n_pages, int ntok, int nq, int nkv, int d, float scale, int window, int splits,
+                      int* status, cudaStream_t stream) {
     if (ntok <= 0) return 0;
     if (page_size != PAGE || nq <= 0 || nkv <= 0 || nq % nkv || nq / nkv > 16 || (d != 64 && d != 128) || splits < 1 ||
         nkv > 65535 || splits > 65535)
@@ -1148,11 +1163,11 @@ GG_API gg_attn_decode(const void* q, const void* k_pool, const void* v_pool, voi
     if (d == 128)
         gg_launch(attn_decode_kernel<128>, dim3(grid), dim3(128), 0, stream, 1, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
                                                           part_o, part_ml, positions, seq_of_token, page_table, max_pages,
-                                                          nq, nkv, scale_log2, window, splits);
+                                                          nq, nkv, scale_log2, window, splits, PageBounds{n_pages, status});
     else
         gg_launch(attn_decode_kernel<64>, dim3(grid), dim3(128), 0, stream, 1, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
                                                          part_o, part_ml, positions, seq_of_token, page_table, max_pages,
-                                                         nq, nkv, scale_log2, window, splits);
+                                                         nq, nkv, scale_log2, window, splits, PageBounds{n_pages, status});
     int rc = gg_last_error();
     if (rc != 0 || splits == 1) return rc;
     if (d == 128) gg_launch(attn_combine_kernel<128>, dim3(ntok * nq), dim3(128), 0, stream, 1, part_o, part_ml, (bf16*)out, splits);
@@ -1164,8 +1179,8 @@ GG_API gg_attn_decode(const void* q, const void* k_pool, const void* v_pool, voi
 // absolute positions end at ctx_lens[i]-1.  max_tiles >= sum over sequences of ceil(new tokens / 64).
 GG_API gg_attn_prefill(const void* q, const void* k_pool, const void* v_pool, void* out, const int* cu_seqlens,
                        const int* ctx_lens, const int* seq_of_token, const int* page_table, int max_pages,
-                       int page_size, int n_seqs, int max_tiles, int nq, int nkv, int d, float scale, int window,
-                       cudaStream_t stream) {
+                       int page_size, int n_pages, int n_seqs, int max_tiles, int nq, int nkv, int d, float scale,
+                       int window, int* status, cudaStream_t stream) {
     if (n_seqs <= 0 || max_tiles <= 0) return 0;
     if (page_size != PAGE || nq <= 0 || nkv <= 0 || nq % nkv || (d != 64 && d != 128) || nq > 65535) return GG_ERR_ARG;
     const float scale_log2 = scale * 1.4426950408889634f;
@@ -1181,11 +1196,11 @@ GG_API gg_attn_prefill(const void* q, const void* k_pool, const void* v_pool, vo
         }
         gg_launch(attn_prefill_kernel<128>, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
                                                               cu_seqlens, ctx_lens, seq_of_token, page_table, max_pages, n_seqs,
-                                                              nq, nkv, scale_log2, window);
+                                                              nq, nkv, scale_log2, window, PageBounds{n_pages, status});
     } else {
         gg_launch(attn_prefill_kernel<64>, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
                                                              cu_seqlens, ctx_lens, seq_of_token, page_table, max_pages, n_seqs,
-                                                             nq, nkv, scale_log2, window);
+                                                             nq, nkv, scale_log2, window, PageBounds{n_pages, status});
     }
     return gg_last_error();
 }
@@ -1237,10 +1252,10 @@ GG_API gg_attn_decode_tma(const void* q, const void* k_pool, const void* v_pool,
     const float scale_log2 = scale * 1.4426950408889634f;
     if (d == 128)
         rc = launch_decode_tma<128, 3>(tk, tv, q, out, part_o, part_ml, positions, seq_of_token, page_table, max_pages, ntok,
-                                       nq, nkv, scale_log2, window, splits, cluster, status, stream);
+                                       nq, nkv, scale_log2, window, splits, cluster, n_pages, status, stream);
     else
         rc = launch_decode_tma<64, 4>(tk, tv, q, out, part_o, part_ml, positions, seq_of_token, page_table, max_pages, ntok,
-                                      nq, nkv, scale_log2, window, splits, cluster, status, stream);
+                                      nq, nkv, scale_log2, window, splits, cluster, n_pages, status, stream);
     if (rc != 0 || splits == 1 || cluster) return rc;
     if (d == 128) gg_launch(attn_combine_kernel<128>, dim3(ntok * nq), dim3(128), 0, stream, 1, part_o, part_ml, (bf16*)out, splits);
     else gg_launch(attn_combine_kernel<64>, dim3(ntok * nq), dim3(64), 0, stream, 1, part_o, part_ml, (bf16*)out, splits);
@@ -1276,7 +1291,7 @@ GG_API gg_attn_prefill_tc(const void* q, const void* k_pool, const void* v_pool,
             cfg = true;
         }
         return gg_launch(attn_prefill_tc_kernel<128>, grid, dim3(192), smem, stream, 1, tq, tk, tv, (bf16*)out, cu_seqlens,
-                         ctx_lens, seq_of_token, page_table, max_pages, n_seqs, nq, nkv, scale_log2, window, status);
+                         ctx_lens, seq_of_token, page_table, max_pages, n_seqs, nq, nkv, scale_log2, window, n_pages, status);
     }
     constexpr int smem = 16384 + 2 * 8192 + 2 * 8192 + 16384 + 256;
     static bool cfg64 = false;
@@ -1286,5 +1301,8 @@ GG_API gg_attn_prefill_tc(const void* q, const void* k_pool, const void* v_pool,
         cfg64 = true;
     }
     return gg_launch(attn_prefill_tc_kernel<64>, grid, dim3(192), smem, stream, 1, tq, tk, tv, (bf16*)out, cu_seqlens,
-                     ctx_lens, seq_of_token, page_table, max_pages, n_seqs, nq, nkv, scale_log2, window, status);
+                     ctx_lens, seq_of_token, page_table, max_pages, n_seqs, nq, nkv, scale_log2, window, n_pages, status);
 }
+
+// 1 if this library was built with checked page tables (the debug build), else 0.
+GG_API gg_attention_fast_checked() { return gg_debug_bounds(); }

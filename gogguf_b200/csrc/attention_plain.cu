@@ -18,7 +18,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_plain_kernel(
     const T* q, const T* k_pool, const T* v_pool, T* __restrict__ out,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int page_size,
-    int nq, int nkv, int d, float scale, int window) {
+    int nq, int nkv, int d, float scale, int window, const PageBounds pb) {
     pdl_launch();
     pdl_wait();
     extern __shared__ float sm[];
@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_plain_kernel(
     float m = -INFINITY, l = 0.f;
     const int* pt = page_table + (size_t)b * max_pages;
     for (int j = lo + warp; j <= pos; j += ATT_WARPS) {
-        const int page = pt[j / page_size];
+        const int page = gg_page(pt, j / page_size, max_pages, pb, 41);
         const size_t base = (((size_t)page * nkv + g) * page_size + (j % page_size)) * d;
         const T* kp = k_pool + base;
         const T* vp = v_pool + base;
@@ -85,11 +85,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_plain_kernel(
     }
 }
 
-// q[T, nq, d] and out[T, nq, d] in `dtype`; pools [page][nkv][page_size][d] in `dtype`.
+// q[T, nq, d] and out[T, nq, d] in `dtype`; pools [page][nkv][page_size][d] in `dtype`, n_pages of them.
+// status (may be null): where the debug build records a page id or table index out of range (code 41).
 GG_API gg_attention_plain(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
                           const int* positions, const int* seq_of_token, const int* page_table,
-                          int max_pages, int page_size, int ntok, int nq, int nkv, int d,
-                          float scale, int window, cudaStream_t stream) {
+                          int max_pages, int page_size, int n_pages, int ntok, int nq, int nkv, int d,
+                          float scale, int window, int* status, cudaStream_t stream) {
     if (ntok <= 0) return 0;
     if (d <= 0 || d > ATT_MAXD || nq <= 0 || nkv <= 0 || nq % nkv || nq > 65535 || page_size <= 0) return GG_ERR_ARG;
     const size_t smem = ((size_t)(1 + ATT_WARPS) * d + 2 * ATT_WARPS) * sizeof(float);
@@ -97,6 +98,9 @@ GG_API gg_attention_plain(const void* q, const void* k_pool, const void* v_pool,
     GG_DISPATCH_DTYPE(dtype, T,
         gg_launch(attention_plain_kernel<T>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 1, 
             (const T*)q, (const T*)k_pool, (const T*)v_pool, (T*)out, positions, seq_of_token, page_table,
-            max_pages, page_size, nq, nkv, d, scale, window));
+            max_pages, page_size, nq, nkv, d, scale, window, PageBounds{n_pages, status}));
     return gg_last_error();
 }
+
+// 1 if this library was built with checked page tables (the debug build), else 0.
+GG_API gg_attention_plain_checked() { return gg_debug_bounds(); }

@@ -39,6 +39,13 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
 ]
 
+# GOGGUF_B200_DEBUG=1: the debug build.  Kernels that follow a page table check every index and page id
+# before they use it and record a bad one in the status word instead of reading there (common.cuh); the
+# libraries of the two builds carry different hashes and live side by side.
+DEBUG = os.environ.get("GOGGUF_B200_DEBUG", "0") == "1"
+if DEBUG:
+    NVCC_FLAGS.append("-DGG_DEBUG_BOUNDS")
+
 # module name -> source file (relative to this folder)
 MODULES: Dict[str, str] = {
     "elementwise": "elementwise.cu",
@@ -48,13 +55,16 @@ MODULES: Dict[str, str] = {
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_fast": "attention_fast.cu",
     "gemm_tcgen05_static": "gemm_tcgen05_static.cu",
+    "diagnostics": "diagnostics.cu",
 }
 
 _HEADERS = ["common.cuh"]
 # further files a module's source includes (they take part in its hash)
 _INCLUDES: Dict[str, List[str]] = {
     "attention_fast.cu": ["tma_util.cuh"],
-    "gemm_tcgen05_static.cu": ["gemm_tcgen05.cu", "gemm_tcgen05_static.h"],
+    "gemm_tcgen05.cu": ["tma_util.cuh"],
+    "gemm_tcgen05_static.cu": ["gemm_tcgen05.cu", "gemm_tcgen05_static.h", "tma_util.cuh"],
+    "diagnostics.cu": ["tma_util.cuh"],
 }
 
 

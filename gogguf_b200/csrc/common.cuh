@@ -73,6 +73,40 @@ __device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats o
         else return GG_ERR_DTYPE;                             \
     } while (0)
 
+// ----------------------------------------------------------------------------- checked page tables
+// The debug build (-DGG_DEBUG_BOUNDS; GOGGUF_B200_DEBUG=1 selects it) makes every kernel that follows a page
+// table check the index into the table and the page id it finds there before it uses them.  A bad one is
+// recorded in the status word (code 41-45 names the kernel) and page 0 is read instead, so the kernel never
+// touches memory outside the pools; the host raises when it next checks the status word.  In the normal
+// build gg_page() is the plain table read.  It stands in for a memory checker, which cannot run here.
+struct PageBounds {
+    int n_pages;         // pages in the pool
+    int* status;         // the device's status word (may be null: nothing is recorded)
+};
+__device__ __forceinline__ int gg_page(const int* pt, int idx, int max_pages, const PageBounds& pb, int code) {
+#ifdef GG_DEBUG_BOUNDS
+    if (idx < 0 || idx >= max_pages) {
+        if (pb.status != nullptr) atomicCAS(pb.status, 0, code);
+        return 0;
+    }
+    const int page = pt[idx];
+    if (page < 0 || page >= pb.n_pages) {
+        if (pb.status != nullptr) atomicCAS(pb.status, 0, code);
+        return 0;
+    }
+    return page;
+#else
+    return pt[idx];
+#endif
+}
+static inline int gg_debug_bounds() {
+#ifdef GG_DEBUG_BOUNDS
+    return 1;
+#else
+    return 0;
+#endif
+}
+
 // ----------------------------------------------------------------------------- dependent launches
 // Kernels of a step are launched with programmatic stream serialisation: a kernel may become
 // resident while its predecessor in the stream is still draining, run its prologue (barrier set-up,

@@ -16,11 +16,13 @@ def decode_splits(n_tokens: int, nkv: int, max_ctx: int) -> int:
 
 def attn_decode(q, k_pool, v_pool, out, positions, seq_of_token, table, page_size, n_tokens, nq, nkv, d,
                 scale, window, splits, part_o=None, part_ml=None) -> None:
+    from .tcgen05_gemm import status_word
     kernel("attention_fast", "gg_attn_decode")(
         q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
         part_o.data_ptr() if part_o is not None else 0, part_ml.data_ptr() if part_ml is not None else 0,
         positions.data_ptr(), seq_of_token.data_ptr(), table.data_ptr(), table.shape[-1], page_size,
-        n_tokens, nq, nkv, d, float(scale), int(window), int(splits), torch.cuda.current_stream().cuda_stream)
+        k_pool.shape[0], n_tokens, nq, nkv, d, float(scale), int(window), int(splits),
+        status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
 
 
 def decode_tma_splits(n_tokens: int, nkv: int, max_ctx: int, cluster: bool = False) -> int:
@@ -43,10 +45,12 @@ def attn_decode_tma(q, k_pool, v_pool, out, positions, seq_of_token, table, page
 
 def attn_prefill(q, k_pool, v_pool, out, cu_seqlens, ctx_lens, seq_of_token, table, page_size, n_seqs,
                  max_tiles, nq, nkv, d, scale, window) -> None:
+    from .tcgen05_gemm import status_word
     kernel("attention_fast", "gg_attn_prefill")(
         q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), cu_seqlens.data_ptr(),
         ctx_lens.data_ptr(), seq_of_token.data_ptr(), table.data_ptr(), table.shape[-1], page_size,
-        n_seqs, max_tiles, nq, nkv, d, float(scale), int(window), torch.cuda.current_stream().cuda_stream)
+        k_pool.shape[0], n_seqs, max_tiles, nq, nkv, d, float(scale), int(window),
+        status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
 
 
 def attn_prefill_tc(q, k_pool, v_pool, out, cu_seqlens, ctx_lens, seq_of_token, table, page_size, n_tokens,

@@ -37,6 +37,7 @@
 // The reference multiplies with a one-thread-per-row scalar PTX kernel (pkg/gpu/cuda/ptx.go:67-129).
 #include <cuda.h>
 #include "common.cuh"
+#include "tma_util.cuh"
 
 namespace {
 
@@ -45,91 +46,31 @@ constexpr int BK = 64;            // bf16 elements per stage row = 128 bytes = o
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int NUM_THREADS = 192;
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // about one second
 
 enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_SWIGLU = 3, OUT_QKV = 4 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false when it gave up (own limit, or another role raised the abort flag).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    int spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 63) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                atomicCAS(status, 0, code);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
+// mbarrier, TMA and tcgen05 wrappers: one set for every kernel of the package (tma_util.cuh)
+using tma::smem_u32;
+using tma::mbar_init;
+using tma::mbar_expect_tx;
+using tma::mbar_arrive;
+using tma::mbar_try_wait;
+using tma::mbar_wait;
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+    tma::load_2d(dst, map, bar, x, y);
 }
-
-// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes, 128-byte swizzle:
-// 8-row groups are 1024 bytes apart (stride byte offset), the leading byte offset is not used.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);        // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                         // leading byte offset (ignored for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset
-    d |= (uint64_t)1 << 46;                         // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
-    return d;
-}
-
-// Instruction descriptor, kind::f16: bf16 x bf16 -> f32, both operands K-major.
-__device__ __forceinline__ uint32_t make_idesc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
+// K-major tile with rows of 128 bytes, 128-byte swizzle: 8-row groups are 1024 bytes apart
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) { return tc5::smem_desc(saddr, 16, 1024); }
+// kind::f16: bf16 x bf16 -> f32, both operands K-major
+__device__ __forceinline__ uint32_t make_idesc(int m, int n) { return tc5::idesc_bf16(m, n, 0); }
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+    tc5::mma(tmem_d, adesc, bdesc, idesc, acc);
 }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint64_t* bar) { tc5::commit(bar); }
+__device__ __forceinline__ void tc_fence_before() { tc5::fence_before(); }
+__device__ __forceinline__ void tc_fence_after() { tc5::fence_after(); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) { tc5::ld16(taddr, r); }
+__device__ __forceinline__ void tmem_ld_wait() { tc5::wait_ld(); }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
 

@@ -143,9 +143,20 @@ def attention_plain(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     page_size: int, n_tokens: int, nq: int, nkv: int, d: int, scale: float, window: int) -> None:
     if not (q.dtype == k_pool.dtype == v_pool.dtype == out.dtype):
         raise KernelError("attention: q, cache and out must share one dtype")
+    from .tcgen05_gemm import status_word
     kernel("attention_plain", "gg_attention_plain")(
         _p(q), _p(k_pool), _p(v_pool), _p(out), dtype_code(q.dtype), _p(positions), _p(seq_of_token),
-        _p(page_table), page_table.shape[-1], page_size, n_tokens, nq, nkv, d, float(scale), int(window), _stream())
+        _p(page_table), page_table.shape[-1], page_size, k_pool.shape[0], n_tokens, nq, nkv, d, float(scale),
+        int(window), _p(status_word(q.device)), _stream())
+
+
+def wait_probe(limit_cycles: int, code: int, status: torch.Tensor) -> torch.Tensor:
+    """Run the package's bounded wait on a barrier nothing arrives at (csrc/diagnostics.cu) and return the
+    kernel's report (5 int32 on the device): both roles' return values, their elapsed cycles / 1024, the
+    abort flag.  `status` is the int32 status word the code is to land in."""
+    report = torch.full((5,), -1, dtype=torch.int32, device=status.device)
+    kernel("diagnostics", "gg_wait_probe")(int(limit_cycles), int(code), _p(status), _p(report), _stream())
+    return report
 
 
 # ------------------------------------------------------------------------------- sampling

@@ -13,7 +13,8 @@ _status: Dict[torch.device, torch.Tensor] = {}
 
 
 def status_word(device: torch.device) -> torch.Tensor:
-    """One int32 on the device that kernels with bounded waits write to when a wait runs out."""
+    """One int32 on the device that kernels write to when a bounded wait runs out or, in the debug build,
+    when a page table holds an index or page id out of range."""
     device = torch.device(device)
     t = _status.get(device)
     if t is None:
@@ -22,15 +23,21 @@ def status_word(device: torch.device) -> torch.Tensor:
 
 
 def check_status(device: torch.device) -> None:
-    """Raise if a bounded wait ran out in any kernel since the last check (reads one int: a sync)."""
+    """Raise if a kernel left a code in the status word since the last check (reads one int: a sync)."""
     t = _status.get(torch.device(device))
     if t is None:
         return
     v = int(t.item())
     if v != 0:
         t.zero_()
-        raise KernelError(f"a bounded wait inside a tensor-core kernel ran out (code {v}: "
-                          "1 TMA producer, 2 MMA issuer, 3 epilogue); results of that step are invalid")
+        if 41 <= v <= 45:
+            who = {41: "attention_plain", 42: "attn_decode", 43: "attn_prefill", 44: "attn_decode_tma",
+                   45: "attn_prefill_tc"}[v]
+            raise KernelError(f"debug build: kernel {who} met a page-table index or page id out of range (code {v}); "
+                              "it read page 0 instead, results of that step are invalid")
+        raise KernelError(f"a bounded wait inside a kernel ran out (code {v}: 1 TMA producer, 2 MMA issuer, "
+                          "3 epilogue of a product, 11-12 decode attention, 21-28 prefill attention); "
+                          "results of that step are invalid")
 
 
 def splits_for(M: int, N: int, K: int, cluster: bool = False) -> int:

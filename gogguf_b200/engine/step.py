@@ -31,6 +31,9 @@ from ..parts.base import StepContext, Workspace
 from .model import Model
 
 
+from ..csrc.build import DEBUG as _DEBUG
+
+
 class StepError(ValueError):
     """A step, or one entry of it, that cannot run.  `code` is one of "empty_step", "duplicate_slot",
     "unknown_slot", "no_tokens", "bad_token", "bad_want", "context_overflow", "cache_full"."""
@@ -322,6 +325,9 @@ class Stepper:
             self.cache.unplan(slots)            # the pages reserved for this step go back
             raise
         self.cache.commit(slots, counts)
+        if _DEBUG and self.model.rt.device.type == "cuda":
+            from ..csrc.tcgen05_gemm import check_status
+            check_status(self.model.rt.device)      # debug build: a page table out of range raises here
         if taps is not None and taps.on_logits is not None and logits is not None:
             taps.on_logits(logits.clone())
         return logits

@@ -713,6 +713,39 @@ def test_attention_decode_reads_every_page_of_a_long_context(nq, nkv, d, ctxs):
             kp[page, g, off] = old
 
 
+def test_a_bounded_wait_that_runs_out_leaves_its_code_and_ends_the_kernel():
+    """The time-out path of the kernels' mbarrier waits, run for its own sake: a barrier nothing arrives at, a
+    limit of a millisecond.  The wait returns false, its code is in the status word, the abort flag is up, the
+    second role left because of the flag long before its own limit, and the host's check raises."""
+    from gogguf_b200.csrc import tcgen05_gemm as tc
+    from gogguf_b200.csrc.build import KernelError
+    word = torch.zeros(1, dtype=torch.int32, device=DEV)
+    limit = 2_000_000
+    rep = K().wait_probe(limit, 7, word).cpu().tolist()
+    assert rep[0] == 0 and rep[1] == 0 and rep[4] == 1
+    assert int(word.item()) == 7                               # the first code stays; the second role adds none
+    assert limit // 1024 <= rep[2] < 50 * (limit // 1024)
+    assert rep[3] < 100 * (limit // 1024)                      # not its own limit of a thousand times that
+    word.fill_(3)
+    K().wait_probe(limit, 7, word)
+    assert int(word.item()) == 3                               # an earlier code is never overwritten
+    K().wait_probe(limit, 2, tc.status_word(DEV))
+    with pytest.raises(KernelError, match="code 2"):
+        tc.check_status(DEV)
+    tc.check_status(DEV)                                       # the word is clear again
+
+
+def test_debug_build_checks_page_tables_instead_of_reading_out_of_range():
+    """GOGGUF_B200_DEBUG=1 builds the kernels with checked page tables: the stand-in for a memory checker."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, GOGGUF_B200_DEBUG="1")
+    p = subprocess.run([sys.executable, os.path.join(root, "tests", "debug_bounds_script.py"), root], env=env,
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0 and "debug bounds ok" in p.stdout, p.stdout[-2000:] + p.stderr[-4000:]
+
+
 # ------------------------------------------------------------------------------------------ sampling chain
 @pytest.mark.parametrize("temp,top_k,top_p,min_p", [(0.8, 20, 0.95, 0.0), (0.0, 3, 1.0, 0.0), (1.0, 1, 0.5, 0.0),
                                                      (1.3, 40, 0.6, 0.1), (0.6, 1000, 0.9, 0.0), (2.5, 64, 1.0, 0.3),
