@@ -34,6 +34,7 @@ class LoadOptions:
     max_batch: int = 64
     fast: bool = True             # False: plain kernels only (for comparisons)
     graphs: bool = True           # replay captured decode steps where possible
+    timing: bool = False          # bracket prefill, decode steps and sampling with CUDA events (Context.last_timing)
 
 
 class Engine:
@@ -65,13 +66,25 @@ class Context:
             self.stepper = Stepper(model, self.cache)
         self.generator = Generator(self.stepper, model.spec.vocab_size, model.spec.max_positions,
                                    default_stop=model.spec.stop_token_ids, max_batch=max_batch)
+        if engine.options.timing:
+            from .engine.timing import PhaseTimer
+            self.generator.timer = PhaseTimer(model.rt.device)
 
     def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
                  params: Optional[GenerateParams] = None) -> Union[GenerationResult, List[GenerationResult]]:
         """One prompt (a list of ids) gives one result; a list of prompts gives a list."""
         single = len(prompts) > 0 and isinstance(prompts[0], int)
+        if self.generator.timer is not None:
+            self.generator.timer.reset()
         res = self.generator.generate([list(prompts)] if single else [list(p) for p in prompts], params)
         return res[0] if single else res
+
+    def last_timing(self):
+        """The `PhaseReport` of the last `generate` call (LoadOptions(timing=True)): prefill, time to the first
+        token, decode split into model steps and sampling, on the device (cmd/tools/bench.go:302-364)."""
+        if self.generator.timer is None:
+            raise ValueError("this context was not made with LoadOptions(timing=True)")
+        return self.generator.timer.report()
 
     def start_generation(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
                          stop_token_ids: Optional[Sequence[int]] = None) -> GenerationSession:

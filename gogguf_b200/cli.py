@@ -27,6 +27,7 @@ import json
 import os
 import re
 import sys
+import time
 from typing import List, Optional
 
 
@@ -48,8 +49,11 @@ def cmd_run(a) -> int:
             prompts += [_ids(line) for line in f if line.strip()]
     if not prompts and not a.i:
         raise SystemExit("give a prompt with -p (token ids) or --prompt-file, or use -i")
-    engine = gg.load(a.m, gg.LoadOptions(dtype=a.dtype, max_tokens=a.cache_tokens, max_batch=a.max_batch))
+    t_load = time.perf_counter()
+    engine = gg.load(a.m, gg.LoadOptions(dtype=a.dtype, max_tokens=a.cache_tokens, max_batch=a.max_batch,
+                                         timing=a.timing))
     ctx = engine.new_context()
+    t_load = (time.perf_counter() - t_load) * 1e3
     params = gg.GenerateParams(
         max_tokens=a.n,
         sampler=gg.SamplerConfig(temp=a.temp, top_k=a.top_k, top_p=a.top_p, min_p=a.min_p, seed=a.seed),
@@ -61,6 +65,11 @@ def cmd_run(a) -> int:
         print(" ".join(str(t) for t in r.tokens))
         print(f"# prompt {r.prompt_tokens} tokens, generated {len(r.tokens)}, finish: {r.finish_reason}",
               file=sys.stderr)
+    if a.timing:
+        # the reference's bench lines (cmd/tools/bench.go:296-299) for this run
+        print(f"Load: {t_load:.1f} ms", file=sys.stderr)
+        for line in ctx.last_timing().lines():
+            print(line, file=sys.stderr)
     return 0
 
 
@@ -272,6 +281,8 @@ def build_parser() -> argparse.ArgumentParser:
     r.add_argument("--stop-ids", default=None, help="stop token ids (default: the model's eos_token_id)")
     r.add_argument("--cache-tokens", type=int, default=0, help="cache capacity in tokens (0 = context length)")
     r.add_argument("--max-batch", type=int, default=64)
+    r.add_argument("--timing", action="store_true",
+                   help="print load, prefill, time to first token, decode (model steps / sampling) timed on the device")
     r.set_defaults(fn=cmd_run)
     i = sub.add_parser("info", help="short summary of a model folder")
     i.add_argument("-m")

@@ -82,6 +82,15 @@ class Generator:
         # The prompts of a batch run in as few steps as hold this many tokens each (a longer prompt is cut):
         # the activations of a step grow with its tokens, the time of a token does not shrink beyond this.
         self.prefill_tokens = prefill_tokens
+        self.timer = None            # a PhaseTimer (engine.timing) when per-phase timing was asked for
+
+    def _tic(self, phase: str, tokens: int = 0) -> None:
+        if self.timer is not None:
+            self.timer.begin(phase, tokens)
+
+    def _toc(self) -> None:
+        if self.timer is not None:
+            self.timer.end()
 
     def _prefill(self, live: List[int], prompts, slots, cached=None):
         """The prompts of the batch, in order; returns the logits of their last tokens, one row per request.
@@ -106,7 +115,9 @@ class Generator:
         for st in steps:
             entries = [StepEntry(slots[i], list(prompts[i][a:e]), want=[e - a - 1] if e == len(prompts[i]) else [])
                        for i, a, e in st]
+            self._tic("prefill", sum(e - a for _, a, e in st))
             logits = self.stepper.step(entries)
+            self._toc()
             ends = [i for i, a, e in st if e == len(prompts[i])]
             if len(steps) == 1:
                 return logits
@@ -199,8 +210,10 @@ class Generator:
                 return
             while live:
                 hist = [list(prompts[i]) + generated[i] for i in live] if sampler.penalised else None
+                self._tic("sample", len(live))
                 nxt = sampler.sample(logits, streams=live, steps=[len(generated[i]) for i in live],
                                      histories=hist)
+                self._toc()
                 go_on: List[int] = []
                 for i, t in zip(live, nxt):
                     reason = self._finish_reason(i, t, prompts, generated, params, max_new, stop)
@@ -213,7 +226,9 @@ class Generator:
                 if not live:
                     break
                 entries = [StepEntry(slots[i], [generated[i][-1]], want=[0]) for i in live]
+                self._tic("decode", len(live))
                 logits = self.stepper.step(entries)
+                self._toc()
         finally:
             for i in list(slots):
                 self._let_go(i, slots, held, prompts, generated)
@@ -225,7 +240,9 @@ class Generator:
         out to be a stop token (or whose callback says stop) was then run one step too far; its extra row
         is dropped and its slot is given back, and nobody else's result depends on it."""
         rows = list(live)                                   # requests whose ids are on their way
+        self._tic("sample", len(rows))
         pending = sampler.sample_async(logits, rows, [len(generated[i]) for i in rows])
+        self._toc()
         dev_row = {i: r for r, i in enumerate(rows)}        # where each request's id sits in the device buffer
         while rows:
             # who certainly goes on after the id that is on its way (its value is not needed for this)?
@@ -234,8 +251,12 @@ class Generator:
             nxt_pending = None
             if cont:
                 src = [dev_row[i] for i in cont]
+                self._tic("decode", len(cont))
                 logits = self.stepper.decode_from_device([slots[i] for i in cont], pending.device_tokens, src)
+                self._toc()
+                self._tic("sample")
                 nxt_pending = sampler.sample_async(logits, cont, [len(generated[i]) + 1 for i in cont])
+                self._toc()
             ids = pending.tokens()                           # the host catches up with the previous step
             stopped = set()
             for i, t in zip(rows, ids):

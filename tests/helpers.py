@@ -82,6 +82,10 @@ def rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
     return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
 
 
-# tolerances: float32 engine against the float32/float64 plain implementation, and bfloat16 engine
+# tolerances: float32 engine against the float32/float64 plain implementation, and bfloat16 engine.
+# The bfloat16 bound is for models whose weights were scaled up (make_folder(scale=4)) and for drawn
+# configurations: rounding activations to bfloat16 alone costs up to 2.5e-2 there (the plain kernels show the
+# same).  Tests of fixed configurations use tighter bounds beside it (tests/test_gpu_whole.py,
+# tests/test_gpu_bench_shapes.py), and each kernel alone is held to 8e-3.
 TOL_F32 = 2e-5
 TOL_BF16 = 4e-2

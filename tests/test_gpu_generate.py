@@ -321,3 +321,34 @@ def test_top_k_beyond_the_kernels_shared_memory_falls_back_to_the_host_chain():
     assert s2.device_chain
     l2 = logits[:, :V2].contiguous()
     assert s2.sample(l2.cuda(), [0, 1, 2], [5, 5, 5]) == Sampler(cfg).sample(l2, [0, 1, 2], [5, 5, 5])
+
+
+def test_per_phase_timing_behind_a_flag(tmp_path_factory, capsys):
+    """LoadOptions(timing=True): prefill, time to the first token and decode (model steps and sampling apart)
+    from CUDA events around the loop's phases; `run --timing` prints the reference's bench lines."""
+    import gogguf_b200 as gg
+    from gogguf_b200 import cli
+    folder = make_folder(tmp_path_factory.getbasetemp(), "L", "bfloat16", scale=4.0)
+    cfg, _ = read_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], n, 90 + n) for n in (200, 31, 7)]
+    plain_ctx = gg.load(folder, gg.LoadOptions(max_tokens=4096)).new_context()
+    with pytest.raises(ValueError):
+        plain_ctx.last_timing()
+    want = plain_ctx.generate(prompts, gg.GenerateParams(max_tokens=9, stop_token_ids=[]))
+    for sampler in (gg.SamplerConfig(), gg.SamplerConfig(temp=0.8, top_p=0.9, seed=1)):       # a step ahead / host chain
+        ctx = gg.load(folder, gg.LoadOptions(max_tokens=4096, timing=True)).new_context()
+        out = ctx.generate(prompts, gg.GenerateParams(max_tokens=9, stop_token_ids=[], sampler=sampler))
+        if sampler.greedy:
+            assert [r.tokens for r in out] == [r.tokens for r in want]          # timing changes no result
+        t = ctx.last_timing()
+        assert t.prompt_tokens == 238 and t.decode_tokens == 27 and t.prefill_steps == 1 and t.decode_steps == 8
+        assert 0 < t.prefill_ms <= t.ttft_ms <= t.total_ms and 0 < t.step_ms < t.decode_ms < t.total_ms
+        assert t.sampling_ms > 0 and t.decode_tps > 0 and t.prefill_tps > 0 and t.host_ms > 0
+        assert len(t.lines()) == 4 and t.lines()[0].startswith("Prefill (238 tok, 1 step)")
+        # a second call starts from zero
+        ctx.generate(prompts[:1], gg.GenerateParams(max_tokens=2, stop_token_ids=[]))
+        assert ctx.last_timing().prompt_tokens == 200 and ctx.last_timing().decode_tokens == 2
+    ids = " ".join(map(str, prompts[2]))
+    assert cli.main(["run", "-m", folder, "-p", ids, "-n", "5", "--timing", "--stop-ids", ""]) == 0
+    err = capsys.readouterr().err
+    assert "Load: " in err and "Prefill (7 tok" in err and "TTFT: " in err and "Decode (5 tok, 4 steps)" in err

@@ -58,13 +58,19 @@ def test_whole_bf16(tmp_path_factory, name):
     tokens = random_tokens(cfg["vocab_size"], 200, seed=3)
     want = plain.forward(cfg, w, tokens, wide=True)
     got = engine_whole(folder, "bfloat16", tokens)
-    assert rel_err(got, want) < TOL_BF16
+    # These weights are four times the usual size, so that the logits are not flat; rounding the activations to
+    # bfloat16 then costs 1.0e-2 to 2.5e-2 of the largest logit whatever the kernels (measured: the twins' error).
+    tight = 3e-2
+    assert rel_err(got, want) < tight
     # the plain kernels on the same bfloat16 weights (the twins of the tensor-core kernels) agree too
     twin = engine_whole(folder, "bfloat16", tokens, fast=False)
-    assert rel_err(twin, want) < TOL_BF16
+    assert rel_err(twin, want) < tight
+    # the fast path differs from the twin in its kernels only: it may not add to the twin's own error
+    assert rel_err(got, want) < 1.5 * rel_err(twin, want) + 5e-3
     # and the tensor-core path with every norm as a kernel of its own instead of folded into the products
     unfolded = engine_whole(folder, "bfloat16", tokens, fold_norms=False)
-    assert rel_err(unfolded, want) < TOL_BF16
+    assert rel_err(unfolded, want) < tight
+    assert rel_err(unfolded, want) < 1.5 * rel_err(twin, want) + 5e-3
     if os.environ.get("GOGGUF_B200_FOLD_NORMS", "1") != "0":
         assert not torch.equal(unfolded, got)    # the two really are different routes
 
