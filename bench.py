@@ -2,7 +2,7 @@
 """Measurement: Qwen3-8B-shaped random-weight model, bfloat16, one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
-                    [--shape 8b|14b|32b] [--workload] [--prefill-lengths 256,1024]
+                    [--shape 8b|14b|32b] [--workload] [--prefill-lengths 256,1024] [--decode-contexts 16384,32768]
 
 A "step" is one decode step of a batch: every sequence goes on by one token, sampled greedily on the
 device.  The timed region is exactly K steps after W warm-up steps, timed with CUDA events on the
@@ -19,6 +19,7 @@ launching stream.  One JSON line is printed:
   config       every size, flat
   workload     (--workload) the shape's own request mix through Context.generate: prefill and decode rates
   prefill_sweep_ms  (--prefill-lengths) one prefill step per listed prompt length
+  decode_by_context (--decode-contexts) decode steps of sequences that already hold that many tokens
 
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from the
 fallback figures of an earlier measurement on this pool.  The weights (16 GB) are far larger than
@@ -161,6 +162,9 @@ def main():
                     help="also run the shape's own request mix through the entry point (14b: 16 prompts of 128 to 2,048 "
                     "tokens and 256 new tokens each; 32b: 8 prompts of 4,096 tokens and 128 new tokens; 8b: 8 prompts "
                     "of 2,048 tokens and 64 new tokens); added to the line as workload")
+    ap.add_argument("--decode-contexts", default="", help="comma separated context lengths: time decode steps of batch "
+                    "--batch (and of one sequence) whose sequences already hold that many tokens (added to the line as "
+                    "decode_by_context)")
     ap.add_argument("--prefill-lengths", default="", help="comma separated prompt lengths: time one prefill step of each "
                     "(printed on stderr, added to the line as prefill_sweep)")
     a = ap.parse_args()
@@ -189,6 +193,9 @@ def main():
     if a.layers <= 0:
         a.layers = base["num_hidden_layers"]
     cdict = dict(base, num_hidden_layers=a.layers)
+    long_ctx = [int(x) for x in a.decode_contexts.split(",") if x.strip()]
+    if long_ctx:        # the rotary tables are computed per step, so the context length is only a bound
+        cdict["max_position_embeddings"] = max(cdict["max_position_embeddings"], max(long_ctx) + 128)
     cfg = config_from_dict(cdict)
     pk = peaks()
     t0 = time.time()
@@ -202,13 +209,14 @@ def main():
     def rand_tokens(n):
         return torch.randint(0, V, (n,), generator=g).tolist()
 
-    def decode_run(batch, steps, warmup, sampler_cfg=None):
-        """Prefill `batch` prompts of PROMPT_LEN tokens, then time `steps` greedy decode steps on the device."""
+    def decode_run(batch, steps, warmup, sampler_cfg=None, prompt_len=PROMPT_LEN):
+        """Prefill `batch` prompts of `prompt_len` tokens, then time `steps` greedy decode steps on the device."""
+        PROMPT_LEN = prompt_len
         room = PROMPT_LEN + warmup + steps + 8
         cache = model.new_cache(batch * (-(-room // 64) * 64))
         st = GraphStepper(model, cache)
         slots = [cache.open() for _ in range(batch)]
-        chunk = 4       # prompts per prefill step, bounds the workspace
+        chunk = max(1, 8192 // PROMPT_LEN)       # prompts per prefill step, bounds the workspace
         logits_last = []
         for i in range(0, batch, chunk):
             ents = [StepEntry(s, rand_tokens(PROMPT_LEN), want=[PROMPT_LEN - 1]) for s in slots[i:i + chunk]]
@@ -275,7 +283,8 @@ def main():
         dt = stamps[warmup + steps] - stamps[warmup]
         # bytes per decode step: the packed integer inputs (tokens, positions, slots, lengths, page tables)
         # copied from pinned host memory, and the sampled ids read back
-        return {"tok_s": batch * steps / dt, "h2d": getattr(ctx.stepper, "last_h2d_bytes", None), "d2h": batch * 4}
+        return {"tok_s": batch * steps / dt, "h2d": getattr(ctx.stepper, "last_h2d_bytes", None), "d2h": batch * 4,
+                "warmup": warmup}
 
     def workload_run():
         """The request mix named for this shape, through Context.generate: host ids in, host ids out.
@@ -339,7 +348,7 @@ def main():
     main_run = decode_run(a.batch, a.steps, a.warmup)
     print(f"[bench] decode batch {a.batch}: {main_run['tok_s']:.1f} tok/s, {main_run['ms_per_step']:.3f} ms/step", file=sys.stderr)
     if a.no_e2e:
-        e2e = {"tok_s": None, "h2d": None, "d2h": None}
+        e2e = {"tok_s": None, "h2d": None, "d2h": None, "warmup": None}
     else:
         e2e = e2e_run(a.batch, a.steps, a.warmup)
         print(f"[bench] e2e batch {a.batch}: {e2e['tok_s']:.1f} tok/s", file=sys.stderr)
@@ -366,6 +375,16 @@ def main():
         sweep[str(t)] = round(r["ms"], 3)
         print(f"[bench] prefill of {t} tokens: {r['ms']:.3f} ms, {r['value']:.0f} tok/s, {r['tflops']:.0f} TFLOP/s", file=sys.stderr)
 
+    by_context = {}
+    for c in long_ctx:
+        for b in sorted({1, a.batch}):
+            r = decode_run(b, 16, 3, prompt_len=c)
+            frac = r["bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"]
+            by_context[f"ctx{c}_b{b}"] = {"tok_s": round(r["tok_s"], 1), "ms_per_step": round(r["ms_per_step"], 3),
+                                          "hbm_frac": round(frac, 3)}
+            print(f"[bench] decode at context {c}, batch {b}: {r['tok_s']:.1f} tok/s, {r['ms_per_step']:.3f} ms/step, "
+                  f"{frac:.3f} of the HBM roofline", file=sys.stderr)
+
     workload = None
     if a.workload:
         workload = workload_run()
@@ -389,7 +408,8 @@ def main():
             "sampling": "greedy on device", "l2": "inputs>L2 (16 GB of weights per step)",
             "peaks": pk["source"],
         },
-        "e2e": {"value": e2e["tok_s"], "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
+        "e2e": {"value": e2e["tok_s"], "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                "warmup": e2e["warmup"]},       # untimed decode steps of this arm (at least 32, see e2e_run)
         "gpu_launches": main_run["launches"],
         "clocks": main_run["clocks"],
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -400,6 +420,8 @@ def main():
         line["points"] = points
     if sweep:
         line["prefill_sweep_ms"] = sweep
+    if by_context:
+        line["decode_by_context"] = by_context
     if workload is not None:
         line["workload"] = workload
     print(json.dumps(line))
