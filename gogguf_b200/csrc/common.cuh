@@ -119,9 +119,12 @@ static inline int gg_debug_bounds() {
 // CTAs cannot share an SM with the CTAs of the kernel after it (both need most of the shared
 // memory) does NOT call pdl_launch().  With the early release, the persistent product that follows
 // prefill attention took over SMs as they came free while attention CTAs were still waiting to be
-// scheduled, and the two kernels waited for each other; the cause inside the scheduler was not
-// established, so such kernels simply release their successor by completing.  Light kernels with
-// many CTAs (norms, rotary) share SMs with whatever follows and keep the early release.
+// scheduled, and the two kernels waited for each other; the cause was not established (reading the
+// two kernels again found no wait of one on the other: they never share an SM, so not tensor memory;
+// the pair's cluster barriers and the dependency wait need nothing an attention CTA holds), so such
+// kernels simply release their successor by completing.  Decode attention releases at its top only
+// when its whole grid is resident at once, and after its pages otherwise.  Light kernels with many
+// CTAs (norms, rotary) share SMs with whatever follows and keep the early release.
 //
 // A second rule, for the compiler: a pointer to data that an earlier kernel of the same step writes
 // (activations, the residual stream, q, the cache, rotary tables, logits, partial results) is never

@@ -25,8 +25,10 @@
  *     GG_STATIC_SCRATCH_FLOATS; larger products are refused with status -1 before anything is
  *     launched.  Products that need no split (M > 128, or few K slabs) never touch the array.
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
- *     that device current) and sets the kernels' shared-memory attribute.  Make that first call
- *     outside any stream capture.
+ *     that device current).  The kernels' shared-memory attribute is set once per process, by the
+ *     first call of all (this library drives one GPU; a process that uses it on a second device
+ *     should call once there as well and check the return code).  Make these first calls outside
+ *     any stream capture.
  *   - All calls share the one array, and it keeps what the last call left in it.  Nothing in it has
  *     to start at zero: a call reads back only elements that the same call has just written.  Two
  *     calls that may overlap on the GPU (different streams without an ordering between them) race

@@ -140,6 +140,10 @@ class Model:
         self.final_norm = ncls(spec.final_norm, _local(tensors, spec.final_norm, ncls, consume), rt)
         hcls = _part_class(R.HEADS, spec.head, "head")
         tied = getattr(self.embedding, "weight", None) if spec.head.get("tied_to") is not None else None
+        if tied is not None and spec.head.prefix + "weight" in found:
+            import warnings
+            warnings.warn(f"the configuration ties the head to the embedding; the stored {spec.head.prefix}weight "
+                          "is not used", stacklevel=2)
         self.head = hcls(spec.head, _local(tensors, spec.head, hcls, consume), rt, tied)
 
     # ------------------------------------------------------------------ constructors

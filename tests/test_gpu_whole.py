@@ -192,3 +192,16 @@ def test_prefill_projection_does_the_per_head_work_too(tmp_path_factory, monkeyp
     assert rel_err(logits["1"], logits["0"]) < 2e-2
     want = torch.cat([plain.forward(cfg, w, prompts[0], wide=True)[5:], plain.forward(cfg, w, prompts[1], wide=True)])
     assert rel_err(logits["1"], want) < TOL_BF16
+
+
+def test_a_stored_head_of_a_tied_model_is_named_and_not_used(tmp_path):
+    from gogguf_b200.weights.safetensors_io import write_safetensors
+    folder = make_folder(tmp_path, "A", "float32")
+    cfg, w = read_folder(folder)
+    tokens = random_tokens(cfg["vocab_size"], 12, seed=2)
+    want = engine_whole(folder, "float32", tokens)
+    w["lm_head.weight"] = torch.randn_like(w["model.embed_tokens.weight"])       # another matrix altogether
+    write_safetensors(os.path.join(folder, "model.safetensors"), w)
+    with pytest.warns(UserWarning, match="ties the head"):
+        got = engine_whole(folder, "float32", tokens)
+    assert torch.equal(got, want)
