@@ -18,9 +18,11 @@
 // out[m, n] = D[n, m].  In decode the product is a stream of weights from HBM: the grid is
 // widened by splitting K over blockIdx.z and several CTAs share an SM.  The CTAs that hold the
 // partial sums of one output tile form a thread-block cluster: each dumps its accumulator into its
-// own shared memory, and after a cluster barrier every CTA adds one slice of the tile over all
-// ranks through distributed shared memory, always in rank order, and writes it out.  No scratch
-// memory, no second launch, no float atomics: results do not depend on timing.  (A second form
+// own shared memory, and every CTA adds one slice of the tile over all ranks through distributed
+// shared memory, always in rank order, and writes it out (up to 16 tokens the slices are sent with
+// st.async and counted by an mbarrier of the receiver, so no cluster barrier stands at the end of
+// the kernel; above that cluster barriers frame the exchange).  No scratch memory, no second
+// launch, no float atomics: results do not depend on timing.  (A second form
 // keeps the partial sums in a float32 scratch buffer in global memory and adds them in a second
 // kernel; it serves callers that ask for it and split counts beyond a cluster.)
 //
@@ -514,7 +516,23 @@ __device__ __forceinline__ void st_cluster_f32x4(uint32_t local_addr, uint32_t r
                  ::"r"(remote), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
+// A row of four floats into the shared memory of CTA `rank` of the cluster, completing 16 bytes of the transaction
+// count of that CTA's mbarrier `bar_local_addr` (same offset in every CTA) once the store is visible there.
+__device__ __forceinline__ void st_async_f32x4(uint32_t local_addr, uint32_t bar_local_addr, uint32_t rank, float4 v) {
+    uint32_t remote, rbar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(bar_local_addr), "r"(rank));
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(remote), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(rbar) : "memory");
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
 constexpr int MAX_CLUSTER = 8;
+// The 16-token decode form keeps a receive area of its own beside the pipeline stages: RECV16_SLOTS rows of 128
+// floats, enough for [source rank][owner's token] with up to 8 ranks (S * ceil(16 / S) <= 21).
+constexpr int RECV16_SLOTS = 22;
+template <int BN, bool SWAP> constexpr int recv_bytes() { return (SWAP && BN == 16) ? RECV16_SLOTS * BM * 4 : 0; }
 
 // cluster_reduce != 0: the grid was launched with clusters of gridDim.z CTAs along z (the K splits).
 template <int BN, int STAGES, bool SWAP, int MINB>
@@ -529,13 +547,24 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* accum = empty + STAGES;
+    uint64_t* recv_bar = accum + 1;
     // the tile goes through shared memory when K splits are added inside the cluster, for the fused
     // activation, and (decode form) whenever a norm is folded into this product
     // (only the decode form splits K or fuses the activation; the launcher sees to that)
     const bool staged = SWAP && (cluster_reduce || out_mode == OUT_SWIGLU || out_mode == OUT_QKV ||
                                  (partial == nullptr && (nio.in_ssq != nullptr || nio.out_ssq != nullptr)));
-    uint32_t* tmem_slot = (uint32_t*)(accum + 1);
+    uint32_t* tmem_slot = (uint32_t*)(recv_bar + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    // Up to 16 tokens the K splits of a cluster are added without any barrier at the end: every CTA sends the
+    // partial rows of token j to the CTA that owns it (rank j mod S) with st.async into a receive area that is
+    // not part of the pipeline stages, each row completing 512 bytes of the owner's mbarrier; the owner waits
+    // for the bytes it expects and adds them in rank order.  The one cluster barrier that is left says "my
+    // mbarrier is initialised": its arriving half is in the prologue, its waiting half right before the first
+    // row is sent, by which time it has long completed.  (Both end-of-kernel barriers and the exchange between
+    // them cost 6 % of a decode step at batch 1 and 8, measured by compiling them out.)
+    constexpr bool HAS_RECV = recv_bytes<BN, SWAP>() > 0;
+    const bool push2 = HAS_RECV && staged && cluster_reduce != 0;
+    uint8_t* recv2 = smem + STAGES * STAGE_BYTES + 256;
 
     pdl_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -547,6 +576,7 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(accum, 1);
+        mbar_init(recv_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
@@ -561,6 +591,14 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // tokens of this tile that this CTA adds up when the splits are pushed: j with j mod S == split
+    int n_owned = 0;
+    if (push2) {
+        const int S = (int)gridDim.z, cols = min(BN, M - tile_b * BN);
+        n_owned = split < cols ? (cols - split + S - 1) / S : 0;
+        if (threadIdx.x == 0 && n_owned > 0) mbar_expect_tx(recv_bar, (uint32_t)(S * n_owned * BM * 4));
+        cluster_arrive();
+    }
 
     if (warp == 0) {
         if (lane == 0) {
@@ -677,13 +715,14 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     __syncthreads();
     if (staged) {
         // Every CTA of the cluster passes its barriers exactly once each, whatever happened before.
-        if (cluster_reduce) cluster_sync_all();
+        if (cluster_reduce && !push2) cluster_sync_all();
         // Decode form: a warp per token.  Each lane adds four consecutive features of the 128 of this tile over
         // the cluster's ranks, in rank order, then the epilogue of the output mode.  Up to 32 tokens per tile
-        // the partial sums are *pushed*: after the first barrier (every CTA's pipeline memory is free) each CTA
-        // stores the rows of token j into the shared memory of the CTA that owns it (rank j mod S), a second
-        // barrier makes the stores visible, and the owner adds what it received from its own memory: remote
-        // stores need no round trip (measured: 9.1 -> 8.6 us for the O product at 8 tokens).  With 64 tokens
+        // the partial sums are *pushed* to the CTA that owns the token (rank j mod S) and the owner adds what it
+        // received from its own shared memory: remote stores need no round trip (measured: 9.1 -> 8.6 us for the
+        // O product at 8 tokens).  At 16 tokens the rows go out with st.async and no cluster barrier is left at
+        // the end of the kernel (see `push2` above); at 32 tokens the receive area lies in the pipeline stages,
+        // so one barrier says that they are free and a second one that the rows have landed.  With 64 tokens
         // per tile the exchange is bound by its volume, not its latency, and pushing was slower than pulling
         // (whole step at batch 64: 6.88 against 6.75 ms), so from there on the owner pulls.
         const int S = cluster_reduce ? (int)gridDim.z : 1;
@@ -692,8 +731,21 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
         constexpr int WARPS = NUM_THREADS / 32;
         const bool push = cluster_reduce && BN <= 32;
         const int LJ = (cols + S - 1) / S;                           // tokens an owner handles at most
-        const uint32_t recv = stage + (uint32_t)(BN * BM * 4);       // [source rank][owner's token][128] float32
-        if (push) {
+        // where the pushed rows land, [source rank][owner's token][128] float32: beside the stages (16 tokens) or
+        // behind the tile in them (32 tokens)
+        const uint32_t recv = push2 ? smem_u32(recv2) : stage + (uint32_t)(BN * BM * 4);
+        const uint8_t* recv_mine = push2 ? recv2 : smem + (size_t)BN * BM * 4;
+        if (push2) {
+            cluster_wait();              // every CTA of the cluster has initialised its mbarrier (long ago)
+            if (!*abort_flag) {
+                for (int j = warp; j < cols; j += WARPS) {
+                    const float4 v = *reinterpret_cast<const float4*>(smem + (size_t)(j * BM + 4 * lane) * 4);
+                    st_async_f32x4(recv + 4u * (uint32_t)((split * LJ + j / S) * BM + 4 * lane), smem_u32(recv_bar),
+                                   (uint32_t)(j % S), v);
+                }
+            }
+            if (n_owned > 0) mbar_wait(recv_bar, 0, abort_flag, status, 5);
+        } else if (push) {
             if (!*abort_flag) {
                 for (int j = warp; j < cols; j += WARPS) {
                     const float4 v = *reinterpret_cast<const float4*>(smem + (size_t)(j * BM + 4 * lane) * 4);
@@ -708,7 +760,7 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                 const int gj = tile_b * BN + j;                      // token
                 float4 v[MAX_CLUSTER];
                 if (push) {
-                    const uint8_t* mine = smem + (size_t)BN * BM * 4 + (size_t)((j / S) * BM + 4 * lane) * 4;
+                    const uint8_t* mine = recv_mine + (size_t)((j / S) * BM + 4 * lane) * 4;
 #pragma unroll
                     for (int qq = 0; qq < MAX_CLUSTER; ++qq)
                         v[qq] = qq < S ? *reinterpret_cast<const float4*>(mine + (size_t)qq * LJ * BM * 4)
@@ -1285,10 +1337,10 @@ template <int BN, int STAGES, bool SWAP, int MINB>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N, int K,
            int splits, int kb_per_split, float* partial, bool cluster, int* status, const NormIO& nio,
            const QkvIO& qio, cudaStream_t stream) {
-    constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256;
+    constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256 + recv_bytes<BN, SWAP>();
     static_assert(STAGES * (A_BYTES + BN * BK * 2) >= BN * BM * 4, "the stages must hold a float32 tile");
-    static_assert(BN > 32 || STAGES * (A_BYTES + BN * BK * 2) >= (2 * BN + MAX_CLUSTER - 1) * BM * 4,
-                  "up to 32 tokens the stages must also hold what the other ranks push");
+    static_assert(BN != 32 || STAGES * (A_BYTES + BN * BK * 2) >= (2 * BN + MAX_CLUSTER - 1) * BM * 4,
+                  "at 32 tokens the stages must also hold what the other ranks push");
     static bool configured = false;
     auto kern = gemm_tc_kernel<BN, STAGES, SWAP, MINB>;
     if (!configured) {
@@ -1374,7 +1426,7 @@ static int gemm_tc_impl(const void* x, const void* w, void* out, int out_mode, i
         const bool deep = deep_ok && ctas <= 296 && bn <= 32;    // measured in whole steps: a gain up to 32 tokens only
 #define GG_DECODE(BN_, ST_, MINB_) launch<BN_, ST_, true, MINB_>(ta, tb, out, out_mode, ldo, M, N, K, splits, per, scratch, \
                                                                  cluster, status, nio, qio, stream)
-        if (bn == 16) rc = deep ? GG_DECODE(16, 6, 2) : GG_DECODE(16, 4, 3);
+        if (bn == 16) rc = deep ? GG_DECODE(16, 5, 2) : GG_DECODE(16, 3, 3);     // stages + the receive area fill the SM
         else if (bn == 32) rc = deep ? GG_DECODE(32, 5, 2) : GG_DECODE(32, 3, 3);
         else if (bn == 64) rc = deep ? GG_DECODE(64, 4, 2) : GG_DECODE(64, 3, 3);
         else rc = deep ? GG_DECODE(128, 3, 2) : GG_DECODE(128, 2, 3);
