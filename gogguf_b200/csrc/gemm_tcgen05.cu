@@ -509,12 +509,6 @@ __device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local_addr, uint32_t
     return v;
 }
 
-__device__ __forceinline__ void st_cluster_f32x4(uint32_t local_addr, uint32_t rank, float4 v) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
-                 ::"r"(remote), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
-}
 
 // A row of four floats into the shared memory of CTA `rank` of the cluster, completing 16 bytes of the transaction
 // count of that CTA's mbarrier `bar_local_addr` (same offset in every CTA) once the store is visible there.
@@ -562,9 +556,15 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     // mbarrier is initialised": its arriving half is in the prologue, its waiting half right before the first
     // row is sent, by which time it has long completed.  (Both end-of-kernel barriers and the exchange between
     // them cost 6 % of a decode step at batch 1 and 8, measured by compiling them out.)
+    // At 32 tokens the receive area lies in the pipeline stages behind the CTA's own tile, so the barrier has
+    // to say "my stages are free" as well: there its arriving half is executed by every thread as soon as
+    // this CTA's last MMA has completed (`push3`; 12 layers at batch 32: 1.769 -> 1.754 ms).  From 64 tokens on
+    // the owner pulls, with a barrier before and one after: the same scheme measured slower there (batch 64:
+    // 2.404 -> 2.423 ms), and at 128 tokens tile and receive area would not fit the stages.
     constexpr bool HAS_RECV = recv_bytes<BN, SWAP>() > 0;
     const bool push2 = HAS_RECV && staged && cluster_reduce != 0;
-    uint8_t* recv2 = smem + STAGES * STAGE_BYTES + 256;
+    const bool push3 = !HAS_RECV && SWAP && BN == 32 && staged && cluster_reduce != 0;
+    uint8_t* recv2 = HAS_RECV ? smem + STAGES * STAGE_BYTES + 256 : smem + (size_t)BN * BM * 4;
 
     pdl_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -593,11 +593,11 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     const uint32_t tmem_base = *tmem_slot;
     // tokens of this tile that this CTA adds up when the splits are pushed: j with j mod S == split
     int n_owned = 0;
-    if (push2) {
+    if (push2 || push3) {
         const int S = (int)gridDim.z, cols = min(BN, M - tile_b * BN);
         n_owned = split < cols ? (cols - split + S - 1) / S : 0;
         if (threadIdx.x == 0 && n_owned > 0) mbar_expect_tx(recv_bar, (uint32_t)(S * n_owned * BM * 4));
-        cluster_arrive();
+        if (push2) cluster_arrive();
     }
 
     if (warp == 0) {
@@ -627,6 +627,11 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                 tma_load_2d(sa + A_BYTES, &tmB, &full[s], (kb0 + i) * BK, tile_b * BN);
             }
         }
+        if (push3) {
+            __syncwarp();
+            mbar_wait(accum, 0, abort_flag, status, 1);       // the last MMA has read the stages
+            cluster_arrive();
+        }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = make_idesc(BM, BN);
@@ -649,6 +654,11 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
             }
             if (ok) umma_commit(accum);
         }
+        if (push3) {
+            __syncwarp();
+            mbar_wait(accum, 0, abort_flag, status, 2);
+            cluster_arrive();
+        }
     } else {
         // epilogue: warp w reads tensor-memory lanes 32*(w%4) .. +31 (row i of D is lane i)
         const int q = warp & 3;
@@ -658,6 +668,7 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
         pdl_wait();                              // the output may still be in use by earlier kernels
         const float sc = (!SWAP && gi < RA) ? norm_factor(nio, gi) : 1.0f;
         mbar_wait(accum, 0, abort_flag, status, 3);
+        if (push3) cluster_arrive();             // the tile is complete in tensor memory: the stages are free from here
         if (!*abort_flag) {
             tc_fence_after();
             float ss = 0.f;
@@ -715,28 +726,28 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     __syncthreads();
     if (staged) {
         // Every CTA of the cluster passes its barriers exactly once each, whatever happened before.
-        if (cluster_reduce && !push2) cluster_sync_all();
+        if (cluster_reduce && !push2 && !push3) cluster_sync_all();
         // Decode form: a warp per token.  Each lane adds four consecutive features of the 128 of this tile over
         // the cluster's ranks, in rank order, then the epilogue of the output mode.  Up to 32 tokens per tile
         // the partial sums are *pushed* to the CTA that owns the token (rank j mod S) and the owner adds what it
         // received from its own shared memory: remote stores need no round trip (measured: 9.1 -> 8.6 us for the
         // O product at 8 tokens).  At 16 tokens the rows go out with st.async and no cluster barrier is left at
         // the end of the kernel (see `push2` above); at 32 tokens the receive area lies in the pipeline stages,
-        // so one barrier says that they are free and a second one that the rows have landed.  With 64 tokens
-        // per tile the exchange is bound by its volume, not its latency, and pushing was slower than pulling
-        // (whole step at batch 64: 6.88 against 6.75 ms), so from there on the owner pulls.
+        // so the one barrier also says that they are free (`push3`).  With 64 tokens per tile the exchange is
+        // bound by its volume, not its latency, and pushing was slower than pulling in either form, so from
+        // there on the owner pulls.
         const int S = cluster_reduce ? (int)gridDim.z : 1;
         const int cols = min(BN, M - tile_b * BN);
         const uint32_t stage = smem_u32(smem);
         constexpr int WARPS = NUM_THREADS / 32;
-        const bool push = cluster_reduce && BN <= 32;
+        const bool push = push2 || push3;
         const int LJ = (cols + S - 1) / S;                           // tokens an owner handles at most
         // where the pushed rows land, [source rank][owner's token][128] float32: beside the stages (16 tokens) or
         // behind the tile in them (32 tokens)
-        const uint32_t recv = push2 ? smem_u32(recv2) : stage + (uint32_t)(BN * BM * 4);
-        const uint8_t* recv_mine = push2 ? recv2 : smem + (size_t)BN * BM * 4;
-        if (push2) {
-            cluster_wait();              // every CTA of the cluster has initialised its mbarrier (long ago)
+        const uint32_t recv = smem_u32(recv2);
+        const uint8_t* recv_mine = recv2;
+        if (push) {
+            cluster_wait();              // every CTA of the cluster has initialised its mbarrier (and freed its stages)
             if (!*abort_flag) {
                 for (int j = warp; j < cols; j += WARPS) {
                     const float4 v = *reinterpret_cast<const float4*>(smem + (size_t)(j * BM + 4 * lane) * 4);
@@ -745,14 +756,6 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                 }
             }
             if (n_owned > 0) mbar_wait(recv_bar, 0, abort_flag, status, 5);
-        } else if (push) {
-            if (!*abort_flag) {
-                for (int j = warp; j < cols; j += WARPS) {
-                    const float4 v = *reinterpret_cast<const float4*>(smem + (size_t)(j * BM + 4 * lane) * 4);
-                    st_cluster_f32x4(recv + 4u * (uint32_t)((split * LJ + j / S) * BM + 4 * lane), (uint32_t)(j % S), v);
-                }
-            }
-            cluster_sync_all();
         }
         if (!*abort_flag && SWAP) {
             const int j_first = push ? warp * S + split : split * WARPS + warp;
@@ -1339,7 +1342,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode
            const QkvIO& qio, cudaStream_t stream) {
     constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256 + recv_bytes<BN, SWAP>();
     static_assert(STAGES * (A_BYTES + BN * BK * 2) >= BN * BM * 4, "the stages must hold a float32 tile");
-    static_assert(BN != 32 || STAGES * (A_BYTES + BN * BK * 2) >= (2 * BN + MAX_CLUSTER - 1) * BM * 4,
+    static_assert(!SWAP || BN != 32 || STAGES * (A_BYTES + BN * BK * 2) >= (2 * BN + MAX_CLUSTER - 1) * BM * 4,
                   "at 32 tokens the stages must also hold what the other ranks push");
     static bool configured = false;
     auto kern = gemm_tc_kernel<BN, STAGES, SWAP, MINB>;
