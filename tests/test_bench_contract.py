@@ -66,3 +66,19 @@ def test_peaks_come_from_the_measured_file_when_it_is_there(tmp_path, monkeypatc
     assert p["bf16_tflops_sustained"] == b.FALLBACK_PEAKS["bf16_tflops_sustained"]
     (tmp_path / "MEASURED_PEAKS.json").write_text("not json")
     assert b.peaks()["source"] == "fallback"
+
+
+def test_kernel_microbenchmarks_name_their_cases_and_need_a_gpu():
+    """`python -m gogguf_b200.csrc.microbench` is the script that the per-kernel figures under profiles/ were made
+    with: its cases are listed by --help, and without a CUDA device it ends with an error, never with numbers."""
+    import torch
+    mb = [sys.executable, "-m", "gogguf_b200.csrc.microbench"]
+    r = subprocess.run(mb + ["--help"], capture_output=True, text=True, timeout=120, cwd=ROOT)
+    assert r.returncode == 0
+    for case in ("gemm", "gemm_layer", "attn", "prefill_attn", "sample"):
+        assert case in r.stdout
+    r = subprocess.run(mb + ["nonsense"], capture_output=True, text=True, timeout=120, cwd=ROOT)
+    assert r.returncode != 0 and "invalid choice" in r.stderr
+    if not torch.cuda.is_available():
+        r = subprocess.run(mb + ["sample", "--m", "1"], capture_output=True, text=True, timeout=300, cwd=ROOT)
+        assert r.returncode != 0 and "us" not in r.stdout
