@@ -205,3 +205,37 @@ def test_a_stored_head_of_a_tied_model_is_named_and_not_used(tmp_path):
     with pytest.warns(UserWarning, match="ties the head"):
         got = engine_whole(folder, "float32", tokens)
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_a_status_per_entry_and_the_good_entries_still_run(tmp_path_factory, graphs):
+    """try_step on the device: bad entries are named and change nothing, the others give the logits they give
+    alone, for prompts and (through captured graphs too) for decode steps."""
+    from gogguf_b200.engine import Model, StepEntry, Stepper
+    from gogguf_b200.engine.graphs import GraphStepper
+    folder = make_folder(tmp_path_factory.getbasetemp(), "B", "float32")
+    cfg, w = read_folder(folder)
+    V = cfg["vocab_size"]
+    a, b = random_tokens(V, 21, 1), random_tokens(V, 9, 2)
+    wa, wb = plain.forward(cfg, w, a, wide=True), plain.forward(cfg, w, b, wide=True)
+    model = Model.load(folder, dtype="float32")
+    cache = model.new_cache(64 * 4)
+    st = (GraphStepper if graphs else Stepper)(model, cache)
+    sa, sb, sc = cache.open(), cache.open(), cache.open()
+    out = st.try_step([StepEntry(sa, a[:-1], want=[19]), StepEntry(sc, [1, V], want=[0]), StepEntry(sb, b[:-1], want=[0, 7]),
+                       StepEntry(99, [1])])
+    assert [s.code if s else None for s in out.status] == [None, "bad_token", None, "unknown_slot"]
+    assert rel_err(out.logits, torch.cat([wa[19:20], wb[[0, 7]]])) < TOL_F32
+    assert cache.length(sc) == 0 and cache.length(sa) == 20
+    # a decode step: one entry would pass the context's end, the others go on
+    cache.lengths[sc] = cfg["max_position_embeddings"]            # as if slot c were full
+    out = st.try_step([StepEntry(sa, a[-1:], want=[0]), StepEntry(sc, [3], want=[0]), StepEntry(sb, b[-1:], want=[0])])
+    assert [s.code if s else None for s in out.status] == [None, "context_overflow", None]
+    assert rel_err(out.logits, torch.cat([wa[-1:], wb[-1:]])) < TOL_F32
+    if graphs:
+        assert st.replays == 1
+    cache.lengths[sc] = 0
+    assert st.try_step([StepEntry(sc, [], want=[])]).logits is None
+    for s in (sa, sb, sc):
+        cache.close(s)
+    cache.check()
