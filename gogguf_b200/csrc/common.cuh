@@ -76,7 +76,7 @@ __device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats o
 // ----------------------------------------------------------------------------- checked page tables
 // The debug build (-DGG_DEBUG_BOUNDS; GOGGUF_B200_DEBUG=1 selects it) makes every kernel that follows a page
 // table check the index into the table and the page id it finds there before it uses them.  A bad one is
-// recorded in the status word (code 41-45 names the kernel) and page 0 is read instead, so the kernel never
+// recorded in the status word (code 41-48 names the kernel) and page 0 is read instead, so the kernel never
 // touches memory outside the pools; the host raises when it next checks the status word.  In the normal
 // build gg_page() is the plain table read.  It stands in for a memory checker, which cannot run here.
 struct PageBounds {
@@ -93,6 +93,20 @@ __device__ __forceinline__ int gg_page(const int* pt, int idx, int max_pages, co
     if (page < 0 || page >= pb.n_pages) {
         if (pb.status != nullptr) atomicCAS(pb.status, 0, code);
         return 0;
+    }
+    return page;
+#else
+    return pt[idx];
+#endif
+}
+// The same for a kernel that WRITES through the table (the cache writers): a bad index or page id is recorded
+// (codes 46-48) and -1 comes back, on which the caller writes nothing.  In the normal build: the plain read.
+__device__ __forceinline__ int gg_page_w(const int* pt, int idx, int max_pages, const PageBounds& pb, int code) {
+#ifdef GG_DEBUG_BOUNDS
+    const int page = (idx < 0 || idx >= max_pages) ? -1 : pt[idx];
+    if (page < 0 || page >= pb.n_pages) {
+        if (pb.status != nullptr) atomicCAS(pb.status, 0, code);
+        return -1;
     }
     return page;
 #else

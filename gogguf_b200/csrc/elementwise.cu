@@ -215,7 +215,7 @@ __global__ void qk_norm_rope_cache_kernel(
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int page_size,
     T* __restrict__ k_pool, T* __restrict__ v_pool,
-    int ntok, int nq, int nkv, int d, int rot) {
+    int ntok, int nq, int nkv, int d, int rot, const PageBounds pb) {
     pdl_launch();
     pdl_wait();
     extern __shared__ float sm[];
@@ -234,7 +234,8 @@ __global__ void qk_norm_rope_cache_kernel(
         dst = q_out + ((size_t)t * nq + h) * d;
     } else {
         const int pos = positions[t];
-        const int page = page_table[(size_t)b * max_pages + pos / page_size];
+        const int page = gg_page_w(page_table + (size_t)b * max_pages, pos / page_size, max_pages, pb, 46);
+        if (page < 0) return;            // (debug build) outside the pool: nothing is written
         const int kvh = is_k ? h - nq : h - nq - nkv;
         T* pool = is_k ? k_pool : v_pool;
         dst = pool + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * d;
@@ -283,7 +284,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_cache_vec_kernel(
     const float* cosv, const float* sinv,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int page_size,
-    bf16* __restrict__ k_pool, bf16* __restrict__ v_pool, int ntok, int nq, int nkv) {
+    bf16* __restrict__ k_pool, bf16* __restrict__ v_pool, int ntok, int nq, int nkv, const PageBounds pb) {
     pdl_launch();
     pdl_wait();
     constexpr int HALF = D / 2, LPH = D / 16, HPW = 32 / LPH;      // lanes per head, heads per warp
@@ -295,7 +296,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_cache_vec_kernel(
     const int t = in_range ? (int)(item / nheads) : 0, h = in_range ? (int)(item - (long long)t * nheads) : 0;
     const int b = in_range ? seq_of_token[t] : -1;
     const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
-    const bool live = in_range && (is_q || (k_pool != nullptr && b >= 0));     // every lane stays for the shuffles
+    bool live = in_range && (is_q || (k_pool != nullptr && b >= 0));     // every lane stays for the shuffles
     const bf16* src = qkv + ((size_t)t * nheads + h) * D;
     bf16* dst = nullptr;
     if (live) {
@@ -303,9 +304,10 @@ __global__ void __launch_bounds__(128) qk_norm_rope_cache_vec_kernel(
             dst = q_out + ((size_t)t * nq + h) * D;
         } else {
             const int pos = positions[t];
-            const int page = page_table[(size_t)b * max_pages + pos / page_size];
+            const int page = gg_page_w(page_table + (size_t)b * max_pages, pos / page_size, max_pages, pb, 47);
             const int kvh = is_k ? h - nq : h - nq - nkv;
-            dst = (is_k ? k_pool : v_pool) + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * D;
+            if (page < 0) live = false;      // (debug build) outside the pool: nothing is written
+            else dst = (is_k ? k_pool : v_pool) + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * D;
         }
     }
     const int i0 = sub * 8;             // first index of this lane in the low half
@@ -362,8 +364,8 @@ __global__ void __launch_bounds__(128) qk_norm_rope_cache_vec_kernel(
 
 GG_API gg_qk_norm_rope_cache(const void* qkv, int dtype, void* q_out, const float* qw, const float* kw, float eps,
                              const float* cosv, const float* sinv, const int* positions, const int* seq_of_token,
-                             const int* page_table, int max_pages, int page_size, void* k_pool, void* v_pool,
-                             int ntok, int nq, int nkv, int d, int rot, cudaStream_t stream) {
+                             const int* page_table, int max_pages, int page_size, int n_pages, void* k_pool, void* v_pool,
+                             int ntok, int nq, int nkv, int d, int rot, int* status, cudaStream_t stream) {
     if (ntok <= 0) return 0;
     if (d <= 0 || d > 1024 || rot < 0 || rot > d || (rot & 1) || nq <= 0 || nkv <= 0 || page_size <= 0) return GG_ERR_ARG;
     const int warps = 4;
@@ -376,7 +378,7 @@ GG_API gg_qk_norm_rope_cache(const void* qkv, int dtype, void* q_out, const floa
         const unsigned vgrid = (unsigned)((total + per_block - 1) / per_block);
 #define GG_QK_VEC(D_) gg_launch(qk_norm_rope_cache_vec_kernel<D_>, dim3(vgrid), dim3(warps * 32), 0, stream, 1,  \
             (const bf16*)qkv, (bf16*)q_out, qw, kw, eps, cosv, sinv, positions, seq_of_token, page_table, max_pages, \
-            page_size, (bf16*)k_pool, (bf16*)v_pool, ntok, nq, nkv)
+            page_size, (bf16*)k_pool, (bf16*)v_pool, ntok, nq, nkv, PageBounds{n_pages, status})
         if (d == 64) GG_QK_VEC(64); else if (d == 128) GG_QK_VEC(128); else GG_QK_VEC(256);
 #undef GG_QK_VEC
         return gg_last_error();
@@ -385,7 +387,7 @@ GG_API gg_qk_norm_rope_cache(const void* qkv, int dtype, void* q_out, const floa
     GG_DISPATCH_DTYPE(dtype, T,
         gg_launch(qk_norm_rope_cache_kernel<T>, dim3(grid), dim3(warps * 32), smem, stream, 1, 
             (const T*)qkv, (T*)q_out, qw, kw, eps, cosv, sinv, positions, seq_of_token, page_table, max_pages,
-            page_size, (T*)k_pool, (T*)v_pool, ntok, nq, nkv, d, rot));
+            page_size, (T*)k_pool, (T*)v_pool, ntok, nq, nkv, d, rot, PageBounds{n_pages, status}));
     return gg_last_error();
 }
 
@@ -477,3 +479,6 @@ GG_API gg_feed_tokens(int* tokens, const int* src, const int* sampled, int n, cu
     if (n <= 0) return 0;
     return gg_launch(feed_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, 1, tokens, src, sampled, n);
 }
+
+// 1 if this library was built with checked page tables (the debug build), else 0.
+GG_API gg_elementwise_checked() { return gg_debug_bounds(); }

@@ -115,6 +115,8 @@ struct QkvIO {
     bf16* v_pool;
     int nq;
     int nkv;
+    int n_pages;                 // pages in the pools (the debug build checks every page id against it)
+    int* status;                 // where the debug build records a page id or table index out of range (code 48)
 };
 
 // One thread computes its token's factor (four running sums keep the loads independent).
@@ -328,7 +330,9 @@ __device__ __forceinline__ void epilogue_row_qkv(uint32_t taddr, int gi, int tn,
         b = qio.seq_of_token[gi];
         if (qio.k_pool != nullptr && b >= 0) {
             pos = qio.positions[gi];
-            page = qio.page_table[(size_t)b * qio.max_pages + pos / qio.page_size];
+            page = gg_page_w(qio.page_table + (size_t)b * qio.max_pages, pos / qio.page_size, qio.max_pages,
+                             PageBounds{qio.n_pages, qio.status}, 48);
+            if (page < 0) b = -1;            // (debug build) outside the pools: this token writes no cache
         }
     }
     const float* cs = qio.cosv + (size_t)(live ? gi : 0) * 64;
@@ -812,7 +816,9 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                         dst = qio.q_out + ((size_t)gj * qio.nq + h) * 128;
                     } else {
                         const int pos = qio.positions[gj];
-                        const int page = qio.page_table[(size_t)b * qio.max_pages + pos / qio.page_size];
+                        const int page = gg_page_w(qio.page_table + (size_t)b * qio.max_pages, pos / qio.page_size,
+                                                   qio.max_pages, PageBounds{qio.n_pages, qio.status}, 48);
+                        if (page < 0) continue;      // (debug build) outside the pools: nothing is written
                         const int kvh = is_k ? h - qio.nq : h - qio.nq - qio.nkv;
                         dst = (is_k ? qio.k_pool : qio.v_pool) +
                               (((size_t)page * qio.nkv + kvh) * qio.page_size + (pos % qio.page_size)) * 128;
@@ -1507,12 +1513,12 @@ GG_API gg_gemm_tc_pair_scratch_elems(int M, int N, int K, long long* elems) {
 GG_API gg_gemm_tc_qkv_rope(const void* x, const void* w, int M, int K, long long ldx, const float* in_ssq, int in_parts,
                            float in_eps, void* q_out, const float* qw, const float* kw, float eps, const float* cosv,
                            const float* sinv, const int* positions, const int* seq_of_token, const int* page_table,
-                           int max_pages, int page_size, void* k_pool, void* v_pool, int nq, int nkv, int* status,
-                           cudaStream_t stream) {
+                           int max_pages, int page_size, int n_pages, void* k_pool, void* v_pool, int nq, int nkv,
+                           int* status, cudaStream_t stream) {
     if (in_ssq != nullptr && (in_parts != (K + 127) / 128 || !(in_eps > 0.f))) return GG_ERR_ARG;
     const NormIO nio = {in_ssq, in_parts, K > 0 ? 1.0f / (float)K : 0.f, in_eps, nullptr, nullptr};
     const QkvIO qio = {(bf16*)q_out, qw, kw, eps, cosv, sinv, positions, seq_of_token, page_table, max_pages, page_size,
-                       (bf16*)k_pool, (bf16*)v_pool, nq, nkv};
+                       (bf16*)k_pool, (bf16*)v_pool, nq, nkv, n_pages, status};
     const int N = (nq + 2 * nkv) * 128;
     return gemm_tc_impl(x, w, q_out, OUT_QKV, M, N, K, ldx, N, nullptr, 0, 1, status, nio, qio, stream);
 }

@@ -95,10 +95,12 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optiona
                        n_tokens: int, nq: int, nkv: int, d: int, rot: int) -> None:
     if q_out.dtype != qkv.dtype or (k_pool is not None and k_pool.dtype != qkv.dtype):
         raise KernelError("qk_norm_rope_cache: qkv, q_out and the cache must share one dtype")
+    from .tcgen05_gemm import status_word
     kernel("elementwise", "gg_qk_norm_rope_cache")(
         _p(qkv), dtype_code(qkv.dtype), _p(q_out), _p(q_weight), _p(k_weight), float(eps), _p(cos), _p(sin),
-        _p(positions), _p(seq_of_token), _p(page_table), page_table.shape[-1], page_size, _p(k_pool), _p(v_pool),
-        n_tokens, nq, nkv, d, rot, _stream())
+        _p(positions), _p(seq_of_token), _p(page_table), page_table.shape[-1], page_size,
+        k_pool.shape[0] if k_pool is not None else 0, _p(k_pool), _p(v_pool),
+        n_tokens, nq, nkv, d, rot, _p(status_word(qkv.device)), _stream())
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, n_tokens: int, inter: int) -> None:

@@ -30,11 +30,12 @@ def check_status(device: torch.device) -> None:
     v = int(t.item())
     if v != 0:
         t.zero_()
-        if 41 <= v <= 45:
+        if 41 <= v <= 48:
             who = {41: "attention_plain", 42: "attn_decode", 43: "attn_prefill", 44: "attn_decode_tma",
-                   45: "attn_prefill_tc"}[v]
+                   45: "attn_prefill_tc", 46: "qk_norm_rope_cache", 47: "qk_norm_rope_cache (16-byte form)",
+                   48: "the q/k/v product's cache write"}[v]
             raise KernelError(f"debug build: kernel {who} met a page-table index or page id out of range (code {v}); "
-                              "it read page 0 instead, results of that step are invalid")
+                              "it read page 0 (a reader) or wrote nothing (a writer), results of that step are invalid")
         raise KernelError(f"a bounded wait inside a kernel ran out (code {v}: 1 TMA producer, 2 MMA issuer, "
                           "3 epilogue of a product, 11-12 decode attention, 21-28 prefill attention); "
                           "results of that step are invalid")
@@ -182,7 +183,7 @@ def gemm_tc_qkv_rope(x: torch.Tensor, w: torch.Tensor, m: int, q_out: torch.Tens
         x.data_ptr(), w.data_ptr(), m, K, x.stride(0), in_ssq.data_ptr() if in_ssq is not None else 0, in_parts,
         float(in_eps), q_out.data_ptr(), qw.data_ptr() if qw is not None else 0, kw.data_ptr() if kw is not None else 0,
         float(eps), cos.data_ptr(), sin.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(),
-        page_table.data_ptr(), page_table.shape[-1], int(page_size),
+        page_table.data_ptr(), page_table.shape[-1], int(page_size), k_pool.shape[0] if k_pool is not None else 0,
         k_pool.data_ptr() if k_pool is not None else 0, v_pool.data_ptr() if v_pool is not None else 0,
         nq, nkv, st.data_ptr(), torch.cuda.current_stream().cuda_stream)
 

@@ -73,6 +73,47 @@ for kind, code in codes.items():
         short = good[:, :4].contiguous()              # the context needs six table entries, the table has four
         run(kind, dt, short, ctx_len, n_new)
         assert read_status() == code, (kind, "table index out of range")
+# The cache writers: a bad page id or a table that is too short makes them write nothing at all for that token
+# (every byte of the larger buffers keeps its sentinel), a good table makes them write exactly one row per head.
+assert build.module("elementwise").lib.gg_elementwise_checked() == 1
+
+
+def write_run(kind, dt, table, pos_list):
+    big_k = torch.full((n_pages + spare, nkv, 64, d), 7.0, device=DEV, dtype=dt)
+    big_v = torch.full((n_pages + spare, nkv, 64, d), 7.0, device=DEV, dtype=dt)
+    kp, vp = big_k[:n_pages], big_v[:n_pages]
+    T = len(pos_list)
+    mk = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)      # noqa: E731
+    pos, sot = mk(pos_list), mk([0] * T)
+    cos = torch.ones(T, d // 2, device=DEV); sin = torch.zeros(T, d // 2, device=DEV)
+    q_out = torch.empty(T, nq * d, device=DEV, dtype=dt)
+    if kind == "plain":
+        qkv = torch.randn(T, (nq + 2 * nkv) * d, device=DEV, generator=g).to(dt)
+        K.qk_norm_rope_cache(qkv, q_out, None, None, 1e-6, cos, sin, pos, sot, table, 64, kp, vp, T, nq, nkv, d, d)
+    else:
+        Kd = 256
+        x = torch.randn(T, Kd, device=DEV, generator=g).to(dt)
+        w = (torch.randn((nq + 2 * nkv) * d, Kd, device=DEV, generator=g) * 0.1).to(dt)
+        tc.gemm_tc_qkv_rope(x, w, T, q_out=q_out, qw=None, kw=None, eps=1e-6, cos=cos, sin=sin, positions=pos,
+                            seq_of_token=sot, page_table=table, page_size=64, k_pool=kp, v_pool=vp, nq=nq, nkv=nkv)
+    torch.cuda.synchronize()
+    changed = int((big_k != 7.0).any(-1).sum()) + int((big_v != 7.0).any(-1).sum())
+    return changed
+
+
+for kind, dt, code, T in (("plain", torch.float32, 46, 5), ("plain", torch.bfloat16, 47, 5), ("product", torch.bfloat16, 48, 5),
+                          ("product", torch.bfloat16, 48, 300)):
+    pos_list = list(range(64 * 2 + 3, 64 * 2 + 3 + T)) if T < 64 else list(range(T))
+    changed = write_run(kind, dt, good, pos_list)
+    assert read_status() == 0 and changed == 2 * nkv * T, (kind, dt, changed)
+    bad = good.clone()
+    bad[0, :] = n_pages + 2                                   # every page id beyond the pool
+    changed = write_run(kind, dt, bad, pos_list)
+    assert read_status() == code and changed == 0, (kind, dt, T, changed)
+    short = good[:, :2].contiguous()
+    changed = write_run(kind, dt, short, [64 * 2 + 3 + i for i in range(min(T, 5))])     # page index 2: beyond the table
+    assert read_status() == code and changed == 0, (kind, dt, "short table", changed)
+
 # the host raises with the kernel's name when it next checks the word
 bad = good.clone(); bad[0, 1] = 99
 run("decode_tma", torch.bfloat16, bad, ctx_len, 1)
