@@ -851,14 +851,23 @@ int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* 
 // query head).  Per 64-key page:  S = Q K^T  (tcgen05.mma 128 x 64 x 16, eight times; Q and K are
 // K-major tiles staged by TMA) lands in tensor memory; the four softmax warps read it, one query row
 // per thread, so the row maximum and sum need no exchange between threads; they write P as bfloat16
-// into shared memory in the K-major swizzled layout, and  O += P V  (128 x D x 16, four times; V is
-// the MN-major operand: one 128-byte row per key) accumulates in tensor memory.  O is rescaled in
+// back into tensor memory, over the first half of the score buffer it was made from (tcgen05.st), and
+//  O += P V  (128 x D x 16, four times; P is the A operand straight from tensor memory, V the MN-major
+// B operand in shared memory: one 128-byte row per key) accumulates in tensor memory.  O is rescaled in
 // place only when a row's maximum has grown by more than 2^8 since the scale in use was set (the
 // sums stay exact: P and the row sum use the same stale maximum), so most pages cost no pass over O.
 // Two CTAs share an SM (96 KB of shared memory and 256 tensor-memory columns each): while one runs
 // its softmax the other's MMAs keep the tensor pipe busy.
 // Every POLY_EVERY-th pair of exponentials of the softmax is computed by exp2_poly2.
 constexpr int POLY_EVERY = 3;
+// P as a tensor-memory operand: no P tile in shared memory and a quarter less for the tensor core to read
+// from shared memory per page (2,048 tokens: 747 -> 800 TFLOP/s; 8,192: 1,067 -> 1,125).  -DGG_ATTN_P_SMEM builds
+// the earlier form, which writes P into a swizzled K-major tile in shared memory.
+#ifndef GG_ATTN_P_SMEM
+constexpr bool P_IN_TMEM = true;
+#else
+constexpr bool P_IN_TMEM = false;
+#endif
 
 template <int D>
 __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
@@ -872,22 +881,25 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
     constexpr int Q_BYTES = HALVES * QBOX, K_STAGE = HALVES * KBOX, V_BYTES = HALVES * KBOX, P_BYTES = 128 * 64 * 2;
     constexpr int TMEM_COLS = 256;
     // The dynamic segment is the only shared memory of this kernel and is asked to start on a 1024-byte
-    // boundary (the swizzled tiles need it); there is no slack to round up in: two CTAs of 112.25 KB share an SM.
+    // boundary (the swizzled tiles need it) instead of being rounded up in the kernel: two CTAs of 96.25 KB share an SM.
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* Qs = smem;
     uint8_t* Ks = Qs + Q_BYTES;                     // two stages
+    // (a third stage of V in the place the P tile had was measured and changed nothing: 792 against 800 TFLOP/s
+    // at 2,048 tokens, 1,118 against 1,125 at 8,192)
+    constexpr int VST = 2;
     uint8_t* Vs = Ks + 2 * K_STAGE;                 // two stages
-    uint8_t* Ps = Vs + 2 * V_BYTES;
-    uint64_t* bars = (uint64_t*)(Ps + P_BYTES);
+    uint8_t* Ps = Vs + 2 * V_BYTES;                 // the P tile, only where P goes through shared memory
+    uint64_t* bars = (uint64_t*)(Ps + (P_IN_TMEM ? 0 : P_BYTES));
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;                    // [2]
     uint64_t* k_empty = bars + 3;                   // [2]
-    uint64_t* v_full = bars + 5;                    // [2]
-    uint64_t* v_empty = bars + 7;                   // [2]
-    uint64_t* s_full = bars + 9;                    // [2]
-    uint64_t* p_ready = bars + 11;
-    uint64_t* pv_done = bars + 12;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 13);
+    uint64_t* v_full = bars + 5;                    // [3]
+    uint64_t* v_empty = bars + 8;                   // [3]
+    uint64_t* s_full = bars + 11;                   // [2]
+    uint64_t* p_ready = bars + 13;
+    uint64_t* pv_done = bars + 14;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 15);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     // no early release of the next kernel here: see the note on dependent launches in common.cuh
@@ -895,7 +907,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
     if (threadIdx.x == 0) {
         tma::mbar_init(q_full, 1);
         for (int i = 0; i < 2; ++i) { tma::mbar_init(&k_full[i], 1); tma::mbar_init(&k_empty[i], 1); }
-        for (int i = 0; i < 2; ++i) { tma::mbar_init(&v_full[i], 1); tma::mbar_init(&v_empty[i], 1); }
+        for (int i = 0; i < 3; ++i) { tma::mbar_init(&v_full[i], 1); tma::mbar_init(&v_empty[i], 1); }
         tma::mbar_init(&s_full[0], 1); tma::mbar_init(&s_full[1], 1); tma::mbar_init(p_ready, 128); tma::mbar_init(pv_done, 1);
         *abort_flag = 0;
         tma::mbar_fence_init();
@@ -946,10 +958,11 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
                 tma::mbar_expect_tx(&k_full[s], K_STAGE);
 #pragma unroll
                 for (int hf = 0; hf < HALVES; ++hf) tma::load_2d(Ks + s * K_STAGE + hf * KBOX, &tmK, &k_full[s], hf * 64, row);
-                if (!tma::mbar_wait(&v_empty[s], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, status, 22)) break;
-                tma::mbar_expect_tx(&v_full[s], V_BYTES);
+                const int vs = j % VST;
+                if (!tma::mbar_wait(&v_empty[vs], (uint32_t)((j / VST) & 1) ^ 1u, abort_flag, status, 22)) break;
+                tma::mbar_expect_tx(&v_full[vs], V_BYTES);
 #pragma unroll
-                for (int hf = 0; hf < HALVES; ++hf) tma::load_2d(Vs + s * V_BYTES + hf * KBOX, &tmV, &v_full[s], hf * 64, row);
+                for (int hf = 0; hf < HALVES; ++hf) tma::load_2d(Vs + vs * V_BYTES + hf * KBOX, &tmV, &v_full[vs], hf * 64, row);
             }
         }
     } else if (warp == 5) {
@@ -982,17 +995,23 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
                 }
                 ok = tma::mbar_wait(p_ready, (uint32_t)(j & 1), abort_flag, status, 25);
                 if (!ok) break;
-                ok = tma::mbar_wait(&v_full[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, status, 26);
+                const int vs = j % VST;
+                ok = tma::mbar_wait(&v_full[vs], (uint32_t)((j / VST) & 1), abort_flag, status, 26);
                 if (!ok) break;
                 tc5::fence_after();
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
-                    const uint64_t a = tc5::smem_desc(p_a + kk * 32, 16, 1024);
-                    const uint64_t bb = tc5::smem_desc(v_a + (j & 1) * V_BYTES + kk * 2048, KBOX, 1024);
-                    tc5::mma(O_t, a, bb, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    const uint64_t bb = tc5::smem_desc(v_a + vs * V_BYTES + kk * 2048, KBOX, 1024);
+                    if (P_IN_TMEM) {
+                        // P of page j lies in the first 32 columns of score buffer j & 1: 16 keys are 8 columns
+                        tc5::mma_a_tmem(O_t, S_t + (uint32_t)((j & 1) * 64 + kk * 8), bb, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    } else {
+                        const uint64_t a = tc5::smem_desc(p_a + kk * 32, 16, 1024);
+                        tc5::mma(O_t, a, bb, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    }
                 }
                 tc5::commit(pv_done);
-                tc5::commit(&v_empty[j & 1]);
+                tc5::commit(&v_empty[vs]);
             }
         }
     } else if (active) {
@@ -1087,12 +1106,19 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
             if (!pv_seen) {
                 if (!tma::mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag, status, 28)) { ok = false; break; }
             }
-            uint8_t* prow = Ps + row * 128;
+            if (P_IN_TMEM) {
+                // P over this thread's own row of the scores it has just read (the first 32 of the buffer's 64
+                // columns): the next MMA into this buffer is issued after the P V that reads it
+                tc5::st32(S_t + lane_off + (uint32_t)((j & 1) * 64), pk);
+                tc5::wait_st();
+            } else {
+                uint8_t* prow = Ps + row * 128;
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) =
-                    make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-            tc5::fence_proxy_async_smem();     // P was written with ordinary stores; the tensor core reads it
+                for (int ch = 0; ch < 8; ++ch)
+                    *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) =
+                        make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+                tc5::fence_proxy_async_smem();     // P was written with ordinary stores; the tensor core reads it
+            }
             tc5::fence_before();
             tma::mbar_arrive(p_ready);
         }
@@ -1283,7 +1309,7 @@ GG_API gg_attn_prefill_tc(const void* q, const void* k_pool, const void* v_pool,
     const float scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(nq, max_tiles);
     if (d == 128) {
-        constexpr int smem = 2 * 16384 + 2 * 16384 + 2 * 16384 + 16384 + 256;       // Q, K x 2, V x 2, P, barriers
+        constexpr int smem = 2 * 16384 + 2 * 16384 + 2 * 16384 + (P_IN_TMEM ? 0 : 16384) + 256;   // Q, K x 2, V x 2, (P,) barriers
         static bool cfg = false;
         if (!cfg) {
             cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -1293,7 +1319,7 @@ GG_API gg_attn_prefill_tc(const void* q, const void* k_pool, const void* v_pool,
         return gg_launch(attn_prefill_tc_kernel<128>, grid, dim3(192), smem, stream, 1, tq, tk, tv, (bf16*)out, cu_seqlens,
                          ctx_lens, seq_of_token, page_table, max_pages, n_seqs, nq, nkv, scale_log2, window, n_pages, status);
     }
-    constexpr int smem = 16384 + 2 * 8192 + 2 * 8192 + 16384 + 256;
+    constexpr int smem = 16384 + 2 * 8192 + 2 * 8192 + (P_IN_TMEM ? 0 : 16384) + 256;
     static bool cfg64 = false;
     if (!cfg64) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
