@@ -429,8 +429,22 @@ __device__ __forceinline__ void epilogue_row_qkv(uint32_t taddr, int gi, int tn,
 // [128 tile_a, 128 tile_a + 128), four per lane, already summed over the K splits and multiplied by the folded
 // norm's factor, and applies the output mode (bf16 or float32 store, float32 add with the row statistics of the
 // updated rows, or SwiGLU over interleaved gate/up blocks).  All 32 lanes call it.
+// residual_prefetch() loads the four residual values at a lane's place ahead of time and says whether it did (the
+// aligned path of finish_token_block, which then takes them as `old_pre` instead of loading them itself).
+__device__ __forceinline__ bool residual_prefetch(int gj, int tile_a, int lane, void* out, int out_mode, long long ldo,
+                                                  int N, const NormIO& nio, float4& old) {
+    if (out_mode != OUT_F32_ACC) return false;
+    const int gi0 = tile_a * BM + 4 * lane;
+    if (gi0 + 4 > N) return false;
+    const float* op = (const float*)out + (size_t)gj * ldo + gi0;
+    const bool stats = nio.out_ssq != nullptr;
+    if ((((uintptr_t)op) & 15) != 0 || (stats && (((uintptr_t)(nio.out_xhat + (size_t)gj * N + gi0)) & 7) != 0)) return false;
+    old = *reinterpret_cast<const float4*>(op);
+    return true;
+}
 __device__ __forceinline__ void finish_token_block(float4 acc, int gj, int tile_a, int lane, void* __restrict__ out,
-                                                   int out_mode, long long ldo, int N, const NormIO& nio) {
+                                                   int out_mode, long long ldo, int N, const NormIO& nio,
+                                                   bool have_old = false, float4 old_pre = make_float4(0.f, 0.f, 0.f, 0.f)) {
     if (out_mode == OUT_SWIGLU) {
         // lanes 0..15 hold gates of 64 features, lanes 16..31 their ups
         const float ux = __shfl_down_sync(0xffffffffu, acc.x, 16), uy = __shfl_down_sync(0xffffffffu, acc.y, 16);
@@ -471,7 +485,7 @@ __device__ __forceinline__ void finish_token_block(float4 acc, int gj, int tile_
             if (whole && (((uintptr_t)op) & 15) == 0 && (!stats || (((uintptr_t)xp) & 7) == 0)) {
                 float4 w4 = make_float4(f[0], f[1], f[2], f[3]);
                 if (out_mode == OUT_F32_ACC) {
-                    const float4 old = *reinterpret_cast<float4*>(op);
+                    const float4 old = have_old ? old_pre : *reinterpret_cast<float4*>(op);
                     w4.x += old.x; w4.y += old.y; w4.z += old.z; w4.w += old.w;
                 }
                 *reinterpret_cast<float4*>(op) = w4;
@@ -759,12 +773,42 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                                    (uint32_t)(j % S), v);
                 }
             }
-            if (n_owned > 0) mbar_wait(recv_bar, 0, abort_flag, status, 5);
         }
         if (!*abort_flag && SWAP) {
             const int j_first = push ? warp * S + split : split * WARPS + warp;
+            bool received = !push;           // pushed rows: the wait comes after everything that does not need them
             for (int j = j_first; j < cols; j += S * WARPS) {
                 const int gj = tile_b * BN + j;                      // token
+                // What the epilogue reads from global memory does not depend on the sums: the folded norm's
+                // factor, the residual values, for q/k/v the token's sequence, position, page and rotation.  All of
+                // it is asked for here, before the wait for the other ranks' rows, so that its latency (two to
+                // three dependent loads for q/k/v) runs beside the exchange instead of behind it.
+                const float sc = nio.in_ssq != nullptr ? norm_factor_warp(nio, gj, lane) : 1.0f;
+                float4 old4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                const bool have_old = out_mode != OUT_QKV && residual_prefetch(gj, tile_a, lane, out, out_mode, ldo, N, nio, old4);
+                int qb = -1, qpos = 0, qpage = 0;
+                float4 qc4 = make_float4(1.f, 1.f, 1.f, 1.f), qs4 = make_float4(0.f, 0.f, 0.f, 0.f), qw4 = make_float4(1.f, 1.f, 1.f, 1.f);
+                if (out_mode == OUT_QKV) {
+                    const int h = tile_a;
+                    const bool is_q = h < qio.nq, is_k = !is_q && h < qio.nq + qio.nkv;
+                    qb = qio.seq_of_token[gj];
+                    if (!is_q && qio.k_pool != nullptr && qb >= 0) {
+                        qpos = qio.positions[gj];
+                        qpage = gg_page_w(qio.page_table + (size_t)qb * qio.max_pages, qpos / qio.page_size, qio.max_pages,
+                                          PageBounds{qio.n_pages, qio.status}, 48);
+                    }
+                    if (is_q || is_k) {
+                        const float* w = is_q ? qio.qw : qio.kw;
+                        if (w != nullptr) qw4 = *reinterpret_cast<const float4*>(w + 4 * lane);
+                        const int i0 = 4 * (lane & 15);
+                        qc4 = *reinterpret_cast<const float4*>(qio.cosv + (size_t)gj * 64 + i0);
+                        qs4 = *reinterpret_cast<const float4*>(qio.sinv + (size_t)gj * 64 + i0);
+                    }
+                }
+                if (!received) {
+                    if (!mbar_wait(recv_bar, 0, abort_flag, status, 5)) break;
+                    received = true;
+                }
                 float4 v[MAX_CLUSTER];
                 if (push) {
                     const uint8_t* mine = recv_mine + (size_t)((j / S) * BM + 4 * lane) * 4;
@@ -781,30 +825,21 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                 for (int qq = 0; qq < MAX_CLUSTER; ++qq) { acc.x += v[qq].x; acc.y += v[qq].y; acc.z += v[qq].z; acc.w += v[qq].w; }
-                if (nio.in_ssq != nullptr) {
-                    const float sc = norm_factor_warp(nio, gj, lane);
-                    acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc;
-                }
+                if (nio.in_ssq != nullptr) { acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc; }
                 if (out_mode == OUT_QKV) {
                     // this tile is head `tile_a` of token gj; the lane holds features 4 lane .. 4 lane + 3
                     const int h = tile_a;
                     const bool is_q = h < qio.nq, is_k = !is_q && h < qio.nq + qio.nkv;
-                    const int b = qio.seq_of_token[gj];
-                    if (!is_q && (qio.k_pool == nullptr || b < 0)) continue;
+                    if (!is_q && (qio.k_pool == nullptr || qb < 0)) continue;
                     float f[4] = {acc.x, acc.y, acc.z, acc.w};
                     if (is_q || is_k) {
-                        const float* w = is_q ? qio.qw : qio.kw;
-                        if (w != nullptr) {
+                        if ((is_q ? qio.qw : qio.kw) != nullptr) {
                             float ss = fmaf(f[0], f[0], fmaf(f[1], f[1], fmaf(f[2], f[2], f[3] * f[3])));
                             ss = warp_sum(ss);
                             const float scale = 1.0f / sqrtf(ss * (1.0f / 128.0f) + qio.eps);
-                            const float4 w4 = *reinterpret_cast<const float4*>(w + 4 * lane);
-                            f[0] *= scale * w4.x; f[1] *= scale * w4.y; f[2] *= scale * w4.z; f[3] *= scale * w4.w;
+                            f[0] *= scale * qw4.x; f[1] *= scale * qw4.y; f[2] *= scale * qw4.z; f[3] *= scale * qw4.w;
                         }
-                        const int i0 = 4 * (lane & 15);
-                        const float4 c4 = *reinterpret_cast<const float4*>(qio.cosv + (size_t)gj * 64 + i0);
-                        const float4 s4 = *reinterpret_cast<const float4*>(qio.sinv + (size_t)gj * 64 + i0);
-                        const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+                        const float cs[4] = {qc4.x, qc4.y, qc4.z, qc4.w}, sn[4] = {qs4.x, qs4.y, qs4.z, qs4.w};
 #pragma unroll
                         for (int t = 0; t < 4; ++t) {
                             const float p = __shfl_xor_sync(0xffffffffu, f[t], 16);      // the other half of the pair
@@ -815,20 +850,17 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                     if (is_q) {
                         dst = qio.q_out + ((size_t)gj * qio.nq + h) * 128;
                     } else {
-                        const int pos = qio.positions[gj];
-                        const int page = gg_page_w(qio.page_table + (size_t)b * qio.max_pages, pos / qio.page_size,
-                                                   qio.max_pages, PageBounds{qio.n_pages, qio.status}, 48);
-                        if (page < 0) continue;      // (debug build) outside the pools: nothing is written
+                        if (qpage < 0) continue;      // (debug build) outside the pools: nothing is written
                         const int kvh = is_k ? h - qio.nq : h - qio.nq - qio.nkv;
                         dst = (is_k ? qio.k_pool : qio.v_pool) +
-                              (((size_t)page * qio.nkv + kvh) * qio.page_size + (pos % qio.page_size)) * 128;
+                              (((size_t)qpage * qio.nkv + kvh) * qio.page_size + (qpos % qio.page_size)) * 128;
                     }
                     __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), bb = __floats2bfloat162_rn(f[2], f[3]);
                     *reinterpret_cast<uint2*>(dst + 4 * lane) =
                         make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&bb));
                     continue;
                 }
-                finish_token_block(acc, gj, tile_a, lane, out, out_mode, ldo, N, nio);
+                finish_token_block(acc, gj, tile_a, lane, out, out_mode, ldo, N, nio, have_old, old4);
             }
         }
         if (cluster_reduce && !push) cluster_sync_all();     // nobody leaves while its shared memory may still be read
