@@ -62,29 +62,6 @@ __device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigne
     return d;
 }
 
-// 2^x for two arguments x <= 0 (minus infinity included) on the FMA pipe instead of the special-function
-// unit: x = n + f with n the nearest integer and f in [-0.5, 0.5] (the magic-number addition leaves n in the
-// low mantissa bits of t), 2^f by a cubic whose relative error is below 7.5e-5 (the results are rounded to
-// bfloat16, 3.9e-3), and n added to the exponent field.  Prefill attention computes a third of its
-// exponentials this way: the special-function unit (16 results per clock and SM) is what bounds its softmax.
-__device__ __forceinline__ void exp2_poly2(float x0, float x1, float& r0, float& r1) {
-    const float MAGIC = 12582912.0f;                        // 1.5 * 2^23
-    x0 = fmaxf(x0, -126.0f);
-    x1 = fmaxf(x1, -126.0f);
-    const unsigned long long x = pack2(x0, x1);
-    const unsigned long long t = add2(x, pack2(MAGIC, MAGIC));
-    const unsigned long long n = add2(t, pack2(-MAGIC, -MAGIC));
-    const unsigned long long f = fma2(n, pack2(-1.0f, -1.0f), x);
-    unsigned long long p = fma2(pack2(0.0551716685f, 0.0551716685f), f, pack2(0.2426111251f, 0.2426111251f));
-    p = fma2(p, f, pack2(0.6932609677f, 0.6932609677f));
-    p = fma2(p, f, pack2(0.9999280572f, 0.9999280572f));
-    float p0, p1, t0, t1;
-    unpack2(p, p0, p1);
-    unpack2(t, t0, t1);
-    r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
-    r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
-}
-
 __device__ __forceinline__ void st_dsmem_f32(uint32_t local_addr, uint32_t rank, float v) {
     uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
@@ -853,22 +830,16 @@ int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* 
 // per thread, so the row maximum and sum need no exchange between threads; they write P as bfloat16
 // back into tensor memory, over the first half of the score buffer it was made from (tcgen05.st), and
 //  O += P V  (128 x D x 16, four times; P is the A operand straight from tensor memory, V the MN-major
-// B operand in shared memory: one 128-byte row per key) accumulates in tensor memory.  O is rescaled in
-// place only when a row's maximum has grown by more than 2^8 since the scale in use was set (the
-// sums stay exact: P and the row sum use the same stale maximum), so most pages cost no pass over O.
+// B operand in shared memory: one 128-byte row per key) accumulates in tensor memory.
+// The maximum that P and the row sum are taken against is the one in use from the pages before (the result
+// is exact whatever it is, as long as nothing overflows), so a page costs no pass over its scores for their
+// maximum and no pass over O; only when the page's sum shows that a score lies more than 2^64 above it (or
+// the row has no maximum yet) does the warp find the page's maximum, rescale O in place where it has grown
+// by more than 2^8, and compute the page again.
 // Two CTAs share an SM (96 KB of shared memory and 256 tensor-memory columns each): while one runs
 // its softmax the other's MMAs keep the tensor pipe busy.
-// Every POLY_EVERY-th pair of exponentials of the softmax is computed by exp2_poly2.
-constexpr int POLY_EVERY = 3;
-// P as a tensor-memory operand: no P tile in shared memory and a quarter less for the tensor core to read
-// from shared memory per page (2,048 tokens: 747 -> 800 TFLOP/s; 8,192: 1,067 -> 1,125).  -DGG_ATTN_P_SMEM builds
-// the earlier form, which writes P into a swizzled K-major tile in shared memory.
-#ifndef GG_ATTN_P_SMEM
-constexpr bool P_IN_TMEM = true;
-#else
-constexpr bool P_IN_TMEM = false;
-#endif
-
+// All exponentials go to the special-function unit: computing a share of them as polynomials on the FMA pipe,
+// and a pass over the scores for their maximum, cost more issue slots than the unit's time they saved.
 template <int D>
 __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -878,7 +849,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
     constexpr int HALVES = D / 64;
     constexpr int QBOX = 128 * 64 * 2;              // [64 columns x 128 rows] box of Q: 16 KB
     constexpr int KBOX = 64 * 64 * 2;               // [64 columns x 64 rows] box of K or V: 8 KB
-    constexpr int Q_BYTES = HALVES * QBOX, K_STAGE = HALVES * KBOX, V_BYTES = HALVES * KBOX, P_BYTES = 128 * 64 * 2;
+    constexpr int Q_BYTES = HALVES * QBOX, K_STAGE = HALVES * KBOX, V_BYTES = HALVES * KBOX;
     constexpr int TMEM_COLS = 256;
     // The dynamic segment is the only shared memory of this kernel and is asked to start on a 1024-byte
     // boundary (the swizzled tiles need it) instead of being rounded up in the kernel: two CTAs of 96.25 KB share an SM.
@@ -889,8 +860,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
     // at 2,048 tokens, 1,118 against 1,125 at 8,192)
     constexpr int VST = 2;
     uint8_t* Vs = Ks + 2 * K_STAGE;                 // two stages
-    uint8_t* Ps = Vs + 2 * V_BYTES;                 // the P tile, only where P goes through shared memory
-    uint64_t* bars = (uint64_t*)(Ps + (P_IN_TMEM ? 0 : P_BYTES));
+    uint64_t* bars = (uint64_t*)(Vs + 2 * V_BYTES);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;                    // [2]
     uint64_t* k_empty = bars + 3;                   // [2]
@@ -908,7 +878,8 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
         tma::mbar_init(q_full, 1);
         for (int i = 0; i < 2; ++i) { tma::mbar_init(&k_full[i], 1); tma::mbar_init(&k_empty[i], 1); }
         for (int i = 0; i < 3; ++i) { tma::mbar_init(&v_full[i], 1); tma::mbar_init(&v_empty[i], 1); }
-        tma::mbar_init(&s_full[0], 1); tma::mbar_init(&s_full[1], 1); tma::mbar_init(p_ready, 128); tma::mbar_init(pv_done, 1);
+        tma::mbar_init(&s_full[0], 1); tma::mbar_init(&s_full[1], 1); tma::mbar_init(pv_done, 1);
+        tma::mbar_init(p_ready, 4);           // one arrival per softmax warp
         *abort_flag = 0;
         tma::mbar_fence_init();
         tma::prefetch_map(&tmQ); tma::prefetch_map(&tmK); tma::prefetch_map(&tmV);
@@ -968,7 +939,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
     } else if (warp == 5) {
         if (lane == 0 && active) {
             const uint32_t idesc_qk = tc5::idesc_bf16(128, 64, 0), idesc_pv = tc5::idesc_bf16(128, D, 1);
-            const uint32_t q_a = tma::smem_u32(Qs), k_a = tma::smem_u32(Ks), v_a = tma::smem_u32(Vs), p_a = tma::smem_u32(Ps);
+            const uint32_t q_a = tma::smem_u32(Qs), k_a = tma::smem_u32(Ks), v_a = tma::smem_u32(Vs);
             bool ok = tma::mbar_wait(q_full, 0, abort_flag, status, 23);
             // scores of page j into buffer j & 1
             auto issue_scores = [&](int j) -> bool {
@@ -1002,13 +973,8 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     const uint64_t bb = tc5::smem_desc(v_a + vs * V_BYTES + kk * 2048, KBOX, 1024);
-                    if (P_IN_TMEM) {
-                        // P of page j lies in the first 32 columns of score buffer j & 1: 16 keys are 8 columns
-                        tc5::mma_a_tmem(O_t, S_t + (uint32_t)((j & 1) * 64 + kk * 8), bb, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                    } else {
-                        const uint64_t a = tc5::smem_desc(p_a + kk * 32, 16, 1024);
-                        tc5::mma(O_t, a, bb, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                    }
+                    // P of page j lies in the first 32 columns of score buffer j & 1: 16 keys are 8 columns
+                    tc5::mma_a_tmem(O_t, S_t + (uint32_t)((j & 1) * 64 + kk * 8), bb, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 tc5::commit(pv_done);
                 tc5::commit(&v_empty[vs]);
@@ -1029,8 +995,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
             tc5::wait_ld();
             const int key0 = (kt_first + j) * PAGE;
             const bool edge = (key0 + PAGE - 1 > pos0) || (window > 0 && key0 < pos0 + 127 - window + 1);
-            // the maximum of the raw scores (the scale is positive); masked keys become minus infinity first
-            float mraw = -INFINITY;
+            // masked keys become minus infinity (the scale is positive)
             if (edge) {
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
@@ -1040,88 +1005,90 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
                     if (!vis) sr[c] = 0xff800000u;
                 }
             }
-            {
-                // eight independent running maxima: one chain of 64 dependent operations would cost more
-                // than the exponentials (only two softmax warps share a scheduler)
-                float m8[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) m8[k] = __uint_as_float(sr[k]);
-#pragma unroll
-                for (int c = 8; c < 64; ++c) m8[c & 7] = fmaxf(m8[c & 7], __uint_as_float(sr[c]));
-                mraw = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
-            }
-            const float mx = mraw * scale_log2;
-            // P V of the page before must be complete before O is rescaled and before P is overwritten (its
-            // scores were issued ahead of it, so s_full does not say so any more).  The exponentials do not
-            // depend on it: they are computed into registers first, and the wait comes as late as it can.
-            bool pv_seen = j == 0;
-            // the scale in use is kept while the maximum has not grown by more than 2^8
-            const bool grow = mx > m_used + 8.0f || (m_used == -INFINITY && mx != -INFINITY);
-            if (__any_sync(0xffffffffu, grow)) {
-                float corr = 1.0f;
-                if (grow) {
-                    corr = m_used == -INFINITY ? 0.f : fast_exp2(m_used - mx);
-                    m_used = mx;
-                    l *= corr;
-                }
-                if (j > 0) {
-                    if (!tma::mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag, status, 28)) { ok = false; break; }
-                    tc5::fence_after();
-                    pv_seen = true;
-#pragma unroll 1
-                    for (int c0 = 0; c0 < D; c0 += 32) {
-                        uint32_t orow[32];
-                        tc5::ld32(O_t + lane_off + c0, orow);
-                        tc5::wait_ld();
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * corr);
-                        tc5::st32(O_t + lane_off + c0, orow);
-                    }
-                    tc5::wait_st();
-                }
-            }
-            const float mu = m_used == -INFINITY ? 0.f : m_used;
-            const unsigned long long sc2 = pack2(scale_log2, scale_log2), nmu2 = pack2(-mu, -mu);
-            unsigned long long l4[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
             uint32_t pk[32];
+            // P = 2^(score * scale - maximum in use) as bfloat16 pairs; returns the sum of the page's P
+            auto exponentials = [&]() -> float {
+                const float mu = m_used == -INFINITY ? 0.f : m_used;
+                const unsigned long long sc2 = pack2(scale_log2, scale_log2), nmu2 = pack2(-mu, -mu);
+                unsigned long long l4[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-                // exponent of the pair: score * scale - maximum in use, one packed multiply-add
-                float x0, x1, p0, p1;
-                unpack2(fma2(pack2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1])), sc2, nmu2), x0, x1);
-                if (e % POLY_EVERY == 0) {
-                    exp2_poly2(x0, x1, p0, p1);
-                } else {
+                for (int e = 0; e < 32; ++e) {
+                    // exponent of the pair: score * scale - maximum in use, one packed multiply-add
+                    float x0, x1, p0, p1;
+                    unpack2(fma2(pack2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1])), sc2, nmu2), x0, x1);
                     p0 = fast_exp2(x0);
                     p1 = fast_exp2(x1);
+                    l4[e & 3] = add2(l4[e & 3], pack2(p0, p1));
+                    pk[e] = pack_bf16(p0, p1);
                 }
-                l4[e & 3] = add2(l4[e & 3], pack2(p0, p1));
-                pk[e] = pack_bf16(p0, p1);
-            }
-            {
                 float la, lb;
                 unpack2(add2(add2(l4[0], l4[1]), add2(l4[2], l4[3])), la, lb);
-                l += la + lb;
+                return la + lb;
+            };
+            // The maximum in use is stale on purpose: P and the row sum use the same one, so the result is exact
+            // whatever it is, as long as nothing overflows.  So a page is first computed with the maximum of
+            // the pages before it, without looking for its own; only when a row has no maximum yet, or the
+            // page's sum says that a score lies more than 2^64 above it, the warp finds the page's maximum,
+            // rescales O where it has grown by more than 2^8 and computes the page again.
+            float lpage = 0.f;
+            bool again = m_used == -INFINITY;
+            if (!__any_sync(0xffffffffu, again)) {
+                lpage = exponentials();
+                again = !(lpage < 1.8446744e19f);
             }
-            if (!pv_seen) {
-                if (!tma::mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag, status, 28)) { ok = false; break; }
-            }
-            if (P_IN_TMEM) {
-                // P over this thread's own row of the scores it has just read (the first 32 of the buffer's 64
-                // columns): the next MMA into this buffer is issued after the P V that reads it
-                tc5::st32(S_t + lane_off + (uint32_t)((j & 1) * 64), pk);
-                tc5::wait_st();
-            } else {
-                uint8_t* prow = Ps + row * 128;
+            if (__any_sync(0xffffffffu, again)) {
+                float mraw;
+                {
+                    // eight independent running maxima instead of one chain of 64 dependent operations
+                    float m8[8];
 #pragma unroll
-                for (int ch = 0; ch < 8; ++ch)
-                    *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) =
-                        make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-                tc5::fence_proxy_async_smem();     // P was written with ordinary stores; the tensor core reads it
+                    for (int k = 0; k < 8; ++k) m8[k] = __uint_as_float(sr[k]);
+#pragma unroll
+                    for (int c = 8; c < 64; ++c) m8[c & 7] = fmaxf(m8[c & 7], __uint_as_float(sr[c]));
+                    mraw = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+                }
+                const float mx = mraw * scale_log2;
+                const bool grow = mx > m_used + 8.0f || (m_used == -INFINITY && mx != -INFINITY);
+                if (__any_sync(0xffffffffu, grow)) {
+                    float corr = 1.0f;
+                    if (grow) {
+                        corr = m_used == -INFINITY ? 0.f : fast_exp2(m_used - mx);
+                        m_used = mx;
+                        l *= corr;
+                    }
+                    if (j > 0) {
+                        // P V of the page before must be complete before O is rescaled
+                        if (!tma::mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag, status, 28)) { ok = false; break; }
+                        tc5::fence_after();
+#pragma unroll 1
+                        for (int c0 = 0; c0 < D; c0 += 32) {
+                            uint32_t orow[32];
+                            tc5::ld32(O_t + lane_off + c0, orow);
+                            tc5::wait_ld();
+#pragma unroll
+                            for (int c = 0; c < 32; ++c) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * corr);
+                            tc5::st32(O_t + lane_off + c0, orow);
+                        }
+                        tc5::wait_st();
+                    }
+                }
+                lpage = exponentials();
             }
+            l += lpage;
+            // P over this thread's own row of the scores it has read (the first 32 of the buffer's 64 columns).
+            // Nothing else uses this buffer now: the P V that read the P of two pages ago from it was issued
+            // before the scores read above, and the tensor core works in order; the next scores into it are
+            // issued after the P V that reads this P.  (The P V of the page before reads the other buffer; only
+            // a rescaling of O has to wait for it.)
+            tc5::st32(S_t + lane_off + (uint32_t)((j & 1) * 64), pk);
+            tc5::wait_st();
             tc5::fence_before();
-            tma::mbar_arrive(p_ready);
+            __syncwarp();
+            if (lane == 0) tma::mbar_arrive(p_ready);
         }
+        // The last P V.  The scores of the last page say that the P V of two pages before is complete; the one
+        // in between has not been waited for, and a wait by parity can only tell neighbouring phases apart.
+        if (ok && ntiles > 1) ok = tma::mbar_wait(pv_done, (uint32_t)((ntiles - 2) & 1), abort_flag, status, 28);
         if (ok && tma::mbar_wait(pv_done, (uint32_t)((ntiles - 1) & 1), abort_flag, status, 28)) {
             tc5::fence_after();
             const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -1309,7 +1276,7 @@ GG_API gg_attn_prefill_tc(const void* q, const void* k_pool, const void* v_pool,
     const float scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(nq, max_tiles);
     if (d == 128) {
-        constexpr int smem = 2 * 16384 + 2 * 16384 + 2 * 16384 + (P_IN_TMEM ? 0 : 16384) + 256;   // Q, K x 2, V x 2, (P,) barriers
+        constexpr int smem = 2 * 16384 + 2 * 16384 + 2 * 16384 + 256;   // Q, K x 2, V x 2, barriers
         static bool cfg = false;
         if (!cfg) {
             cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -1319,7 +1286,7 @@ GG_API gg_attn_prefill_tc(const void* q, const void* k_pool, const void* v_pool,
         return gg_launch(attn_prefill_tc_kernel<128>, grid, dim3(192), smem, stream, 1, tq, tk, tv, (bf16*)out, cu_seqlens,
                          ctx_lens, seq_of_token, page_table, max_pages, n_seqs, nq, nkv, scale_log2, window, n_pages, status);
     }
-    constexpr int smem = 16384 + 2 * 8192 + 2 * 8192 + (P_IN_TMEM ? 0 : 16384) + 256;
+    constexpr int smem = 16384 + 2 * 8192 + 2 * 8192 + 256;
     static bool cfg64 = false;
     if (!cfg64) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

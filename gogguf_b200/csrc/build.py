@@ -42,7 +42,7 @@ NVCC_FLAGS = [
 # GOGGUF_B200_DEBUG=1: the debug build.  Kernels that follow a page table check every index and page id
 # before they use it and record a bad one in the status word instead of reading there (common.cuh); the
 # libraries of the two builds carry different hashes and live side by side.
-# GOGGUF_B200_NVCC_EXTRA: further compiler flags (for instance -DGG_ATTN_P_SMEM); they take part in the hash
+# GOGGUF_B200_NVCC_EXTRA: further compiler flags; they take part in the hash
 if os.environ.get("GOGGUF_B200_NVCC_EXTRA"):
     NVCC_FLAGS.extend(os.environ["GOGGUF_B200_NVCC_EXTRA"].split())
 DEBUG = os.environ.get("GOGGUF_B200_DEBUG", "0") == "1"

@@ -583,6 +583,36 @@ def test_attention_prefill_tensor_cores(nq, nkv, d, window, seqs):
     assert rel(out2, twin) < 8e-3
 
 
+@pytest.mark.parametrize("step", [5.0, 30.0, 140.0])
+@pytest.mark.parametrize("window", [0, 150])
+def test_attention_prefill_scores_that_grow_from_page_to_page(step, window):
+    """The tensor-core prefill kernel computes a page with the maximum of the pages before it and looks for the
+    page's own maximum only when the page's sum says that it must.  Here every page's scores lie `step` powers of
+    two above those of the page before: within the margin that needs no rescaling (5), far beyond it but still
+    representable (30), and beyond what a float holds (140), where the page has to be computed again."""
+    from gogguf_b200.csrc import fast_attention as fa
+    from gogguf_b200.csrc import tcgen05_gemm as tc
+    dt = torch.bfloat16
+    nq, nkv, d, n = 4, 1, 128, 384
+    seqs = [(n, n)]
+    kp, vp, table, _, vs = make_paged(seqs, nkv, d, dt, seed=31)
+    pos, sot, cu, cl = step_meta(seqs)
+    scale = 1.0 / math.sqrt(d)
+    q = torch.randn(n, nq, d, device=DEV, generator=torch.Generator(device=DEV).manual_seed(32)).to(dt)
+    q[:, :, 0] = 16.0
+    # key t has (t // 64) * c in its first component: score * scale * log2(e) grows by `step` per page
+    c = step / (16.0 * scale * 1.4426950408889634)
+    pages = table[0].tolist()
+    for t in range(n):
+        kp[pages[t // 64], :, t % 64, 0] = (t // 64) * c
+    ks = [torch.cat([kp[pg] for pg in pages[:n // 64]], dim=1)[:, :n]]
+    want = attention_reference(q, ks, vs, seqs, nq, nkv, scale, window)
+    out = torch.full((n, nq, d), float("nan"), device=DEV, dtype=dt)
+    fa.attn_prefill_tc(q, kp, vp, out, cu, cl, sot, table, 64, n, 1, n // 128 + 1, nq, nkv, d, scale, window)
+    tc.check_status(DEV)
+    assert rel(out, want) < 8e-3
+
+
 @pytest.mark.parametrize("nq,nkv,d,window,ctxs", [
     (8, 2, 128, 0, [1, 64, 65, 300, 2049]), (32, 8, 128, 0, [2048] * 3 + [17]), (8, 8, 64, 0, [100, 1000]),
     (16, 1, 64, 90, [500, 89, 90, 91]), (12, 2, 128, 33, [4000, 5])])
