@@ -38,6 +38,7 @@
 //
 // The reference multiplies with a one-thread-per-row scalar PTX kernel (pkg/gpu/cuda/ptx.go:67-129).
 #include <cuda.h>
+#include <type_traits>
 #include "common.cuh"
 #include "tma_util.cuh"
 
@@ -567,6 +568,9 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                                  (partial == nullptr && (nio.in_ssq != nullptr || nio.out_ssq != nullptr)));
     uint32_t* tmem_slot = (uint32_t*)(recv_bar + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    // decode form with a folded norm: the factor of every token of the tile, computed by the epilogue warps while
+    // the weights still stream (inside the barrier area for 16 tokens, behind it otherwise)
+    float* sfac = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + (BN <= 16 ? 128 : 256));
     // Up to 16 tokens the K splits of a cluster are added without any barrier at the end: every CTA sends the
     // partial rows of token j to the CTA that owns it (rank j mod S) with st.async into a receive area that is
     // not part of the pipeline stages, each row completing 512 bytes of the owner's mbarrier; the owner waits
@@ -685,6 +689,10 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
         const int RA = SWAP ? N : M, RB = SWAP ? M : N;
         pdl_wait();                              // the output may still be in use by earlier kernels
         const float sc = (!SWAP && gi < RA) ? norm_factor(nio, gi) : 1.0f;
+        if (SWAP && staged && nio.in_ssq != nullptr) {
+            const int t = (int)threadIdx.x - 64;             // the epilogue warps are threads 64 .. 191
+            if (t < BN && tile_b * BN + t < M) sfac[t] = norm_factor(nio, tile_b * BN + t);
+        }
         mbar_wait(accum, 0, abort_flag, status, 3);
         if (push3) cluster_arrive();             // the tile is complete in tensor memory: the stages are free from here
         if (!*abort_flag) {
@@ -744,7 +752,8 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
     __syncthreads();
     if (staged) {
         // Every CTA of the cluster passes its barriers exactly once each, whatever happened before.
-        if (cluster_reduce && !push2 && !push3) cluster_sync_all();
+        const bool pull_reduce = cluster_reduce && !push2 && !push3;
+        if (pull_reduce) cluster_arrive();       // (waited for below, after the loads that do not need the other ranks)
         // Decode form: a warp per token.  Each lane adds four consecutive features of the 128 of this tile over
         // the cluster's ranks, in rank order, then the epilogue of the output mode.  Up to 32 tokens per tile
         // the partial sums are *pushed* to the CTA that owns the token (rank j mod S) and the owner adds what it
@@ -774,18 +783,75 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                 }
             }
         }
-        if (!*abort_flag && SWAP) {
-            const int j_first = push ? warp * S + split : split * WARPS + warp;
+        // The residual values of this warp's first rounds are asked for before the wait for the other ranks (a
+        // round is one token per warp; a pulling owner has cols / S tokens on six warps).
+        const int j_first = push ? warp * S + split : split * WARPS + warp;
+        constexpr int RPRE = 3;
+        float4 old_r[RPRE];
+        bool have_r[RPRE];
+#pragma unroll
+        for (int r = 0; r < RPRE; ++r) {
+            const int j = j_first + r * S * WARPS;
+            old_r[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+            have_r[r] = SWAP && !push && out_mode != OUT_QKV && j < cols &&
+                        residual_prefetch(tile_b * BN + j, tile_a, lane, out, out_mode, ldo, N, nio, old_r[r]);
+        }
+        if (pull_reduce) cluster_wait();
+        // An owner that pulls from at most four ranks asks for the rows of several of its tokens at once (a gate-up
+        // product of 64 tokens has 32 tokens per owner, five to six per warp: one round trip through the cluster
+        // per token would stand in the open six times).
+        auto pull_grouped = [&](auto uc) {
+            constexpr int U = decltype(uc)::value, SP = MAX_CLUSTER / U;
+            const int stride = S * WARPS;
+            int round = 0;
+            for (int j0 = j_first; j0 < cols; j0 += U * stride, round += U) {
+                float4 v[U][SP];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int j = j0 + u * stride;
+#pragma unroll
+                    for (int qq = 0; qq < SP; ++qq)
+                        v[u][qq] = (qq < S && j < cols) ? ld_cluster_f32x4(stage + 4u * (uint32_t)(j * BM + 4 * lane), qq)
+                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int j = j0 + u * stride, r = round + u;
+                    if (j >= cols) break;
+                    const int gj = tile_b * BN + j;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int qq = 0; qq < SP; ++qq) { acc.x += v[u][qq].x; acc.y += v[u][qq].y; acc.z += v[u][qq].z; acc.w += v[u][qq].w; }
+                    if (nio.in_ssq != nullptr) { const float sc = sfac[j]; acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc; }
+                    float4 old4 = r == 0 ? old_r[0] : (r == 1 ? old_r[1] : old_r[2]);
+                    bool have_old = r < RPRE && (r == 0 ? have_r[0] : (r == 1 ? have_r[1] : have_r[2]));
+                    if (r >= RPRE) have_old = residual_prefetch(gj, tile_a, lane, out, out_mode, ldo, N, nio, old4);
+                    finish_token_block(acc, gj, tile_a, lane, out, out_mode, ldo, N, nio, have_old, old4);
+                }
+            }
+        };
+        // (only the forms that pull: up to 32 tokens the rows are pushed)
+        const bool grouped = SWAP && BN >= 64 && !push && out_mode != OUT_QKV && S <= 4 && !*abort_flag;
+        if constexpr (SWAP && BN >= 64) {
+            if (grouped) {
+                if (S <= 2) pull_grouped(std::integral_constant<int, 4>{});
+                else pull_grouped(std::integral_constant<int, 2>{});
+            }
+        }
+        if (!*abort_flag && SWAP && !grouped) {
             bool received = !push;           // pushed rows: the wait comes after everything that does not need them
-            for (int j = j_first; j < cols; j += S * WARPS) {
+            int round = 0;
+            for (int j = j_first; j < cols; j += S * WARPS, ++round) {
                 const int gj = tile_b * BN + j;                      // token
                 // What the epilogue reads from global memory does not depend on the sums: the folded norm's
                 // factor, the residual values, for q/k/v the token's sequence, position, page and rotation.  All of
                 // it is asked for here, before the wait for the other ranks' rows, so that its latency (two to
                 // three dependent loads for q/k/v) runs beside the exchange instead of behind it.
-                const float sc = nio.in_ssq != nullptr ? norm_factor_warp(nio, gj, lane) : 1.0f;
-                float4 old4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                const bool have_old = out_mode != OUT_QKV && residual_prefetch(gj, tile_a, lane, out, out_mode, ldo, N, nio, old4);
+                const float sc = nio.in_ssq != nullptr ? sfac[j] : 1.0f;
+                float4 old4 = round == 0 ? old_r[0] : (round == 1 ? old_r[1] : old_r[2]);
+                bool have_old = round < RPRE && (round == 0 ? have_r[0] : (round == 1 ? have_r[1] : have_r[2]));
+                if (!have_old && out_mode != OUT_QKV && (push || round >= RPRE))
+                    have_old = residual_prefetch(gj, tile_a, lane, out, out_mode, ldo, N, nio, old4);
                 int qb = -1, qpos = 0, qpage = 0;
                 float4 qc4 = make_float4(1.f, 1.f, 1.f, 1.f), qs4 = make_float4(0.f, 0.f, 0.f, 0.f), qw4 = make_float4(1.f, 1.f, 1.f, 1.f);
                 if (out_mode == OUT_QKV) {
@@ -1378,7 +1444,7 @@ template <int BN, int STAGES, bool SWAP, int MINB>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N, int K,
            int splits, int kb_per_split, float* partial, bool cluster, int* status, const NormIO& nio,
            const QkvIO& qio, cudaStream_t stream) {
-    constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256 + recv_bytes<BN, SWAP>();
+    constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256 + recv_bytes<BN, SWAP>() + (SWAP && BN > 16 ? 512 : 0);
     static_assert(STAGES * (A_BYTES + BN * BK * 2) >= BN * BM * 4, "the stages must hold a float32 tile");
     static_assert(!SWAP || BN != 32 || STAGES * (A_BYTES + BN * BK * 2) >= (2 * BN + MAX_CLUSTER - 1) * BM * 4,
                   "at 32 tokens the stages must also hold what the other ranks push");
