@@ -771,6 +771,7 @@ def test_debug_build_checks_page_tables_instead_of_reading_out_of_range():
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, GOGGUF_B200_DEBUG="1")
+    env.pop("GOGGUF_B200_GEMM_PAIR", None)        # the script drives the CTA-pair q/k/v epilogue, whatever this run's switches
     p = subprocess.run([sys.executable, os.path.join(root, "tests", "debug_bounds_script.py"), root], env=env,
                        capture_output=True, text=True, timeout=600)
     assert p.returncode == 0 and "debug bounds ok" in p.stdout, p.stdout[-2000:] + p.stderr[-4000:]
