@@ -800,6 +800,10 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
         // An owner that pulls from at most four ranks asks for the rows of several of its tokens at once (a gate-up
         // product of 64 tokens has 32 tokens per owner, five to six per warp: one round trip through the cluster
         // per token would stand in the open six times).
+        // A pulling owner says "I have read what I need from your shared memory" as soon as the rows of its last
+        // tokens are in its registers, and waits for the others to say so after its last epilogue: the last
+        // global stores run beside the barrier instead of before it.
+        bool left = !(cluster_reduce && !push);       // no closing barrier in the other forms
         auto pull_grouped = [&](auto uc) {
             constexpr int U = decltype(uc)::value, SP = MAX_CLUSTER / U;
             const int stride = S * WARPS;
@@ -814,14 +818,20 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                         v[u][qq] = (qq < S && j < cols) ? ld_cluster_f32x4(stage + 4u * (uint32_t)(j * BM + 4 * lane), qq)
                                                         : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
+                float4 accs[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    accs[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int qq = 0; qq < SP; ++qq) { accs[u].x += v[u][qq].x; accs[u].y += v[u][qq].y; accs[u].z += v[u][qq].z; accs[u].w += v[u][qq].w; }
+                }
+                if (!left && j0 + U * stride >= cols) { cluster_arrive(); left = true; }
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const int j = j0 + u * stride, r = round + u;
                     if (j >= cols) break;
                     const int gj = tile_b * BN + j;
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                    for (int qq = 0; qq < SP; ++qq) { acc.x += v[u][qq].x; acc.y += v[u][qq].y; acc.z += v[u][qq].z; acc.w += v[u][qq].w; }
+                    float4 acc = accs[u];
                     if (nio.in_ssq != nullptr) { const float sc = sfac[j]; acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc; }
                     float4 old4 = r == 0 ? old_r[0] : (r == 1 ? old_r[1] : old_r[2]);
                     bool have_old = r < RPRE && (r == 0 ? have_r[0] : (r == 1 ? have_r[1] : have_r[2]));
@@ -891,6 +901,7 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                 for (int qq = 0; qq < MAX_CLUSTER; ++qq) { acc.x += v[qq].x; acc.y += v[qq].y; acc.z += v[qq].z; acc.w += v[qq].w; }
+                if (!left && j + S * WARPS >= cols) { cluster_arrive(); left = true; }
                 if (nio.in_ssq != nullptr) { acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc; }
                 if (out_mode == OUT_QKV) {
                     // this tile is head `tile_a` of token gj; the lane holds features 4 lane .. 4 lane + 3
@@ -929,7 +940,10 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                 finish_token_block(acc, gj, tile_a, lane, out, out_mode, ldo, N, nio, have_old, old4);
             }
         }
-        if (cluster_reduce && !push) cluster_sync_all();     // nobody leaves while its shared memory may still be read
+        if (cluster_reduce && !push) {
+            if (!left) cluster_arrive();          // (a warp without a token, or a kernel that gave up)
+            cluster_wait();                       // nobody leaves while its shared memory may still be read
+        }
     }
     if (*abort_flag) {
         // a wait ran out: give copies and instructions in flight time to land before the memory goes away
