@@ -31,6 +31,7 @@ class GenerateParams:
     repeat_last_n: int = 64
     stop_token_ids: Optional[Sequence[int]] = None     # None: the model's own (eos_token_id)
     on_token: Optional[Callable[[int, int], bool]] = None   # (request index, token) -> go on?
+    keep_logits: bool = False      # results carry the float32 logits every sampled token was drawn from (host copies)
 
 
 @dataclass
@@ -38,6 +39,8 @@ class GenerationResult:
     tokens: List[int]
     finish_reason: str        # "stop" | "length" | "callback"
     prompt_tokens: int
+    logits: Optional[list] = None     # with GenerateParams.keep_logits: one [vocab] float32 row per sampling step, the
+                                      # one that ended the sequence with a stop token included
 
 
 def plan_batches(prompt_lens: Sequence[int], max_new: int, max_batch: int, capacity_tokens: int,
@@ -200,8 +203,10 @@ class Generator:
                     slots[i] = cache.open()
             logits = self._prefill(live, prompts, slots, cached)
             # a step ahead of the host needs a stepper that replays captured decode steps
+            # (and no copies of every step's logits to the host, which the loop below makes)
             ahead = (hasattr(self.stepper, "decode_from_device") and getattr(self.stepper, "capturable", True)
-                     and getattr(logits, "is_cuda", False) and len(live) <= 256)
+                     and getattr(logits, "is_cuda", False) and len(live) <= 256 and not params.keep_logits)
+            kept = {i: [] for i in batch} if params.keep_logits else None
             if ahead:
                 sampler.begin(live, [prompts[i] for i in live], logits.device)     # rings for a repeat penalty
             if ahead and sampler.device_only:
@@ -214,13 +219,18 @@ class Generator:
                 nxt = sampler.sample(logits, streams=live, steps=[len(generated[i]) for i in live],
                                      histories=hist)
                 self._toc()
+                if kept is not None:
+                    host = logits[:len(live)].float().cpu()
+                    for r, i in enumerate(live):
+                        kept[i].append(host[r])
                 go_on: List[int] = []
                 for i, t in zip(live, nxt):
                     reason = self._finish_reason(i, t, prompts, generated, params, max_new, stop)
                     if reason is None:
                         go_on.append(i)
                     else:
-                        results[i] = GenerationResult(generated[i], reason, len(prompts[i]))
+                        results[i] = GenerationResult(generated[i], reason, len(prompts[i]),
+                                                      kept[i] if kept is not None else None)
                         self._let_go(i, slots, held, prompts, generated)
                 live = go_on
                 if not live:

@@ -74,6 +74,19 @@ def test_stop_token_is_neither_kept_nor_fed_and_others_go_on():
     st.cache.check()
 
 
+def test_results_can_carry_the_logits_each_token_was_drawn_from():
+    st = ScriptedStepper()
+    out = gen(st).generate([[1], [9]], GenerateParams(max_tokens=4, stop_token_ids=[4], keep_logits=True))
+    assert out[0].tokens == [2, 3] and out[1].tokens == [10, 11, 12, 13]
+    # one row per sampling step: the step whose token was the stop token is there too
+    assert len(out[0].logits) == 3 and len(out[1].logits) == 4
+    for r in out:
+        assert all(row.shape == (V,) and row.dtype == torch.float32 for row in r.logits)
+    assert [int(row.argmax()) for row in out[0].logits] == [2, 3, 4]
+    assert [int(row.argmax()) for row in out[1].logits] == [10, 11, 12, 13]
+    assert gen(ScriptedStepper()).generate([[1]], GenerateParams(max_tokens=2))[0].logits is None
+
+
 def test_default_stop_tokens_come_from_the_model():
     st = ScriptedStepper()
     out = gen(st, default_stop=(3,)).generate([[1]], GenerateParams(max_tokens=9))

@@ -32,6 +32,14 @@ def test_greedy_generation_through_the_entry_point(tmp_path_factory):
     # a function of the row's logits in the sampler's place (gogguf.Greedy is one)
     out = ctx.generate(prompts, gg.GenerateParams(max_tokens=4, stop_token_ids=[], sampler=gg.Greedy))
     assert [r.tokens for r in out] == [ref0[:4], ref1[:4]]
+    # the logits every token was drawn from, on request
+    out = ctx.generate(prompts, gg.GenerateParams(max_tokens=3, stop_token_ids=[], keep_logits=True))
+    for p, r in zip(prompts, out):
+        assert len(r.logits) == 3
+        whole = plain.forward(cfg, w, list(p) + r.tokens[:2], wide=True)
+        for k, row in enumerate(r.logits):
+            assert rel_err(row, whole[len(p) - 1 + k]) < TOL_F32
+            assert int(row.argmax()) == r.tokens[k]
     ctx.cache.check()
     assert ctx.cache.live_slots == 0
 
