@@ -6,12 +6,12 @@
 """
 from . import config  # noqa: F401  (registers architectures)
 from . import parts   # noqa: F401  (registers part kinds)
-from .api import Context, Conversation, Engine, Greedy, LoadOptions, load, new_sampler
+from .api import Context, Conversation, Engine, Greedy, LoadOptions, load, load_random, new_sampler
 from .engine.generate import GenerateParams, GenerationResult, GenerationSession
 from .engine.step import LayerTaps, StepEntry, StepError, StepOutcome
 from .sampling.sampler import Sampler, SamplerConfig
 
 __version__ = "0.1.0"
-__all__ = ["Context", "Conversation", "Engine", "Greedy", "LoadOptions", "load", "new_sampler", "GenerateParams",
+__all__ = ["Context", "Conversation", "Engine", "Greedy", "LoadOptions", "load", "load_random", "new_sampler", "GenerateParams",
            "GenerationResult", "GenerationSession", "Sampler", "SamplerConfig", "LayerTaps", "StepEntry", "StepError",
            "StepOutcome"]

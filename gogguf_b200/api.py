@@ -191,6 +191,25 @@ def load(path: str, options: Optional[LoadOptions] = None) -> Engine:
     return Engine(model, options)
 
 
+def load_random(config, seed: int = 0, options: Optional[LoadOptions] = None, std: Optional[float] = None,
+                norm_std: float = 0.0) -> Engine:
+    """An engine over random weights made on the device from a configuration (a config.json path or its
+    dictionary) and a seed: the random-weights mode without a folder in between.  The values come from the
+    device's generator, so a seed names another model here than in a folder written by `random` (which draws
+    on the host); the same seed gives the same model every time."""
+    import json
+    from .config import config_from_dict
+    options = options or LoadOptions()
+    if not torch.cuda.is_available():
+        raise RuntimeError("gogguf_b200 needs a CUDA device (B200); there is no CPU path")
+    if not isinstance(config, dict):
+        with open(config) as f:
+            config = json.load(f)
+    model = Model.random(config_from_dict(config), seed=seed, dtype=options.dtype, device=options.device,
+                         fast=options.fast, std=std, norm_std=norm_std)
+    return Engine(model, options)
+
+
 def new_sampler(cfg: SamplerConfig) -> Sampler:
     """gogguf.NewSampler (gogguf.go:63-66)."""
     return Sampler(cfg)

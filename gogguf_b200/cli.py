@@ -1,7 +1,8 @@
 """Command line, in the manner of the reference's `gogguf` (cmd/gogguf/main.go:21-51):
 
-    gogguf_b200 run -m DIR -p "1 2 3" [-p "4 5"] [-n 128] [--temp 0] [--top-k 0] [--top-p 1] [--min-p 0]
-                    [--repeat-penalty 1] [--repeat-last-n 64] [--seed 0] [--dtype bfloat16] [-i]
+    gogguf_b200 run (-m DIR | --random CONFIG.json [--weights-seed 0]) -p "1 2 3" [-p "4 5"] [-n 128] [--temp 0]
+                    [--top-k 0] [--top-p 1] [--min-p 0] [--repeat-penalty 1] [--repeat-last-n 64] [--seed 0]
+                    [--dtype bfloat16] [-i]
     gogguf_b200 info -m DIR
     gogguf_b200 inspect DIR
     gogguf_b200 random -c CONFIG.json -o DIR [--seed 0] [--dtype bfloat16] [--std S] [--norm-std S]
@@ -41,8 +42,10 @@ def _ids(text: str) -> List[int]:
 
 def cmd_run(a) -> int:
     import gogguf_b200 as gg
-    if not a.m:
-        raise SystemExit("usage: gogguf_b200 run -m DIR -p \"token ids\" [-n 128]")
+    if not a.m and not a.random:
+        raise SystemExit("usage: gogguf_b200 run (-m DIR | --random CONFIG.json [--weights-seed S]) -p \"token ids\" [-n 128]")
+    if a.m and a.random:
+        raise SystemExit("give a model folder (-m) or a configuration for random weights (--random), not both")
     prompts: List[List[int]] = [_ids(p) for p in (a.p or [])]
     if a.prompt_file:
         with open(a.prompt_file) as f:
@@ -50,8 +53,8 @@ def cmd_run(a) -> int:
     if not prompts and not a.i:
         raise SystemExit("give a prompt with -p (token ids) or --prompt-file, or use -i")
     t_load = time.perf_counter()
-    engine = gg.load(a.m, gg.LoadOptions(dtype=a.dtype, max_tokens=a.cache_tokens, max_batch=a.max_batch,
-                                         timing=a.timing))
+    options = gg.LoadOptions(dtype=a.dtype, max_tokens=a.cache_tokens, max_batch=a.max_batch, timing=a.timing)
+    engine = gg.load(a.m, options) if a.m else gg.load_random(a.random, a.weights_seed, options)
     ctx = engine.new_context()
     t_load = (time.perf_counter() - t_load) * 1e3
     params = gg.GenerateParams(
@@ -266,6 +269,8 @@ def build_parser() -> argparse.ArgumentParser:
     sub = ap.add_subparsers(dest="cmd")
     r = sub.add_parser("run", help="generate tokens")
     r.add_argument("-m", help="model folder (config.json + model.safetensors)")
+    r.add_argument("--random", metavar="CONFIG.json", help="instead of -m: random weights made on the device from this configuration")
+    r.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights (--random)")
     r.add_argument("-p", action="append", help="prompt as token ids; repeat for a batch")
     r.add_argument("--prompt-file", help="one prompt of token ids per line")
     r.add_argument("-i", action="store_true", help="interactive: a conversation, one line of token ids per turn")

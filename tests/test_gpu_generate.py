@@ -360,3 +360,27 @@ def test_per_phase_timing_behind_a_flag(tmp_path_factory, capsys):
     assert cli.main(["run", "-m", folder, "-p", ids, "-n", "5", "--timing", "--stop-ids", ""]) == 0
     err = capsys.readouterr().err
     assert "Load: " in err and "Prefill (7 tok" in err and "TTFT: " in err and "Decode (5 tok, 4 steps)" in err
+
+
+def test_random_weights_without_a_folder(tmp_path_factory, capsys):
+    """`load_random` makes a model on the device from a configuration and a seed, without a folder;
+    `run --random CONFIG.json` is its command line."""
+    import os
+    import gogguf_b200 as gg
+    from gogguf_b200 import cli
+    from helpers import TINY
+    cfg, seed, std, nstd = TINY["B"]
+    folder = make_folder(tmp_path_factory.getbasetemp(), "B", "float32")
+    prompts = [random_tokens(cfg["vocab_size"], n, 40 + n) for n in (6, 2)]
+    params = gg.GenerateParams(max_tokens=6, stop_token_ids=[])
+    opts = gg.LoadOptions(dtype="float32", max_tokens=1024)
+    first = gg.load_random(dict(cfg), seed, opts, std=std, norm_std=nstd)
+    got = first.new_context().generate(prompts, params)
+    again = gg.load_random(dict(cfg), seed, opts, std=std, norm_std=nstd).new_context().generate(prompts, params)
+    assert [r.tokens for r in got] == [r.tokens for r in again]                 # a seed names one model
+    other = gg.load_random(dict(cfg), seed + 1, opts, std=std, norm_std=nstd).new_context().generate(prompts, params)
+    assert [r.tokens for r in other] != [r.tokens for r in got]
+    ids = " ".join(map(str, prompts[0]))
+    assert cli.main(["run", "--random", os.path.join(folder, "config.json"), "--weights-seed", "3", "-p", ids, "-n", "4",
+                     "--dtype", "float32", "--stop-ids", ""]) == 0
+    assert len(capsys.readouterr().out.split()) == 4
