@@ -268,7 +268,9 @@ def test_row_stats(T, H):
 
 NORM_SHAPES = [(1, 128, 128), (8, 256, 512), (8, 4096, 4096), (17, 384, 1000), (64, 1000, 520), (128, 768, 2048),
                (129, 256, 136), (300, 520, 264), (1024, 1024, 4096), (70, 96, 72), (5, 331, 104), (1000, 72, 48),
-               (260, 200, 64)]
+               (260, 200, 64),
+               # owners that pull: from two, three and eight ranks, up to six tokens per warp
+               (48, 24576, 256), (100, 16384, 512), (64, 4096, 4096), (128, 4096, 1024)]
 
 
 @pytest.mark.parametrize("M,N,K_", NORM_SHAPES)
@@ -317,7 +319,8 @@ def test_gemm_tcgen05_with_folded_norm(M, N, K_):
     assert torch.equal(again, out)
 
 
-@pytest.mark.parametrize("M,I,K_", [(1, 128, 128), (8, 12288, 512), (100, 640, 136), (300, 448, 264), (520, 1024, 1024)])
+@pytest.mark.parametrize("M,I,K_", [(1, 128, 128), (8, 12288, 512), (100, 640, 136), (300, 448, 264), (520, 1024, 1024),
+                                    (64, 12288, 512), (128, 6144, 1024), (40, 12288, 256), (33, 12288, 4096)])
 def test_gemm_tcgen05_fused_swiglu_with_folded_norm(M, I, K_):
     from gogguf_b200.csrc import tcgen05_gemm as tc
     g = torch.Generator(device=DEV).manual_seed(35)
