@@ -194,8 +194,9 @@ def main():
         a.layers = base["num_hidden_layers"]
     cdict = dict(base, num_hidden_layers=a.layers)
     long_ctx = [int(x) for x in a.decode_contexts.split(",") if x.strip()]
-    if long_ctx:        # the rotary tables are computed per step, so the context length is only a bound
-        cdict["max_position_embeddings"] = max(cdict["max_position_embeddings"], max(long_ctx) + 128)
+    longest = max(long_ctx + [int(x) for x in a.prefill_lengths.split(",") if x.strip()] + [0])
+    if longest:         # the rotary tables are computed per step, so the context length is only a bound
+        cdict["max_position_embeddings"] = max(cdict["max_position_embeddings"], longest + 128)
     cfg = config_from_dict(cdict)
     pk = peaks()
     t0 = time.time()

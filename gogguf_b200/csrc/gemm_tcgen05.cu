@@ -120,6 +120,66 @@ struct QkvIO {
     int* status;                 // where the debug build records a page id or table index out of range (code 48)
 };
 
+// The q/k/v epilogue of a warp that holds one token's 128 sums of head `h` (all q heads, then the k heads, then
+// the v heads), four per lane.  qkv_token_data() is what it reads from global memory beside the sums (the token's
+// sequence, position and page, its rotation and the norm's weight); it depends on no sum and is asked for early.
+struct QkvTok {
+    int b, pos, page;
+    float4 c4, s4, w4;
+};
+__device__ __forceinline__ QkvTok qkv_token_data(const QkvIO& qio, int gj, int h, int lane) {
+    QkvTok t;
+    t.b = -1; t.pos = 0; t.page = 0;
+    t.c4 = make_float4(1.f, 1.f, 1.f, 1.f); t.s4 = make_float4(0.f, 0.f, 0.f, 0.f); t.w4 = make_float4(1.f, 1.f, 1.f, 1.f);
+    const bool is_q = h < qio.nq, is_k = !is_q && h < qio.nq + qio.nkv;
+    t.b = qio.seq_of_token[gj];
+    if (!is_q && qio.k_pool != nullptr && t.b >= 0) {
+        t.pos = qio.positions[gj];
+        t.page = gg_page_w(qio.page_table + (size_t)t.b * qio.max_pages, t.pos / qio.page_size, qio.max_pages,
+                           PageBounds{qio.n_pages, qio.status}, 48);
+    }
+    if (is_q || is_k) {
+        const float* w = is_q ? qio.qw : qio.kw;
+        if (w != nullptr) t.w4 = *reinterpret_cast<const float4*>(w + 4 * lane);
+        const int i0 = 4 * (lane & 15);
+        t.c4 = *reinterpret_cast<const float4*>(qio.cosv + (size_t)gj * 64 + i0);
+        t.s4 = *reinterpret_cast<const float4*>(qio.sinv + (size_t)gj * 64 + i0);
+    }
+    return t;
+}
+// acc: features 4 lane .. 4 lane + 3 of head h of token gj, already multiplied by the folded norm's factor.
+// Per-head RMSNorm and rotation for q and k; q to its buffer, k and v into the paged cache.  All 32 lanes call it.
+__device__ __forceinline__ void qkv_token_finish(float4 acc, int gj, int h, int lane, const QkvIO& qio, const QkvTok& t) {
+    const bool is_q = h < qio.nq, is_k = !is_q && h < qio.nq + qio.nkv;
+    if (!is_q && (qio.k_pool == nullptr || t.b < 0)) return;
+    float f[4] = {acc.x, acc.y, acc.z, acc.w};
+    if (is_q || is_k) {
+        if ((is_q ? qio.qw : qio.kw) != nullptr) {
+            float ss = fmaf(f[0], f[0], fmaf(f[1], f[1], fmaf(f[2], f[2], f[3] * f[3])));
+            ss = warp_sum(ss);
+            const float scale = 1.0f / sqrtf(ss * (1.0f / 128.0f) + qio.eps);
+            f[0] *= scale * t.w4.x; f[1] *= scale * t.w4.y; f[2] *= scale * t.w4.z; f[3] *= scale * t.w4.w;
+        }
+        const float cs[4] = {t.c4.x, t.c4.y, t.c4.z, t.c4.w}, sn[4] = {t.s4.x, t.s4.y, t.s4.z, t.s4.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float p = __shfl_xor_sync(0xffffffffu, f[u], 16);      // the other half of the pair
+            f[u] = lane < 16 ? f[u] * cs[u] - p * sn[u] : p * sn[u] + f[u] * cs[u];
+        }
+    }
+    bf16* dst;
+    if (is_q) {
+        dst = qio.q_out + ((size_t)gj * qio.nq + h) * 128;
+    } else {
+        if (t.page < 0) return;      // (debug build) outside the pools: nothing is written
+        const int kvh = is_k ? h - qio.nq : h - qio.nq - qio.nkv;
+        dst = (is_k ? qio.k_pool : qio.v_pool) +
+              (((size_t)t.page * qio.nkv + kvh) * qio.page_size + (t.pos % qio.page_size)) * 128;
+    }
+    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), bb = __floats2bfloat162_rn(f[2], f[3]);
+    *reinterpret_cast<uint2*>(dst + 4 * lane) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&bb));
+}
+
 // One thread computes its token's factor (four running sums keep the loads independent).
 __device__ __forceinline__ float norm_factor(const NormIO& nio, int token) {
     if (nio.in_ssq == nullptr) return 1.0f;
@@ -862,25 +922,8 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                 bool have_old = round < RPRE && (round == 0 ? have_r[0] : (round == 1 ? have_r[1] : have_r[2]));
                 if (!have_old && out_mode != OUT_QKV && (push || round >= RPRE))
                     have_old = residual_prefetch(gj, tile_a, lane, out, out_mode, ldo, N, nio, old4);
-                int qb = -1, qpos = 0, qpage = 0;
-                float4 qc4 = make_float4(1.f, 1.f, 1.f, 1.f), qs4 = make_float4(0.f, 0.f, 0.f, 0.f), qw4 = make_float4(1.f, 1.f, 1.f, 1.f);
-                if (out_mode == OUT_QKV) {
-                    const int h = tile_a;
-                    const bool is_q = h < qio.nq, is_k = !is_q && h < qio.nq + qio.nkv;
-                    qb = qio.seq_of_token[gj];
-                    if (!is_q && qio.k_pool != nullptr && qb >= 0) {
-                        qpos = qio.positions[gj];
-                        qpage = gg_page_w(qio.page_table + (size_t)qb * qio.max_pages, qpos / qio.page_size, qio.max_pages,
-                                          PageBounds{qio.n_pages, qio.status}, 48);
-                    }
-                    if (is_q || is_k) {
-                        const float* w = is_q ? qio.qw : qio.kw;
-                        if (w != nullptr) qw4 = *reinterpret_cast<const float4*>(w + 4 * lane);
-                        const int i0 = 4 * (lane & 15);
-                        qc4 = *reinterpret_cast<const float4*>(qio.cosv + (size_t)gj * 64 + i0);
-                        qs4 = *reinterpret_cast<const float4*>(qio.sinv + (size_t)gj * 64 + i0);
-                    }
-                }
+                QkvTok qt;
+                if (out_mode == OUT_QKV) qt = qkv_token_data(qio, gj, tile_a, lane);       // this tile is head `tile_a`
                 if (!received) {
                     if (!mbar_wait(recv_bar, 0, abort_flag, status, 5)) break;
                     received = true;
@@ -904,37 +947,7 @@ __global__ void __launch_bounds__(NUM_THREADS, MINB) gemm_tc_kernel(
                 if (!left && j + S * WARPS >= cols) { cluster_arrive(); left = true; }
                 if (nio.in_ssq != nullptr) { acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc; }
                 if (out_mode == OUT_QKV) {
-                    // this tile is head `tile_a` of token gj; the lane holds features 4 lane .. 4 lane + 3
-                    const int h = tile_a;
-                    const bool is_q = h < qio.nq, is_k = !is_q && h < qio.nq + qio.nkv;
-                    if (!is_q && (qio.k_pool == nullptr || qb < 0)) continue;
-                    float f[4] = {acc.x, acc.y, acc.z, acc.w};
-                    if (is_q || is_k) {
-                        if ((is_q ? qio.qw : qio.kw) != nullptr) {
-                            float ss = fmaf(f[0], f[0], fmaf(f[1], f[1], fmaf(f[2], f[2], f[3] * f[3])));
-                            ss = warp_sum(ss);
-                            const float scale = 1.0f / sqrtf(ss * (1.0f / 128.0f) + qio.eps);
-                            f[0] *= scale * qw4.x; f[1] *= scale * qw4.y; f[2] *= scale * qw4.z; f[3] *= scale * qw4.w;
-                        }
-                        const float cs[4] = {qc4.x, qc4.y, qc4.z, qc4.w}, sn[4] = {qs4.x, qs4.y, qs4.z, qs4.w};
-#pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            const float p = __shfl_xor_sync(0xffffffffu, f[t], 16);      // the other half of the pair
-                            f[t] = lane < 16 ? f[t] * cs[t] - p * sn[t] : p * sn[t] + f[t] * cs[t];
-                        }
-                    }
-                    bf16* dst;
-                    if (is_q) {
-                        dst = qio.q_out + ((size_t)gj * qio.nq + h) * 128;
-                    } else {
-                        if (qpage < 0) continue;      // (debug build) outside the pools: nothing is written
-                        const int kvh = is_k ? h - qio.nq : h - qio.nq - qio.nkv;
-                        dst = (is_k ? qio.k_pool : qio.v_pool) +
-                              (((size_t)qpage * qio.nkv + kvh) * qio.page_size + (qpos % qio.page_size)) * 128;
-                    }
-                    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), bb = __floats2bfloat162_rn(f[2], f[3]);
-                    *reinterpret_cast<uint2*>(dst + 4 * lane) =
-                        make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&bb));
+                    qkv_token_finish(acc, gj, tile_a, lane, qio, qt);
                     continue;
                 }
                 finish_token_block(acc, gj, tile_a, lane, out, out_mode, ldo, N, nio, have_old, old4);
@@ -1376,7 +1389,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
 // out (mode) = sum over splits of partial[s], scaled by the folded norm's factor: a warp per (token, block of 128
 // columns), the epilogue of the decode form.
 __global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* partial, int splits, void* __restrict__ out,
-                                                                 int out_mode, long long ldo, int M, int N, const NormIO nio) {
+                                                                 int out_mode, long long ldo, int M, int N, const NormIO nio,
+                                                                 const QkvIO qio) {
     pdl_launch();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -1384,6 +1398,8 @@ __global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* pa
     const int tile_a = blockIdx.x;                               // block of 128 columns
     if (gj >= M) return;
     const int c0 = tile_a * 128 + 4 * lane;
+    QkvTok qt;
+    if (out_mode == OUT_QKV) qt = qkv_token_data(qio, gj, tile_a, lane);       // a block of 128 columns is one head
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c0 + 4 <= N && (N & 3) == 0) {
         for (int s = 0; s < splits; ++s) {
@@ -1400,6 +1416,10 @@ __global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* pa
     if (nio.in_ssq != nullptr) {
         const float sc = norm_factor_warp(nio, gj, lane);
         acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc;
+    }
+    if (out_mode == OUT_QKV) {
+        qkv_token_finish(acc, gj, tile_a, lane, qio, qt);
+        return;
     }
     finish_token_block(acc, gj, tile_a, lane, out, out_mode, ldo, N, nio);
 }
@@ -1451,7 +1471,7 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out
                         used, per, partial, qio);
     if (rc != 0 || used == 1) return rc;
     return gg_launch(gemm_splitk_finish_kernel, dim3((N + 127) / 128, (M + 7) / 8), dim3(256), 0, stream, 1,
-                     (const float*)partial, used, out, out_mode, ldo, M, N, nio);
+                     (const float*)partial, used, out, out_mode, ldo, M, N, nio, qio);
 }
 
 template <int BN, int STAGES, bool SWAP, int MINB>
@@ -1563,7 +1583,7 @@ static int gemm_tc_impl(const void* x, const void* w, void* out, int out_mode, i
             if ((rc = make_map(&tb, w, N, K, K, 128)) != 0) return rc;
             int ps = pair_splits(M, N, K);
             if (scratch == nullptr || scratch_elems < (long long)ps * M * N) ps = 1;     // no room for partial tiles
-            if (out_mode == OUT_QKV) ps = 1;             // the per-head epilogue needs the whole sums in tensor memory
+            // (a split q/k/v product leaves the per-head epilogue to the kernel that adds the partial tiles)
             rc = launch_pair(ta, tb, out, out_mode, ldo, M, N, K, status, nio, qio, ps, scratch, stream);
         } else if (out_mode == OUT_QKV) rc = GG_ERR_ARG;       // only the CTA-pair form has the q/k/v epilogue
         else if (bn == 256) rc = launch_persistent(ta, tb, out, out_mode, ldo, M, N, K, status, nio, stream);
@@ -1626,11 +1646,11 @@ GG_API gg_gemm_tc_qkv_rope(const void* x, const void* w, int M, int K, long long
                            float in_eps, void* q_out, const float* qw, const float* kw, float eps, const float* cosv,
                            const float* sinv, const int* positions, const int* seq_of_token, const int* page_table,
                            int max_pages, int page_size, int n_pages, void* k_pool, void* v_pool, int nq, int nkv,
-                           int* status, cudaStream_t stream) {
+                           float* scratch, long long scratch_elems, int* status, cudaStream_t stream) {
     if (in_ssq != nullptr && (in_parts != (K + 127) / 128 || !(in_eps > 0.f))) return GG_ERR_ARG;
     const NormIO nio = {in_ssq, in_parts, K > 0 ? 1.0f / (float)K : 0.f, in_eps, nullptr, nullptr};
     const QkvIO qio = {(bf16*)q_out, qw, kw, eps, cosv, sinv, positions, seq_of_token, page_table, max_pages, page_size,
                        (bf16*)k_pool, (bf16*)v_pool, nq, nkv, n_pages, status};
     const int N = (nq + 2 * nkv) * 128;
-    return gemm_tc_impl(x, w, q_out, OUT_QKV, M, N, K, ldx, N, nullptr, 0, 1, status, nio, qio, stream);
+    return gemm_tc_impl(x, w, q_out, OUT_QKV, M, N, K, ldx, N, scratch, scratch_elems, 1, status, nio, qio, stream);
 }

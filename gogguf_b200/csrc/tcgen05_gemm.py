@@ -157,9 +157,12 @@ def gemm_tc_qkv_rope(x: torch.Tensor, w: torch.Tensor, m: int, q_out: torch.Tens
                      kw: Optional[torch.Tensor], eps: float, cos: torch.Tensor, sin: torch.Tensor,
                      positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor, page_size: int,
                      k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], nq: int, nkv: int,
-                     in_ssq: Optional[torch.Tensor] = None, in_eps: float = 0.0) -> None:
+                     in_ssq: Optional[torch.Tensor] = None, in_eps: float = 0.0,
+                     scratch: Optional[torch.Tensor] = None) -> None:
     """The q/k/v projection of a step (head size 128; any m, see `qkv_rope_takes`) with the per-head q/k RMSNorm,
-    the rotation and the cache write in the product's epilogue (csrc/gemm_tcgen05.cu, gg_gemm_tc_qkv_rope)."""
+    the rotation and the cache write in the product's epilogue (csrc/gemm_tcgen05.cu, gg_gemm_tc_qkv_rope).
+    scratch: room for the partial tiles of a K split at more than 128 tokens (`pair_scratch_elems`); the kernel that
+    adds them then does the per-head work."""
     N, K = w.shape
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16:
         raise KernelError("gemm_tc_qkv_rope takes bfloat16 operands")
@@ -185,7 +188,8 @@ def gemm_tc_qkv_rope(x: torch.Tensor, w: torch.Tensor, m: int, q_out: torch.Tens
         float(eps), cos.data_ptr(), sin.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(),
         page_table.data_ptr(), page_table.shape[-1], int(page_size), k_pool.shape[0] if k_pool is not None else 0,
         k_pool.data_ptr() if k_pool is not None else 0, v_pool.data_ptr() if v_pool is not None else 0,
-        nq, nkv, st.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        nq, nkv, scratch.data_ptr() if scratch is not None else 0, scratch.numel() if scratch is not None else 0,
+        st.data_ptr(), torch.cuda.current_stream().cuda_stream)
 
 
 def make_linear(weight: torch.Tensor, swiglu: bool = False) -> Optional[Callable]:

@@ -104,7 +104,7 @@ class AttentionMixer:
         table = ctx.page_tables[cache.group]
         if self._fused_rope and tcgen05_gemm.qkv_rope_takes(T):
             # norm, rotation and cache write happen in the projection's epilogue
-            self.qkv.qkv_rope(h, T, q_out=q, qw=self.q_norm, kw=self.k_norm, eps=self.eps, cos=cos, sin=sin,
+            self.qkv.qkv_rope(h, T, ws=ctx.ws, q_out=q, qw=self.q_norm, kw=self.k_norm, eps=self.eps, cos=cos, sin=sin,
                               positions=ctx.positions, seq_of_token=ctx.seq_of_token, page_table=table,
                               page_size=cache.page_size, k_pool=cache.k if writes_cache else None,
                               v_pool=cache.v if writes_cache else None, nq=nq, nkv=nkv)

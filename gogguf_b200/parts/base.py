@@ -148,10 +148,15 @@ class Linear:
     def tensor_core(self) -> bool:
         return self._fast is not None
 
-    def qkv_rope(self, x, m: int, **outputs) -> None:
-        """This projection as the q/k/v projection of a decode step, with q/k norm, rotation and cache write
-        in its epilogue (`csrc.tcgen05_gemm.gemm_tc_qkv_rope`, whose keyword arguments `outputs` are)."""
+    def qkv_rope(self, x, m: int, ws: Optional[Workspace] = None, **outputs) -> None:
+        """This projection as the q/k/v projection of a step, with q/k norm, rotation and cache write
+        in its epilogue (`csrc.tcgen05_gemm.gemm_tc_qkv_rope`, whose keyword arguments `outputs` are).  With a
+        workspace, a product of a few hundred tokens may split K over the CTA pairs."""
         from ..csrc import tcgen05_gemm
+        if ws is not None and m > 128:
+            need = tcgen05_gemm.pair_scratch_elems(m, self.weight.shape[0], self.weight.shape[1])
+            if need:
+                outputs["scratch"] = ws.get("gemm_partial_tiles", (need,), torch.float32)
         if self.folded_eps is not None:
             if not isinstance(x, RowStats):
                 raise TypeError("Linear: a projection with a folded norm reads RowStats, not normalised rows")

@@ -341,7 +341,8 @@ def test_gemm_tcgen05_fused_swiglu_with_folded_norm(M, I, K_):
 @pytest.mark.parametrize("M,nq,nkv,K_,norm,fold", [(1, 2, 1, 128, True, False), (8, 8, 2, 512, True, True),
                                                    (37, 3, 3, 264, False, True), (128, 4, 1, 1024, True, False),
                                                    (300, 8, 2, 512, True, True), (1000, 5, 5, 136, False, False),
-                                                   (129, 3, 1, 264, True, False), (600, 2, 1, 2048, True, True)])
+                                                   (129, 3, 1, 264, True, False), (600, 2, 1, 2048, True, True),
+                                                   (256, 32, 8, 4096, True, True), (384, 4, 4, 1024, False, False)])
 def test_gemm_tcgen05_qkv_with_norm_rope_and_cache_write(M, nq, nkv, K_, norm, fold):
     """The q/k/v product with the per-head work in its epilogue (decode form up to 128 tokens, CTA-pair form
     above), against the unfused pair (product, then the qk_norm_rope_cache kernel), and against the plain
@@ -412,6 +413,21 @@ def test_gemm_tcgen05_qkv_with_norm_rope_and_cache_write(M, nq, nkv, K_, norm, f
     tc.gemm_tc_qkv_rope(xh, w, M, q3, qw, kw, eps, cos, sin, pos, seq_of, table, ps, None, None, nq, nkv,
                         in_ssq=ssq if fold else None, in_eps=eps_in)
     assert torch.equal(q3, q2)
+    # with room for partial tiles a product of a few hundred tokens splits K over the CTA pairs, and the kernel
+    # that adds the partial tiles does the per-head work
+    need = tc.pair_scratch_elems(M, w.shape[0], K_) if M > 128 else 0
+    if need:
+        scratch = torch.full((need,), float("nan"), device=DEV)
+        q4 = torch.full((M, nq * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+        k4, v4 = pools()
+        tc.gemm_tc_qkv_rope(xh, w, M, q4, qw, kw, eps, cos, sin, pos, seq_of, table, ps, k4, v4, nq, nkv,
+                            in_ssq=ssq if fold else None, in_eps=eps_in, scratch=scratch)
+        tc.check_status(DEV)
+        assert torch.equal(k4 == UNWRITTEN, k1 == UNWRITTEN) and torch.equal(v4 == UNWRITTEN, v1 == UNWRITTEN)
+        assert rel(q4, want) < 6e-3 and rel(q4, q2) < 6e-3
+        assert rel(k4[wk], k2[wk]) < 6e-3 and rel(v4[wv], v2[wv]) < 6e-3
+    if (M, K_) in ((600, 2048), (256, 4096)):
+        assert need > 0              # these shapes are here because they split
 
 
 @pytest.mark.parametrize("M,N,K_", [(256, 4096, 4096), (300, 520, 2048), (512, 1024, 8192), (200, 264, 1024),
