@@ -1216,7 +1216,7 @@ template <int STAGES>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
     void* __restrict__ out, int out_mode, long long ldo, int M, int N, int K, int* __restrict__ status,
-    const NormIO nio, int splits, int kb_per_split, float* __restrict__ partial, const QkvIO qio) {
+    const NormIO nio, int splits, int whole, int kb_per_split, float* __restrict__ partial, const QkvIO qio) {
     constexpr int BN = 256;                     // columns of the pair's tile (each CTA stages 128 of the B rows)
     constexpr int HALF_B_BYTES = 128 * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + HALF_B_BYTES;      // per CTA: 32 KB
@@ -1237,11 +1237,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     const int num_kb = (K + BK - 1) / BK;
     const int tiles_m = (M + 255) / 256, tiles_n = (N + BN - 1) / BN;
-    // With few tiles (prompts of a few hundred tokens) the K range of every tile is split over `splits` work
-    // items, so that all pairs have work; the items leave float32 partial tiles in `partial`
-    // [splits][M][N] and gemm_splitk_finish_kernel adds them and applies the output mode.
+    // With few tiles (prompts of a few hundred tokens) the K range of a tile is split over `splits` work items,
+    // so that all pairs have work.  The first `whole` tiles (in tile order, a multiple of tiles_m: whole tile
+    // columns) are not split: the waves that the tiles fill anyway; the rest, a last wave that would be nearly
+    // empty, or all of them, are.  The items of a split tile leave float32 partial tiles in `partial`
+    // [splits][M][columns from the first split tile column on] and gemm_splitk_finish_kernel adds them and
+    // applies the output mode.
     const int tiles = tiles_m * tiles_n;
-    const int total = tiles * splits;
+    const int total = whole + (tiles - whole) * splits;
+    const int tn_split = whole / tiles_m;                       // first tile column that is split
+    const int NS = N - tn_split * BN;                           // columns of the partial tiles
+    // work item t -> (tile, split, is it one of a split tile's)
+    auto item_of = [&](int t, int& tile, int& split, bool& parted) {
+        if (t < whole) { tile = t; split = 0; parted = false; }
+        else { const int u = t - whole; tile = whole + u / splits; split = u % splits; parted = partial != nullptr; }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -1267,10 +1277,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
             int it = 0;
             bool first = true, ok = true;
             for (int t = pair; t < total && ok; t += num_pairs) {
-                const int tile = t % tiles, split = t / tiles;
+                int tile, split;
+                bool parted;
+                item_of(t, tile, split, parted);
                 const int tm = tile % tiles_m, tn = tile / tiles_m;
                 const int arow = tm * 256 + (int)rank * 128, brow = tn * BN + (int)rank * 128;
-                const int kb0 = split * kb_per_split, kb1 = min(num_kb, kb0 + kb_per_split);
+                const int kb0 = parted ? split * kb_per_split : 0, kb1 = parted ? min(num_kb, kb0 + kb_per_split) : num_kb;
                 int kb = kb0;
                 if (first) {
                     const int pre = kb1 - kb0 < STAGES ? kb1 - kb0 : STAGES;
@@ -1308,8 +1320,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t tacc = tmem_base + (uint32_t)(buf * BN);
-                const int split = t / tiles;
-                const int kb0 = split * kb_per_split, kb1 = min(num_kb, kb0 + kb_per_split);
+                int tile, split;
+                bool parted;
+                item_of(t, tile, split, parted);
+                const int kb0 = parted ? split * kb_per_split : 0, kb1 = parted ? min(num_kb, kb0 + kb_per_split) : num_kb;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
@@ -1333,18 +1347,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
         pdl_wait();
         int i = 0;
         for (int t = pair; t < total; t += num_pairs, ++i) {
-            const int tile = t % tiles, split = t / tiles;
+            int tile, split;
+            bool parted;
+            item_of(t, tile, split, parted);
             const int tm = tile % tiles_m, tn = tile / tiles_m;
             const int buf = i & 1;
             const uint32_t aph = (uint32_t)(i >> 1) & 1u;
             const int gi = tm * 256 + (int)rank * 128 + row;
-            const float sc = (gi < M && partial == nullptr) ? norm_factor(nio, gi) : 1.0f;   // while the tile is still being multiplied
+            const float sc = (gi < M && !parted) ? norm_factor(nio, gi) : 1.0f;   // while the tile is still being multiplied
             if (!mbar_wait(&acc_full[buf], aph, abort_flag, status, 3)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
-            if (partial != nullptr) {
-                // the raw sums of this K range: row gi of split's [M][N] float32 tile
-                float* prow = partial + ((size_t)split * M + gi) * N + tn * BN;
+            if (parted) {
+                // the raw sums of this K range: row gi of split's [M][NS] float32 tile
+                float* prow = partial + ((size_t)split * M + gi) * NS + (tn - tn_split) * BN;
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 16) {
                     if (tn * BN + c0 >= N) break;
@@ -1387,30 +1403,31 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_pair_kernel(
 }
 
 // out (mode) = sum over splits of partial[s], scaled by the folded norm's factor: a warp per (token, block of 128
-// columns), the epilogue of the decode form.
+// columns), the epilogue of the decode form.  The partial tiles cover the columns from `col0` on (the tile columns
+// that were split), NS of them per row.
 __global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* partial, int splits, void* __restrict__ out,
-                                                                 int out_mode, long long ldo, int M, int N, const NormIO nio,
-                                                                 const QkvIO qio) {
+                                                                 int out_mode, long long ldo, int M, int N, int col0, int NS,
+                                                                 const NormIO nio, const QkvIO qio) {
     pdl_launch();
     pdl_wait();
     const int lane = threadIdx.x & 31;
     const int gj = blockIdx.y * 8 + (threadIdx.x >> 5);          // token
-    const int tile_a = blockIdx.x;                               // block of 128 columns
+    const int tile_a = col0 / 128 + blockIdx.x;                  // block of 128 columns
     if (gj >= M) return;
     const int c0 = tile_a * 128 + 4 * lane;
     QkvTok qt;
     if (out_mode == OUT_QKV) qt = qkv_token_data(qio, gj, tile_a, lane);       // a block of 128 columns is one head
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (c0 + 4 <= N && (N & 3) == 0) {
+    if (c0 + 4 <= N && (NS & 3) == 0) {
         for (int s = 0; s < splits; ++s) {
-            const float4 v = *reinterpret_cast<const float4*>(partial + ((size_t)s * M + gj) * N + c0);
+            const float4 v = *reinterpret_cast<const float4*>(partial + ((size_t)s * M + gj) * NS + (c0 - col0));
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
     } else {
         float f[4] = {0.f, 0.f, 0.f, 0.f};
         for (int s = 0; s < splits; ++s)
             for (int t = 0; t < 4; ++t)
-                if (c0 + t < N) f[t] += partial[((size_t)s * M + gj) * N + c0 + t];
+                if (c0 + t < N) f[t] += partial[((size_t)s * M + gj) * NS + (c0 - col0) + t];
         acc = make_float4(f[0], f[1], f[2], f[3]);
     }
     if (nio.in_ssq != nullptr) {
@@ -1424,30 +1441,65 @@ __global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* pa
     finish_token_block(acc, gj, tile_a, lane, out, out_mode, ldo, N, nio);
 }
 
-// K splits of the CTA-pair form for a product with few tiles: the count that fills the 74 pairs best, as long as
-// every split keeps eight 64-wide slabs and the float32 partial tiles (written and read once) cost less than
-// the idle pairs.  1: no split.
-int pair_splits(int M, int N, int K) {
-    const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+// Work items of the CTA-pair form for a product whose tiles do not fill the 74 pairs well.  `splits` > 1: the K range
+// of a tile is split that many ways; `whole`: the first tiles (in tile order; a multiple of the tile rows, so
+// whole tile columns) that are not split.  Two shapes of plan: every tile split (few tiles: prompts of a few
+// hundred tokens), or the full waves whole and only the tiles of a last wave that is less than half full split.  Every split
+// keeps eight 64-wide slabs, and the float32 partial tiles (written and read once, then a second kernel) must cost
+// less than the idle pairs.  {1, tiles}: no split.
+struct PairPlan {
+    int splits;
+    int whole;
+    long long scratch_elems(int M, int N) const {
+        if (splits <= 1) return 0;
+        const int tiles_m = (M + 255) / 256;
+        return (long long)splits * M * (N - (whole / tiles_m) * 256);
+    }
+};
+PairPlan pair_plan(int M, int N, int K, bool uneven_ok) {
+    const int tiles_m = (M + 255) / 256, tiles = tiles_m * ((N + 255) / 256);
     const int num_kb = (K + BK - 1) / BK;
     const int pairs = 74;
+    // time of the product in units of seconds: a 256 x 256 x K tile takes about 2 * 256 * 256 * K / (1.3e15 / 74) s;
+    // 6e12 bytes/s for the partial tiles
+    const double tile_s = 2.0 * 256 * 256 * K / (1.3e15 / pairs);
     double best_cost = 1e30;
-    int best = 1;
+    PairPlan best = {1, tiles};
     for (int s = 1; s <= 8; ++s) {
         if (s > 1 && num_kb / s < 8) break;
         const int items = tiles * s;
         const int waves = (items + pairs - 1) / pairs;
-        // time of the product in units of "one tile over the whole K", plus the partial tiles' traffic in the same
-        // units (a 256 x 256 x K tile takes about 2 * 256 * 256 * K / (1.3e15 / 74) s; 6e12 bytes/s for the partials)
-        const double tile_s = 2.0 * 256 * 256 * K / (1.3e15 / pairs);
         const double cost = waves * tile_s / s + (s > 1 ? 2.0 * s * M * (double)N * 4 / 6e12 : 0.0);
-        if (cost < best_cost * 0.97) { best_cost = cost; best = s; }
+        if (cost < best_cost * 0.97) { best_cost = cost; best = PairPlan{s, s > 1 ? 0 : tiles}; }
+    }
+    // The second shape, for products in the compute-bound range (more than 768 tokens; measured: the gate-up product
+    // of 256 tokens, which streams its weights at the memory's rate, gains nothing from it).  The pairs walk the
+    // items round-robin, whole tiles first, so the estimate is the longest pair's sum of its items.
+    if (uneven_ok && tiles > pairs && tiles_m >= 4) {
+        const int base = ((tiles / pairs) * pairs / tiles_m) * tiles_m;       // the full waves, in whole tile columns
+        for (int whole = base; whole > 0 && whole > base - 2 * tiles_m; whole -= tiles_m) {
+            const int rest = tiles - whole;
+            if (rest > pairs / 2) continue;       // (measured: with a last wave more than half full the split gains nothing)
+            for (int s = 2; s <= 4 && rest > 0; ++s) {
+                if (num_kb / s < 8) break;
+                const int total = whole + rest * s;
+                double longest = 0.0;
+                for (int p = 0; p < pairs; ++p) {
+                    double sum = 0.0;
+                    for (int t = p; t < total; t += pairs) sum += t < whole ? tile_s : tile_s / s + 3e-6;
+                    if (sum > longest) longest = sum;
+                }
+                const double cols = (double)(rest / tiles_m) * 256;
+                const double cost = longest + 2.0 * s * M * cols * 4 / 6e12 + 4e-6;
+                if (cost < best_cost * 0.97) { best_cost = cost; best = PairPlan{s, whole}; }
+            }
+        }
     }
     return best;
 }
 
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out_mode, long long ldo, int M, int N,
-                int K, int* status, const NormIO& nio, const QkvIO& qio, int splits, float* partial, cudaStream_t stream) {
+                int K, int* status, const NormIO& nio, const QkvIO& qio, PairPlan plan, float* partial, cudaStream_t stream) {
     constexpr int STAGES = 6;
     constexpr int smem = STAGES * (A_BYTES + 128 * BK * 2) + 1024 + 256;
     static int sms = 0;
@@ -1460,18 +1512,21 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int out
         if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
         sms = n > 0 ? n : 148;
     }
-    const int total = ((M + 255) / 256) * ((N + 255) / 256) * splits;
+    const int tiles_m = (M + 255) / 256, tiles = tiles_m * ((N + 255) / 256);
+    const int num_kb = (K + BK - 1) / BK;
+    const int per = (num_kb + plan.splits - 1) / plan.splits;
+    const int used = (num_kb + per - 1) / per;           // no empty split
+    int whole = plan.whole;
+    if (used == 1) { partial = nullptr; whole = tiles; }
+    const int total = whole + (tiles - whole) * used;
     int pairs = sms / 2;
     if (pairs > total) pairs = total;
-    const int num_kb = (K + BK - 1) / BK;
-    const int per = (num_kb + splits - 1) / splits;
-    const int used = (num_kb + per - 1) / per;           // no empty split
-    if (used == 1) partial = nullptr;
     int rc = gg_launch2(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, stream, ta, tb, out, out_mode, ldo, M, N, K, status, nio,
-                        used, per, partial, qio);
+                        used, whole, per, partial, qio);
     if (rc != 0 || used == 1) return rc;
-    return gg_launch(gemm_splitk_finish_kernel, dim3((N + 127) / 128, (M + 7) / 8), dim3(256), 0, stream, 1,
-                     (const float*)partial, used, out, out_mode, ldo, M, N, nio, qio);
+    const int col0 = (whole / tiles_m) * 256, NS = N - col0;
+    return gg_launch(gemm_splitk_finish_kernel, dim3((NS + 127) / 128, (M + 7) / 8), dim3(256), 0, stream, 1,
+                     (const float*)partial, used, out, out_mode, ldo, M, N, col0, NS, nio, qio);
 }
 
 template <int BN, int STAGES, bool SWAP, int MINB>
@@ -1581,10 +1636,11 @@ static int gemm_tc_impl(const void* x, const void* w, void* out, int out_mode, i
         if (bn == 256 && use_pair) {
             // CTA pairs: A tiles of 128 rows per CTA as before, B staged in halves of 128 rows per CTA
             if ((rc = make_map(&tb, w, N, K, K, 128)) != 0) return rc;
-            int ps = pair_splits(M, N, K);
-            if (scratch == nullptr || scratch_elems < (long long)ps * M * N) ps = 1;     // no room for partial tiles
             // (a split q/k/v product leaves the per-head epilogue to the kernel that adds the partial tiles)
-            rc = launch_pair(ta, tb, out, out_mode, ldo, M, N, K, status, nio, qio, ps, scratch, stream);
+            PairPlan plan = pair_plan(M, N, K, true);
+            if (plan.splits > 1 && (scratch == nullptr || scratch_elems < plan.scratch_elems(M, N)))
+                plan = PairPlan{1, 0};                                                   // no room for partial tiles
+            rc = launch_pair(ta, tb, out, out_mode, ldo, M, N, K, status, nio, qio, plan, scratch, stream);
         } else if (out_mode == OUT_QKV) rc = GG_ERR_ARG;       // only the CTA-pair form has the q/k/v epilogue
         else if (bn == 256) rc = launch_persistent(ta, tb, out, out_mode, ldo, M, N, K, status, nio, stream);
         else rc = launch<128, 6, false, 1>(ta, tb, out, out_mode, ldo, M, N, K, 1, per, scratch, false, status, nio, qio, stream);
@@ -1633,8 +1689,7 @@ GG_API gg_gemm_tc_pair_scratch_elems(int M, int N, int K, long long* elems) {
     if (elems == nullptr) return GG_ERR_ARG;
     *elems = 0;
     if (M <= 128 || N <= 128 || K <= 0) return 0;
-    const int ps = pair_splits(M, N, K);
-    if (ps > 1) *elems = (long long)ps * M * N;
+    *elems = pair_plan(M, N, K, true).scratch_elems(M, N);
     return 0;
 }
 

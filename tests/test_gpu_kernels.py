@@ -431,14 +431,19 @@ def test_gemm_tcgen05_qkv_with_norm_rope_and_cache_write(M, nq, nkv, K_, norm, f
 
 
 @pytest.mark.parametrize("M,N,K_", [(256, 4096, 4096), (300, 520, 2048), (512, 1024, 8192), (200, 264, 1024),
-                                    (1024, 768, 4096)])
+                                    (1024, 768, 4096),
+                                    # more tiles than CTA pairs: the full wave whole, the tiles of the last wave split
+                                    (1280, 4096, 4096), (1100, 4200, 4096), (1536, 4096, 4096), (2560, 4096, 4096)])
 def test_gemm_tcgen05_prefill_form_splits_k_when_it_has_few_tiles(M, N, K_):
-    """A few hundred tokens give the CTA-pair form fewer tiles than there are pairs; with scratch it splits K,
-    leaves float32 partial tiles and a second kernel applies the output mode.  Every mode, against float64."""
+    """A few hundred tokens give the CTA-pair form fewer tiles than there are pairs, or a last wave that is nearly
+    empty; with scratch it splits K (of all tiles, or of the last wave's), leaves float32 partial tiles and a second
+    kernel applies the output mode.  Every mode, against float64."""
     from gogguf_b200.csrc import tcgen05_gemm as tc
     g = torch.Generator(device=DEV).manual_seed(43)
     need = tc.pair_scratch_elems(M, N, K_)
-    assert need > 0 and need % (M * N) == 0, "these shapes are meant to split"
+    assert need > 0 and need % M == 0, "these shapes are meant to split"
+    tiles = -(-M // 256) * -(-N // 256)
+    assert (need % (M * N) == 0) == (tiles <= 74), "every tile is split where there are few, else only some tile columns"
     scratch = torch.full((need,), float("nan"), device=DEV)
     resid = torch.randn(M, K_, device=DEV, generator=g) * 2
     w = (torch.randn(N, K_, device=DEV, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
